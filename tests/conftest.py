@@ -1,0 +1,40 @@
+"""Shared pytest configuration: the ``gpu`` marker and the import paths of the package."""
+
+import os
+import sys
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+for p in (ROOT, os.path.join(ROOT, "attention-gym_b200")):
+    if p not in sys.path:
+        sys.path.insert(0, p)
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (run with -m gpu on a B200)")
+
+
+def pytest_collection_modifyitems(config, items):
+    import torch
+
+    if torch.cuda.is_available():
+        return
+    skip = pytest.mark.skip(reason="no CUDA device")
+    for item in items:
+        if "gpu" in item.keywords:
+            item.add_marker(skip)
+
+
+@pytest.fixture(scope="session")
+def golden():
+    import numpy as np
+    import torch
+
+    folder = os.path.join(ROOT, "tests", "golden")
+
+    def load(name):
+        with np.load(os.path.join(folder, name + ".npz")) as data:
+            return {k: torch.from_numpy(data[k]) for k in data.files}
+
+    return load
