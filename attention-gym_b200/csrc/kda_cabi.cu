@@ -1,0 +1,75 @@
+// Library identification and the optional per-kernel event timing of the C ABI.
+#include <mutex>
+#include <vector>
+
+#include "../../include/kda_b200.h"
+#include "kda_timing.cuh"
+
+namespace kda {
+
+static const char* kStageNames[kStageCount] = {
+    "intra_solve", "wu", "state_fwd", "state_bwd", "bwd_wy", "bwd_intra", "recurrent",
+    "gate_fwd", "gate_bwd", "l2norm", "conv", "chunk_offsets", "state_affine"};
+
+struct Pair { cudaEvent_t a, b; };
+static bool g_enabled = false;
+static std::mutex g_mu;
+static std::vector<Pair> g_pairs[kStageCount];
+static std::vector<cudaEvent_t> g_free;
+
+static cudaEvent_t get_event() {
+  if (!g_free.empty()) { cudaEvent_t e = g_free.back(); g_free.pop_back(); return e; }
+  cudaEvent_t e;
+  cudaEventCreate(&e);
+  return e;
+}
+
+void stage_begin(int stage, cudaStream_t s) {
+  if (!g_enabled) return;
+  std::lock_guard<std::mutex> lock(g_mu);
+  Pair p{get_event(), get_event()};
+  cudaEventRecord(p.a, s);
+  g_pairs[stage].push_back(p);
+}
+void stage_end(int stage, cudaStream_t s) {
+  if (!g_enabled) return;
+  std::lock_guard<std::mutex> lock(g_mu);
+  if (!g_pairs[stage].empty()) cudaEventRecord(g_pairs[stage].back().b, s);
+}
+
+}  // namespace kda
+
+extern "C" int kda_b200_version(void) { return 100; }
+
+extern "C" int kda_stage_count(void) { return kda::kStageCount; }
+
+extern "C" const char* kda_stage_name(int stage) {
+  return (stage >= 0 && stage < kda::kStageCount) ? kda::kStageNames[stage] : "";
+}
+
+extern "C" int kda_stage_timing_enable(int on) {
+  std::lock_guard<std::mutex> lock(kda::g_mu);
+  kda::g_enabled = on != 0;
+  return KDA_OK;
+}
+
+extern "C" int kda_stage_timing_read(int64_t* launches, float* total_ms, int reset) {
+  if (!launches || !total_ms) return KDA_ERR_ARG;
+  std::lock_guard<std::mutex> lock(kda::g_mu);
+  for (int st = 0; st < kda::kStageCount; ++st) {
+    launches[st] = 0;
+    total_ms[st] = 0.f;
+    for (auto& p : kda::g_pairs[st]) {
+      float ms = 0.f;
+      if (cudaEventSynchronize(p.b) == cudaSuccess && cudaEventElapsedTime(&ms, p.a, p.b) == cudaSuccess) {
+        launches[st] += 1;
+        total_ms[st] += ms;
+      }
+    }
+    if (reset) {
+      for (auto& p : kda::g_pairs[st]) { kda::g_free.push_back(p.a); kda::g_free.push_back(p.b); }
+      kda::g_pairs[st].clear();
+    }
+  }
+  return KDA_OK;
+}

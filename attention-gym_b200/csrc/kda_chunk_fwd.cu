@@ -1,0 +1,521 @@
+// Chunked KDA forward for K = V = 128, chunk = 64, bf16 operands, fp32 state and accumulation.
+//
+// Three kernels replace the reference's seven forward launches
+// (attn_gym/linear/kda/fwd/cute/chunk_kda_fwd.py:79-131):
+//
+//  intra_solve  per (chunk, head): the gated pairwise products and the WY solve
+//               Aqk = scale tril(Q~ K~^T),  A = (I + stril(diag(beta) K~ K~^T))^-1
+//               (reference stages: fwd/triton/chunk_kda_fwd_intra_sub_chunk_forloop.py:66,
+//                fwd/cute/chunk_kda_k3b_offdiag_cutedsl.py:177, fwd/cute/chunk_kda_k4b_inverse_cutedsl.py:188)
+//  wu           per (chunk, head): w = A (beta k 2^G), u = A (beta v), kg = k 2^{G_last-G},
+//               qg = scale q 2^G   (reference: fwd/triton/recompute_w_u.py:257); reused by backward
+//  state_fwd    per (sequence, head, V half), serial over chunks with the fp32 state in registers:
+//               v_new = u - w h;  o = qg h + Aqk v_new;  h <- diag(2^{G_last}) h + kg^T v_new
+//               (fuses reference fwd/triton/chunk_delta_h.py:40-162 and fwd/triton/chunk_gla_fwd_o.py:202-226,
+//                so the per-chunk state never goes to HBM in the forward pass)
+//
+// Gate rebasing: 2^{G_i - G_j} is split as 2^{G_i - R} * 2^{R - G_j} with R the gate of the first
+// row of the 16-row block that holds i, so the row factor is <= 1 and the column factor is <= 1
+// for every earlier block; inside the diagonal block the column factor spans at most 15 tokens,
+// the same exponent budget as the reference (fwd/triton/gate_fwd.py:619-631).
+#include "kda_common.cuh"
+#include "kda_timing.cuh"
+
+namespace kda {
+
+constexpr int D = 128;     // K = V
+constexpr int LDD = 136;   // padded row stride of a [*, 128] bf16 tile (272 B: conflict-free ldmatrix)
+constexpr int LD64 = 72;   // padded row stride of a [*, 64] bf16 tile
+constexpr int LDP = 68;    // padded row stride of a [64, 64] fp32 tile
+
+struct ChunkParams {
+  const bf16* q; const bf16* k; const bf16* v; const float* g; const float* beta;
+  bf16* aqk; bf16* akk;                 // tape [N, H, 64]
+  bf16* w; bf16* u; bf16* kg; bf16* qg;  // [N, H, 128]
+  const float* h0; float* ht;
+  bf16* o; bf16* h_out; bf16* vnew_out;
+  const int32_t* cu_seqlens; const int32_t* chunk_offsets;
+  int nseq, H;
+  float scale;
+};
+
+// ------------------------------------------------------------------------------------------
+// intra_solve
+// ------------------------------------------------------------------------------------------
+struct IntraSmem {
+  bf16 q[64 * LDD];
+  bf16 k[64 * LDD];
+  float g[64 * D];
+  bf16 kn[64 * LDD];     // column operand of the current row block; later holds A (fp32 [64][LDP])
+  bf16 rk[16 * LDD];     // gated k rows of the current row block
+  float pk[64 * LDP];    // L = stril(beta_i P_ij)
+  float beta[64];
+  float tmp[3 * 256];
+};
+static_assert(sizeof(bf16) * 64 * LDD >= sizeof(float) * 64 * LDP, "A overlay must fit");
+
+// dst[i][j] = sign * sum_{k<kk} A[i][k] B[k][j] for a 16x16 tile; thread t -> (t >> 4, t & 15)
+__device__ __forceinline__ void block_mm16(float* dst, int ldd, const float* A, int lda,
+                                           const float* B, int ldb, int kk, float sign, int tid) {
+  int i = tid >> 4, j = tid & 15;
+  float s = 0.f;
+  for (int k = 0; k < kk; ++k) s += A[i * lda + k] * B[k * ldb + j];
+  dst[i * ldd + j] = sign * s;
+}
+
+__global__ void __launch_bounds__(256) kda_intra_solve_kernel(const ChunkParams p) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  IntraSmem& sm = *reinterpret_cast<IntraSmem*>(smem_raw);
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int head = blockIdx.y, H = p.H;
+  const ChunkWork cw = locate_chunk(p.cu_seqlens, p.chunk_offsets, p.nseq, blockIdx.x);
+  if (cw.valid == 0) return;
+  const int valid = cw.valid;
+  const int64_t rowD = (cw.token0 * H + head) * D;
+  const int64_t gld = (int64_t)H * D;
+
+  load_tile_b16<64, D, LDD, 256>(sm.q, p.q + rowD, gld, valid, tid);
+  load_tile_b16<64, D, LDD, 256>(sm.k, p.k + rowD, gld, valid, tid);
+  load_tile_f32<64, D, D, 256>(sm.g, p.g + rowD, gld, valid, tid);
+  cp_async_commit();
+  if (tid < 64) sm.beta[tid] = tid < valid ? p.beta[(cw.token0 + tid) * H + head] : 0.f;
+  cp_async_wait<0>();
+  __syncthreads();
+  // rows past the tail repeat the last cumulative gate, so they neither decay nor overflow
+  if (valid < 64) {
+    for (int idx = tid; idx < (64 - valid) * D; idx += 256) {
+      int r = valid + idx / D, c = idx % D;
+      sm.g[r * D + c] = sm.g[(valid - 1) * D + c];
+    }
+    __syncthreads();
+  }
+
+  for (int ri = 0; ri < 4; ++ri) {
+    const int ncol = 16 * (ri + 1);
+    const float* R = sm.g + (16 * ri) * D;
+    // row operands (in place for q, separate for k): x_i 2^{G_i - R}
+    for (int idx = tid; idx < 16 * (D / 2); idx += 256) {
+      int r = idx / (D / 2), c = (idx % (D / 2)) * 2;
+      int i = 16 * ri + r;
+      float e0 = fexp2(sm.g[i * D + c] - R[c]), e1 = fexp2(sm.g[i * D + c + 1] - R[c + 1]);
+      float2 qv = unpack_bf16(*reinterpret_cast<uint32_t*>(&sm.q[i * LDD + c]));
+      float2 kv = unpack_bf16(*reinterpret_cast<uint32_t*>(&sm.k[i * LDD + c]));
+      *reinterpret_cast<uint32_t*>(&sm.q[i * LDD + c]) = pack_bf16(qv.x * e0, qv.y * e1);
+      *reinterpret_cast<uint32_t*>(&sm.rk[r * LDD + c]) = pack_bf16(kv.x * e0, kv.y * e1);
+    }
+    // column operand: k_j 2^{R - G_j}, j < ncol (entries with j > i are masked after the product)
+    for (int idx = tid; idx < ncol * (D / 2); idx += 256) {
+      int j = idx / (D / 2), c = (idx % (D / 2)) * 2;
+      float e0 = fexp2(fminf(R[c] - sm.g[j * D + c], 126.f));
+      float e1 = fexp2(fminf(R[c + 1] - sm.g[j * D + c + 1], 126.f));
+      float2 kv = unpack_bf16(*reinterpret_cast<uint32_t*>(&sm.k[j * LDD + c]));
+      *reinterpret_cast<uint32_t*>(&sm.kn[j * LDD + c]) = pack_bf16(kv.x * e0, kv.y * e1);
+    }
+    __syncthreads();
+    {
+      const int which = warp & 1, nb = warp >> 1;
+      float acc[1][2][4];
+      zero_acc<1, 2>(acc);
+      if (nb <= ri) {
+        if (which == 0)
+          warp_gemm<1, 1, false, false>(acc, sm.q, LDD, 16 * ri, 0, sm.kn, LDD, 0, 16 * nb, 8, lane);
+        else
+          warp_gemm<1, 1, false, false>(acc, sm.rk, LDD, 0, 0, sm.kn, LDD, 0, 16 * nb, 8, lane);
+      }
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+          int i = 16 * ri + (lane >> 2) + 8 * hh;
+          int j = 16 * nb + 8 * nt + 2 * (lane & 3);
+          float a0 = acc[0][nt][2 * hh], a1 = acc[0][nt][2 * hh + 1];
+          if (which == 0) {
+            float x0 = (j <= i) ? a0 * p.scale : 0.f;
+            float x1 = (j + 1 <= i) ? a1 * p.scale : 0.f;
+            if (i < valid)
+              *reinterpret_cast<uint32_t*>(p.aqk + ((cw.token0 + i) * H + head) * 64 + j) =
+                  pack_bf16(x0, x1);
+          } else {
+            float b = sm.beta[i];
+            sm.pk[i * LDP + j] = (j < i) ? a0 * b : 0.f;
+            sm.pk[i * LDP + j + 1] = (j + 1 < i) ? a1 * b : 0.f;
+          }
+        }
+    }
+    __syncthreads();
+  }
+
+  // ---- A = (I + L)^-1 by 16x16 blocks, fp32 -------------------------------------------------
+  float* A = reinterpret_cast<float*>(sm.kn);
+  for (int idx = tid; idx < 64 * LDP; idx += 256) A[idx] = 0.f;
+  __syncthreads();
+  if (tid < 64) {  // diagonal blocks: column c of block b by forward substitution
+    const int b = tid >> 4, c = tid & 15;
+    const float* L = sm.pk + (16 * b) * LDP + 16 * b;
+    float x[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      float s = (i == c) ? 1.f : 0.f;
+#pragma unroll
+      for (int j = 0; j < i; ++j) s -= L[i * LDP + j] * x[j];
+      x[i] = s;
+    }
+#pragma unroll
+    for (int i = 0; i < 16; ++i) A[(16 * b + i) * LDP + 16 * b + c] = x[i];
+  }
+  __syncthreads();
+  // A[r][c] = -A[r][r] * sum_{c<=m<r} L[r][m] A[m][c], one block diagonal at a time
+  for (int dist = 1; dist < 4; ++dist) {
+    for (int c = 0; c + dist < 4; ++c) {
+      int r = c + dist;
+      block_mm16(sm.tmp + 256 * c, 16, sm.pk + (16 * r) * LDP + 16 * c, LDP,
+                 A + (16 * c) * LDP + 16 * c, LDP, 16 * dist, 1.f, tid);
+    }
+    __syncthreads();
+    for (int c = 0; c + dist < 4; ++c) {
+      int r = c + dist;
+      block_mm16(A + (16 * r) * LDP + 16 * c, LDP, A + (16 * r) * LDP + 16 * r, LDP,
+                 sm.tmp + 256 * c, 16, 16, -1.f, tid);
+    }
+    __syncthreads();
+  }
+  for (int idx = tid; idx < 64 * 8; idx += 256) {
+    int r = idx >> 3, c = (idx & 7) * 8;
+    if (r < valid) {
+      const float* a = A + r * LDP + c;
+      uint4 o;
+      o.x = pack_bf16(a[0], a[1]); o.y = pack_bf16(a[2], a[3]);
+      o.z = pack_bf16(a[4], a[5]); o.w = pack_bf16(a[6], a[7]);
+      *reinterpret_cast<uint4*>(p.akk + ((cw.token0 + r) * H + head) * 64 + c) = o;
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// wu: w, u, kg, qg from k, v, q, G, beta and the stored A
+// ------------------------------------------------------------------------------------------
+struct WuSmem {
+  bf16 k[64 * LDD];
+  bf16 v[64 * LDD];
+  float g[64 * D];
+  bf16 a[64 * LD64];
+  float beta[64];
+};
+
+__global__ void __launch_bounds__(256) kda_wu_kernel(const ChunkParams p) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  WuSmem& sm = *reinterpret_cast<WuSmem*>(smem_raw);
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int head = blockIdx.y, H = p.H;
+  const ChunkWork cw = locate_chunk(p.cu_seqlens, p.chunk_offsets, p.nseq, blockIdx.x);
+  if (cw.valid == 0) return;
+  const int valid = cw.valid;
+  const int64_t rowD = (cw.token0 * H + head) * D;
+  const int64_t gld = (int64_t)H * D;
+
+  load_tile_b16<64, D, LDD, 256>(sm.k, p.k + rowD, gld, valid, tid);
+  load_tile_b16<64, D, LDD, 256>(sm.v, p.v + rowD, gld, valid, tid);
+  load_tile_f32<64, D, D, 256>(sm.g, p.g + rowD, gld, valid, tid);
+  load_tile_b16<64, 64, LD64, 256>(sm.a, p.akk + (cw.token0 * H + head) * 64, (int64_t)H * 64,
+                                   valid, tid);
+  cp_async_commit();
+  if (tid < 64) sm.beta[tid] = tid < valid ? p.beta[(cw.token0 + tid) * H + head] : 0.f;
+  cp_async_wait<0>();
+  __syncthreads();
+
+  const float* glast = sm.g + (valid - 1) * D;
+  for (int idx = tid; idx < 64 * (D / 2); idx += 256) {
+    int r = idx / (D / 2), c = (idx % (D / 2)) * 2;
+    float g0 = sm.g[r * D + c], g1 = sm.g[r * D + c + 1];
+    float e0 = fexp2(g0), e1 = fexp2(g1);
+    float2 kv = unpack_bf16(*reinterpret_cast<uint32_t*>(&sm.k[r * LDD + c]));
+    float2 vv = unpack_bf16(*reinterpret_cast<uint32_t*>(&sm.v[r * LDD + c]));
+    float b = sm.beta[r];
+    if (r < valid) {
+      int64_t gi = rowD + (int64_t)r * gld + c;
+      float2 qv = unpack_bf16(*reinterpret_cast<const uint32_t*>(p.q + gi));
+      *reinterpret_cast<uint32_t*>(p.qg + gi) = pack_bf16(qv.x * e0 * p.scale, qv.y * e1 * p.scale);
+      *reinterpret_cast<uint32_t*>(p.kg + gi) =
+          pack_bf16(kv.x * fexp2(glast[c] - g0), kv.y * fexp2(glast[c + 1] - g1));
+    }
+    *reinterpret_cast<uint32_t*>(&sm.k[r * LDD + c]) = pack_bf16(kv.x * e0 * b, kv.y * e1 * b);
+    *reinterpret_cast<uint32_t*>(&sm.v[r * LDD + c]) = pack_bf16(vv.x * b, vv.y * b);
+  }
+  __syncthreads();
+  const int mt = warp & 3, nh = warp >> 2;
+  float accw[1][8][4], accu[1][8][4];
+  zero_acc<1, 8>(accw);
+  zero_acc<1, 8>(accu);
+  warp_gemm<1, 4, false, true>(accw, sm.a, LD64, 16 * mt, 0, sm.k, LDD, 0, 64 * nh, 4, lane);
+  warp_gemm<1, 4, false, true>(accu, sm.a, LD64, 16 * mt, 0, sm.v, LDD, 0, 64 * nh, 4, lane);
+  __syncthreads();
+#pragma unroll
+  for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh) {
+      int r = 16 * mt + (lane >> 2) + 8 * hh, c = 64 * nh + 8 * nt + 2 * (lane & 3);
+      *reinterpret_cast<uint32_t*>(&sm.k[r * LDD + c]) =
+          pack_bf16(accw[0][nt][2 * hh], accw[0][nt][2 * hh + 1]);
+      *reinterpret_cast<uint32_t*>(&sm.v[r * LDD + c]) =
+          pack_bf16(accu[0][nt][2 * hh], accu[0][nt][2 * hh + 1]);
+    }
+  __syncthreads();
+  store_tile_b16<64, D, LDD, 256>(p.w + rowD, gld, sm.k, valid, tid);
+  store_tile_b16<64, D, LDD, 256>(p.u + rowD, gld, sm.v, valid, tid);
+}
+
+// ------------------------------------------------------------------------------------------
+// state_fwd: serial over the chunks of one sequence; one CTA per (sequence, head, V half)
+// ------------------------------------------------------------------------------------------
+struct StateStage {
+  bf16 w[64 * LDD];
+  bf16 qg[64 * LDD];
+  bf16 kg[64 * LDD];
+  bf16 u[64 * LD64];
+  bf16 aqk[64 * LD64];
+  float dec[D];
+};
+struct StateSmem {
+  StateStage st[2];
+  bf16 h[D * LD64];
+  bf16 vn[64 * LD64];
+};
+
+__device__ __forceinline__ void state_load_stage(StateStage& s, const ChunkParams& p, int64_t token0,
+                                                 int valid, int head, int vh, int tid) {
+  const int H = p.H;
+  const int64_t rowD = (token0 * H + head) * D;
+  const int64_t gld = (int64_t)H * D;
+  load_tile_b16<64, D, LDD, 256>(s.w, p.w + rowD, gld, valid, tid);
+  load_tile_b16<64, D, LDD, 256>(s.qg, p.qg + rowD, gld, valid, tid);
+  load_tile_b16<64, D, LDD, 256>(s.kg, p.kg + rowD, gld, valid, tid);
+  load_tile_b16<64, 64, LD64, 256>(s.u, p.u ? p.u + rowD + 64 * vh : p.w, gld, p.u ? valid : 0,
+                                   tid);
+  load_tile_b16<64, 64, LD64, 256>(s.aqk, p.aqk + (token0 * H + head) * 64, (int64_t)H * 64, valid,
+                                   tid);
+  if (tid < D / 4)
+    cp_async16(s.dec + tid * 4, p.g + rowD + (int64_t)(valid - 1) * gld + tid * 4, true);
+}
+
+__global__ void __launch_bounds__(256) kda_state_fwd_kernel(const ChunkParams p) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  StateSmem& sm = *reinterpret_cast<StateSmem*>(smem_raw);
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int H = p.H;
+  const int vh = blockIdx.x & 1;
+  const int head = (blockIdx.x >> 1) % H;
+  const int seq = (blockIdx.x >> 1) / H;
+  const int64_t bos = p.cu_seqlens[seq], eos = p.cu_seqlens[seq + 1];
+  const int chunk0 = p.chunk_offsets[seq];
+  const int nchunks = p.chunk_offsets[seq + 1] - chunk0;
+  const int g8 = lane >> 2, t2 = 2 * (lane & 3);
+
+  // state rows 16*warp + {g8, g8+8}, columns 64*vh + 8*nt + t2 + {0,1}
+  float h[1][8][4];
+  const int64_t sbase = ((int64_t)seq * H + head) * D * D + 64 * vh;
+#pragma unroll
+  for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh) {
+      int r = 16 * warp + g8 + 8 * hh, c = 8 * nt + t2;
+      float2 x = make_float2(0.f, 0.f);
+      if (p.h0) x = *reinterpret_cast<const float2*>(p.h0 + sbase + (int64_t)r * D + c);
+      h[0][nt][2 * hh] = x.x;
+      h[0][nt][2 * hh + 1] = x.y;
+    }
+
+  auto chunk_valid = [&](int c) {
+    int64_t rem = eos - (bos + (int64_t)c * 64);
+    return rem >= 64 ? 64 : (int)rem;
+  };
+  if (nchunks > 0) state_load_stage(sm.st[0], p, bos, chunk_valid(0), head, vh, tid);
+  cp_async_commit();
+  if (nchunks > 1) state_load_stage(sm.st[1], p, bos + 64, chunk_valid(1), head, vh, tid);
+  cp_async_commit();
+
+  const int mt = warp & 3, nq = warp >> 2;
+  for (int c = 0; c < nchunks; ++c) {
+    StateStage& st = sm.st[c & 1];
+    const int64_t token0 = bos + (int64_t)c * 64;
+    const int valid = chunk_valid(c);
+    cp_async_wait<1>();
+    __syncthreads();
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+      for (int hh = 0; hh < 2; ++hh)
+        *reinterpret_cast<uint32_t*>(&sm.h[(16 * warp + g8 + 8 * hh) * LD64 + 8 * nt + t2]) =
+            pack_bf16(h[0][nt][2 * hh], h[0][nt][2 * hh + 1]);
+    __syncthreads();
+    if (p.h_out)
+      store_tile_b16<D, 64, LD64, 256>(
+          p.h_out + (((int64_t)(chunk0 + c) * H + head) * D) * D + 64 * vh, D, sm.h, D, tid);
+
+    float accv[1][4][4], acco[1][4][4];
+    zero_acc<1, 4>(accv);
+    zero_acc<1, 4>(acco);
+    warp_gemm<1, 2, false, true>(accv, st.w, LDD, 16 * mt, 0, sm.h, LD64, 0, 32 * nq, 8, lane);
+    warp_gemm<1, 2, false, true>(acco, st.qg, LDD, 16 * mt, 0, sm.h, LD64, 0, 32 * nq, 8, lane);
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+      for (int hh = 0; hh < 2; ++hh) {
+        int r = 16 * mt + g8 + 8 * hh, cc = 32 * nq + 8 * nt + t2;
+        float2 uu = unpack_bf16(*reinterpret_cast<uint32_t*>(&st.u[r * LD64 + cc]));
+        *reinterpret_cast<uint32_t*>(&sm.vn[r * LD64 + cc]) =
+            pack_bf16(uu.x - accv[0][nt][2 * hh], uu.y - accv[0][nt][2 * hh + 1]);
+      }
+    __syncthreads();
+    if (p.vnew_out)
+      store_tile_b16<64, 64, LD64, 256>(p.vnew_out + (token0 * H + head) * D + 64 * vh,
+                                        (int64_t)H * D, sm.vn, valid, tid);
+    warp_gemm<1, 2, false, true>(acco, st.aqk, LD64, 16 * mt, 0, sm.vn, LD64, 0, 32 * nq, 4, lane);
+    {
+      float d0 = fexp2(st.dec[16 * warp + g8]), d1 = fexp2(st.dec[16 * warp + g8 + 8]);
+#pragma unroll
+      for (int nt = 0; nt < 8; ++nt) {
+        h[0][nt][0] *= d0; h[0][nt][1] *= d0; h[0][nt][2] *= d1; h[0][nt][3] *= d1;
+      }
+    }
+    warp_gemm<1, 4, true, true>(h, st.kg, LDD, 16 * warp, 0, sm.vn, LD64, 0, 0, 4, lane);
+    if (p.o) {
+#pragma unroll
+      for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+          int r = 16 * mt + g8 + 8 * hh, cc = 32 * nq + 8 * nt + t2;
+          *reinterpret_cast<uint32_t*>(&st.u[r * LD64 + cc]) =
+              pack_bf16(acco[0][nt][2 * hh], acco[0][nt][2 * hh + 1]);
+        }
+    }
+    __syncthreads();
+    if (p.o)
+      store_tile_b16<64, 64, LD64, 256>(p.o + (token0 * H + head) * D + 64 * vh, (int64_t)H * D,
+                                        st.u, valid, tid);
+    __syncthreads();
+    if (c + 2 < nchunks)
+      state_load_stage(st, p, token0 + 128, chunk_valid(c + 2), head, vh, tid);
+    cp_async_commit();
+  }
+  cp_async_wait<0>();
+  if (p.ht) {
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+      for (int hh = 0; hh < 2; ++hh) {
+        int r = 16 * warp + g8 + 8 * hh, c = 8 * nt + t2;
+        *reinterpret_cast<float2*>(p.ht + sbase + (int64_t)r * D + c) =
+            make_float2(h[0][nt][2 * hh], h[0][nt][2 * hh + 1]);
+      }
+  }
+}
+
+static int check_launch() { return cudaGetLastError() == cudaSuccess ? KDA_OK : KDA_ERR_LAUNCH; }
+
+template <typename Kern>
+static int set_smem(Kern kern, size_t bytes) {
+  return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes) ==
+                 cudaSuccess ? KDA_OK : KDA_ERR_LAUNCH;
+}
+
+int launch_intra_solve(const ChunkParams& p, int chunks, cudaStream_t s) {
+  if (chunks == 0) return KDA_OK;
+  if (set_smem(kda_intra_solve_kernel, sizeof(IntraSmem))) return KDA_ERR_LAUNCH;
+  StageScope timing(kStageIntraSolve, s);
+  kda_intra_solve_kernel<<<dim3(chunks, p.H), 256, sizeof(IntraSmem), s>>>(p);
+  return check_launch();
+}
+int launch_wu(const ChunkParams& p, int chunks, cudaStream_t s) {
+  if (chunks == 0) return KDA_OK;
+  if (set_smem(kda_wu_kernel, sizeof(WuSmem))) return KDA_ERR_LAUNCH;
+  StageScope timing(kStageWu, s);
+  kda_wu_kernel<<<dim3(chunks, p.H), 256, sizeof(WuSmem), s>>>(p);
+  return check_launch();
+}
+int launch_state_fwd(const ChunkParams& p, cudaStream_t s) {
+  if (p.nseq == 0) return KDA_OK;
+  if (set_smem(kda_state_fwd_kernel, sizeof(StateSmem))) return KDA_ERR_LAUNCH;
+  StageScope timing(kStageStateFwd, s);
+  kda_state_fwd_kernel<<<(unsigned)(p.nseq * p.H * 2), 256, sizeof(StateSmem), s>>>(p);
+  return check_launch();
+}
+
+// Backward's recompute leg: w, u, kg, qg from the stored A, then the chunk-entry states h[c]
+// and v_new (no output, no final state).
+int launch_recompute(const void* q, const void* k, const void* v, const float* g, const float* beta,
+                     const void* aqk, const void* akk, const float* h0, void* w, void* u, void* kg,
+                     void* qg, void* h_out, void* vnew_out, const int32_t* cu, const int32_t* co,
+                     int nseq, int H, int chunks, cudaStream_t s) {
+  ChunkParams p{};
+  p.q = (const bf16*)q; p.k = (const bf16*)k; p.v = (const bf16*)v; p.g = g; p.beta = beta;
+  p.aqk = (bf16*)aqk; p.akk = (bf16*)akk;
+  p.w = (bf16*)w; p.u = (bf16*)u; p.kg = (bf16*)kg; p.qg = (bf16*)qg;
+  p.h0 = h0; p.ht = nullptr; p.o = nullptr;
+  p.h_out = (bf16*)h_out; p.vnew_out = (bf16*)vnew_out;
+  p.cu_seqlens = cu; p.chunk_offsets = co; p.nseq = nseq; p.H = H;
+  p.scale = 0.08838834764831845f;
+  int rc = launch_wu(p, chunks, s);
+  if (rc) return rc;
+  return launch_state_fwd(p, s);
+}
+
+}  // namespace kda
+
+using kda::bf16;
+
+extern "C" int kda_chunk_fwd(const void* q, const void* k, const void* v, const float* cum_gate,
+                             const float* beta, const float* initial_state, float* final_state,
+                             void* out, void* aqk, void* akk, const int32_t* cu_seqlens,
+                             const int32_t* chunk_offsets, int nseq, int64_t tokens, int heads,
+                             int key_dim, int value_dim, int num_chunks, void* workspace,
+                             int64_t workspace_bytes, void* stream) {
+  if (!q || !k || !v || !cum_gate || !beta || !out || !aqk || !akk || !cu_seqlens ||
+      !chunk_offsets || !workspace)
+    return KDA_ERR_ARG;
+  if (key_dim != 128 || value_dim != 128) return KDA_ERR_UNSUPPORTED;
+  if (nseq < 1 || heads < 1 || tokens < 1 || num_chunks < 0) return KDA_ERR_ARG;
+  if ((int64_t)nseq * heads * 2 > 0x7fffffffLL) return KDA_ERR_UNSUPPORTED;
+  if (workspace_bytes < kda_chunk_fwd_workspace_bytes(tokens, heads)) return KDA_ERR_ARG;
+  kda::ChunkParams p{};
+  const int64_t nd = tokens * heads * 128;
+  bf16* ws = reinterpret_cast<bf16*>(workspace);
+  p.q = (const bf16*)q; p.k = (const bf16*)k; p.v = (const bf16*)v; p.g = cum_gate; p.beta = beta;
+  p.aqk = (bf16*)aqk; p.akk = (bf16*)akk;
+  p.w = ws; p.u = ws + nd; p.kg = ws + 2 * nd; p.qg = ws + 3 * nd;
+  p.h0 = initial_state; p.ht = final_state; p.o = (bf16*)out;
+  p.h_out = nullptr; p.vnew_out = nullptr;
+  p.cu_seqlens = cu_seqlens; p.chunk_offsets = chunk_offsets; p.nseq = nseq; p.H = heads;
+  p.scale = 0.08838834764831845f;  // 128^-0.5
+  cudaStream_t s = (cudaStream_t)stream;
+  int rc = kda::launch_intra_solve(p, num_chunks, s);
+  if (rc) return rc;
+  rc = kda::launch_wu(p, num_chunks, s);
+  if (rc) return rc;
+  return kda::launch_state_fwd(p, s);
+}
+
+extern "C" int64_t kda_chunk_fwd_workspace_bytes(int64_t tokens, int heads) {
+  return 4 * tokens * heads * 128 * (int64_t)sizeof(bf16);
+}
+
+// Slice transition for context parallelism: with u = 0 and an identity initial state the state
+// recurrence returns M = prod_t (I - beta_t k_t k_t^T) diag(2^{g_t}) of the slice ([H,K,K] fp32,
+// one "sequence"), so that h_out = M h_in + b.  Needs w, kg (and any qg/aqk) from a previous
+// kda_chunk_fwd on the same workspace.
+extern "C" int kda_chunk_transition(const float* cum_gate, const float* identity_state,
+                                    float* transition, const int32_t* cu_seqlens,
+                                    const int32_t* chunk_offsets, int nseq, int64_t tokens,
+                                    int heads, void* aqk, void* workspace, void* stream) {
+  if (!cum_gate || !identity_state || !transition || !cu_seqlens || !chunk_offsets || !workspace ||
+      !aqk)
+    return KDA_ERR_ARG;
+  kda::ChunkParams p{};
+  const int64_t nd = tokens * heads * 128;
+  bf16* ws = reinterpret_cast<bf16*>(workspace);
+  p.g = cum_gate;
+  p.aqk = (bf16*)aqk;
+  p.w = ws; p.u = nullptr; p.kg = ws + 2 * nd; p.qg = ws + 3 * nd;
+  p.h0 = identity_state; p.ht = transition; p.o = nullptr;
+  p.cu_seqlens = cu_seqlens; p.chunk_offsets = chunk_offsets; p.nseq = nseq; p.H = heads;
+  return kda::launch_state_fwd(p, (cudaStream_t)stream);
+}

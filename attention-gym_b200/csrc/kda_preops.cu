@@ -1,0 +1,324 @@
+// Bandwidth-bound pre-ops of the KDA path: packed-chunk offsets, the bounded gate with its
+// chunk-local prefix sum (forward and backward), and the L2 row normalisation.
+//
+// Replaces (reference files):
+//   attn_gym/linear/kda/chunk_scheduler.py:279          chunk offsets prefix kernel
+//   attn_gym/linear/kda/fwd/triton/gate_fwd.py:59,220   gate + chunk-local cumsum
+//   attn_gym/linear/kda/bwd/cute/gate_bwd_fused.py:153, bwd/triton/gate_bwd.py:141  gate backward
+//   attn_gym/linear/kda/fwd/triton/l2norm_fwd.py:22, bwd/triton/l2norm_bwd.py:37    l2norm
+//
+// All of them stream each element once: a thread owns 4 adjacent channels (8-byte bf16 loads,
+// 16-byte fp32 stores), a warp covers a contiguous 256/512-byte row segment.
+#include "kda_common.cuh"
+#include "kda_timing.cuh"
+
+namespace kda {
+
+// ------------------------------------------------------------------------------------------
+// chunk_offsets[i+1] = sum_{s<=i} ceil(len_s / chunk)
+// ------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(1024) chunk_offsets_kernel(const int32_t* __restrict__ cu,
+                                                             int nseq, int chunk,
+                                                             int32_t* __restrict__ out) {
+  __shared__ int s_warp[32];
+  __shared__ int s_carry;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  if (tid == 0) { s_carry = 0; out[0] = 0; }
+  __syncthreads();
+  for (int base = 0; base < nseq; base += 1024) {
+    int i = base + tid;
+    int cnt = 0;
+    if (i < nseq) {
+      int len = cu[i + 1] - cu[i];
+      cnt = len > 0 ? (len + chunk - 1) / chunk : 0;
+    }
+    int x = cnt;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      int y = __shfl_up_sync(0xffffffffu, x, d);
+      if (lane >= d) x += y;
+    }
+    if (lane == 31) s_warp[warp] = x;
+    __syncthreads();
+    if (warp == 0) {
+      int w = s_warp[lane];
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        int y = __shfl_up_sync(0xffffffffu, w, d);
+        if (lane >= d) w += y;
+      }
+      s_warp[lane] = w;
+    }
+    __syncthreads();
+    int incl = x + (warp > 0 ? s_warp[warp - 1] : 0) + s_carry;
+    if (i < nseq) out[i + 1] = incl;
+    __syncthreads();
+    if (tid == 1023) s_carry = incl;
+    __syncthreads();
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// bounded gate + chunk-local inclusive prefix sum (log2 units)
+// ------------------------------------------------------------------------------------------
+struct GateParams {
+  const void* raw; int dt_raw;
+  const float* A_log; const float* dt_bias;
+  float* out;                 // forward: cumulative gate, fp32
+  const float* d_cum;         // backward: gradient of the cumulative gate
+  void* d_raw;                // backward: gradient of the raw gate (dtype of raw)
+  float* dA_part; float* dbias_part;  // backward: per-chunk partials [chunks, H*K]
+  const int32_t* cu_seqlens; const int32_t* chunk_offsets; int nseq;
+  int batch, T, H, K, chunk;
+  float lower_bound;
+};
+
+__device__ __forceinline__ bool gate_locate(const GateParams& p, int gc, int64_t& token0,
+                                            int& valid) {
+  if (p.cu_seqlens) {
+    if (gc >= p.chunk_offsets[p.nseq]) return false;
+    int lo = 0, hi = p.nseq;
+    while (lo < hi) {
+      int mid = (lo + hi + 1) >> 1;
+      if (p.chunk_offsets[mid] <= gc) lo = mid; else hi = mid - 1;
+    }
+    int64_t bos = p.cu_seqlens[lo], eos = p.cu_seqlens[lo + 1];
+    token0 = bos + (int64_t)(gc - p.chunk_offsets[lo]) * p.chunk;
+    int64_t rem = eos - token0;
+    valid = rem >= p.chunk ? p.chunk : (int)rem;
+    return valid > 0;
+  }
+  int cpr = (p.T + p.chunk - 1) / p.chunk;
+  int row = gc / cpr, lc = gc % cpr;
+  if (row >= p.batch) return false;
+  int64_t t0 = (int64_t)lc * p.chunk;
+  token0 = (int64_t)row * p.T + t0;
+  int64_t rem = p.T - t0;
+  valid = rem >= p.chunk ? p.chunk : (int)rem;
+  return true;
+}
+
+__device__ __forceinline__ void load4(const void* p, int dt, int64_t i, float (&x)[4]) {
+  if (dt == KDA_BF16) {
+    uint2 u = *reinterpret_cast<const uint2*>(reinterpret_cast<const bf16*>(p) + i);
+    float2 a = unpack_bf16(u.x), b = unpack_bf16(u.y);
+    x[0] = a.x; x[1] = a.y; x[2] = b.x; x[3] = b.y;
+  } else if (dt == KDA_F16) {
+    const __half* h = reinterpret_cast<const __half*>(p) + i;
+    uint2 u = *reinterpret_cast<const uint2*>(h);
+    __half2 a = *reinterpret_cast<__half2*>(&u.x), b = *reinterpret_cast<__half2*>(&u.y);
+    x[0] = __low2float(a); x[1] = __high2float(a); x[2] = __low2float(b); x[3] = __high2float(b);
+  } else {
+    float4 f = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p) + i);
+    x[0] = f.x; x[1] = f.y; x[2] = f.z; x[3] = f.w;
+  }
+}
+__device__ __forceinline__ void store4(void* p, int dt, int64_t i, const float (&x)[4]) {
+  if (dt == KDA_BF16) {
+    uint2 u; u.x = pack_bf16(x[0], x[1]); u.y = pack_bf16(x[2], x[3]);
+    *reinterpret_cast<uint2*>(reinterpret_cast<bf16*>(p) + i) = u;
+  } else if (dt == KDA_F16) {
+    __half2 a = __floats2half2_rn(x[0], x[1]), b = __floats2half2_rn(x[2], x[3]);
+    uint2 u; u.x = *reinterpret_cast<uint32_t*>(&a); u.y = *reinterpret_cast<uint32_t*>(&b);
+    *reinterpret_cast<uint2*>(reinterpret_cast<__half*>(p) + i) = u;
+  } else {
+    *reinterpret_cast<float4*>(reinterpret_cast<float*>(p) + i) =
+        make_float4(x[0], x[1], x[2], x[3]);
+  }
+}
+
+__global__ void __launch_bounds__(128) gate_cumsum_fwd_kernel(const GateParams p) {
+  const int HK = p.H * p.K;
+  const int f0 = (blockIdx.y * 128 + threadIdx.x) * 4;
+  if (f0 >= HK) return;
+  int64_t token0; int valid;
+  if (!gate_locate(p, blockIdx.x, token0, valid)) return;
+  const float a = expf(p.A_log[f0 / p.K]);
+  const float4 b4 = *reinterpret_cast<const float4*>(p.dt_bias + f0);
+  const float bias[4] = {b4.x, b4.y, b4.z, b4.w};
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 4
+  for (int r = 0; r < valid; ++r) {
+    int64_t idx = (token0 + r) * HK + f0;
+    float x[4], o[4];
+    load4(p.raw, p.dt_raw, idx, x);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float z = a * (x[j] + bias[j]);
+      acc[j] += p.lower_bound / (1.f + expf(-z));
+      o[j] = acc[j] * kLog2e;
+    }
+    store4(p.out, KDA_F32, idx, o);
+  }
+}
+
+__global__ void __launch_bounds__(128) gate_cumsum_bwd_kernel(const GateParams p) {
+  const int HK = p.H * p.K;
+  const int f0 = (blockIdx.y * 128 + threadIdx.x) * 4;
+  if (f0 >= HK) return;
+  int64_t token0; int valid;
+  float pa[4] = {0.f, 0.f, 0.f, 0.f}, pb[4] = {0.f, 0.f, 0.f, 0.f};
+  if (gate_locate(p, blockIdx.x, token0, valid)) {
+    const float a = expf(p.A_log[f0 / p.K]);
+    const float4 b4 = *reinterpret_cast<const float4*>(p.dt_bias + f0);
+    const float bias[4] = {b4.x, b4.y, b4.z, b4.w};
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 4
+    for (int r = valid - 1; r >= 0; --r) {
+      int64_t idx = (token0 + r) * HK + f0;
+      float x[4], d[4], o[4];
+      load4(p.raw, p.dt_raw, idx, x);
+      load4(p.d_cum, KDA_F32, idx, d);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        acc[j] += d[j];
+        float z = x[j] + bias[j];
+        float s = 1.f / (1.f + expf(-a * z));
+        o[j] = acc[j] * kLog2e * p.lower_bound * a * s * (1.f - s);
+        pa[j] += o[j] * z;
+        pb[j] += o[j];
+      }
+      store4(p.d_raw, p.dt_raw, idx, o);
+    }
+  }
+  int64_t pidx = (int64_t)blockIdx.x * HK + f0;
+  store4(p.dA_part, KDA_F32, pidx, pa);
+  store4(p.dbias_part, KDA_F32, pidx, pb);
+}
+
+// ------------------------------------------------------------------------------------------
+// L2 row normalisation: one warp per row
+// ------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) l2norm_fwd_kernel(const void* x, int dt, void* y,
+                                                         float* rstd, int64_t rows, int D,
+                                                         float eps) {
+  const int lane = threadIdx.x & 31;
+  int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  float ss = 0.f;
+  for (int c = lane * 4; c < D; c += 128) {
+    float v[4];
+    load4(x, dt, row * D + c, v);
+    ss += v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3];
+  }
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, d);
+  float r = rsqrtf(ss + eps);
+  if (lane == 0 && rstd) rstd[row] = r;
+  for (int c = lane * 4; c < D; c += 128) {
+    float v[4];
+    load4(x, dt, row * D + c, v);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) v[j] *= r;
+    store4(y, dt, row * D + c, v);
+  }
+}
+
+__global__ void __launch_bounds__(256) l2norm_bwd_kernel(const void* y, const float* rstd,
+                                                         const void* dy, int dt, void* dx,
+                                                         int64_t rows, int D) {
+  const int lane = threadIdx.x & 31;
+  int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  float dot = 0.f;
+  for (int c = lane * 4; c < D; c += 128) {
+    float a[4], b[4];
+    load4(y, dt, row * D + c, a);
+    load4(dy, dt, row * D + c, b);
+    dot += a[0] * b[0] + a[1] * b[1] + a[2] * b[2] + a[3] * b[3];
+  }
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, d);
+  float r = rstd[row];
+  for (int c = lane * 4; c < D; c += 128) {
+    float a[4], b[4], o[4];
+    load4(y, dt, row * D + c, a);
+    load4(dy, dt, row * D + c, b);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) o[j] = r * (b[j] - a[j] * dot);
+    store4(dx, dt, row * D + c, o);
+  }
+}
+
+static int check_launch() { return cudaGetLastError() == cudaSuccess ? KDA_OK : KDA_ERR_LAUNCH; }
+
+}  // namespace kda
+
+extern "C" int kda_prepare_chunk_offsets(const int32_t* cu_seqlens, int nseq, int chunk_size,
+                                         int32_t* chunk_offsets, void* stream) {
+  if (!cu_seqlens || !chunk_offsets || nseq < 1 || chunk_size < 1) return KDA_ERR_ARG;
+  kda::chunk_offsets_kernel<<<1, 1024, 0, (cudaStream_t)stream>>>(cu_seqlens, nseq, chunk_size,
+                                                                  chunk_offsets);
+  return kda::check_launch();
+}
+
+static int gate_common(kda::GateParams& p, const int32_t* cu, const int32_t* co, int nseq,
+                       int batch, int tokens, int heads, int dim, int chunk, int64_t chunks) {
+  if (heads <= 0 || dim <= 0 || dim % 4 || chunk < 1 || batch < 1 || tokens < 1) return KDA_ERR_ARG;
+  if ((cu != nullptr) != (co != nullptr)) return KDA_ERR_ARG;
+  if (cu && batch != 1) return KDA_ERR_ARG;
+  if (chunks > 0x7fffffffLL) return KDA_ERR_UNSUPPORTED;
+  p.cu_seqlens = cu; p.chunk_offsets = co; p.nseq = nseq;
+  p.batch = batch; p.T = tokens; p.H = heads; p.K = dim; p.chunk = chunk;
+  return KDA_OK;
+}
+
+extern "C" int kda_gate_cumsum_fwd(const void* raw_gate, int dt_raw, const float* A_log,
+                                   const float* dt_bias, float* out, const int32_t* cu_seqlens,
+                                   const int32_t* chunk_offsets, int nseq, int batch, int tokens,
+                                   int heads, int dim, int chunk_size, float lower_bound,
+                                   int64_t num_chunks, void* stream) {
+  if (!raw_gate || !A_log || !dt_bias || !out) return KDA_ERR_ARG;
+  kda::GateParams p{};
+  int rc = gate_common(p, cu_seqlens, chunk_offsets, nseq, batch, tokens, heads, dim, chunk_size,
+                       num_chunks);
+  if (rc) return rc;
+  if (num_chunks == 0) return KDA_OK;
+  p.raw = raw_gate; p.dt_raw = dt_raw; p.A_log = A_log; p.dt_bias = dt_bias; p.out = out;
+  p.lower_bound = lower_bound;
+  dim3 grid((unsigned)num_chunks, (unsigned)((heads * dim / 4 + 127) / 128));
+  kda::StageScope timing(kda::kStageGateFwd, (cudaStream_t)stream);
+  kda::gate_cumsum_fwd_kernel<<<grid, 128, 0, (cudaStream_t)stream>>>(p);
+  return kda::check_launch();
+}
+
+extern "C" int kda_gate_cumsum_bwd(const void* raw_gate, int dt_raw, const float* A_log,
+                                   const float* dt_bias, const float* d_cumulative, void* d_raw,
+                                   float* dA_partial, float* dbias_partial,
+                                   const int32_t* cu_seqlens, const int32_t* chunk_offsets,
+                                   int nseq, int batch, int tokens, int heads, int dim,
+                                   int chunk_size, float lower_bound, int64_t num_chunks,
+                                   void* stream) {
+  if (!raw_gate || !A_log || !dt_bias || !d_cumulative || !d_raw || !dA_partial || !dbias_partial)
+    return KDA_ERR_ARG;
+  kda::GateParams p{};
+  int rc = gate_common(p, cu_seqlens, chunk_offsets, nseq, batch, tokens, heads, dim, chunk_size,
+                       num_chunks);
+  if (rc) return rc;
+  if (num_chunks == 0) return KDA_OK;
+  p.raw = raw_gate; p.dt_raw = dt_raw; p.A_log = A_log; p.dt_bias = dt_bias;
+  p.d_cum = d_cumulative; p.d_raw = d_raw; p.dA_part = dA_partial; p.dbias_part = dbias_partial;
+  p.lower_bound = lower_bound;
+  dim3 grid((unsigned)num_chunks, (unsigned)((heads * dim / 4 + 127) / 128));
+  kda::StageScope timing(kda::kStageGateBwd, (cudaStream_t)stream);
+  kda::gate_cumsum_bwd_kernel<<<grid, 128, 0, (cudaStream_t)stream>>>(p);
+  return kda::check_launch();
+}
+
+extern "C" int kda_l2norm_fwd(const void* x, int dtype, void* y, float* rstd, int64_t rows,
+                              int dim, float eps, void* stream) {
+  if (!x || !y || rows < 0 || dim <= 0 || dim % 4) return KDA_ERR_ARG;
+  if (rows == 0) return KDA_OK;
+  kda::l2norm_fwd_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, (cudaStream_t)stream>>>(
+      x, dtype, y, rstd, rows, dim, eps);
+  return kda::check_launch();
+}
+
+extern "C" int kda_l2norm_bwd(const void* y, const float* rstd, const void* dy, int dtype, void* dx,
+                              int64_t rows, int dim, void* stream) {
+  if (!y || !rstd || !dy || !dx || rows < 0 || dim <= 0 || dim % 4) return KDA_ERR_ARG;
+  if (rows == 0) return KDA_OK;
+  kda::l2norm_bwd_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, (cudaStream_t)stream>>>(
+      y, rstd, dy, dtype, dx, rows, dim);
+  return kda::check_launch();
+}

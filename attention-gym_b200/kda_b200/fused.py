@@ -1,0 +1,94 @@
+"""Autograd wrapper around the fused chunk operators.
+
+Same role and call signature as the reference's ``impl/fused.py`` (chunk_forward :147-216,
+_ChunkKDA :35-144): normalise dtypes (q, k, v -> bf16; gate, beta, state -> fp32), pick the
+dense or packed operator, save (q, k, v, gate, beta, tape, h0, offsets) and run the first-order
+backward operator.  Dense inputs of any batch size and length go to the kernels as equal-length
+packed sequences, built inside the operator.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from . import ops
+from .chunk_schedule import RaggedChunkMetadata, prepare_ragged_chunk_metadata
+
+_CHUNK = 64
+_HEAD_DIM = 128
+
+
+def _validate_fused_constraints(q, v):
+    if not q.is_cuda:
+        raise ValueError("the fused KDA core requires CUDA tensors")
+    if q.shape[-1] != _HEAD_DIM or v.shape[-1] != _HEAD_DIM:
+        raise ValueError("the fused KDA core requires K=V=128")
+
+
+class _ChunkKDA(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, gate, beta, initial_state, cu_seqlens, chunk_offsets,
+                output_final_state, fastmath, autotune):
+        state = None
+        if cu_seqlens is None:
+            if output_final_state:
+                out, state, aqk, akk = ops.chunk_fwd_with_state_op(q, k, v, gate, beta,
+                                                                   initial_state, autotune)
+            else:
+                out, aqk, akk = ops.chunk_fwd_op(q, k, v, gate, beta, initial_state, autotune)
+        elif output_final_state:
+            out, state, aqk, akk = ops.chunk_fwd_ragged_with_state_op(
+                q, k, v, gate, beta, initial_state, cu_seqlens, chunk_offsets, autotune)
+        else:
+            out, aqk, akk = ops.chunk_fwd_ragged_op(q, k, v, gate, beta, initial_state, cu_seqlens,
+                                                    chunk_offsets, autotune)
+        ctx.save_for_backward(q, k, v, gate, beta, aqk, akk, initial_state, cu_seqlens,
+                              chunk_offsets)
+        ctx.fastmath, ctx.autotune = fastmath, autotune
+        ctx.set_materialize_grads(False)
+        return (out, state) if output_final_state else out
+
+    @staticmethod
+    @torch.autograd.function.once_differentiable
+    def backward(ctx, d_output, d_final_state=None):
+        q, k, v, gate, beta, aqk, akk, initial_state, cu_seqlens, chunk_offsets = ctx.saved_tensors
+        args = (q, k, v, gate, beta, aqk, akk, cu_seqlens, chunk_offsets, d_output, d_final_state,
+                initial_state, ctx.fastmath, ctx.autotune)
+        if initial_state is not None:
+            dq, dk, dv, dg, db, dh0 = ops.chunk_bwd_with_state_grad_op(*args)
+        else:
+            dq, dk, dv, dg, db = ops.chunk_bwd_op(*args)
+            dh0 = None
+        return dq, dk, dv, dg, db, dh0, None, None, None, None, None
+
+
+def chunk_forward(q, k, v, cumulative_gate, beta, initial_state=None, *, cu_seqlens=None,
+                  metadata: RaggedChunkMetadata | None = None, output_final_state=False,
+                  fastmath=False, autotune=True):
+    """Normalise inputs and run the fused chunk operators (reference: impl/fused.py:147-216)."""
+    if metadata is not None:
+        assert cu_seqlens is None
+        metadata.validate_chunk_size(_CHUNK)
+        cu_seqlens = metadata.cu_seqlens
+    _validate_fused_constraints(q, v)
+    out_dtype, out_shape = q.dtype, q.shape
+    q, k, v = (t.to(torch.bfloat16) for t in (q, k, v))
+    cumulative_gate = cumulative_gate.float().contiguous()
+    beta = beta.float().contiguous()
+    if cu_seqlens is not None and metadata is None:
+        metadata = prepare_ragged_chunk_metadata(cu_seqlens, q.shape[1], _CHUNK)
+    if initial_state is not None:
+        initial_state = initial_state.float().contiguous()
+    cu = None if metadata is None else metadata.cu_seqlens
+    offsets = None if metadata is None else metadata.chunk_offsets
+    if output_final_state:
+        out, state = _ChunkKDA.apply(q, k, v, cumulative_gate, beta, initial_state, cu, offsets,
+                                     True, fastmath, autotune)
+    else:
+        out = _ChunkKDA.apply(q, k, v, cumulative_gate, beta, initial_state, cu, offsets, False,
+                              fastmath, autotune)
+        state = None
+    return out.reshape(out_shape).to(out_dtype), state
+
+
+__all__ = ["chunk_forward"]

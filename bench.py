@@ -1,0 +1,339 @@
+"""Benchmark of the KDA hot path: chunked forward + backward tokens/s (H32, K=V=128, bf16).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--small]
+
+One step = one forward + backward pass of ``chunk_kda`` over one batch of synthetic input with the
+shapes and value distributions of the headline configuration (B=8, T=4096, H=32, K=V=128,
+chunk 64; q, k L2-normalised N(0,1), v ~ N(0,1), g = logsigmoid(N(0,1)), beta = sigmoid(N(0,1)),
+dO ~ N(0,1)).  Inputs (1.5 GiB) are far larger than L2, so no flush is needed between steps.
+
+Rank 0 prints one JSON line.  ``value`` is device-resident throughput (CUDA events, max over
+ranks); ``e2e`` is the same step with pinned HOST buffers, host<->device copies inside the timed
+region; ``roofline`` describes the kernel that takes the largest share of the step (timed live
+with CUDA events on the launching stream); ``cpu_baseline`` is the CPU oracle port timed on a
+bounded sample on this machine's cores.  Multi-GPU runs shard by (batch, head) with no collective:
+every rank runs the full per-GPU workload (weak scaling).
+
+``--impl reference`` times the CPU port of the reference path (the oracle) instead.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for _p in (ROOT, os.path.join(ROOT, "attention-gym_b200")):
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
+
+import torch  # noqa: E402
+
+METRIC = "KDA fwd+bwd tokens/s (H32,K=V=128,bf16)"
+H, D, CHUNK = 32, 128, 64
+
+# algorithmic HBM bytes per (token, head) of each kernel: what its interface must read + write
+STAGE_BYTES = {
+    "intra_solve": 2 * 256 + 512 + 4 + 2 * 128,                 # q,k bf16 + G fp32 + beta -> Aqk, Akk
+    "wu": 3 * 256 + 512 + 4 + 128 + 4 * 256,                    # q,k,v,G,beta,Akk -> w,u,kg,qg
+    "state_fwd": 4 * 256 + 128 + 8 + 256,                       # w,u,kg,qg,Aqk,G_last -> o
+    "state_fwd_recompute": 4 * 256 + 128 + 8 + 512 + 256,       # ... -> h[c] (bf16) + v_new
+    "state_bwd": 3 * 256 + 256 + 128 + 8 + 512 + 256,           # w,kg,qg,dO,Aqk -> dh[c], dv2
+    "bwd_wy": 1024 + 6 * 256 + 512 + 128 + 4 + 3 * 512 + 256 + 2 * 256 + 4,
+    "bwd_intra": 2 * 256 + 512 + 2 * 256 + 3 * 512 + 8 + 2 * 256 + 512 + 4,
+}
+# the path's algorithmic minimum (inputs once, outputs once), bytes per token per head
+PATH_BYTES_FWD_BWD = 4620
+PATH_FLOP_FWD_BWD = 576171
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d.get("bf16_tflops_sustained", d["bf16_tflops"]),
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.samples, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-i", str(self.index), "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) >= 6:
+                self.samples.append(parts)
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unavailable"]}
+        mhz = sorted(int(s[0]) for s in self.samples if s[0].isdigit())
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(s[2 + i] == "Active" for s in self.samples)]
+        mx = [int(s[1]) for s in self.samples if s[1].isdigit()]
+        return {"sm_mhz": mhz[len(mhz) // 2] if mhz else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(self.samples)}
+
+
+def make_host_inputs(batch, tokens, seed, pin):
+    """Synthetic step inputs on the host (pinned when asked), in the dtypes the kernels consume."""
+    from oracle.kda_oracle import LOG2E  # constants only; inputs are generated with torch here
+
+    gen = torch.Generator().manual_seed(seed)
+    shape = (batch, tokens, H, D)
+
+    def rnd(*s):
+        return torch.randn(*s, generator=gen)
+
+    q = torch.nn.functional.normalize(rnd(*shape), dim=-1).bfloat16()
+    k = torch.nn.functional.normalize(rnd(*shape), dim=-1).bfloat16()
+    v = rnd(*shape).bfloat16()
+    g = torch.nn.functional.logsigmoid(rnd(*shape)) * LOG2E
+    g = g.view(batch, tokens // CHUNK, CHUNK, H, D).cumsum(2).view(shape).contiguous()
+    beta = torch.sigmoid(rnd(batch, tokens, H))
+    do = rnd(*shape).bfloat16()
+    out = {"q": q, "k": k, "v": v, "g": g, "beta": beta, "do": do}
+    if pin:
+        out = {n: t.pin_memory() for n, t in out.items()}
+    return out
+
+
+def step_device(kda_b200, dev):
+    q, k, v, g, beta = (dev[n].detach().requires_grad_(True) for n in ("q", "k", "v", "g", "beta"))
+    o, _ = kda_b200.chunk_kda(q, k, v, g, beta)
+    grads = torch.autograd.grad(o, (q, k, v, g, beta), dev["do"])
+    return o, grads
+
+
+def run_ours(args):
+    import kda_b200
+    from kda_b200 import _cabi
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=device)
+    batch, tokens = (2, 1024) if args.small else (8, 4096)
+    tokens_per_step = batch * tokens
+    host = make_host_inputs(batch, tokens, seed=1234 + rank, pin=True)
+    dev = {n: t.to(device, non_blocking=True) for n, t in host.items()}
+    torch.cuda.synchronize()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step_device(kda_b200, dev)
+    barrier()
+    _cabi.stage_timing(True)
+    _cabi.read_stage_timing(reset=True)
+    launches0 = _cabi.launch_count
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local_rank) as clocks:
+        barrier()
+        start.record()
+        for _ in range(args.steps):
+            step_device(kda_b200, dev)
+        stop.record()
+        barrier()
+    ms = start.elapsed_time(stop)
+    stages = _cabi.read_stage_timing(reset=True)
+    _cabi.stage_timing(False)
+    launches = _cabi.launch_count - launches0
+
+    # ---- end to end: pinned host buffers in, host buffers out, copies inside the timed region ----
+    out_host = None
+    e2e_steps = max(1, min(args.steps, 3))
+
+    def step_e2e():
+        nonlocal out_host
+        d = {n: t.to(device, non_blocking=True) for n, t in host.items()}
+        o, grads = step_device(kda_b200, d)
+        outs = (o,) + tuple(grads)
+        if out_host is None:
+            out_host = [torch.empty(t.shape, dtype=t.dtype).pin_memory() for t in outs]
+        for h, t in zip(out_host, outs):
+            h.copy_(t, non_blocking=True)
+
+    step_e2e()
+    barrier()
+    s2, e2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s2.record()
+    for _ in range(e2e_steps):
+        step_e2e()
+    e2.record()
+    barrier()
+    ms_e2e = s2.elapsed_time(e2)
+    h2d = sum(t.numel() * t.element_size() for t in host.values())
+    d2h = sum(t.numel() * t.element_size() for t in out_host)
+
+    if world > 1:
+        t = torch.tensor([ms, ms_e2e], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, ms_e2e = float(t[0]), float(t[1])
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    peaks = load_peaks()
+    value = world * tokens_per_step * args.steps / (ms * 1e-3)
+    e2e_value = world * tokens_per_step * e2e_steps / (ms_e2e * 1e-3)
+    # dominant kernel = largest share of the timed region
+    roofline, breakdown = None, {}
+    total_stage_ms = sum(v[1] for v in stages.values()) or 1.0
+    for name, (n, tot) in stages.items():
+        breakdown[name] = {"launches": n, "ms_per_launch": round(tot / n, 4),
+                           "share": round(tot / total_stage_ms, 4)}
+    if stages:
+        top = max(stages, key=lambda n: stages[n][1])
+        n, tot = stages[top]
+        per_launch_ms = tot / n
+        units = tokens_per_step * H
+        key = top
+        if top in ("state_fwd", "wu"):  # two launches per step with different traffic: average
+            per_unit = (STAGE_BYTES["state_fwd"] + STAGE_BYTES["state_fwd_recompute"]) / 2 \
+                if top == "state_fwd" else STAGE_BYTES["wu"]
+        else:
+            per_unit = STAGE_BYTES.get(key, 0)
+        achieved = per_unit * units / (per_launch_ms * 1e-3) / 1e9
+        roofline = {"kernel": top, "bound": "hbm", "achieved": round(achieved, 1),
+                    "peak": peaks["hbm_gbs"], "peak_source": peaks["source"], "unit": "GB/s",
+                    "frac": round(achieved / peaks["hbm_gbs"], 4), "traffic": None,
+                    "bytes_per_token_head": per_unit, "ms_per_launch": round(per_launch_ms, 4)}
+    path = {"hbm_frac": round(value * H * PATH_BYTES_FWD_BWD / 1e9 / world / peaks["hbm_gbs"], 4),
+            "tensor_frac": round(value * H * PATH_FLOP_FWD_BWD / 1e12 / world / peaks["bf16_tflops"], 4),
+            "achieved_gbs": round(value * H * PATH_BYTES_FWD_BWD / 1e9 / world, 1),
+            "achieved_tflops": round(value * H * PATH_FLOP_FWD_BWD / 1e12 / world, 1)}
+    cpu = cpu_baseline(bounded=True) if world == 1 or rank == 0 else None
+    line = {
+        "metric": METRIC, "value": round(value, 1), "unit": "tokens/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms / args.steps, 4),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic",
+        "config": {"workload": f"config1: chunk_kda fwd+bwd B={batch} T={tokens} H={H} K=V={D} "
+                               f"chunk={CHUNK} per GPU, sharded by (batch, head), no collective",
+                   "l2": "inputs (1.5 GiB) larger than L2, no flush"},
+        "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": d2h, "steps": e2e_steps},
+        "gpu_launches": launches,
+        "clocks": clocks.summary(),
+        "roofline": roofline,
+        "path_roofline": path,
+        "kernels": breakdown,
+        "cpu_baseline": cpu,
+    }
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def cpu_sample_step(threads):
+    """One bounded CPU sample: the oracle port, fwd+bwd, B=1 T=1024 H=32 K=V=128 fp32."""
+    from oracle import kda_oracle as orc
+
+    torch.set_num_threads(threads)
+    inp = orc.make_inputs(1, 1024, H, D, D, seed=7)
+    gen = torch.Generator().manual_seed(3)
+    do = torch.randn(inp["v"].shape, generator=gen)
+    t0 = time.perf_counter()
+    orc.chunk_kda_grads_ref(inp["q"], inp["k"], inp["v"], inp["cum_gate"], inp["beta"], do,
+                            dtype=torch.float32)
+    return 1024, time.perf_counter() - t0
+
+
+def cpu_baseline(bounded=True):
+    threads = os.cpu_count() or 1
+    tokens, secs = cpu_sample_step(threads)
+    return {"value": round(tokens / secs, 2), "unit": "tokens/s", "cores": threads, "kind": "port",
+            "sample": "oracle port (eager PyTorch fp32) chunk fwd+bwd, B=1 T=1024 H=32 K=V=128, "
+                      "1 run"}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    for _ in range(args.warmup):
+        cpu_sample_step(threads)
+    total_tokens, total_s = 0, 0.0
+    for _ in range(args.steps):
+        n, s = cpu_sample_step(threads)
+        total_tokens += n
+        total_s += s
+    value = total_tokens / total_s
+    line = {
+        "impl": "reference", "metric": METRIC, "value": round(value, 2), "unit": "tokens/s",
+        "n_gpus": int(os.environ.get("WORLD_SIZE", "1")), "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": round(1e3 * total_s / args.steps, 2),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic",
+        "config": {"workload": "config1 shape, bounded CPU sample per step: chunk_kda fwd+bwd "
+                               f"B=1 T=1024 H={H} K=V={D} chunk={CHUNK} (fp32, host cores)"},
+        "cpu_baseline": {"value": round(value, 2), "unit": "tokens/s", "cores": threads,
+                         "kind": "port", "sample": "oracle port, B=1 T=1024 H=32 per step"},
+        "e2e": {"value": round(value, 2), "unit": "tokens/s", "h2d_bytes_per_step": 0,
+                "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--small", action="store_true", help="B=2 T=1024 (for profiler captures)")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+        return
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback of the fused path)")
+    run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,172 @@
+/* C ABI of libkda_b200.so: hand-written sm_100a CUDA kernels for the KDA (Kimi Delta Attention)
+ * gated delta-rule path of meta-pytorch/attention-gym (attn_gym.linear).
+ *
+ * The reference has no native ABI on this path: its kernels are Triton / CuTeDSL callables bound
+ * behind torch.library operators (attn_gym/linear/kda/ops.py:18-136).  Each entry point below is
+ * what the CUDA implementation of one of those operators binds to; the citation names the
+ * operator (or launcher) it replaces.
+ *
+ * Conventions
+ *   - every pointer is a device pointer; sizes are element counts unless named *_bytes;
+ *   - `stream` is a cudaStream_t passed as void*; calls are asynchronous on it, never synchronise,
+ *     never allocate (callers provide outputs and workspaces) and are re-entrant;
+ *   - activations are token-major [N, H, D] with D contiguous; states are [nseq, H, K, V] fp32;
+ *   - gates are log2 decays (a = 2^g);
+ *   - packed sequences: int32 cu_seqlens[nseq + 1] (starts at 0, non-decreasing, may repeat, may end
+ *     before N) and chunk_offsets[nseq + 1] from kda_prepare_chunk_offsets; a dense [B, T] batch is
+ *     the packed form with cu_seqlens = {0, T, 2T, ...};
+ *   - return value: KDA_OK or a negative KDA_ERR_* code.
+ */
+#ifndef KDA_B200_H_
+#define KDA_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define KDA_F32 0
+#define KDA_BF16 1
+#define KDA_F16 2
+
+#define KDA_OK 0
+#define KDA_ERR_ARG (-1)         /* null pointer, bad size or inconsistent arguments */
+#define KDA_ERR_UNSUPPORTED (-2) /* shape outside what the kernels are built for */
+#define KDA_ERR_LAUNCH (-3)      /* the CUDA runtime refused the launch */
+
+/* Library identification: returns 100 * major + minor. */
+int kda_b200_version(void);
+
+/* Optional per-kernel timing with CUDA events recorded on the launching stream (off by default).
+ * kda_stage_timing_read synchronises the recorded events and fills launches[] / total_ms[] (arrays of
+ * kda_stage_count() entries, indexed like kda_stage_name); reset != 0 clears the records.
+ * No reference counterpart: the reference times stages with torch.profiler ranges
+ * (attn_gym/linear/kda/utils.py:269-273). */
+int kda_stage_count(void);
+const char* kda_stage_name(int stage);
+int kda_stage_timing_enable(int on);
+int kda_stage_timing_read(int64_t* launches, float* total_ms, int reset);
+
+/* chunk_offsets[i + 1] = sum_{s <= i} ceil(len_s / chunk_size), chunk_offsets[0] = 0.
+ * Replaces attn_gym::kda_prepare_chunk_offsets (kda/ops.py:73-76,
+ * kda/chunk_scheduler.py:279 `_prepare_ragged_chunk_offsets_kernel`). */
+int kda_prepare_chunk_offsets(const int32_t* cu_seqlens, int nseq, int chunk_size,
+                              int32_t* chunk_offsets, void* stream);
+
+/* Token-sequential scan (decode step and inference prefill):
+ *   S <- diag(2^g) S; d = beta (v - S^T k); S <- S + k d^T; o = scale S^T q.
+ * q, k, gate: [*, H, K]; v, out: [*, H, V]; beta: [*, H]; dtypes by code.  Dense: nseq rows of
+ * tokens_per_row tokens (cu_seqlens NULL); packed: one row, sequence i = [cu[i], cu[i+1]).
+ * initial_state may be NULL (zeros); final_state may be NULL.  Paged form: state_indices != NULL,
+ * initial_state is the pool [num_slots, H, K, V] with `slot_stride` elements between slots and is
+ * advanced in place; entries <= 0 (or >= num_slots) are padding: zero output rows, pool untouched.
+ * Replaces attn_gym::kda_recurrent_fwd / _no_state / _paged (kda/ops.py:60-72,
+ * fwd/triton/recurrent.py:41 `_kda_recurrent_fwd_kernel`). */
+int kda_recurrent_fwd(const void* q, const void* k, const void* v, const void* gate,
+                      const void* beta, int dt_q, int dt_k, int dt_v, int dt_gate, int dt_beta,
+                      const float* initial_state, float* final_state, void* out, int dt_out,
+                      const int32_t* cu_seqlens, const int32_t* state_indices, int64_t slot_stride,
+                      int num_slots, int nseq, int tokens_per_row, int heads, int key_dim,
+                      int value_dim, float scale, void* stream);
+
+/* out = log2(e) * chunk_local_cumsum(lower_bound * sigmoid(exp(A_log[h]) * (raw + dt_bias[h, :]))).
+ * raw: [batch, tokens, H, dim] (dtype code), out fp32 of the same shape; dim % 4 == 0.
+ * num_chunks = batch * ceil(tokens / chunk_size) for dense input, the chunk capacity for packed
+ * input (cu_seqlens / chunk_offsets built with the same chunk_size; both NULL when dense).
+ * Replaces attn_gym::kda_bounded_gate_fwd_dense / _ragged (fwd/triton/gate_fwd.py:379-393, :59, :220). */
+int kda_gate_cumsum_fwd(const void* raw_gate, int dt_raw, const float* A_log, const float* dt_bias,
+                        float* out, const int32_t* cu_seqlens, const int32_t* chunk_offsets,
+                        int nseq, int batch, int tokens, int heads, int dim, int chunk_size,
+                        float lower_bound, int64_t num_chunks, void* stream);
+
+/* Backward of the above: d_raw (dtype of raw) and per-chunk partial sums
+ * dA_partial, dbias_partial: fp32 [num_chunks, H * dim]; dA_log[h] = sum over chunks and dim of
+ * dA_partial, d_dt_bias = sum over chunks of dbias_partial.
+ * Replaces attn_gym::kda_fused_gate_bwd (bwd/cute/gate_bwd_fused.py:498-502) and
+ * attn_gym::kda_bounded_gate_bwd_ragged (fwd/triton/gate_fwd.py:389-393, bwd/triton/gate_bwd.py:141). */
+int kda_gate_cumsum_bwd(const void* raw_gate, int dt_raw, const float* A_log, const float* dt_bias,
+                        const float* d_cumulative, void* d_raw, float* dA_partial,
+                        float* dbias_partial, const int32_t* cu_seqlens,
+                        const int32_t* chunk_offsets, int nseq, int batch, int tokens, int heads,
+                        int dim, int chunk_size, float lower_bound, int64_t num_chunks,
+                        void* stream);
+
+/* y = x * rsqrt(sum(x^2) + eps) per row of `dim` elements; rstd (fp32 [rows]) may be NULL.
+ * Replaces attn_gym::kda_l2norm_fwd / _bwd (fwd/triton/l2norm_fwd.py:84,143; bwd/triton/l2norm_bwd.py:37). */
+int kda_l2norm_fwd(const void* x, int dtype, void* y, float* rstd, int64_t rows, int dim, float eps,
+                   void* stream);
+int kda_l2norm_bwd(const void* y, const float* rstd, const void* dy, int dtype, void* dx,
+                   int64_t rows, int dim, void* stream);
+
+/* Chunked forward, bf16 q/k/v [tokens, H, 128], fp32 cumulative log2 gate and beta, chunk 64.
+ * Writes out (bf16 [tokens, H, 128]), the tape aqk / akk (bf16 [tokens, H, 64]) and, when
+ * final_state != NULL, the fp32 final states.  workspace: kda_chunk_fwd_workspace_bytes() bytes,
+ * 16-byte aligned; num_chunks is the launch bound on active chunks (the capacity).
+ * Replaces attn_gym::kda_chunk_fwd / _with_state / _ragged / _ragged_with_state
+ * (kda/ops.py:18-42, fwd/cute/chunk_kda_fwd.py:134-200). */
+int64_t kda_chunk_fwd_workspace_bytes(int64_t tokens, int heads);
+int kda_chunk_fwd(const void* q, const void* k, const void* v, const float* cum_gate,
+                  const float* beta, const float* initial_state, float* final_state, void* out,
+                  void* aqk, void* akk, const int32_t* cu_seqlens, const int32_t* chunk_offsets,
+                  int nseq, int64_t tokens, int heads, int key_dim, int value_dim, int num_chunks,
+                  void* workspace, int64_t workspace_bytes, void* stream);
+
+/* Chunked backward.  d_out bf16 [tokens, H, 128] (required), d_final_state / initial_state /
+ * d_initial_state fp32 or NULL.  dq, dk, dv bf16; dg (w.r.t. the cumulative gate) and dbeta fp32.
+ * Replaces attn_gym::kda_chunk_bwd / _with_state_grad (kda/ops.py:44-58,
+ * bwd/cute/chunk_kda_bwd.py:21). */
+int64_t kda_chunk_bwd_workspace_bytes(int64_t tokens, int heads, int64_t num_chunks);
+int kda_chunk_bwd(const void* q, const void* k, const void* v, const float* cum_gate,
+                  const float* beta, const void* aqk, const void* akk, const float* initial_state,
+                  const void* d_out, const float* d_final_state, void* dq, void* dk, void* dv,
+                  float* dg, float* dbeta, float* d_initial_state, const int32_t* cu_seqlens,
+                  const int32_t* chunk_offsets, int nseq, int64_t tokens, int heads, int key_dim,
+                  int value_dim, int num_chunks, void* workspace, int64_t workspace_bytes,
+                  void* stream);
+
+/* Context parallelism: dense slice transition M [nseq, H, 128, 128] such that the state leaving a
+ * slice is M h_in + b (b = the slice's final state from a zero initial state).  Must follow a
+ * kda_chunk_fwd call on the same inputs and workspace; identity_state holds nseq*H identity
+ * matrices.  The reference has no counterpart (docs/linear.md:220-222 leaves context parallelism
+ * to the caller). */
+int kda_chunk_transition(const float* cum_gate, const float* identity_state, float* transition,
+                         const int32_t* cu_seqlens, const int32_t* chunk_offsets, int nseq,
+                         int64_t tokens, int heads, void* aqk, void* workspace, void* stream);
+
+/* h_out = transition * h_in + b for `count` independent [key_dim x value_dim] fp32 states
+ * (transition: [count, key_dim, key_dim]); key_dim and value_dim multiples of 64.  Applies the
+ * boundary-state correction of the context-parallel prefix chain; no reference counterpart. */
+int kda_state_affine(const float* transition, const float* h_in, const float* b, float* h_out,
+                     int count, int key_dim, int value_dim, void* stream);
+
+/* Causal depthwise convolution y[t,c] = act(sum_j w[c,j] x[t-(W-1)+j, c]), x/y [batch, tokens, C],
+ * w [C, W] (W <= 8), same dtype code for x, w, y, state; C a multiple of 16 bytes of elements.
+ * initial_state [nseq, W-1, C] (oldest first) or NULL; activation: 0 none, 1 SiLU.
+ * Packed input: batch == 1 and cu_seqlens[nseq + 1]; rows past cu_seqlens[nseq] are not written.
+ * Replaces attn_gym::_cute_short_conv_fwd (kda/ops.py:91-95, short_conv/cute.py:296). */
+int kda_conv1d_fwd(const void* x, const void* weight, const void* initial_state, void* y, int dtype,
+                   const int32_t* cu_seqlens, int nseq, int batch, int tokens, int channels,
+                   int width, int activation, void* stream);
+
+/* Backward of kda_conv1d_fwd.  dx like x; dw_partial fp32 [kda_conv1d_bwd_blocks(), C, W] (sum over
+ * the first axis gives dw); dstate fp32 [nseq, W-1, C] zero-initialised by the caller, or NULL;
+ * dpre_scratch fp32 [batch * tokens, C].
+ * Replaces attn_gym::_cute_short_conv_bwd (kda/ops.py:106-110; short_conv/cute.py:582, :791, :1960). */
+int64_t kda_conv1d_bwd_blocks(int batch, int tokens, int packed);
+int kda_conv1d_bwd(const void* x, const void* weight, const void* initial_state, const void* dy,
+                   void* dx, float* dw_partial, float* dstate, float* dpre_scratch, int dtype,
+                   const int32_t* cu_seqlens, int nseq, int batch, int tokens, int channels,
+                   int width, int activation, void* stream);
+
+/* One token per sequence over a paged history pool state [num_slots, W-1, C], advanced in place;
+ * state_indices NULL means sequence i uses slot i; entries <= 0 are padding (zero output).
+ * Replaces attn_gym::_cute_short_conv_decode (kda/ops.py:96-100, short_conv/cute.py:470). */
+int kda_conv1d_decode(const void* x, const void* weight, void* state, const int32_t* state_indices,
+                      void* y, int dtype, int nseq, int num_slots, int channels, int width,
+                      int activation, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* KDA_B200_H_ */

@@ -127,7 +127,7 @@ def _chunk_intra(qc, kc, vc, gc, bc, sc):
     return aqk, a, w, u, kg, qg, d_last
 
 
-def _chunk_sequence(q, k, v, g, beta, state, sc, chunk):
+def _chunk_sequence(q, k, v, g, beta, state, sc, chunk, trace=None):
     """One sequence ``[T, H, D]`` -> (o [T,H,V], final state [H,K,V]).
 
     Pads the tail chunk the way naive.py:196-201 does (zero q/k/v/beta, the last
@@ -148,14 +148,23 @@ def _chunk_sequence(q, k, v, g, beta, state, sc, chunk):
     qc, kc, vc, gc = map(split, (q, k, v, g))
     bc = beta.reshape(n, chunk, h).permute(2, 0, 1)
     outs = []
-    group = max(1, 4096 // max(1, h))  # bound the [.., C, C, K] pairwise tensor
+    group = max(1, 64 // max(1, h))  # bound the [.., C, C, K] pairwise tensor (~130 MB)
     intra = []
     for c0 in range(0, n, group):
         sl = slice(c0, min(n, c0 + group))
         intra.append(_chunk_intra(qc[:, sl], kc[:, sl], vc[:, sl], gc[:, sl], bc[:, sl], sc))
     aqk, a, w, u, kg, qg, d_last = (torch.cat([x[i] for x in intra], 1) for i in range(7))
+    if trace is not None:
+        trace.setdefault("intra", []).append(
+            {"aqk": aqk, "akk": a, "w": w, "u": u, "kg": kg, "qg": qg})
     for c in range(n):
         v_new = u[:, c] - w[:, c] @ state
+        if trace is not None:
+            if state.requires_grad:
+                state.retain_grad()
+                v_new.retain_grad()
+            trace.setdefault("h", []).append(state)
+            trace.setdefault("v_new", []).append(v_new)
         outs.append(qg[:, c] @ state + aqk[:, c] @ v_new)
         state = state * torch.exp2(d_last[:, c])[..., None] + kg[:, c].transpose(-1, -2) @ v_new
     o = torch.stack(outs, 1).reshape(h, n * chunk, vd).permute(1, 0, 2)[:t]
@@ -172,6 +181,7 @@ def chunk_kda_ref(
     cu_seqlens: Optional[torch.Tensor] = None,
     scale: Optional[float] = None,
     chunk_size: int = CHUNK,
+    trace: Optional[dict] = None,
 ) -> Tuple[torch.Tensor, torch.Tensor]:
     """Chunk-parallel KDA from the chunk-local cumulative log2 gate; differentiable.
 
@@ -205,7 +215,7 @@ def chunk_kda_ref(
             continue
         o, s1 = _chunk_sequence(
             qf[row, bos:eos], kf[row, bos:eos], vf[row, bos:eos], gf[row, bos:eos],
-            bf[row, bos:eos], s0, sc, chunk_size,
+            bf[row, bos:eos], s0, sc, chunk_size, trace,
         )
         rows[row].append(o)
         cursor[row] = eos

@@ -1,0 +1,162 @@
+"""Chunked forward / backward parity of the bf16 K=V=128 kernels (C ABI: kda_chunk_fwd / kda_chunk_bwd)
+against the fp32 CPU oracle evaluated on the same bf16-rounded inputs.
+
+Tolerance (stated by the task): <= 2e-2 max abs error on normalised outputs, gradients and final
+states for bf16 inputs, against an fp32 reference.
+"""
+
+import pytest
+import torch
+
+import kda_b200
+from oracle import kda_oracle as orc
+from helpers import assert_normalised, norm_err
+
+pytestmark = pytest.mark.gpu
+TOL = 2e-2
+
+
+def _case(batch, tokens, heads, seed, lengths=None, with_state=True):
+    inp = orc.make_inputs(batch, tokens, heads, 128, 128, seed=seed, with_state=with_state,
+                          lengths=lengths)
+    for n in ("q", "k", "v"):
+        inp[n] = inp[n].bfloat16()
+    return inp
+
+
+def _run_fused(inp, do=None, dst=None, grad=False):
+    q, k, v = (inp[n].cuda().requires_grad_(grad) for n in ("q", "k", "v"))
+    g = inp["cum_gate"].cuda().requires_grad_(grad)
+    beta = inp["beta"].cuda().requires_grad_(grad)
+    h0 = None if inp["h0"] is None else inp["h0"].cuda().requires_grad_(grad)
+    cu = None if inp["cu_seqlens"] is None else inp["cu_seqlens"].cuda()
+    o, st = kda_b200.chunk_kda(q, k, v, g, beta, h0, cu_seqlens=cu, output_final_state=True)
+    res = {"o": o, "state": st}
+    if grad:
+        loss = (o.float() * do.cuda()).sum()
+        if dst is not None:
+            loss = loss + (st * dst.cuda()).sum()
+        wrt = [q, k, v, g, beta] + ([h0] if h0 is not None else [])
+        grads = torch.autograd.grad(loss, wrt)
+        for name, gr in zip(["dq", "dk", "dv", "dg", "dbeta", "dh0"], grads):
+            res[name] = gr
+    return res
+
+
+def _active(inp, x):
+    """Slice a [1, T, ...] tensor of a packed case to its active prefix."""
+    if inp["cu_seqlens"] is None:
+        return x
+    return x[:, : int(inp["cu_seqlens"][-1])]
+
+
+CASES = [
+    dict(batch=1, tokens=64, heads=1, seed=1),
+    dict(batch=2, tokens=256, heads=2, seed=2),
+    dict(batch=1, tokens=130, heads=2, seed=3),                       # partial tail chunk
+    dict(batch=3, tokens=100, heads=1, seed=4),                       # dense rows not chunk aligned
+    dict(batch=1, tokens=300, heads=2, seed=5, lengths=[65, 63, 0, 30, 128]),
+    dict(batch=1, tokens=200, heads=1, seed=6, lengths=[0, 1, 64, 0, 65]),
+]
+
+
+@pytest.mark.parametrize("case", CASES, ids=lambda c: f"B{c['batch']}T{c['tokens']}H{c['heads']}")
+def test_forward(case):
+    inp = _case(**case)
+    res = _run_fused(inp)
+    ref_o, ref_s = orc.chunk_kda_ref(inp["q"].float(), inp["k"].float(), inp["v"].float(),
+                                     inp["cum_gate"], inp["beta"], inp["h0"], inp["cu_seqlens"])
+    assert res["o"].dtype == torch.bfloat16 and res["state"].dtype == torch.float32
+    assert_normalised(_active(inp, res["o"]).float(), _active(inp, ref_o), TOL, "output")
+    assert_normalised(res["state"], ref_s, TOL, "final state")
+    if inp["cu_seqlens"] is not None:
+        lens = inp["cu_seqlens"][1:] - inp["cu_seqlens"][:-1]
+        for s in (lens == 0).nonzero().flatten().tolist():
+            assert torch.equal(res["state"][s].cpu(), inp["h0"][s]), "empty sequence state"
+
+
+@pytest.mark.parametrize("case", CASES, ids=lambda c: f"B{c['batch']}T{c['tokens']}H{c['heads']}")
+def test_backward(case):
+    inp = _case(**case)
+    gen = torch.Generator().manual_seed(100 + case["seed"])
+    do = torch.randn(inp["v"].shape, generator=gen).bfloat16().float()
+    nseq = case["batch"] if inp["cu_seqlens"] is None else inp["cu_seqlens"].numel() - 1
+    dst = 0.1 * torch.randn(nseq, case["heads"], 128, 128, generator=gen)
+    if inp["cu_seqlens"] is not None:
+        do[:, int(inp["cu_seqlens"][-1]):] = 0
+    res = _run_fused(inp, do, dst, grad=True)
+    ref = orc.chunk_kda_grads_ref(inp["q"].float(), inp["k"].float(), inp["v"].float(),
+                                  inp["cum_gate"], inp["beta"], do, inp["h0"], dst,
+                                  inp["cu_seqlens"], dtype=torch.float32)
+    report = {n: norm_err(_active(inp, res[n]).float() if n != "dh0" else res[n],
+                          _active(inp, ref[n]) if n != "dh0" else ref[n])
+              for n in ("dq", "dk", "dv", "dg", "dbeta", "dh0")}
+    print("normalised gradient errors:", {k: f"{v:.2e}" for k, v in report.items()})
+    for name, err in report.items():
+        assert err <= TOL, f"{name}: normalised max error {err:.3e} > {TOL}"
+    if inp["cu_seqlens"] is not None:
+        lens = inp["cu_seqlens"][1:] - inp["cu_seqlens"][:-1]
+        for s in (lens == 0).nonzero().flatten().tolist():
+            assert torch.equal(res["dh0"][s].cpu(), dst[s]), "empty sequence state gradient"
+
+
+def test_dense_batch_equals_packed():
+    """A dense batch and its explicit equal-length packing give bitwise-equal results
+    (reference: test/test_kda_cute_forward.py:368-410)."""
+    inp = _case(2, 192, 2, seed=7)
+    res = _run_fused(inp)
+    packed = dict(inp)
+    for n in ("q", "k", "v", "cum_gate"):
+        packed[n] = inp[n].reshape(1, 384, 2, 128)
+    packed["beta"] = inp["beta"].reshape(1, 384, 2)
+    packed["cu_seqlens"] = torch.tensor([0, 192, 384], dtype=torch.int32)
+    res_p = _run_fused(packed)
+    assert torch.equal(res["o"].reshape(1, 384, 2, 128), res_p["o"])
+    assert torch.equal(res["state"], res_p["state"])
+
+
+def test_causality_is_bitwise():
+    """Perturbing tokens >= cut leaves outputs < cut bitwise unchanged
+    (reference: test/test_kda_cute_forward.py:903-940)."""
+    inp = _case(1, 256, 1, seed=8)
+    base = _run_fused(inp)["o"]
+    cut = 128
+    pert = dict(inp)
+    for n in ("q", "k", "v"):
+        x = inp[n].clone()
+        x[:, cut:] = x[:, cut:] * 1.5
+        pert[n] = x
+    other = _run_fused(pert)["o"]
+    assert torch.equal(base[:, :cut], other[:, :cut])
+
+
+def test_nan_poisoned_suffix_is_ignored():
+    """Rows past cu_seqlens[-1] may hold anything (reference: test_kda_ragged_public_backward.py:125-139)."""
+    inp = _case(1, 200, 1, seed=9, lengths=[70, 50])
+    clean = _run_fused(inp)
+    bad = dict(inp)
+    for n in ("q", "k", "v", "cum_gate", "beta"):
+        x = inp[n].clone()
+        x[:, 120:] = float("nan")
+        bad[n] = x
+    res = _run_fused(bad)
+    assert torch.equal(clean["o"][:, :120], res["o"][:, :120])
+    assert torch.equal(clean["state"], res["state"])
+
+
+def test_rejections():
+    inp = _case(1, 64, 1, seed=1)
+    c = {k: (v.cuda() if torch.is_tensor(v) else v) for k, v in inp.items()}
+    with pytest.raises(ValueError):  # K != 128 on the fused bf16 path
+        kda_b200.chunk_kda(c["q"][..., :64], c["k"][..., :64], c["v"], c["cum_gate"][..., :64],
+                           c["beta"])
+    with pytest.raises(ValueError):
+        kda_b200.chunk_kda(c["q"], c["k"], c["v"], c["cum_gate"], c["beta"], impl="bogus")
+    with pytest.raises(ValueError):
+        kda_b200.chunk_kda(c["q"], c["k"], c["v"], c["cum_gate"], c["beta"], fastmath=True,
+                           impl="reference")
+    with pytest.raises(ValueError):  # packed input needs batch one
+        kda_b200.chunk_kda(c["q"].repeat(2, 1, 1, 1), c["k"].repeat(2, 1, 1, 1),
+                           c["v"].repeat(2, 1, 1, 1), c["cum_gate"].repeat(2, 1, 1, 1),
+                           c["beta"].repeat(2, 1, 1),
+                           cu_seqlens=torch.tensor([0, 64], dtype=torch.int32, device="cuda"))

@@ -1,0 +1,122 @@
+"""Recurrent scan / decode step parity (C ABI -> kda_recurrent_fwd) against the CPU oracle and the
+golden vectors.  Tolerances follow the reference's decode tests
+(test/test_kda_recurrent.py:74-98): 1e-5 for fp32 inputs, 2e-2 for 16-bit inputs."""
+
+import pytest
+import torch
+
+import kda_b200
+from oracle import kda_oracle as orc
+from helpers import assert_normalised
+
+pytestmark = pytest.mark.gpu
+
+
+def test_golden_dense(golden):
+    g = {k: v.cuda() for k, v in golden("recurrent_dense").items()}
+    o, st = kda_b200.recurrent_kda(g["q"], g["k"], g["v"], g["gate"], g["beta"], g["h0"],
+                                   output_final_state=True)
+    torch.testing.assert_close(o, g["o"], atol=1e-5, rtol=1e-4)
+    torch.testing.assert_close(st, g["state"], atol=1e-5, rtol=1e-4)
+
+
+def test_golden_packed(golden):
+    g = {k: v.cuda() for k, v in golden("recurrent_packed").items()}
+    o, st = kda_b200.recurrent_kda(g["q"], g["k"], g["v"], g["gate"], g["beta"], g["h0"],
+                                   cu_seqlens=g["cu_seqlens"], output_final_state=True)
+    torch.testing.assert_close(o, g["o"], atol=1e-5, rtol=1e-4)
+    torch.testing.assert_close(st, g["state"], atol=1e-5, rtol=1e-4)
+    assert torch.equal(st[1], g["h0"][1])  # empty sequence: bitwise pass-through
+    o64, _ = kda_b200.recurrent_kda(g["q"], g["k"], g["v"], g["gate"], g["beta"], g["h0"],
+                                    cu_seqlens=g["cu_seqlens"].long())
+    assert torch.equal(o64, o)  # int64 offsets are accepted
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-5), (torch.bfloat16, 2e-2),
+                                       (torch.float16, 2e-2)])
+@pytest.mark.parametrize("kd,vd", [(128, 128), (64, 64), (24, 40), (256, 32)])
+def test_scan_shapes(dtype, tol, kd, vd):
+    inp = orc.make_inputs(2, 19, 3, kd, vd, seed=kd + vd, with_state=True)
+    q, k, v, g = (inp[n].to(dtype) for n in ("q", "k", "v", "gate_log2"))
+    beta = inp["beta"].to(dtype)
+    ref_o, ref_s = orc.recurrent_kda_ref(q.float(), k.float(), v.float(), g.float(), beta.float(),
+                                         inp["h0"])
+    o, st = kda_b200.recurrent_kda(q.cuda(), k.cuda(), v.cuda(), g.cuda(), beta.cuda(),
+                                   inp["h0"].cuda(), output_final_state=True)
+    assert o.dtype == dtype and st.dtype == torch.float32
+    assert_normalised(o.float(), ref_o, tol, "output")
+    assert_normalised(st, ref_s, tol, "state")
+
+
+def test_config0_fp32(golden):
+    """B1 H4 T512 K=V=64 fp32 through chunk_kda and recurrent_kda: <= 2e-3 max relative error."""
+    g = golden("config0")
+    inp = orc.make_inputs(1, 512, 4, 64, 64, seed=0)
+    c = {k: (v.cuda() if torch.is_tensor(v) else v) for k, v in inp.items()}
+    o, st = kda_b200.recurrent_kda(c["q"], c["k"], c["v"], c["gate_log2"], c["beta"],
+                                   output_final_state=True)
+    assert_normalised(o, g["o_recurrent"], 2e-3, "recurrent output")
+    assert_normalised(st, g["state_recurrent"], 2e-3, "recurrent state")
+    oc, sc = kda_b200.chunk_kda(c["q"], c["k"], c["v"], c["cum_gate"], c["beta"],
+                                output_final_state=True)
+    assert_normalised(oc, g["o_recurrent"], 2e-3, "chunk output")
+    assert_normalised(sc, g["state_chunk"], 2e-3, "chunk state")
+    big = g["o_recurrent"].abs() > 1e-2 * g["o_recurrent"].abs().max()
+    rel = ((oc.cpu() - g["o_recurrent"]).abs() / g["o_recurrent"].abs())[big].max()
+    assert rel <= 2e-3, f"max relative error {rel:.3e}"
+
+
+def test_decode_paged_pool():
+    n, h, kd, vd, slots = 6, 2, 128, 128, 9
+    inp = orc.make_inputs(n, 1, h, kd, vd, seed=9)
+    gen = torch.Generator().manual_seed(5)
+    pool = 0.02 * torch.randn(slots, h, kd, vd, generator=gen)
+    idx = torch.tensor([3, -1, 5, 0, 8, 1], dtype=torch.int32)
+    q, k, v, g = (inp[x].bfloat16() for x in ("q", "k", "v", "gate_log2"))
+    beta = inp["beta"].bfloat16()
+    pool_gpu = pool.cuda()
+    o, none = kda_b200.recurrent_kda(q.cuda(), k.cuda(), v.cuda(), g.cuda(), beta.cuda(), pool_gpu,
+                                     state_indices=idx.cuda())
+    assert none is None
+    for i, slot in enumerate(idx.tolist()):
+        if slot <= 0:
+            assert o[i].abs().max() == 0
+            continue
+        ro, rs = orc.recurrent_kda_ref(q[i:i + 1].float(), k[i:i + 1].float(), v[i:i + 1].float(),
+                                       g[i:i + 1].float(), beta[i:i + 1].float(),
+                                       pool[slot:slot + 1])
+        assert_normalised(o[i].float(), ro[0], 2e-2, f"paged output {i}")
+        assert_normalised(pool_gpu[slot], rs[0], 1e-4, f"paged state {i}")
+    untouched = [s for s in range(slots) if s not in (3, 5, 8, 1)]
+    assert torch.equal(pool_gpu[untouched].cpu(), pool[untouched])
+
+
+def test_decode_steps_match_chunk_core():
+    """64 decode steps == one chunk of the chunked core (reference: test_kda_recurrent.py:173-204)."""
+    inp = orc.make_inputs(2, 64, 2, 128, 128, seed=4)
+    c = {k: (v.cuda() if torch.is_tensor(v) else v) for k, v in inp.items()}
+    q, k, v = (c[n].bfloat16() for n in ("q", "k", "v"))
+    state = torch.zeros(2, 2, 128, 128, device="cuda")
+    outs = []
+    for t in range(64):
+        o, state = kda_b200.recurrent_kda(q[:, t:t + 1], k[:, t:t + 1], v[:, t:t + 1],
+                                          c["gate_log2"][:, t:t + 1], c["beta"][:, t:t + 1], state,
+                                          output_final_state=True)
+        outs.append(o)
+    o_dec = torch.cat(outs, 1)
+    o_chunk, s_chunk = kda_b200.chunk_kda(q, k, v, c["cum_gate"], c["beta"],
+                                          output_final_state=True)
+    assert_normalised(o_chunk.float(), o_dec.float(), 5e-2, "chunk vs decode output")
+    assert_normalised(s_chunk, state, 5e-2, "chunk vs decode state")
+
+
+def test_rejects_grad_and_bad_shapes():
+    inp = orc.make_inputs(1, 4, 1, 16, 16, seed=1)
+    c = {k: (v.cuda() if torch.is_tensor(v) else v) for k, v in inp.items()}
+    with pytest.raises(RuntimeError):
+        kda_b200.recurrent_kda(c["q"].requires_grad_(), c["k"], c["v"], c["gate_log2"], c["beta"])
+    with pytest.raises(ValueError):
+        kda_b200.recurrent_kda(c["q"].detach(), c["k"][:, :2], c["v"], c["gate_log2"], c["beta"])
+    with pytest.raises(TypeError):
+        kda_b200.recurrent_kda(c["q"].detach().double(), c["k"].double(), c["v"].double(),
+                               c["gate_log2"].double(), c["beta"].double())
