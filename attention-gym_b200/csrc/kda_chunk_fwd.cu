@@ -498,24 +498,52 @@ extern "C" int64_t kda_chunk_fwd_workspace_bytes(int64_t tokens, int heads) {
   return 4 * tokens * heads * 128 * (int64_t)sizeof(bf16);
 }
 
-// Slice transition for context parallelism: with u = 0 and an identity initial state the state
-// recurrence returns M = prod_t (I - beta_t k_t k_t^T) diag(2^{g_t}) of the slice ([H,K,K] fp32,
-// one "sequence"), so that h_out = M h_in + b.  Needs w, kg (and any qg/aqk) from a previous
-// kda_chunk_fwd on the same workspace.
-extern "C" int kda_chunk_transition(const float* cum_gate, const float* identity_state,
-                                    float* transition, const int32_t* cu_seqlens,
-                                    const int32_t* chunk_offsets, int nseq, int64_t tokens,
-                                    int heads, void* aqk, void* workspace, void* stream) {
-  if (!cum_gate || !identity_state || !transition || !cu_seqlens || !chunk_offsets || !workspace ||
-      !aqk)
+// The two halves of kda_chunk_fwd as separate entry points: `prepare` is the chunk-parallel part
+// (pairwise products, solve, w/u/kg/qg into the workspace), `state` the serial recurrence that
+// consumes the workspace.  Context parallelism runs `prepare` once per slice and `state` several
+// times (zero entering state, identity state for the slice transition, true entering state).
+extern "C" int kda_chunk_fwd_prepare(const void* q, const void* k, const void* v,
+                                     const float* cum_gate, const float* beta, void* aqk, void* akk,
+                                     const int32_t* cu_seqlens, const int32_t* chunk_offsets,
+                                     int nseq, int64_t tokens, int heads, int num_chunks,
+                                     void* workspace, int64_t workspace_bytes, void* stream) {
+  if (!q || !k || !v || !cum_gate || !beta || !aqk || !akk || !cu_seqlens || !chunk_offsets ||
+      !workspace)
     return KDA_ERR_ARG;
+  if (nseq < 1 || heads < 1 || tokens < 1 || num_chunks < 0) return KDA_ERR_ARG;
+  if (workspace_bytes < kda_chunk_fwd_workspace_bytes(tokens, heads)) return KDA_ERR_ARG;
+  kda::ChunkParams p{};
+  const int64_t nd = tokens * heads * 128;
+  bf16* ws = reinterpret_cast<bf16*>(workspace);
+  p.q = (const bf16*)q; p.k = (const bf16*)k; p.v = (const bf16*)v; p.g = cum_gate; p.beta = beta;
+  p.aqk = (bf16*)aqk; p.akk = (bf16*)akk;
+  p.w = ws; p.u = ws + nd; p.kg = ws + 2 * nd; p.qg = ws + 3 * nd;
+  p.cu_seqlens = cu_seqlens; p.chunk_offsets = chunk_offsets; p.nseq = nseq; p.H = heads;
+  p.scale = 0.08838834764831845f;
+  cudaStream_t s = (cudaStream_t)stream;
+  int rc = kda::launch_intra_solve(p, num_chunks, s);
+  if (rc) return rc;
+  return kda::launch_wu(p, num_chunks, s);
+}
+
+// use_u == 0 runs the homogeneous recurrence (u = 0): with identity matrices as initial_state the
+// final state is the slice transition M = prod_t (I - beta_t k_t k_t^T) diag(2^{g_t}), so that the
+// state leaving the slice is M h_in + b.  out may be NULL.
+extern "C" int kda_chunk_fwd_state(const float* cum_gate, const float* initial_state,
+                                   float* final_state, void* out, const void* aqk,
+                                   const int32_t* cu_seqlens, const int32_t* chunk_offsets, int nseq,
+                                   int64_t tokens, int heads, void* workspace, int use_u,
+                                   void* stream) {
+  if (!cum_gate || !aqk || !cu_seqlens || !chunk_offsets || !workspace) return KDA_ERR_ARG;
+  if (nseq < 1 || heads < 1 || tokens < 1) return KDA_ERR_ARG;
+  if ((int64_t)nseq * heads * 2 > 0x7fffffffLL) return KDA_ERR_UNSUPPORTED;
   kda::ChunkParams p{};
   const int64_t nd = tokens * heads * 128;
   bf16* ws = reinterpret_cast<bf16*>(workspace);
   p.g = cum_gate;
   p.aqk = (bf16*)aqk;
-  p.w = ws; p.u = nullptr; p.kg = ws + 2 * nd; p.qg = ws + 3 * nd;
-  p.h0 = identity_state; p.ht = transition; p.o = nullptr;
+  p.w = ws; p.u = use_u ? ws + nd : nullptr; p.kg = ws + 2 * nd; p.qg = ws + 3 * nd;
+  p.h0 = initial_state; p.ht = final_state; p.o = (bf16*)out;
   p.cu_seqlens = cu_seqlens; p.chunk_offsets = chunk_offsets; p.nseq = nseq; p.H = heads;
   return kda::launch_state_fwd(p, (cudaStream_t)stream);
 }

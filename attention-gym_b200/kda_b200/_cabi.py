@@ -47,8 +47,10 @@ _SIGNATURES = {
     "kda_chunk_bwd_workspace_bytes": (c_int64, [c_int64, c_int, c_int64]),
     "kda_chunk_bwd": (c_int, [c_void_p] * 18 + [c_int, c_int64, c_int, c_int, c_int, c_int, c_void_p,
                               c_int64, c_void_p]),
-    "kda_chunk_transition": (c_int, [c_void_p] * 5 + [c_int, c_int64, c_int, c_void_p, c_void_p,
-                                     c_void_p]),
+    "kda_chunk_fwd_prepare": (c_int, [c_void_p] * 9 + [c_int, c_int64, c_int, c_int, c_void_p,
+                                      c_int64, c_void_p]),
+    "kda_chunk_fwd_state": (c_int, [c_void_p] * 7 + [c_int, c_int64, c_int, c_void_p, c_int,
+                                    c_void_p]),
     "kda_state_affine": (c_int, [c_void_p] * 4 + [c_int, c_int, c_int, c_void_p]),
     "kda_conv1d_fwd": (c_int, [c_void_p] * 4 + [c_int, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                c_int, c_void_p]),

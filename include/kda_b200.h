@@ -125,14 +125,21 @@ int kda_chunk_bwd(const void* q, const void* k, const void* v, const float* cum_
                   int value_dim, int num_chunks, void* workspace, int64_t workspace_bytes,
                   void* stream);
 
-/* Context parallelism: dense slice transition M [nseq, H, 128, 128] such that the state leaving a
- * slice is M h_in + b (b = the slice's final state from a zero initial state).  Must follow a
- * kda_chunk_fwd call on the same inputs and workspace; identity_state holds nseq*H identity
- * matrices.  The reference has no counterpart (docs/linear.md:220-222 leaves context parallelism
- * to the caller). */
-int kda_chunk_transition(const float* cum_gate, const float* identity_state, float* transition,
-                         const int32_t* cu_seqlens, const int32_t* chunk_offsets, int nseq,
-                         int64_t tokens, int heads, void* aqk, void* workspace, void* stream);
+/* The two halves of kda_chunk_fwd: `prepare` = the chunk-parallel part (fills aqk, akk and the
+ * workspace), `state` = the serial state recurrence over the workspace (writes out and final_state,
+ * either may be NULL).  use_u == 0 runs the homogeneous recurrence: with identity matrices as
+ * initial_state, final_state is the dense slice transition M [nseq, H, 128, 128] such that the state
+ * leaving the slice is M h_in + b (context parallelism).  The reference fuses neither split nor
+ * transition (kda/ops.py:78-89 `kda_delta_h` is its closest stage operator; docs/linear.md:220-222
+ * leaves context parallelism to the caller). */
+int kda_chunk_fwd_prepare(const void* q, const void* k, const void* v, const float* cum_gate,
+                          const float* beta, void* aqk, void* akk, const int32_t* cu_seqlens,
+                          const int32_t* chunk_offsets, int nseq, int64_t tokens, int heads,
+                          int num_chunks, void* workspace, int64_t workspace_bytes, void* stream);
+int kda_chunk_fwd_state(const float* cum_gate, const float* initial_state, float* final_state,
+                        void* out, const void* aqk, const int32_t* cu_seqlens,
+                        const int32_t* chunk_offsets, int nseq, int64_t tokens, int heads,
+                        void* workspace, int use_u, void* stream);
 
 /* h_out = transition * h_in + b for `count` independent [key_dim x value_dim] fp32 states
  * (transition: [count, key_dim, key_dim]); key_dim and value_dim multiples of 64.  Applies the

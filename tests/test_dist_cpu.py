@@ -1,0 +1,97 @@
+"""Host-side logic of the multi-GPU paths on CPU: sharding arithmetic, and the context-parallel
+boundary-state chain run as two and three gloo ranks with the CPU oracle standing in for the
+kernels (the protocol -- who sends what to whom, and the affine composition -- is what is tested)."""
+
+import os
+import sys
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_shard_ranges_tile_the_grid():
+    from kda_b200.dist import shard_ranges
+
+    for batch, heads, world in [(8, 32, 1), (8, 32, 2), (8, 32, 4), (8, 32, 8), (1, 32, 8),
+                                (2, 32, 8), (3, 8, 4)]:
+        seen = torch.zeros(batch, heads, dtype=torch.int32)
+        for rank in range(world):
+            bs, hs = shard_ranges(batch, heads, world, rank)
+            seen[bs, hs] += 1
+        assert (seen == 1).all(), (batch, heads, world)
+    with pytest.raises(ValueError):
+        shard_ranges(3, 5, 4, 0)
+
+
+class OracleSlice:
+    """CPU stand-in with the interface of kda_b200.dist.CudaSlice."""
+
+    def __init__(self, q, k, v, gate, beta):
+        self.args = (q.double(), k.double(), v.double(), gate.double(), beta.double())
+
+    def run(self, h_in):
+        from oracle import kda_oracle as orc
+
+        h = None if h_in is None else h_in.double()
+        o, s = orc.chunk_kda_ref(*self.args, initial_state=h)
+        return o, s.float()
+
+    def zero_state_result(self):
+        return self.run(None)[1]
+
+    def transition(self):
+        from oracle import kda_oracle as orc
+
+        q, k, v, gate, beta = self.args
+        per_token = gate.clone()
+        t = gate.shape[1]
+        for c0 in range(0, t, 64):
+            per_token[:, c0 + 1:c0 + 64] = gate[:, c0 + 1:c0 + 64] - gate[:, c0:min(t, c0 + 64) - 1]
+        return orc.slice_transition_ref(k[0], per_token[0], beta[0])[None].float()
+
+    def affine(self, trans, h_in, b):
+        return trans @ h_in + b
+
+
+def _cp_worker(rank, world, port, ret):
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "attention-gym_b200"))
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from kda_b200.dist import cp_chunk_forward
+        from oracle import kda_oracle as orc
+
+        torch.set_num_threads(1)
+        total = 64 * 2 * world + 40       # the last slice has a partial tail chunk
+        inp = orc.make_inputs(1, total, 2, 16, 24, seed=21, with_state=True)
+        lo = 128 * rank
+        hi = total if rank + 1 == world else lo + 128
+        sl = slice(lo, hi)
+        out, h_out = cp_chunk_forward(inp["q"][:, sl], inp["k"][:, sl], inp["v"][:, sl],
+                                      inp["cum_gate"][:, sl], inp["beta"][:, sl], inp["h0"],
+                                      slice_factory=OracleSlice)
+        ref_o, ref_s = orc.chunk_kda_ref(inp["q"].double(), inp["k"].double(), inp["v"].double(),
+                                         inp["cum_gate"].double(), inp["beta"].double(),
+                                         inp["h0"].double())
+        err_o = float((out.double() - ref_o[:, sl]).abs().max())
+        err_s = float((h_out.double() - ref_s).abs().max()) if rank + 1 == world else 0.0
+        ret[rank] = (err_o, err_s)
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_context_parallel_chain_gloo(world):
+    port = 29600 + world + (os.getpid() % 200)
+    with mp.Manager() as manager:
+        ret = manager.dict()
+        mp.spawn(_cp_worker, args=(world, port, ret), nprocs=world, join=True)
+        for rank in range(world):
+            err_o, err_s = ret[rank]
+            assert err_o < 1e-5, f"rank {rank}: output error {err_o}"
+            assert err_s < 1e-5, f"rank {rank}: final state error {err_s}"
