@@ -547,3 +547,44 @@ extern "C" int kda_chunk_fwd_state(const float* cum_gate, const float* initial_s
   p.cu_seqlens = cu_seqlens; p.chunk_offsets = chunk_offsets; p.nseq = nseq; p.H = heads;
   return kda::launch_state_fwd(p, (cudaStream_t)stream);
 }
+
+// ------------------------------------------------------------------------------------------------
+// Chunked forward for callers that must not allocate.
+//
+// Some hosts of this library cannot call cudaMalloc: a serving engine that has handed every free
+// byte of the device to its own paged pool, or a plugin running under a runtime that forbids
+// allocation once the model is loaded.  For them the w/u/kg/qg scratch of the forward lives in the
+// file-scope device array below instead of a caller workspace.  Every GPU that loads the library
+// holds the array (KDA_NOALLOC_SCRATCH_BYTES) until the process exits.
+// ------------------------------------------------------------------------------------------------
+namespace kda {
+static __device__ __align__(256) unsigned char g_noalloc_scratch[KDA_NOALLOC_SCRATCH_BYTES];
+static void* g_noalloc_ptr[64] = {nullptr};
+}  // namespace kda
+
+extern "C" int kda_chunk_fwd_noalloc(const void* q, const void* k, const void* v,
+                                     const float* cum_gate, const float* beta,
+                                     const float* initial_state, float* final_state, void* out,
+                                     void* aqk, void* akk, const int32_t* cu_seqlens,
+                                     const int32_t* chunk_offsets, int nseq, int64_t tokens,
+                                     int heads, int key_dim, int value_dim, int num_chunks,
+                                     void* stream) {
+  if (tokens < 1 || heads < 1) return KDA_ERR_ARG;
+  const int64_t need = kda_chunk_fwd_workspace_bytes(tokens, heads);
+  if (need > (int64_t)KDA_NOALLOC_SCRATCH_BYTES) return KDA_ERR_SCRATCH;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return KDA_ERR_LAUNCH;
+  // In host code the array's name is only a handle; the device address comes from the runtime,
+  // once per device, with that device current.
+  void* scratch = kda::g_noalloc_ptr[dev];
+  if (!scratch) {
+    if (cudaGetSymbolAddress(&scratch, kda::g_noalloc_scratch) != cudaSuccess || !scratch)
+      return KDA_ERR_LAUNCH;
+    kda::g_noalloc_ptr[dev] = scratch;
+  }
+  // Nothing in the scratch has to start at zero: every row a kernel reads was written earlier in
+  // the same call, rows past a sequence tail are masked on load.
+  return kda_chunk_fwd(q, k, v, cum_gate, beta, initial_state, final_state, out, aqk, akk,
+                       cu_seqlens, chunk_offsets, nseq, tokens, heads, key_dim, value_dim,
+                       num_chunks, scratch, need, stream);
+}

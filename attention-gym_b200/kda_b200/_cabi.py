@@ -18,7 +18,8 @@ LIB_PATH = os.path.join(HERE, "libkda_b200.so")
 
 KDA_F32, KDA_BF16, KDA_F16 = 0, 1, 2
 _DTYPES = {torch.float32: KDA_F32, torch.bfloat16: KDA_BF16, torch.float16: KDA_F16}
-_ERRORS = {-1: "invalid argument", -2: "unsupported shape", -3: "CUDA launch failed"}
+_ERRORS = {-1: "invalid argument", -2: "unsupported shape", -3: "CUDA launch failed",
+           -4: "problem exceeds the built-in scratch array"}
 
 # kernels launched through this module since import (bench.py reports it as gpu_launches)
 launch_count = 0
@@ -44,6 +45,8 @@ _SIGNATURES = {
     "kda_chunk_fwd_workspace_bytes": (c_int64, [c_int64, c_int]),
     "kda_chunk_fwd": (c_int, [c_void_p] * 12 + [c_int, c_int64, c_int, c_int, c_int, c_int, c_void_p,
                               c_int64, c_void_p]),
+    "kda_chunk_fwd_noalloc": (c_int, [c_void_p] * 12 + [c_int, c_int64, c_int, c_int, c_int, c_int,
+                                      c_void_p]),
     "kda_chunk_bwd_workspace_bytes": (c_int64, [c_int64, c_int, c_int64]),
     "kda_chunk_bwd": (c_int, [c_void_p] * 18 + [c_int, c_int64, c_int, c_int, c_int, c_int, c_void_p,
                               c_int64, c_void_p]),

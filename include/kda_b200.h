@@ -34,6 +34,7 @@ extern "C" {
 #define KDA_ERR_ARG (-1)         /* null pointer, bad size or inconsistent arguments */
 #define KDA_ERR_UNSUPPORTED (-2) /* shape outside what the kernels are built for */
 #define KDA_ERR_LAUNCH (-3)      /* the CUDA runtime refused the launch */
+#define KDA_ERR_SCRATCH (-4)     /* the problem needs more scratch than the built-in array holds */
 
 /* Library identification: returns 100 * major + minor. */
 int kda_b200_version(void);
@@ -111,6 +112,25 @@ int kda_chunk_fwd(const void* q, const void* k, const void* v, const float* cum_
                   void* aqk, void* akk, const int32_t* cu_seqlens, const int32_t* chunk_offsets,
                   int nseq, int64_t tokens, int heads, int key_dim, int value_dim, int num_chunks,
                   void* workspace, int64_t workspace_bytes, void* stream);
+
+/* kda_chunk_fwd for callers that cannot allocate device memory (an inference server whose memory
+ * pool already owns the whole GPU, a plugin that may not call cudaMalloc after start-up).  Same
+ * arguments and results as kda_chunk_fwd without the workspace: the scratch is a static device
+ * array of KDA_NOALLOC_SCRATCH_BYTES that every GPU loading the library keeps until exit.
+ * Limit: tokens * heads <= KDA_NOALLOC_SCRATCH_BYTES / 1024 (e.g. 1024 tokens x 32 heads), otherwise
+ * KDA_ERR_SCRATCH.  The entry point calls no cudaMalloc / cudaFree or other allocating routine.
+ * The first call on a device looks the array's device address up (cudaGetSymbolAddress with that
+ * device current); make that first call before starting any stream capture.  All calls share the
+ * array and it keeps the previous call's contents (nothing in it needs clearing); two calls whose
+ * kernels overlap on the GPU -- different streams, different host threads -- race on it.
+ * It has no counterpart in the reference, whose operators allocate their intermediates with
+ * torch. */
+#define KDA_NOALLOC_SCRATCH_BYTES (32 * 1024 * 1024)
+int kda_chunk_fwd_noalloc(const void* q, const void* k, const void* v, const float* cum_gate,
+                          const float* beta, const float* initial_state, float* final_state,
+                          void* out, void* aqk, void* akk, const int32_t* cu_seqlens,
+                          const int32_t* chunk_offsets, int nseq, int64_t tokens, int heads,
+                          int key_dim, int value_dim, int num_chunks, void* stream);
 
 /* Chunked backward.  d_out bf16 [tokens, H, 128] (required), d_final_state / initial_state /
  * d_initial_state fp32 or NULL.  dq, dk, dv bf16; dg (w.r.t. the cumulative gate) and dbeta fp32.
