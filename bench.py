@@ -151,7 +151,7 @@ def run_ours(args):
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=device)
-    batch, tokens = (2, 1024) if args.small else (8, 4096)
+    batch, tokens = (2, 4096) if args.small else (8, 4096)
     tokens_per_step = batch * tokens
     host = make_host_inputs(batch, tokens, seed=1234 + rank, pin=True)
     dev = {n: t.to(device, non_blocking=True) for n, t in host.items()}
@@ -181,9 +181,11 @@ def run_ours(args):
     _cabi.stage_timing(False)
     launches = _cabi.launch_count - launches0
 
+    decode = None if args.skip_decode else bench_decode(kda_b200, _cabi, device, load_peaks())
+
     # ---- end to end: pinned host buffers in, host buffers out, copies inside the timed region ----
     out_host = None
-    e2e_steps = max(1, min(args.steps, 3))
+    e2e_steps = 0 if args.skip_e2e else max(1, min(args.steps, 3))
 
     def step_e2e():
         nonlocal out_host
@@ -195,17 +197,19 @@ def run_ours(args):
         for h, t in zip(out_host, outs):
             h.copy_(t, non_blocking=True)
 
-    step_e2e()
-    barrier()
-    s2, e2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    s2.record()
-    for _ in range(e2e_steps):
+    ms_e2e, h2d, d2h = float("nan"), 0, 0
+    if e2e_steps:
         step_e2e()
-    e2.record()
-    barrier()
-    ms_e2e = s2.elapsed_time(e2)
-    h2d = sum(t.numel() * t.element_size() for t in host.values())
-    d2h = sum(t.numel() * t.element_size() for t in out_host)
+        barrier()
+        s2, e2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s2.record()
+        for _ in range(e2e_steps):
+            step_e2e()
+        e2.record()
+        barrier()
+        ms_e2e = s2.elapsed_time(e2)
+        h2d = sum(t.numel() * t.element_size() for t in host.values())
+        d2h = sum(t.numel() * t.element_size() for t in out_host)
 
     if world > 1:
         t = torch.tensor([ms, ms_e2e], device=device, dtype=torch.float64)
@@ -218,7 +222,7 @@ def run_ours(args):
 
     peaks = load_peaks()
     value = world * tokens_per_step * args.steps / (ms * 1e-3)
-    e2e_value = world * tokens_per_step * e2e_steps / (ms_e2e * 1e-3)
+    e2e_value = world * tokens_per_step * e2e_steps / (ms_e2e * 1e-3) if e2e_steps else 0.0
     # dominant kernel = largest share of the timed region
     roofline, breakdown = None, {}
     total_stage_ms = sum(v[1] for v in stages.values()) or 1.0
@@ -245,7 +249,7 @@ def run_ours(args):
             "tensor_frac": round(value * H * PATH_FLOP_FWD_BWD / 1e12 / world / peaks["bf16_tflops"], 4),
             "achieved_gbs": round(value * H * PATH_BYTES_FWD_BWD / 1e9 / world, 1),
             "achieved_tflops": round(value * H * PATH_FLOP_FWD_BWD / 1e12 / world, 1)}
-    cpu = cpu_baseline(bounded=True) if world == 1 or rank == 0 else None
+    cpu = None if args.skip_cpu else cpu_baseline(bounded=True)
     line = {
         "metric": METRIC, "value": round(value, 1), "unit": "tokens/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms / args.steps, 4),
@@ -262,10 +266,56 @@ def run_ours(args):
         "path_roofline": path,
         "kernels": breakdown,
         "cpu_baseline": cpu,
+        "decode": decode,
     }
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+def bench_decode(kda_b200, _cabi, device, peaks, nseq=256, steps=200):
+    """Recurrent decode step (256 sequences, H32, K=V=128, fp32 state, bf16 tokens): us per step and
+    achieved HBM bandwidth of the state read-modify-write (2 * 64 KiB per (sequence, head))."""
+    gen = torch.Generator().manual_seed(5)
+    state = (0.02 * torch.randn(nseq, H, D, D, generator=gen)).to(device)
+    ins = []
+    for _ in range(4):
+        q = torch.nn.functional.normalize(torch.randn(nseq, 1, H, D, generator=gen), dim=-1)
+        k = torch.nn.functional.normalize(torch.randn(nseq, 1, H, D, generator=gen), dim=-1)
+        v = torch.randn(nseq, 1, H, D, generator=gen)
+        g = torch.nn.functional.logsigmoid(torch.randn(nseq, 1, H, D, generator=gen)) * 1.4426950408889634
+        b = torch.sigmoid(torch.randn(nseq, 1, H, generator=gen))
+        ins.append(tuple(t.bfloat16().to(device) for t in (q, k, v, g, b)))
+    idx = torch.arange(1, nseq + 1, dtype=torch.int32, device=device)
+    pool = torch.cat((torch.zeros_like(state[:1]), state), 0)  # slot 0 is the padding slot
+
+    def step(i):
+        q, k, v, g, b = ins[i % 4]
+        return kda_b200.recurrent_kda(q, k, v, g, b, pool, state_indices=idx)[0]
+
+    for i in range(5):
+        step(i)
+    torch.cuda.synchronize()
+    _cabi.read_stage_timing(reset=True)
+    _cabi.stage_timing(True)
+    a, z = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for i in range(steps):
+        step(i)
+    z.record()
+    torch.cuda.synchronize()
+    kern = _cabi.read_stage_timing(reset=True).get("recurrent", (0, 0.0))
+    _cabi.stage_timing(False)
+    us = a.elapsed_time(z) * 1e3 / steps
+    kernel_us = kern[1] * 1e3 / max(kern[0], 1)
+    bytes_per_step = nseq * H * (2 * D * D * 4 + 3 * D * 2 + 2 * D * 2 + 2)
+    gbs = bytes_per_step / (kernel_us * 1e-6) / 1e9
+    return {"workload": f"config3: {nseq} sequences x H{H}, K=V={D}, paged fp32 state, bf16 tokens",
+            "us_per_step": round(us, 2), "kernel_us": round(kernel_us, 2),
+            "tokens_per_s": round(nseq / (us * 1e-6), 1),
+            "roofline": {"bound": "hbm", "achieved": round(gbs, 1), "peak": peaks["hbm_gbs"],
+                         "unit": "GB/s", "frac": round(gbs / peaks["hbm_gbs"], 4),
+                         "bytes_per_step": bytes_per_step}}
 
 
 def cpu_sample_step(threads):
@@ -325,7 +375,10 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--small", action="store_true", help="B=2 T=1024 (for profiler captures)")
+    ap.add_argument("--small", action="store_true", help="B=2 T=4096 (for profiler captures)")
+    ap.add_argument("--skip-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--skip-e2e", action="store_true", help="skip the host-buffer leg")
+    ap.add_argument("--skip-decode", action="store_true", help="skip the decode-step measurement")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
