@@ -189,7 +189,14 @@ struct WySmem {
   float kdk[D];        // sum_t k dk_s
 };
 
-__global__ void __launch_bounds__(256) kda_bwd_wy_kernel(const BwdParams p) {
+template <int NW>
+__global__ void __launch_bounds__(32 * NW) kda_bwd_wy_kernel(const BwdParams p) {
+  constexpr int THREADS = 32 * NW;
+  constexpr int NH = NW / 4;        // column groups of the warp grid (4 row tiles x NH)
+  constexpr int CW = D / NH;        // columns per warp in the [64 x 128] products
+  constexpr int NTN = CW / 8;
+  constexpr int CQ = 64 / NH;       // columns per warp in the [64 x 64] products
+  constexpr int NTQ = CQ / 8;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   WySmem& sm = *reinterpret_cast<WySmem*>(smem_raw);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -204,15 +211,15 @@ __global__ void __launch_bounds__(256) kda_bwd_wy_kernel(const BwdParams p) {
   const int64_t hbase = (((int64_t)blockIdx.x * H + head) * D) * D;
   const int g8 = lane >> 2, t2 = 2 * (lane & 3);
 
-  load_tile_b16<D, D, LDD, 256>(sm.hh, p.h + hbase, D, D, tid);
-  load_tile_b16<D, D, LDD, 256>(sm.dh, p.dh + hbase, D, D, tid);
-  load_tile_b16<64, D, LDD, 256>(sm.dO, p.dout + rowD, gld, valid, tid);
-  load_tile_b16<64, D, LDD, 256>(sm.vn, p.vnew + rowD, gld, valid, tid);
-  load_tile_b16<64, D, LDD, 256>(sm.dv2, p.dv2 + rowD, gld, valid, tid);
-  load_tile_b16<64, D, LDD, 256>(sm.v, p.v + rowD, gld, valid, tid);
-  load_tile_b16<64, D, LDD, 256>(sm.k, p.k + rowD, gld, valid, tid);
-  load_tile_f32<64, D, D, 256>(sm.g, p.g + rowD, gld, valid, tid);
-  load_tile_b16<64, 64, LD64, 256>(sm.a, p.akk + row64, gld64, valid, tid);
+  load_tile_b16<D, D, LDD, THREADS>(sm.hh, p.h + hbase, D, D, tid);
+  load_tile_b16<D, D, LDD, THREADS>(sm.dh, p.dh + hbase, D, D, tid);
+  load_tile_b16<64, D, LDD, THREADS>(sm.dO, p.dout + rowD, gld, valid, tid);
+  load_tile_b16<64, D, LDD, THREADS>(sm.vn, p.vnew + rowD, gld, valid, tid);
+  load_tile_b16<64, D, LDD, THREADS>(sm.dv2, p.dv2 + rowD, gld, valid, tid);
+  load_tile_b16<64, D, LDD, THREADS>(sm.v, p.v + rowD, gld, valid, tid);
+  load_tile_b16<64, D, LDD, THREADS>(sm.k, p.k + rowD, gld, valid, tid);
+  load_tile_f32<64, D, D, THREADS>(sm.g, p.g + rowD, gld, valid, tid);
+  load_tile_b16<64, 64, LD64, THREADS>(sm.a, p.akk + row64, gld64, valid, tid);
   cp_async_commit();
   if (tid < 64) {
     sm.beta[tid] = tid < valid ? p.beta[(cw.token0 + tid) * H + head] : 0.f;
@@ -222,8 +229,24 @@ __global__ void __launch_bounds__(256) kda_bwd_wy_kernel(const BwdParams p) {
   cp_async_wait<0>();
   __syncthreads();
 
+  // this thread's q and raw-k elements of its (mt, nh) accumulator tile, fetched before any global
+  // store so the loads overlap instead of serialising behind possibly-aliasing stores
+  uint32_t qreg[NTN][2], kreg[NTN][2];
+  {
+    const int mt_ = warp & 3, nh_ = warp >> 2;
+#pragma unroll
+    for (int nt = 0; nt < NTN; ++nt)
+#pragma unroll
+      for (int hh = 0; hh < 2; ++hh) {
+        int r = 16 * mt_ + g8 + 8 * hh, c = CW * nh_ + 8 * nt + t2;
+        qreg[nt][hh] = r < valid
+            ? *reinterpret_cast<const uint32_t*>(p.q + rowD + (int64_t)r * gld + c) : 0u;
+        kreg[nt][hh] = *reinterpret_cast<uint32_t*>(&sm.k[r * LDD + c]);
+      }
+  }
+  __syncthreads();  // raw k captured by every thread before it is gated in place
   // hd[kappa] = sum_v h dh ; k <- k 2^G
-  for (int r = warp; r < D; r += 8) {
+  for (int r = warp; r < D; r += NW) {
     float s = 0.f;
     for (int c = lane * 4; c < D; c += 128) {
       float2 a0 = unpack_bf16(*reinterpret_cast<uint32_t*>(&sm.hh[r * LDD + c]));
@@ -236,7 +259,7 @@ __global__ void __launch_bounds__(256) kda_bwd_wy_kernel(const BwdParams p) {
     for (int d = 16; d > 0; d >>= 1) s += __shfl_xor_sync(0xffffffffu, s, d);
     if (lane == 0) sm.hd[r] = s;
   }
-  for (int idx = tid; idx < 64 * (D / 2); idx += 256) {
+  for (int idx = tid; idx < 64 * (D / 2); idx += THREADS) {
     int r = idx / (D / 2), c = (idx % (D / 2)) * 2;
     float2 kv = unpack_bf16(*reinterpret_cast<uint32_t*>(&sm.k[r * LDD + c]));
     *reinterpret_cast<uint32_t*>(&sm.k[r * LDD + c]) =
@@ -246,43 +269,40 @@ __global__ void __launch_bounds__(256) kda_bwd_wy_kernel(const BwdParams p) {
 
   const float* glast = sm.g + (valid - 1) * D;
   const int mt = warp & 3, nh = warp >> 2;
-  float dgacc[8][4], dkacc[8][4];
-  float acc[1][8][4];
+  float dgacc[NTN][4], dkacc[NTN][4];
+  float acc[1][NTN][4];
 
   // ---- dq_inter = scale 2^G (do h^T) ---------------------------------------------------------
-  zero_acc<1, 8>(acc);
-  warp_gemm<1, 4, false, false>(acc, sm.dO, LDD, 16 * mt, 0, sm.hh, LDD, 0, 64 * nh, 8, lane);
+  zero_acc<1, NTN>(acc);
+  warp_gemm<1, NTN / 2, false, false>(acc, sm.dO, LDD, 16 * mt, 0, sm.hh, LDD, 0, CW * nh, 8, lane);
 #pragma unroll
-  for (int nt = 0; nt < 8; ++nt)
+  for (int nt = 0; nt < NTN; ++nt)
 #pragma unroll
     for (int hh = 0; hh < 2; ++hh) {
-      int r = 16 * mt + g8 + 8 * hh, c = 64 * nh + 8 * nt + t2;
+      int r = 16 * mt + g8 + 8 * hh, c = CW * nh + 8 * nt + t2;
       float x0 = acc[0][nt][2 * hh] * p.scale * fexp2(sm.g[r * D + c]);
       float x1 = acc[0][nt][2 * hh + 1] * p.scale * fexp2(sm.g[r * D + c + 1]);
-      float2 qv = make_float2(0.f, 0.f);
+      float2 qv = unpack_bf16(qreg[nt][hh]);
       if (r < valid) {
         int64_t gi = rowD + (int64_t)r * gld + c;
-        qv = unpack_bf16(*reinterpret_cast<const uint32_t*>(p.q + gi));
         *reinterpret_cast<float2*>(p.dq_p + gi) = make_float2(x0, x1);
       }
       dgacc[nt][2 * hh] = qv.x * x0;
       dgacc[nt][2 * hh + 1] = qv.y * x1;
     }
   // ---- dk_s = (v_new dh^T) 2^{G_last - G} -----------------------------------------------------
-  zero_acc<1, 8>(acc);
-  warp_gemm<1, 4, false, false>(acc, sm.vn, LDD, 16 * mt, 0, sm.dh, LDD, 0, 64 * nh, 8, lane);
+  zero_acc<1, NTN>(acc);
+  warp_gemm<1, NTN / 2, false, false>(acc, sm.vn, LDD, 16 * mt, 0, sm.dh, LDD, 0, CW * nh, 8, lane);
 #pragma unroll
-  for (int nt = 0; nt < 8; ++nt) {
+  for (int nt = 0; nt < NTN; ++nt) {
     float cs0 = 0.f, cs1 = 0.f;
-    int c = 64 * nh + 8 * nt + t2;
+    int c = CW * nh + 8 * nt + t2;
 #pragma unroll
     for (int hh = 0; hh < 2; ++hh) {
       int r = 16 * mt + g8 + 8 * hh;
       float x0 = acc[0][nt][2 * hh] * fexp2(glast[c] - sm.g[r * D + c]);
       float x1 = acc[0][nt][2 * hh + 1] * fexp2(glast[c + 1] - sm.g[r * D + c + 1]);
-      float2 kv = make_float2(0.f, 0.f);
-      if (r < valid)
-        kv = unpack_bf16(*reinterpret_cast<const uint32_t*>(p.k + rowD + (int64_t)r * gld + c));
+      float2 kv = unpack_bf16(kreg[nt][hh]);
       dkacc[nt][2 * hh] = x0;
       dkacc[nt][2 * hh + 1] = x1;
       dgacc[nt][2 * hh] -= kv.x * x0;
@@ -301,32 +321,32 @@ __global__ void __launch_bounds__(256) kda_bwd_wy_kernel(const BwdParams p) {
     }
   }
   // ---- dw = -(dv2 h^T) ------------------------------------------------------------------------
-  zero_acc<1, 8>(acc);
-  warp_gemm<1, 4, false, false>(acc, sm.dv2, LDD, 16 * mt, 0, sm.hh, LDD, 0, 64 * nh, 8, lane);
+  zero_acc<1, NTN>(acc);
+  warp_gemm<1, NTN / 2, false, false>(acc, sm.dv2, LDD, 16 * mt, 0, sm.hh, LDD, 0, CW * nh, 8, lane);
   __syncthreads();  // every warp is done with h and dh
   bf16* s_dw = sm.hh;
   bf16* s_x = sm.dh;
   bf16* s_y = sm.dh + 64 * LD64;
 #pragma unroll
-  for (int nt = 0; nt < 8; ++nt)
+  for (int nt = 0; nt < NTN; ++nt)
 #pragma unroll
     for (int hh = 0; hh < 2; ++hh) {
-      int r = 16 * mt + g8 + 8 * hh, c = 64 * nh + 8 * nt + t2;
+      int r = 16 * mt + g8 + 8 * hh, c = CW * nh + 8 * nt + t2;
       *reinterpret_cast<uint32_t*>(&s_dw[r * LDD + c]) =
           pack_bf16(-acc[0][nt][2 * hh], -acc[0][nt][2 * hh + 1]);
     }
   __syncthreads();
 
   // ---- dvb = A^T dv2 ; dv = beta dvb ; dbeta += <dvb, v> --------------------------------------
-  zero_acc<1, 8>(acc);
-  warp_gemm<1, 4, true, true>(acc, sm.a, LD64, 16 * mt, 0, sm.dv2, LDD, 0, 64 * nh, 4, lane);
+  zero_acc<1, NTN>(acc);
+  warp_gemm<1, NTN / 2, true, true>(acc, sm.a, LD64, 16 * mt, 0, sm.dv2, LDD, 0, CW * nh, 4, lane);
 #pragma unroll
   for (int hh = 0; hh < 2; ++hh) {
     int r = 16 * mt + g8 + 8 * hh;
     float b = sm.beta[r], dbp = 0.f;
 #pragma unroll
-    for (int nt = 0; nt < 8; ++nt) {
-      int c = 64 * nh + 8 * nt + t2;
+    for (int nt = 0; nt < NTN; ++nt) {
+      int c = CW * nh + 8 * nt + t2;
       float x0 = acc[0][nt][2 * hh], x1 = acc[0][nt][2 * hh + 1];
       float2 vv = unpack_bf16(*reinterpret_cast<uint32_t*>(&sm.v[r * LDD + c]));
       dbp += x0 * vv.x + x1 * vv.y;
@@ -338,15 +358,15 @@ __global__ void __launch_bounds__(256) kda_bwd_wy_kernel(const BwdParams p) {
     if ((lane & 3) == 0) atomicAdd(&sm.db[r], dbp);
   }
   // ---- dkgb = A^T dw ; dk += beta 2^G dkgb ; dG += beta k 2^G dkgb ; dbeta += <dkgb, k 2^G> ----
-  zero_acc<1, 8>(acc);
-  warp_gemm<1, 4, true, true>(acc, sm.a, LD64, 16 * mt, 0, s_dw, LDD, 0, 64 * nh, 4, lane);
+  zero_acc<1, NTN>(acc);
+  warp_gemm<1, NTN / 2, true, true>(acc, sm.a, LD64, 16 * mt, 0, s_dw, LDD, 0, CW * nh, 4, lane);
 #pragma unroll
   for (int hh = 0; hh < 2; ++hh) {
     int r = 16 * mt + g8 + 8 * hh;
     float b = sm.beta[r], dbp = 0.f;
 #pragma unroll
-    for (int nt = 0; nt < 8; ++nt) {
-      int c = 64 * nh + 8 * nt + t2;
+    for (int nt = 0; nt < NTN; ++nt) {
+      int c = CW * nh + 8 * nt + t2;
       float x0 = acc[0][nt][2 * hh], x1 = acc[0][nt][2 * hh + 1];
       float2 kgm = unpack_bf16(*reinterpret_cast<uint32_t*>(&sm.k[r * LDD + c]));  // k 2^G
       dbp += x0 * kgm.x + x1 * kgm.y;
@@ -371,53 +391,53 @@ __global__ void __launch_bounds__(256) kda_bwd_wy_kernel(const BwdParams p) {
 
   // ---- X = stril(dv2 v^T + dw (k 2^G)^T) diag(beta) -------------------------------------------
   const int nq = warp >> 2;
-  float acs[1][4][4];
-  zero_acc<1, 4>(acs);
-  warp_gemm<1, 2, false, false>(acs, sm.dv2, LDD, 16 * mt, 0, sm.v, LDD, 0, 32 * nq, 8, lane);
-  warp_gemm<1, 2, false, false>(acs, s_dw, LDD, 16 * mt, 0, sm.k, LDD, 0, 32 * nq, 8, lane);
+  float acs[1][NTQ][4];
+  zero_acc<1, NTQ>(acs);
+  warp_gemm<1, NTQ / 2, false, false>(acs, sm.dv2, LDD, 16 * mt, 0, sm.v, LDD, 0, CQ * nq, 8, lane);
+  warp_gemm<1, NTQ / 2, false, false>(acs, s_dw, LDD, 16 * mt, 0, sm.k, LDD, 0, CQ * nq, 8, lane);
 #pragma unroll
-  for (int nt = 0; nt < 4; ++nt)
+  for (int nt = 0; nt < NTQ; ++nt)
 #pragma unroll
     for (int hh = 0; hh < 2; ++hh) {
-      int r = 16 * mt + g8 + 8 * hh, c = 32 * nq + 8 * nt + t2;
+      int r = 16 * mt + g8 + 8 * hh, c = CQ * nq + 8 * nt + t2;
       float x0 = (r > c) ? acs[0][nt][2 * hh] * sm.beta[c] : 0.f;
       float x1 = (r > c + 1) ? acs[0][nt][2 * hh + 1] * sm.beta[c + 1] : 0.f;
       *reinterpret_cast<uint32_t*>(&s_x[r * LD64 + c]) = pack_bf16(x0, x1);
     }
   __syncthreads();
   // ---- Y = A^T X ------------------------------------------------------------------------------
-  zero_acc<1, 4>(acs);
-  warp_gemm<1, 2, true, true>(acs, sm.a, LD64, 16 * mt, 0, s_x, LD64, 0, 32 * nq, 4, lane);
+  zero_acc<1, NTQ>(acs);
+  warp_gemm<1, NTQ / 2, true, true>(acs, sm.a, LD64, 16 * mt, 0, s_x, LD64, 0, CQ * nq, 4, lane);
 #pragma unroll
-  for (int nt = 0; nt < 4; ++nt)
+  for (int nt = 0; nt < NTQ; ++nt)
 #pragma unroll
     for (int hh = 0; hh < 2; ++hh) {
-      int r = 16 * mt + g8 + 8 * hh, c = 32 * nq + 8 * nt + t2;
+      int r = 16 * mt + g8 + 8 * hh, c = CQ * nq + 8 * nt + t2;
       *reinterpret_cast<uint32_t*>(&s_y[r * LD64 + c]) =
           pack_bf16(acs[0][nt][2 * hh], acs[0][nt][2 * hh + 1]);
     }
   __syncthreads();
   // ---- dL = -stril(Y A^T) ---------------------------------------------------------------------
-  zero_acc<1, 4>(acs);
-  warp_gemm<1, 2, false, false>(acs, s_y, LD64, 16 * mt, 0, sm.a, LD64, 0, 32 * nq, 4, lane);
+  zero_acc<1, NTQ>(acs);
+  warp_gemm<1, NTQ / 2, false, false>(acs, s_y, LD64, 16 * mt, 0, sm.a, LD64, 0, CQ * nq, 4, lane);
 #pragma unroll
-  for (int nt = 0; nt < 4; ++nt)
+  for (int nt = 0; nt < NTQ; ++nt)
 #pragma unroll
     for (int hh = 0; hh < 2; ++hh) {
-      int r = 16 * mt + g8 + 8 * hh, c = 32 * nq + 8 * nt + t2;
+      int r = 16 * mt + g8 + 8 * hh, c = CQ * nq + 8 * nt + t2;
       if (r < valid)
         *reinterpret_cast<float2*>(p.dl + row64 + (int64_t)r * gld64 + c) =
             make_float2((r > c) ? -acs[0][nt][2 * hh] : 0.f,
                         (r > c + 1) ? -acs[0][nt][2 * hh + 1] : 0.f);
     }
   // ---- dAqk = scale tril(do v_new^T) ----------------------------------------------------------
-  zero_acc<1, 4>(acs);
-  warp_gemm<1, 2, false, false>(acs, sm.dO, LDD, 16 * mt, 0, sm.vn, LDD, 0, 32 * nq, 8, lane);
+  zero_acc<1, NTQ>(acs);
+  warp_gemm<1, NTQ / 2, false, false>(acs, sm.dO, LDD, 16 * mt, 0, sm.vn, LDD, 0, CQ * nq, 8, lane);
 #pragma unroll
-  for (int nt = 0; nt < 4; ++nt)
+  for (int nt = 0; nt < NTQ; ++nt)
 #pragma unroll
     for (int hh = 0; hh < 2; ++hh) {
-      int r = 16 * mt + g8 + 8 * hh, c = 32 * nq + 8 * nt + t2;
+      int r = 16 * mt + g8 + 8 * hh, c = CQ * nq + 8 * nt + t2;
       if (r < valid)
         *reinterpret_cast<float2*>(p.daqk + row64 + (int64_t)r * gld64 + c) =
             make_float2((r >= c) ? acs[0][nt][2 * hh] * p.scale : 0.f,
@@ -427,7 +447,10 @@ __global__ void __launch_bounds__(256) kda_bwd_wy_kernel(const BwdParams p) {
 }
 
 // ------------------------------------------------------------------------------------------
-// intra: gradients through Aqk and L; warp w owns channels [16 w, 16 w + 16) of every row
+// intra: gradients through Aqk and L.
+// 16 warps in two groups of 8.  A group owns two 16-row blocks ({0,3} or {1,2}: equal work) and
+// computes everything that lands on those rows; inside a group warp w owns channels
+// [16 w, 16 w + 16), so every output element has exactly one owner and lives in registers.
 // ------------------------------------------------------------------------------------------
 struct IntraBwdSmem {
   bf16 q[64 * LDD];
@@ -435,17 +458,21 @@ struct IntraBwdSmem {
   float g[64 * D];
   bf16 da[64 * LD64];    // dAqk
   bf16 dl[64 * LD64];    // dL
-  bf16 dlb[64 * LD64];   // beta_i dL_ij
-  bf16 kn[64 * LDD];     // gated k (row phase: columns; column phase: rows)
-  bf16 qn[64 * LDD];     // gated q (column phase)
+  bf16 kn[2][64 * LDD];  // per group: gated k (row phase: columns; column phase: beta-scaled rows)
+  bf16 qn[2][64 * LDD];  // per group: gated q (column phase)
   float beta[64];
   float db[64];
 };
 
-__global__ void __launch_bounds__(256) kda_bwd_intra_kernel(const BwdParams p) {
+__device__ __forceinline__ void group_sync(int group) {
+  asm volatile("bar.sync %0, %1;" ::"r"(group + 1), "r"(256) : "memory");
+}
+
+__global__ void __launch_bounds__(512) kda_bwd_intra_kernel(const BwdParams p) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   IntraBwdSmem& sm = *reinterpret_cast<IntraBwdSmem*>(smem_raw);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int group = warp >> 3, gtid = tid & 255;
   const int head = blockIdx.y, H = p.H;
   const ChunkWork cw = locate_chunk(p.cu_seqlens, p.chunk_offsets, p.nseq, blockIdx.x);
   if (cw.valid == 0) return;
@@ -455,62 +482,62 @@ __global__ void __launch_bounds__(256) kda_bwd_intra_kernel(const BwdParams p) {
   const int64_t row64 = (cw.token0 * H + head) * 64;
   const int64_t gld64 = (int64_t)H * 64;
   const int g8 = lane >> 2, t2 = 2 * (lane & 3);
+  const int n0 = 16 * (warp & 7);
+  bf16* kn = sm.kn[group];
+  bf16* qn = sm.qn[group];
 
-  load_tile_b16<64, D, LDD, 256>(sm.q, p.q + rowD, gld, valid, tid);
-  load_tile_b16<64, D, LDD, 256>(sm.k, p.k + rowD, gld, valid, tid);
-  load_tile_f32<64, D, D, 256>(sm.g, p.g + rowD, gld, valid, tid);
+  load_tile_b16<64, D, LDD, 512>(sm.q, p.q + rowD, gld, valid, tid);
+  load_tile_b16<64, D, LDD, 512>(sm.k, p.k + rowD, gld, valid, tid);
+  load_tile_f32<64, D, D, 512>(sm.g, p.g + rowD, gld, valid, tid);
   cp_async_commit();
   if (tid < 64) {
     sm.beta[tid] = tid < valid ? p.beta[(cw.token0 + tid) * H + head] : 0.f;
     sm.db[tid] = 0.f;
   }
-  __syncthreads();  // beta visible
-  for (int idx = tid; idx < 64 * 16; idx += 256) {
+  for (int idx = tid; idx < 64 * 16; idx += 512) {
     int r = idx >> 4, c = (idx & 15) * 4;
     float4 a = make_float4(0.f, 0.f, 0.f, 0.f), l = a;
     if (r < valid) {
-      a = *reinterpret_cast<const float4*>(p.daqk + row64 + (int64_t)r * gld64 + c);
-      l = *reinterpret_cast<const float4*>(p.dl + row64 + (int64_t)r * gld64 + c);
+      a = __ldg(reinterpret_cast<const float4*>(p.daqk + row64 + (int64_t)r * gld64 + c));
+      l = __ldg(reinterpret_cast<const float4*>(p.dl + row64 + (int64_t)r * gld64 + c));
     }
-    float b = sm.beta[r];
-    uint2 ua, ul, ub;
+    uint2 ua, ul;
     ua.x = pack_bf16(a.x, a.y); ua.y = pack_bf16(a.z, a.w);
     ul.x = pack_bf16(l.x, l.y); ul.y = pack_bf16(l.z, l.w);
-    ub.x = pack_bf16(l.x * b, l.y * b); ub.y = pack_bf16(l.z * b, l.w * b);
     *reinterpret_cast<uint2*>(&sm.da[r * LD64 + c]) = ua;
     *reinterpret_cast<uint2*>(&sm.dl[r * LD64 + c]) = ul;
-    *reinterpret_cast<uint2*>(&sm.dlb[r * LD64 + c]) = ub;
   }
   cp_async_wait<0>();
   __syncthreads();
   if (valid < 64) {
-    for (int idx = tid; idx < (64 - valid) * D; idx += 256) {
+    for (int idx = tid; idx < (64 - valid) * D; idx += 512) {
       int r = valid + idx / D, c = idx % D;
       sm.g[r * D + c] = sm.g[(valid - 1) * D + c];
     }
     __syncthreads();
   }
 
-  float dq[4][2][4], dk[4][2][4], dg[4][2][4];
-  const int n0 = 16 * warp;
+  float dq[2][2][4], dk[2][2][4], dg[2][2][4];
 
   // ---- row phase: dq_i, dk_i, dbeta_i from sum_j (.)_ij 2^{G_i - G_j} k_j ----------------------
-  for (int ri = 0; ri < 4; ++ri) {
+#pragma unroll
+  for (int bi = 0; bi < 2; ++bi) {
+    const int ri = group == 0 ? (bi == 0 ? 0 : 3) : (bi == 0 ? 1 : 2);
     const int ncol = 16 * (ri + 1);
     const float* R = sm.g + (16 * ri) * D;
-    for (int idx = tid; idx < ncol * (D / 2); idx += 256) {
+    for (int idx = gtid; idx < ncol * (D / 2); idx += 256) {
       int j = idx / (D / 2), c = (idx % (D / 2)) * 2;
       float e0 = fexp2(fminf(R[c] - sm.g[j * D + c], 126.f));
       float e1 = fexp2(fminf(R[c + 1] - sm.g[j * D + c + 1], 126.f));
       float2 kv = unpack_bf16(*reinterpret_cast<uint32_t*>(&sm.k[j * LDD + c]));
-      *reinterpret_cast<uint32_t*>(&sm.kn[j * LDD + c]) = pack_bf16(kv.x * e0, kv.y * e1);
+      *reinterpret_cast<uint32_t*>(&kn[j * LDD + c]) = pack_bf16(kv.x * e0, kv.y * e1);
     }
-    __syncthreads();
+    group_sync(group);
     float aq[1][2][4], ax[1][2][4];
     zero_acc<1, 2>(aq);
     zero_acc<1, 2>(ax);
-    warp_gemm<1, 1, false, true>(aq, sm.da, LD64, 16 * ri, 0, sm.kn, LDD, 0, n0, ri + 1, lane);
-    warp_gemm<1, 1, false, true>(ax, sm.dl, LD64, 16 * ri, 0, sm.kn, LDD, 0, n0, ri + 1, lane);
+    warp_gemm<1, 1, false, true>(aq, sm.da, LD64, 16 * ri, 0, kn, LDD, 0, n0, ri + 1, lane);
+    warp_gemm<1, 1, false, true>(ax, sm.dl, LD64, 16 * ri, 0, kn, LDD, 0, n0, ri + 1, lane);
 #pragma unroll
     for (int hh = 0; hh < 2; ++hh) {
       int i = 16 * ri + g8 + 8 * hh;
@@ -523,39 +550,42 @@ __global__ void __launch_bounds__(256) kda_bwd_intra_kernel(const BwdParams p) {
         float2 kv = unpack_bf16(*reinterpret_cast<uint32_t*>(&sm.k[i * LDD + c]));
         float q0 = aq[0][nt][2 * hh] * e0, q1 = aq[0][nt][2 * hh + 1] * e1;
         float x0 = ax[0][nt][2 * hh] * e0, x1 = ax[0][nt][2 * hh + 1] * e1;
-        dq[ri][nt][2 * hh] = q0;
-        dq[ri][nt][2 * hh + 1] = q1;
-        dk[ri][nt][2 * hh] = b * x0;
-        dk[ri][nt][2 * hh + 1] = b * x1;
-        dg[ri][nt][2 * hh] = qv.x * q0 + kv.x * b * x0;
-        dg[ri][nt][2 * hh + 1] = qv.y * q1 + kv.y * b * x1;
+        dq[bi][nt][2 * hh] = q0;
+        dq[bi][nt][2 * hh + 1] = q1;
+        dk[bi][nt][2 * hh] = b * x0;
+        dk[bi][nt][2 * hh + 1] = b * x1;
+        dg[bi][nt][2 * hh] = qv.x * q0 + kv.x * b * x0;
+        dg[bi][nt][2 * hh + 1] = qv.y * q1 + kv.y * b * x1;
         dbp += kv.x * x0 + kv.y * x1;
       }
       dbp += __shfl_xor_sync(0xffffffffu, dbp, 1);
       dbp += __shfl_xor_sync(0xffffffffu, dbp, 2);
       if ((lane & 3) == 0) atomicAdd(&sm.db[i], dbp);
     }
-    __syncthreads();
+    group_sync(group);
   }
 
   // ---- column phase: dk_j from sum_i (.)_ij 2^{G_i - G_j} {q_i, beta_i k_i} --------------------
-  for (int cj = 0; cj < 4; ++cj) {
+#pragma unroll
+  for (int bi = 0; bi < 2; ++bi) {
+    const int cj = group == 0 ? (bi == 0 ? 0 : 3) : (bi == 0 ? 1 : 2);
     const float* R = sm.g + (16 * cj + 15) * D;
     const int r0 = 16 * cj;
-    for (int idx = tid; idx < (64 - r0) * (D / 2); idx += 256) {
+    for (int idx = gtid; idx < (64 - r0) * (D / 2); idx += 256) {
       int i = r0 + idx / (D / 2), c = (idx % (D / 2)) * 2;
       float e0 = fexp2(fminf(sm.g[i * D + c] - R[c], 126.f));
       float e1 = fexp2(fminf(sm.g[i * D + c + 1] - R[c + 1], 126.f));
       float2 qv = unpack_bf16(*reinterpret_cast<uint32_t*>(&sm.q[i * LDD + c]));
       float2 kv = unpack_bf16(*reinterpret_cast<uint32_t*>(&sm.k[i * LDD + c]));
-      *reinterpret_cast<uint32_t*>(&sm.qn[i * LDD + c]) = pack_bf16(qv.x * e0, qv.y * e1);
-      *reinterpret_cast<uint32_t*>(&sm.kn[i * LDD + c]) = pack_bf16(kv.x * e0, kv.y * e1);
+      float b = sm.beta[i];
+      *reinterpret_cast<uint32_t*>(&qn[i * LDD + c]) = pack_bf16(qv.x * e0, qv.y * e1);
+      *reinterpret_cast<uint32_t*>(&kn[i * LDD + c]) = pack_bf16(kv.x * e0 * b, kv.y * e1 * b);
     }
-    __syncthreads();
+    group_sync(group);
     float ac[1][2][4];
     zero_acc<1, 2>(ac);
-    warp_gemm<1, 1, true, true>(ac, sm.da, LD64, r0, r0, sm.qn, LDD, r0, n0, 4 - cj, lane);
-    warp_gemm<1, 1, true, true>(ac, sm.dlb, LD64, r0, r0, sm.kn, LDD, r0, n0, 4 - cj, lane);
+    warp_gemm<1, 1, true, true>(ac, sm.da, LD64, r0, r0, qn, LDD, r0, n0, 4 - cj, lane);
+    warp_gemm<1, 1, true, true>(ac, sm.dl, LD64, r0, r0, kn, LDD, r0, n0, 4 - cj, lane);
 #pragma unroll
     for (int hh = 0; hh < 2; ++hh) {
       int j = r0 + g8 + 8 * hh;
@@ -565,37 +595,52 @@ __global__ void __launch_bounds__(256) kda_bwd_intra_kernel(const BwdParams p) {
         float f0 = fexp2(R[c] - sm.g[j * D + c]), f1 = fexp2(R[c + 1] - sm.g[j * D + c + 1]);
         float2 kv = unpack_bf16(*reinterpret_cast<uint32_t*>(&sm.k[j * LDD + c]));
         float x0 = ac[0][nt][2 * hh] * f0, x1 = ac[0][nt][2 * hh + 1] * f1;
-        dk[cj][nt][2 * hh] += x0;
-        dk[cj][nt][2 * hh + 1] += x1;
-        dg[cj][nt][2 * hh] -= kv.x * x0;
-        dg[cj][nt][2 * hh + 1] -= kv.y * x1;
+        dk[bi][nt][2 * hh] += x0;
+        dk[bi][nt][2 * hh + 1] += x1;
+        dg[bi][nt][2 * hh] -= kv.x * x0;
+        dg[bi][nt][2 * hh + 1] -= kv.y * x1;
       }
     }
-    __syncthreads();
+    group_sync(group);
   }
 
-  // ---- combine with the wy partials -----------------------------------------------------------
+  // ---- combine with the wy partials: all loads first, then the stores -------------------------
+  float2 pa[2][2][2], pb[2][2][2], pc[2][2][2];
 #pragma unroll
-  for (int rb = 0; rb < 4; ++rb)
+  for (int bi = 0; bi < 2; ++bi)
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh)
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt) {
+        const int rb = group == 0 ? (bi == 0 ? 0 : 3) : (bi == 0 ? 1 : 2);
+        int r = 16 * rb + g8 + 8 * hh;
+        int64_t gi = rowD + (int64_t)r * gld + n0 + 8 * nt + t2;
+        float2 z = make_float2(0.f, 0.f);
+        pa[bi][hh][nt] = r < valid ? __ldg(reinterpret_cast<const float2*>(p.dq_p + gi)) : z;
+        pb[bi][hh][nt] = r < valid ? __ldg(reinterpret_cast<const float2*>(p.dk_p + gi)) : z;
+        pc[bi][hh][nt] = r < valid ? __ldg(reinterpret_cast<const float2*>(p.dg_p + gi)) : z;
+      }
+#pragma unroll
+  for (int bi = 0; bi < 2; ++bi)
 #pragma unroll
     for (int hh = 0; hh < 2; ++hh) {
+      const int rb = group == 0 ? (bi == 0 ? 0 : 3) : (bi == 0 ? 1 : 2);
       int r = 16 * rb + g8 + 8 * hh;
       if (r < valid) {
 #pragma unroll
         for (int nt = 0; nt < 2; ++nt) {
           int64_t gi = rowD + (int64_t)r * gld + n0 + 8 * nt + t2;
-          float2 a = *reinterpret_cast<const float2*>(p.dq_p + gi);
-          float2 b = *reinterpret_cast<const float2*>(p.dk_p + gi);
-          float2 c = *reinterpret_cast<const float2*>(p.dg_p + gi);
+          float2 a = pa[bi][hh][nt], b = pb[bi][hh][nt], c = pc[bi][hh][nt];
           *reinterpret_cast<uint32_t*>(p.dq + gi) =
-              pack_bf16(a.x + dq[rb][nt][2 * hh], a.y + dq[rb][nt][2 * hh + 1]);
+              pack_bf16(a.x + dq[bi][nt][2 * hh], a.y + dq[bi][nt][2 * hh + 1]);
           *reinterpret_cast<uint32_t*>(p.dk + gi) =
-              pack_bf16(b.x + dk[rb][nt][2 * hh], b.y + dk[rb][nt][2 * hh + 1]);
+              pack_bf16(b.x + dk[bi][nt][2 * hh], b.y + dk[bi][nt][2 * hh + 1]);
           *reinterpret_cast<float2*>(p.dg + gi) = make_float2(
-              (c.x + dg[rb][nt][2 * hh]) * kLn2, (c.y + dg[rb][nt][2 * hh + 1]) * kLn2);
+              (c.x + dg[bi][nt][2 * hh]) * kLn2, (c.y + dg[bi][nt][2 * hh + 1]) * kLn2);
         }
       }
     }
+  __syncthreads();  // every dbeta contribution is in
   if (tid < valid) {
     int64_t bi = (cw.token0 + tid) * H + head;
     p.db[bi] = p.db_p[bi] + sm.db[tid];
@@ -678,16 +723,16 @@ extern "C" int kda_chunk_bwd(const void* q, const void* k, const void* v, const 
   }
   if ((rc = kda::check_launch())) return rc;
   if (num_chunks == 0) return KDA_OK;
-  if (kda::set_smem(kda::kda_bwd_wy_kernel, sizeof(kda::WySmem))) return KDA_ERR_LAUNCH;
+  if (kda::set_smem(kda::kda_bwd_wy_kernel<16>, sizeof(kda::WySmem))) return KDA_ERR_LAUNCH;
   {
     kda::StageScope timing(kda::kStageBwdWy, s);
-    kda::kda_bwd_wy_kernel<<<dim3(num_chunks, heads), 256, sizeof(kda::WySmem), s>>>(p);
+    kda::kda_bwd_wy_kernel<16><<<dim3(num_chunks, heads), 512, sizeof(kda::WySmem), s>>>(p);
   }
   if ((rc = kda::check_launch())) return rc;
   if (kda::set_smem(kda::kda_bwd_intra_kernel, sizeof(kda::IntraBwdSmem))) return KDA_ERR_LAUNCH;
   {
     kda::StageScope timing(kda::kStageBwdIntra, s);
-    kda::kda_bwd_intra_kernel<<<dim3(num_chunks, heads), 256, sizeof(kda::IntraBwdSmem), s>>>(p);
+    kda::kda_bwd_intra_kernel<<<dim3(num_chunks, heads), 512, sizeof(kda::IntraBwdSmem), s>>>(p);
   }
   return kda::check_launch();
 }

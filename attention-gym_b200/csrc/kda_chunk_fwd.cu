@@ -197,6 +197,7 @@ __global__ void __launch_bounds__(256) kda_intra_solve_kernel(const ChunkParams 
 struct WuSmem {
   bf16 k[64 * LDD];
   bf16 v[64 * LDD];
+  bf16 q[64 * LDD];
   float g[64 * D];
   bf16 a[64 * LD64];
   float beta[64];
@@ -215,6 +216,7 @@ __global__ void __launch_bounds__(256) kda_wu_kernel(const ChunkParams p) {
 
   load_tile_b16<64, D, LDD, 256>(sm.k, p.k + rowD, gld, valid, tid);
   load_tile_b16<64, D, LDD, 256>(sm.v, p.v + rowD, gld, valid, tid);
+  load_tile_b16<64, D, LDD, 256>(sm.q, p.q + rowD, gld, valid, tid);
   load_tile_f32<64, D, D, 256>(sm.g, p.g + rowD, gld, valid, tid);
   load_tile_b16<64, 64, LD64, 256>(sm.a, p.akk + (cw.token0 * H + head) * 64, (int64_t)H * 64,
                                    valid, tid);
@@ -233,7 +235,7 @@ __global__ void __launch_bounds__(256) kda_wu_kernel(const ChunkParams p) {
     float b = sm.beta[r];
     if (r < valid) {
       int64_t gi = rowD + (int64_t)r * gld + c;
-      float2 qv = unpack_bf16(*reinterpret_cast<const uint32_t*>(p.q + gi));
+      float2 qv = unpack_bf16(*reinterpret_cast<uint32_t*>(&sm.q[r * LDD + c]));
       *reinterpret_cast<uint32_t*>(p.qg + gi) = pack_bf16(qv.x * e0 * p.scale, qv.y * e1 * p.scale);
       *reinterpret_cast<uint32_t*>(p.kg + gi) =
           pack_bf16(kv.x * fexp2(glast[c] - g0), kv.y * fexp2(glast[c + 1] - g1));
@@ -287,12 +289,14 @@ __device__ __forceinline__ void state_load_stage(StateStage& s, const ChunkParam
   const int64_t rowD = (token0 * H + head) * D;
   const int64_t gld = (int64_t)H * D;
   load_tile_b16<64, D, LDD, 256>(s.w, p.w + rowD, gld, valid, tid);
-  load_tile_b16<64, D, LDD, 256>(s.qg, p.qg + rowD, gld, valid, tid);
   load_tile_b16<64, D, LDD, 256>(s.kg, p.kg + rowD, gld, valid, tid);
   load_tile_b16<64, 64, LD64, 256>(s.u, p.u ? p.u + rowD + 64 * vh : p.w, gld, p.u ? valid : 0,
                                    tid);
-  load_tile_b16<64, 64, LD64, 256>(s.aqk, p.aqk + (token0 * H + head) * 64, (int64_t)H * 64, valid,
-                                   tid);
+  if (p.o) {  // the output terms need qg and Aqk; the recompute / transition passes do not
+    load_tile_b16<64, D, LDD, 256>(s.qg, p.qg + rowD, gld, valid, tid);
+    load_tile_b16<64, 64, LD64, 256>(s.aqk, p.aqk + (token0 * H + head) * 64, (int64_t)H * 64,
+                                     valid, tid);
+  }
   if (tid < D / 4)
     cp_async16(s.dec + tid * 4, p.g + rowD + (int64_t)(valid - 1) * gld + tid * 4, true);
 }
@@ -355,7 +359,8 @@ __global__ void __launch_bounds__(256) kda_state_fwd_kernel(const ChunkParams p)
     zero_acc<1, 4>(accv);
     zero_acc<1, 4>(acco);
     warp_gemm<1, 2, false, true>(accv, st.w, LDD, 16 * mt, 0, sm.h, LD64, 0, 32 * nq, 8, lane);
-    warp_gemm<1, 2, false, true>(acco, st.qg, LDD, 16 * mt, 0, sm.h, LD64, 0, 32 * nq, 8, lane);
+    if (p.o)
+      warp_gemm<1, 2, false, true>(acco, st.qg, LDD, 16 * mt, 0, sm.h, LD64, 0, 32 * nq, 8, lane);
 #pragma unroll
     for (int nt = 0; nt < 4; ++nt)
 #pragma unroll
@@ -369,7 +374,8 @@ __global__ void __launch_bounds__(256) kda_state_fwd_kernel(const ChunkParams p)
     if (p.vnew_out)
       store_tile_b16<64, 64, LD64, 256>(p.vnew_out + (token0 * H + head) * D + 64 * vh,
                                         (int64_t)H * D, sm.vn, valid, tid);
-    warp_gemm<1, 2, false, true>(acco, st.aqk, LD64, 16 * mt, 0, sm.vn, LD64, 0, 32 * nq, 4, lane);
+    if (p.o)
+      warp_gemm<1, 2, false, true>(acco, st.aqk, LD64, 16 * mt, 0, sm.vn, LD64, 0, 32 * nq, 4, lane);
     {
       float d0 = fexp2(st.dec[16 * warp + g8]), d1 = fexp2(st.dec[16 * warp + g8 + 8]);
 #pragma unroll

@@ -11,6 +11,7 @@
 // The decode step is pure state streaming: 2*K*V*4 bytes per (sequence, head) per step.
 #include "kda_common.cuh"
 #include "kda_timing.cuh"
+#include <cstdlib>
 
 namespace kda {
 
@@ -28,8 +29,8 @@ struct ScanParams {
   float scale;
 };
 
-template <int KR, int VEC>
-__global__ void __launch_bounds__(256) kda_scan_kernel(const ScanParams p) {
+template <int KR, int VEC, int MINB>
+__global__ void __launch_bounds__(256, MINB) kda_scan_kernel(const ScanParams p) {
   constexpr int BV = 32 * VEC;
   constexpr int NW = 8;
   __shared__ float s_q[2][256], s_k[2][256], s_d[2][256];
@@ -78,6 +79,9 @@ __global__ void __launch_bounds__(256) kda_scan_kernel(const ScanParams p) {
       if (VEC == 4 && c0 + 3 < V) {
         float4 x = *reinterpret_cast<const float4*>(sin + (int64_t)r * V + c0);
         S[i][0] = x.x; S[i][1] = x.y; S[i][2] = x.z; S[i][3] = x.w;
+      } else if (VEC == 2 && c0 + 1 < V) {
+        float2 x = *reinterpret_cast<const float2*>(sin + (int64_t)r * V + c0);
+        S[i][0] = x.x; S[i][1] = x.y;
       } else {
 #pragma unroll
         for (int j = 0; j < VEC; ++j)
@@ -168,6 +172,8 @@ __global__ void __launch_bounds__(256) kda_scan_kernel(const ScanParams p) {
         if (VEC == 4 && c0 + 3 < V) {
           *reinterpret_cast<float4*>(sout + (int64_t)r * V + c0) =
               make_float4(S[i][0], S[i][1], S[i][2], S[i][3]);
+        } else if (VEC == 2 && c0 + 1 < V) {
+          *reinterpret_cast<float2*>(sout + (int64_t)r * V + c0) = make_float2(S[i][0], S[i][1]);
         } else {
 #pragma unroll
           for (int j = 0; j < VEC; ++j)
@@ -178,14 +184,14 @@ __global__ void __launch_bounds__(256) kda_scan_kernel(const ScanParams p) {
   }
 }
 
-template <int KR, int VEC>
+template <int KR, int VEC, int MINB = 1>
 static int launch_scan(const ScanParams& p, cudaStream_t stream) {
   constexpr int BV = 32 * VEC;
   int64_t blocks = (int64_t)p.nseq * p.H * ((p.V + BV - 1) / BV);
   if (blocks <= 0) return KDA_OK;
   if (blocks > 0x7fffffffLL) return KDA_ERR_UNSUPPORTED;
   StageScope timing(kStageRecurrent, stream);
-  kda_scan_kernel<KR, VEC><<<(unsigned)blocks, 256, 0, stream>>>(p);
+  kda_scan_kernel<KR, VEC, MINB><<<(unsigned)blocks, 256, 0, stream>>>(p);
   return cudaGetLastError() == cudaSuccess ? KDA_OK : KDA_ERR_LAUNCH;
 }
 
@@ -217,10 +223,22 @@ extern "C" int kda_recurrent_fwd(const void* q, const void* k, const void* v, co
   bool vec4 = (value_dim % 4 == 0) && (slot_stride % 4 == 0) &&
               ((int64_t)nseq * heads * ((value_dim + 127) / 128) >= 296 || value_dim > 1024);
   int kr = (key_dim + 7) / 8;
+  if (const char* mode = getenv("KDA_SCAN_MODE")) {  // tuning hook for the K <= 128 decode shapes
+    if (kr <= 16 && value_dim % 4 == 0 && slot_stride % 4 == 0) {
+      switch (atoi(mode)) {
+        case 0: return launch_scan<16, 4, 1>(p, s);
+        case 1: return launch_scan<16, 4, 2>(p, s);
+        case 2: return launch_scan<16, 2, 2>(p, s);
+        case 3: return launch_scan<16, 2, 3>(p, s);
+        case 4: return launch_scan<16, 1, 4>(p, s);
+        default: break;
+      }
+    }
+  }
   if (vec4) {
     if (kr <= 4) return launch_scan<4, 4>(p, s);
     if (kr <= 8) return launch_scan<8, 4>(p, s);
-    if (kr <= 16) return launch_scan<16, 4>(p, s);
+    if (kr <= 16) return launch_scan<16, 4, 2>(p, s);  // two CTAs per SM: loads overlap stores
     return launch_scan<32, 1>(p, s);
   }
   if (kr <= 4) return launch_scan<4, 1>(p, s);
