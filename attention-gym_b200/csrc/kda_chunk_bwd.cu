@@ -658,7 +658,7 @@ static int set_smem(Kern kern, size_t bytes) {
 int launch_recompute(const void* q, const void* k, const void* v, const float* g, const float* beta,
                      const void* aqk, const void* akk, const float* h0, void* w, void* u, void* kg,
                      void* qg, void* h_out, void* vnew_out, const int32_t* cu, const int32_t* co,
-                     int nseq, int H, int chunks, cudaStream_t s);
+                     int nseq, int H, int chunks, int64_t tokens, cudaStream_t s);
 
 }  // namespace kda
 
@@ -703,7 +703,7 @@ extern "C" int kda_chunk_bwd(const void* q, const void* k, const void* v, const 
   cudaStream_t s = (cudaStream_t)stream;
 
   int rc = kda::launch_recompute(q, k, v, cum_gate, beta, aqk, akk, initial_state, w, u, kg, qg,
-                                 hbuf, vnew, cu_seqlens, chunk_offsets, nseq, heads, num_chunks, s);
+                                 hbuf, vnew, cu_seqlens, chunk_offsets, nseq, heads, num_chunks, tokens, s);
   if (rc) return rc;
 
   kda::BwdParams p{};

@@ -20,6 +20,7 @@
 // the same exponent budget as the reference (fwd/triton/gate_fwd.py:619-631).
 #include "kda_common.cuh"
 #include "kda_timing.cuh"
+#include <cstdlib>
 
 namespace kda {
 
@@ -37,7 +38,13 @@ struct ChunkParams {
   const int32_t* cu_seqlens; const int32_t* chunk_offsets;
   int nseq, H;
   float scale;
+  int64_t tokens;   // rows of the token-major buffers (bounds of the TMA tensor maps)
 };
+
+int launch_state_fwd_tc(const bf16* w, const bf16* u, const bf16* kg, const bf16* qg, const bf16* aqk,
+                        const float* g, const float* h0, float* ht, bf16* o, bf16* h_out,
+                        bf16* vnew_out, const int32_t* cu, const int32_t* co, int nseq, int H,
+                        int64_t tokens, cudaStream_t s);
 
 // ------------------------------------------------------------------------------------------
 // intra_solve
@@ -440,6 +447,11 @@ int launch_wu(const ChunkParams& p, int chunks, cudaStream_t s) {
 }
 int launch_state_fwd(const ChunkParams& p, cudaStream_t s) {
   if (p.nseq == 0) return KDA_OK;
+  if (const char* e = getenv("KDA_STATE_TC")) {
+    if (e[0] == '1')
+      return launch_state_fwd_tc(p.w, p.u, p.kg, p.qg, p.aqk, p.g, p.h0, p.ht, p.o, p.h_out,
+                                 p.vnew_out, p.cu_seqlens, p.chunk_offsets, p.nseq, p.H, p.tokens, s);
+  }
   if (set_smem(kda_state_fwd_kernel, sizeof(StateSmem))) return KDA_ERR_LAUNCH;
   StageScope timing(kStageStateFwd, s);
   kda_state_fwd_kernel<<<(unsigned)(p.nseq * p.H * 2), 256, sizeof(StateSmem), s>>>(p);
@@ -451,7 +463,7 @@ int launch_state_fwd(const ChunkParams& p, cudaStream_t s) {
 int launch_recompute(const void* q, const void* k, const void* v, const float* g, const float* beta,
                      const void* aqk, const void* akk, const float* h0, void* w, void* u, void* kg,
                      void* qg, void* h_out, void* vnew_out, const int32_t* cu, const int32_t* co,
-                     int nseq, int H, int chunks, cudaStream_t s) {
+                     int nseq, int H, int chunks, int64_t tokens, cudaStream_t s) {
   ChunkParams p{};
   p.q = (const bf16*)q; p.k = (const bf16*)k; p.v = (const bf16*)v; p.g = g; p.beta = beta;
   p.aqk = (bf16*)aqk; p.akk = (bf16*)akk;
@@ -460,6 +472,7 @@ int launch_recompute(const void* q, const void* k, const void* v, const float* g
   p.h_out = (bf16*)h_out; p.vnew_out = (bf16*)vnew_out;
   p.cu_seqlens = cu; p.chunk_offsets = co; p.nseq = nseq; p.H = H;
   p.scale = 0.08838834764831845f;
+  p.tokens = tokens;
   int rc = launch_wu(p, chunks, s);
   if (rc) return rc;
   return launch_state_fwd(p, s);
@@ -492,6 +505,7 @@ extern "C" int kda_chunk_fwd(const void* q, const void* k, const void* v, const 
   p.h_out = nullptr; p.vnew_out = nullptr;
   p.cu_seqlens = cu_seqlens; p.chunk_offsets = chunk_offsets; p.nseq = nseq; p.H = heads;
   p.scale = 0.08838834764831845f;  // 128^-0.5
+  p.tokens = tokens;
   cudaStream_t s = (cudaStream_t)stream;
   int rc = kda::launch_intra_solve(p, num_chunks, s);
   if (rc) return rc;
@@ -551,6 +565,7 @@ extern "C" int kda_chunk_fwd_state(const float* cum_gate, const float* initial_s
   p.w = ws; p.u = use_u ? ws + nd : nullptr; p.kg = ws + 2 * nd; p.qg = ws + 3 * nd;
   p.h0 = initial_state; p.ht = final_state; p.o = (bf16*)out;
   p.cu_seqlens = cu_seqlens; p.chunk_offsets = chunk_offsets; p.nseq = nseq; p.H = heads;
+  p.tokens = tokens;
   return kda::launch_state_fwd(p, (cudaStream_t)stream);
 }
 

@@ -44,6 +44,9 @@ int kda_b200_version(void);
  * kda_stage_count() entries, indexed like kda_stage_name); reset != 0 clears the records.
  * No reference counterpart: the reference times stages with torch.profiler ranges
  * (attn_gym/linear/kda/utils.py:269-273). */
+/* 1 if a tensor-memory kernel abandoned a bounded barrier wait since the last call (clears the
+ * flag); synchronises the device.  For tests and debugging; no reference counterpart. */
+int kda_device_error_word(void);
 int kda_stage_count(void);
 const char* kda_stage_name(int stage);
 int kda_stage_timing_enable(int on);
