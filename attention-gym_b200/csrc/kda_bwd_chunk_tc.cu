@@ -1,0 +1,680 @@
+// Per-chunk backward of the chunked KDA path on tcgen05 tensor cores: one kernel replaces the
+// reference's WY/dqkg stage (bwd/cute/chunk_kda_bwd_wy_dqkg_fused.py:2623, oracle
+// attn_gym/testing/kda.py:144-240) and its intra-chunk stage (bwd/cute/chunk_kda_bwd_intra.py:931,
+// oracle attn_gym/testing/kda.py:67-141).
+//
+// Everything is computed transposed, with the channel (kappa or v) on the 128 tensor-memory lanes
+// and the 64 chunk rows on the columns, so every large product is a full-rate M = 128 UMMA and
+// every thread owns one channel: elementwise work is "thread = channel, loop over rows", the
+// per-channel reductions over rows are thread-local, and global stores are coalesced.
+//
+//   phase 0  TMA: h, dh, dO, v_new, dv2, v, k, q, A, G.
+//            UMMA: dq^T = h dO^T, dks^T = dh v_new^T, dw^T = -h dv2^T, dAqk = dO v_new^T
+//   phase 1  epilogue: dq, dk, dG partial sums in registers; dw^T and k 2^G as bf16 tiles; dAqk tile
+//            UMMA: dvb^T = dv2^T A, dkgb^T = dw^T A, X = dv2 v^T + dw (k 2^G)^T
+//   phase 2  epilogue: dv, dk, dG, dbeta terms; X tile
+//            UMMA: Y = A^T X;  dL = -Y A^T  (two short serial products)
+//   phase 3  gated operand tiles for the pairwise products (16-row gate rebasing, as in the
+//            forward), UMMAs with N = 16 per row block:
+//              dq_intra^T, X1^T [kappa][i in block ri] = Kn_ri^T {dAqk, dL}[i, j <= 16 ri + 15]
+//              dk2^T [kappa][j in block cj] = Qn_cj^T dAqk[i >= 16 cj, j] + Kn'_cj^T dL[i >= 16 cj, j]
+//   phase 4  epilogue: combine, last-row gate terms, ln 2, stores; dbeta by a warp butterfly.
+//
+// All barrier waits are bounded (error word + early exit instead of a hang).
+#include "kda_common.cuh"
+#include "kda_sm100.cuh"
+#include "kda_timing.cuh"
+
+namespace kda {
+
+using namespace sm100;
+
+struct BwdTcParams {
+  CUtensorMap tm_h, tm_dh, tm_do, tm_vn, tm_dv2, tm_v, tm_k, tm_q, tm_a, tm_g;
+  const float* beta;
+  bf16* dq; bf16* dk; bf16* dv; float* dg; float* db;
+  const int32_t* cu_seqlens; const int32_t* chunk_offsets;
+  int* error;
+  int nseq, H;
+  float scale;
+  long long* prof;
+};
+
+__device__ __forceinline__ void tc_mark(const BwdTcParams& p, int slot) {
+  if (p.prof && threadIdx.x == 0 && blockIdx.y == 0 && blockIdx.x < 64) {
+    long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    p.prof[blockIdx.x * 32 + slot] = t;
+  }
+}
+
+namespace bl {  // shared-memory layout (bytes)
+constexpr int HH = 0, DHH = 32768, DO = 65536, VN = 81920, DV2 = 98304, V = 114688, K = 131072,
+              Q = 147456, AK = 163840, G = 172032, MISC = 204800, TOTAL = 206848;
+// overlays (valid once their host tiles are dead)
+constexpr int DWT = HH, KGM = HH + 16384;                       // after phase 0
+constexpr int X = DHH, Y = DHH + 8192, DA = DHH + 16384, DL = DHH + 24576;
+constexpr int KN0 = DO;                                         // row-type tiles: 40960 bytes from DO
+constexpr int QN0 = HH, KP0 = HH + 16384;                       // column block 0 (64 rows)
+constexpr int QN1 = 106496, KP1 = 118784;                       // column block 1 (48 rows)
+constexpr int QN2 = DO, KP2 = DO + 8192;                        // column block 2 (32 rows), after R1
+constexpr int QN3 = DO + 16384, KP3 = DO + 20480;               // column block 3 (16 rows)
+}  // namespace bl
+namespace tc {  // tensor-memory columns
+constexpr int DQ = 0, DKS = 64, DW = 128, DVB = 192, DKG = 256, X = 320, Y = 384, DAQK = 448, DL = 448;
+}
+
+__device__ __forceinline__ float ld_bf(const unsigned char* tile, int box_bytes, int row, int col) {
+  return __bfloat162float(*reinterpret_cast<const bf16*>(tile + (col >> 6) * box_bytes + sw128(row, col & 63)));
+}
+__device__ __forceinline__ void st_bf(unsigned char* tile, int box_bytes, int row, int col, float x) {
+  *reinterpret_cast<bf16*>(tile + (col >> 6) * box_bytes + sw128(row, col & 63)) = __float2bfloat16(x);
+}
+// fp32 gate tile: 4 boxes of [64 rows x 32 floats], 128-byte swizzle
+__device__ __forceinline__ float ld_g(const unsigned char* g, int row, int c) {
+  return *reinterpret_cast<const float*>(g + (c >> 5) * 8192 + row * 128 +
+                                         (((((c & 31) >> 2) ^ (row & 7)) << 4) | ((c & 3) << 2)));
+}
+// 8 consecutive channels kappa0 .. kappa0+7 (kappa0 % 8 == 0) of one row
+__device__ __forceinline__ void ld_g8(const unsigned char* g, int row, int kappa0, float (&o)[8]) {
+  const unsigned char* base = g + (kappa0 >> 5) * 8192 + row * 128;
+  const int c = (kappa0 & 31) >> 2, sw = row & 7;
+  const float4 a = *reinterpret_cast<const float4*>(base + ((c ^ sw) << 4));
+  const float4 b = *reinterpret_cast<const float4*>(base + (((c + 1) ^ sw) << 4));
+  o[0] = a.x; o[1] = a.y; o[2] = a.z; o[3] = a.w; o[4] = b.x; o[5] = b.y; o[6] = b.z; o[7] = b.w;
+}
+__device__ __forceinline__ void ld_bf8(const unsigned char* tile, int box_bytes, int row, int c16,
+                                       float (&o)[8]) {
+  const uint4 u = *reinterpret_cast<const uint4*>(tile + (c16 >> 3) * box_bytes + sw128_chunk(row, c16 & 7));
+  const float2 a = unpack_bf16(u.x), b = unpack_bf16(u.y), c = unpack_bf16(u.z), d = unpack_bf16(u.w);
+  o[0] = a.x; o[1] = a.y; o[2] = b.x; o[3] = b.y; o[4] = c.x; o[5] = c.y; o[6] = d.x; o[7] = d.y;
+}
+__device__ __forceinline__ void st_bf8(unsigned char* tile, int box_bytes, int row, int c16,
+                                       const float (&x)[8]) {
+  uint4 u;
+  u.x = pack_bf16(x[0], x[1]); u.y = pack_bf16(x[2], x[3]);
+  u.z = pack_bf16(x[4], x[5]); u.w = pack_bf16(x[6], x[7]);
+  *reinterpret_cast<uint4*>(tile + (c16 >> 3) * box_bytes + sw128_chunk(row, c16 & 7)) = u;
+}
+__device__ __forceinline__ void pack8v(const float* x, uint4& o) {
+  o.x = pack_bf16(x[0], x[1]); o.y = pack_bf16(x[2], x[3]);
+  o.z = pack_bf16(x[4], x[5]); o.w = pack_bf16(x[6], x[7]);
+}
+
+// Sum pb[0..31] over the 32 lanes of the warp: afterwards lane l holds the total of entry l (in pb[0]).
+__device__ __forceinline__ float warp_transpose_reduce(float (&pb)[32], int lid) {
+#pragma unroll
+  for (int off = 16, n = 32; off >= 1; off >>= 1, n >>= 1) {
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      if (j < n / 2) {
+        const bool up = (lid & off) != 0;
+        const float send = up ? pb[j] : pb[j + n / 2];
+        const float keep = up ? pb[j + n / 2] : pb[j];
+        pb[j] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+      }
+    }
+  }
+  return pb[0];
+}
+
+// Sum pb[0..15] over the 32 lanes: afterwards lanes 2e and 2e+1 both hold the total of entry e.
+__device__ __forceinline__ float warp_transpose_reduce16(float (&pb)[16], int lid) {
+#pragma unroll
+  for (int off = 16, n = 16; off >= 2; off >>= 1, n >>= 1) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      if (j < n / 2) {
+        const bool up = (lid & off) != 0;
+        const float send = up ? pb[j] : pb[j + n / 2];
+        const float keep = up ? pb[j + n / 2] : pb[j];
+        pb[j] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+      }
+    }
+  }
+  return pb[0] + __shfl_xor_sync(0xffffffffu, pb[0], 1);
+}
+
+__global__ void __launch_bounds__(256, 1) kda_bwd_chunk_tc_kernel(const __grid_constant__ BwdTcParams p) {
+  extern __shared__ unsigned char smem_dyn[];
+  // 1024-byte alignment by offset, so the compiler still knows this is shared memory
+  unsigned char* sm = smem_dyn + ((1024u - (saddr(smem_dyn) & 1023u)) & 1023u);
+  uint64_t* bar = reinterpret_cast<uint64_t*>(sm + bl::MISC);    // [0] TMA, [1..6] UMMA groups
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm + bl::MISC + 64);
+  volatile int* s_abort = reinterpret_cast<volatile int*>(sm + bl::MISC + 72);
+  float* s_beta = reinterpret_cast<float*>(sm + bl::MISC + 128);          // [64]
+  float* s_db = s_beta + 64;                                              // [64]
+  float* s_hd = s_db + 64;                                                // [2][128]
+  float* s_kdk = s_hd + 256;                                              // [2][128]
+
+  const int tid = threadIdx.x, warp = tid >> 5, lid = tid & 31;
+  const int quad = warp & 3, hf = warp >> 2;
+  const int L = quad * 32 + lid;                 // channel owned by this thread (TMEM lane)
+  const int i0 = 32 * hf;                        // first of the 32 chunk rows it handles
+  const int head = blockIdx.y, H = p.H;
+  const ChunkWork cw = locate_chunk(p.cu_seqlens, p.chunk_offsets, p.nseq, blockIdx.x);
+  if (cw.valid == 0) return;
+  const int valid = cw.valid;
+
+  if (warp == 0) tmem_alloc(tmem_slot, 512);
+  if (tid == 0) {
+    for (int i = 0; i < 7; ++i) mbar_init(&bar[i], 1);
+    mbar_init_fence();
+    *s_abort = 0;
+  }
+  if (tid < 64) {
+    s_beta[tid] = tid < valid ? p.beta[(cw.token0 + tid) * H + head] : 0.f;
+    s_db[tid] = 0.f;
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  const uint32_t tl = tmem + ((uint32_t)(32 * quad) << 16);    // this warp's lane quadrant
+
+  if (tid == 0) {
+    const int y = (int)cw.token0, x = head * 128;
+    const int yh = (blockIdx.x * H + head) * 128;
+    mbar_expect_tx(&bar[0], 2 * 32768 + 6 * 16384 + 8192 + 32768);
+    for (int b = 0; b < 2; ++b) {
+      tma_load_2d(sm + bl::HH + b * 16384, &p.tm_h, 64 * b, yh, &bar[0]);
+      tma_load_2d(sm + bl::DHH + b * 16384, &p.tm_dh, 64 * b, yh, &bar[0]);
+      tma_load_2d(sm + bl::DO + b * 8192, &p.tm_do, x + 64 * b, y, &bar[0]);
+      tma_load_2d(sm + bl::VN + b * 8192, &p.tm_vn, x + 64 * b, y, &bar[0]);
+      tma_load_2d(sm + bl::DV2 + b * 8192, &p.tm_dv2, x + 64 * b, y, &bar[0]);
+      tma_load_2d(sm + bl::V + b * 8192, &p.tm_v, x + 64 * b, y, &bar[0]);
+      tma_load_2d(sm + bl::K + b * 8192, &p.tm_k, x + 64 * b, y, &bar[0]);
+      tma_load_2d(sm + bl::Q + b * 8192, &p.tm_q, x + 64 * b, y, &bar[0]);
+    }
+    tma_load_2d(sm + bl::AK, &p.tm_a, head * 64, y, &bar[0]);
+    for (int b = 0; b < 4; ++b) tma_load_2d(sm + bl::G + b * 8192, &p.tm_g, x + 32 * b, y, &bar[0]);
+  }
+  auto body = [&]() -> int {
+  tc_mark(p, 0);
+  if (!mbar_wait(&bar[0], 0)) *s_abort = 1;
+  tc_mark(p, 1);
+
+  // partial tail chunk: rows >= valid hold another sequence's tokens or unwritten memory.  Zero them
+  // in every token tile and repeat the last gate row, so no later step needs a row guard.
+  if (valid < 64) {
+    const int tiles[6] = {bl::DO, bl::VN, bl::DV2, bl::V, bl::K, bl::Q};
+    for (int idx = tid; idx < (64 - valid) * 16; idx += 256) {
+      const int r = valid + (idx >> 4), ch = idx & 15;
+#pragma unroll
+      for (int t = 0; t < 6; ++t)
+        *reinterpret_cast<uint4*>(sm + tiles[t] + (ch >> 3) * 8192 + sw128_chunk(r, ch & 7)) = make_uint4(0, 0, 0, 0);
+      if (ch < 8) *reinterpret_cast<uint4*>(sm + bl::AK + sw128_chunk(r, ch)) = make_uint4(0, 0, 0, 0);
+    }
+    for (int idx = tid; idx < (64 - valid) * 32; idx += 256) {
+      const int r = valid + (idx >> 5), ch = idx & 31;        // 32 chunks of 4 floats per row
+      const int off = (ch >> 3) * 8192, c = ch & 7;
+      *reinterpret_cast<float4*>(sm + bl::G + off + r * 128 + ((c ^ (r & 7)) << 4)) =
+          *reinterpret_cast<const float4*>(sm + bl::G + off + (valid - 1) * 128 + ((c ^ ((valid - 1) & 7)) << 4));
+    }
+    fence_async_smem();
+  }
+  __syncthreads();
+  if (*s_abort) return 2;
+
+  // ---- phase 0 UMMAs --------------------------------------------------------------------------
+  if (tid == 0) {
+    tc_fence_after();
+    const uint32_t hh = saddr(sm + bl::HH), dhh = saddr(sm + bl::DHH), dO = saddr(sm + bl::DO),
+                   vn = saddr(sm + bl::VN), dv2 = saddr(sm + bl::DV2);
+    const uint32_t i128 = instr_desc(128, 64, 0, 0), i128n = instr_desc(128, 64, 0, 0, 1),
+                   i64 = instr_desc(64, 64, 0, 0);
+#pragma unroll
+    for (int ks = 0; ks < 8; ++ks) {
+      umma(tmem + tc::DQ, desc_kmajor(hh, ks, 16384), desc_kmajor(dO, ks, 8192), i128, ks > 0);
+      umma(tmem + tc::DKS, desc_kmajor(dhh, ks, 16384), desc_kmajor(vn, ks, 8192), i128, ks > 0);
+      umma(tmem + tc::DW, desc_kmajor(hh, ks, 16384), desc_kmajor(dv2, ks, 8192), i128n, ks > 0);
+      umma(tmem + tc::DAQK, desc_kmajor(dO, ks, 8192), desc_kmajor(vn, ks, 8192), i64, ks > 0);
+    }
+    umma_commit(&bar[1]);
+  }
+  // meanwhile: hd[kappa] = sum_v h dh over this thread's v half
+  {
+    float s = 0.f;
+    const unsigned char* hb = sm + bl::HH + hf * 16384;
+    const unsigned char* db = sm + bl::DHH + hf * 16384;
+#pragma unroll
+    for (int ch = 0; ch < 8; ++ch) {
+      uint4 a = *reinterpret_cast<const uint4*>(hb + sw128_chunk(L, ch));
+      uint4 b = *reinterpret_cast<const uint4*>(db + sw128_chunk(L, ch));
+      float2 a0 = unpack_bf16(a.x), a1 = unpack_bf16(a.y), a2 = unpack_bf16(a.z), a3 = unpack_bf16(a.w);
+      float2 b0 = unpack_bf16(b.x), b1 = unpack_bf16(b.y), b2 = unpack_bf16(b.z), b3 = unpack_bf16(b.w);
+      s += a0.x * b0.x + a0.y * b0.y + a1.x * b1.x + a1.y * b1.y + a2.x * b2.x + a2.y * b2.y +
+           a3.x * b3.x + a3.y * b3.y;
+    }
+    s_hd[hf * 128 + L] = s;
+  }
+  const unsigned char* sG = sm + bl::G;
+  const float glast = ld_g(sG, valid - 1, L);
+  auto gfix = [&](int row) { return ld_g(sG, row, L); };
+
+  tc_mark(p, 2);
+  if (!mbar_wait(&bar[1], 0)) *s_abort = 1;
+  tc_fence_after();
+  __syncthreads();
+  tc_mark(p, 3);      // every thread is done with the raw h / dh tiles
+  if (*s_abort) return 3;
+
+  // ---- phase 1 epilogue: operand tiles for the next products; dq^T and dks^T stay in tensor memory
+  {
+    float a[32];
+    tmem_ld32(tl + tc::DW + i0, a);      // dw^T (already negated)
+#pragma unroll
+    for (int qd = 0; qd < 4; ++qd) {
+      uint4 v;
+      pack8v(a + 8 * qd, v);
+      *reinterpret_cast<uint4*>(sm + bl::DWT + sw128_chunk(L, 4 * hf + qd)) = v;
+    }
+    // k 2^G as a K-major tile [s][kappa]
+#pragma unroll 8
+    for (int ii = 0; ii < 32; ++ii) {
+      const int i = i0 + ii;
+      const float kv = ld_bf(sm + bl::K, 8192, i, L);
+      st_bf(sm + bl::KGM, 8192, i, L, kv * fexp2(gfix(i)));
+    }
+    // dAqk (M = 64 accumulator: row r lives on lane 32 (r / 16) + r % 16)
+    tmem_ld32(tl + tc::DAQK + i0, a);
+    if (lid < 16) {
+      const int r = quad * 16 + lid;
+      float y[32];
+#pragma unroll
+      for (int jj = 0; jj < 32; ++jj) {
+        const int j = i0 + jj;
+        y[jj] = (r >= j && r < valid) ? a[jj] * p.scale : 0.f;
+      }
+#pragma unroll
+      for (int qd = 0; qd < 4; ++qd) {
+        uint4 v;
+        pack8v(y + 8 * qd, v);
+        *reinterpret_cast<uint4*>(sm + bl::DA + sw128_chunk(r, 4 * hf + qd)) = v;
+      }
+    }
+  }
+  fence_async_smem();
+  tc_fence_before();
+  __syncthreads();
+
+  tc_mark(p, 4);
+  // ---- phase 1 UMMAs: dvb^T, dkgb^T, X -----------------------------------------------------------
+  if (tid == 0) {
+    tc_fence_after();
+    const uint32_t dv2 = saddr(sm + bl::DV2), ak = saddr(sm + bl::AK), dwt = saddr(sm + bl::DWT),
+                   v = saddr(sm + bl::V), kgm = saddr(sm + bl::KGM);
+#pragma unroll
+    for (int ks = 0; ks < 4; ++ks) {
+      umma(tmem + tc::DVB, desc_mnmajor(dv2, ks, 8192), desc_mnmajor(ak, ks, 0),
+           instr_desc(128, 64, 1, 1), ks > 0);
+      umma(tmem + tc::DKG, desc_kmajor(dwt, ks, 0), desc_mnmajor(ak, ks, 0),
+           instr_desc(128, 64, 0, 1), ks > 0);
+    }
+#pragma unroll
+    for (int ks = 0; ks < 8; ++ks)
+      umma(tmem + tc::X, desc_kmajor(dv2, ks, 8192), desc_kmajor(v, ks, 8192),
+           instr_desc(64, 64, 0, 0), ks > 0);
+#pragma unroll
+    for (int ks = 0; ks < 8; ++ks)
+      umma(tmem + tc::X, desc_mnmajor(dwt, ks, 0), desc_kmajor(kgm, ks, 8192),
+           instr_desc(64, 64, 1, 0), 1);
+    umma_commit(&bar[2]);
+  }
+  if (!mbar_wait(&bar[2], 0)) *s_abort = 1;
+  tc_fence_after();
+  tc_mark(p, 5);
+
+  // ---- phase 2 epilogue: dv and its dbeta term; X tile (dkgb^T stays in tensor memory) -------------
+  {
+    float a[32], pb[32];
+    tmem_ld32(tl + tc::DVB + i0, a);      // this thread = value channel v = L
+#pragma unroll
+    for (int ii = 0; ii < 32; ++ii) {
+      const int s = i0 + ii;
+      pb[ii] = 0.f;
+      if (s < valid) {
+        p.dv[((cw.token0 + s) * H + head) * 128 + L] = __float2bfloat16(a[ii] * s_beta[s]);
+        pb[ii] = a[ii] * ld_bf(sm + bl::V, 8192, s, L);
+      }
+    }
+    atomicAdd(&s_db[i0 + lid], warp_transpose_reduce(pb, lid));
+    tmem_ld32(tl + tc::X + i0, a);
+    if (lid < 16) {
+      const int t = quad * 16 + lid;
+      float y[32];
+#pragma unroll
+      for (int jj = 0; jj < 32; ++jj) {
+        const int s = i0 + jj;
+        y[jj] = (t > s && t < valid) ? a[jj] * s_beta[s] : 0.f;
+      }
+#pragma unroll
+      for (int qd = 0; qd < 4; ++qd) {
+        uint4 v;
+        pack8v(y + 8 * qd, v);
+        *reinterpret_cast<uint4*>(sm + bl::X + sw128_chunk(t, 4 * hf + qd)) = v;
+      }
+    }
+  }
+  fence_async_smem();
+  tc_fence_before();
+  __syncthreads();
+  if (*s_abort) return 4;
+
+  tc_mark(p, 6);
+  // ---- Y = A^T X ------------------------------------------------------------------------------------
+  if (tid == 0) {
+    tc_fence_after();
+    const uint32_t ak = saddr(sm + bl::AK), x = saddr(sm + bl::X);
+#pragma unroll
+    for (int ks = 0; ks < 4; ++ks)
+      umma(tmem + tc::Y, desc_mnmajor(ak, ks, 0), desc_mnmajor(x, ks, 0), instr_desc(64, 64, 1, 1), ks > 0);
+    umma_commit(&bar[3]);
+  }
+  // meanwhile: row-type gated tiles  Kn_ri[j][kappa] = k_j 2^{R_ri - G_j},  j < 16 (ri + 1)
+  {
+    int off = 0;
+#pragma unroll
+    for (int ri = 0; ri < 4; ++ri) {
+      const int rows = 16 * (ri + 1);
+      unsigned char* tile = sm + bl::KN0 + off;
+      for (int task = tid; task < rows * 16; task += 256) {
+        const int j = task >> 4, c16 = task & 15;
+        float kk[8], gj[8], rr[8];
+        ld_bf8(sm + bl::K, 8192, j, c16, kk);
+        ld_g8(sG, j, 8 * c16, gj);
+        ld_g8(sG, 16 * ri, 8 * c16, rr);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) kk[e] *= fexp2(fminf(rr[e] - gj[e], 126.f));
+        st_bf8(tile, rows * 128, j, c16, kk);
+      }
+      off += rows * 256;
+    }
+  }
+  tc_mark(p, 7);
+  if (!mbar_wait(&bar[3], 0)) *s_abort = 1;
+  tc_fence_after();
+  {
+    float a[32];
+    tmem_ld32(tl + tc::Y + i0, a);
+    if (lid < 16) {
+      const int r = quad * 16 + lid;
+#pragma unroll
+      for (int qd = 0; qd < 4; ++qd) {
+        uint4 v;
+        pack8v(a + 8 * qd, v);
+        *reinterpret_cast<uint4*>(sm + bl::Y + sw128_chunk(r, 4 * hf + qd)) = v;
+      }
+    }
+  }
+  fence_async_smem();
+  tc_fence_before();
+  __syncthreads();
+  if (*s_abort) return 5;
+
+  tc_mark(p, 8);
+  // ---- dL = -(Y A^T), and the dAqk half of the row-type products -------------------------------------
+  if (tid == 0) {
+    tc_fence_after();
+    const uint32_t ak = saddr(sm + bl::AK), y = saddr(sm + bl::Y), da = saddr(sm + bl::DA);
+#pragma unroll
+    for (int ks = 0; ks < 4; ++ks)
+      umma(tmem + tc::DL, desc_kmajor(y, ks, 0), desc_kmajor(ak, ks, 0), instr_desc(64, 64, 0, 0, 1), ks > 0);
+    umma_commit(&bar[4]);
+    int off = 0;
+#pragma unroll
+    for (int ri = 0; ri < 4; ++ri) {
+      const int rows = 16 * (ri + 1);
+      const uint32_t kn = saddr(sm + bl::KN0 + off);
+      for (int ks = 0; ks <= ri; ++ks)
+        umma(tmem + tc::DVB + 16 * ri, desc_mnmajor(kn, ks, rows * 128), desc_kmajor(da + 2048 * ri, ks, 0),
+             instr_desc(128, 16, 1, 0), ks > 0);
+      off += rows * 256;
+    }
+  }
+  // meanwhile: column-type gated tiles for blocks 0 and 1
+  auto build_col = [&](int cj, int qoff, int koff) {
+    const int rows = 64 - 16 * cj;
+    for (int task = tid; task < rows * 16; task += 256) {
+      const int r = task >> 4, c16 = task & 15, i = 16 * cj + r;
+      float qq[8], kk[8], gi[8], rr[8];
+      ld_bf8(sm + bl::Q, 8192, i, c16, qq);
+      ld_bf8(sm + bl::K, 8192, i, c16, kk);
+      ld_g8(sG, i, 8 * c16, gi);
+      ld_g8(sG, 16 * cj + 15, 8 * c16, rr);
+      const float b = s_beta[i];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const float ex = fexp2(fminf(gi[e] - rr[e], 126.f));
+        qq[e] *= ex;
+        kk[e] *= ex * b;
+      }
+      st_bf8(sm + qoff, rows * 128, r, c16, qq);
+      st_bf8(sm + koff, rows * 128, r, c16, kk);
+    }
+  };
+  build_col(0, bl::QN0, bl::KP0);
+  build_col(1, bl::QN1, bl::KP1);
+  tc_mark(p, 9);
+  if (!mbar_wait(&bar[4], 0)) *s_abort = 1;
+  tc_fence_after();
+  {
+    float a[32];
+    tmem_ld32(tl + tc::DL + i0, a);
+    if (lid < 16) {
+      const int r = quad * 16 + lid;
+      float y[32];
+#pragma unroll
+      for (int jj = 0; jj < 32; ++jj) y[jj] = (r > i0 + jj && r < valid) ? a[jj] : 0.f;
+#pragma unroll
+      for (int qd = 0; qd < 4; ++qd) {
+        uint4 v;
+        pack8v(y + 8 * qd, v);
+        *reinterpret_cast<uint4*>(sm + bl::DL + sw128_chunk(r, 4 * hf + qd)) = v;
+      }
+    }
+  }
+  fence_async_smem();
+  tc_fence_before();
+  __syncthreads();
+  if (*s_abort) return 6;
+
+  auto issue_col = [&](int cj, int qoff, int koff) {   // thread 0
+    const int rows = 64 - 16 * cj;
+    const uint32_t qn = saddr(sm + qoff), kp = saddr(sm + koff);
+    const uint32_t da = saddr(sm + bl::DA) + 2048 * cj + 32 * cj;
+    const uint32_t dl = saddr(sm + bl::DL) + 2048 * cj + 32 * cj;
+    const uint32_t id = instr_desc(128, 16, 1, 1);
+    for (int ks = 0; ks < 4 - cj; ++ks)
+      umma(tmem + tc::DW + 16 * cj, desc_mnmajor(qn, ks, rows * 128), smem_desc(da + ks * 2048, 0, 1024), id, ks > 0);
+    for (int ks = 0; ks < 4 - cj; ++ks)
+      umma(tmem + tc::DW + 16 * cj, desc_mnmajor(kp, ks, rows * 128), smem_desc(dl + ks * 2048, 0, 1024), id, 1);
+  };
+  if (tid == 0) {
+    tc_fence_after();
+    const uint32_t dl = saddr(sm + bl::DL);
+    int off = 0;
+#pragma unroll
+    for (int ri = 0; ri < 4; ++ri) {     // the dL half of the row-type products
+      const int rows = 16 * (ri + 1);
+      const uint32_t kn = saddr(sm + bl::KN0 + off);
+      for (int ks = 0; ks <= ri; ++ks)
+        umma(tmem + tc::X + 16 * ri, desc_mnmajor(kn, ks, rows * 128), desc_kmajor(dl + 2048 * ri, ks, 0),
+             instr_desc(128, 16, 1, 0), ks > 0);
+      off += rows * 256;
+    }
+    umma_commit(&bar[5]);
+    issue_col(0, bl::QN0, bl::KP0);
+    issue_col(1, bl::QN1, bl::KP1);
+  }
+  tc_mark(p, 10);
+  if (!mbar_wait(&bar[5], 0)) *s_abort = 1;   // row-type tiles are free again
+  tc_fence_after();
+  build_col(2, bl::QN2, bl::KP2);
+  build_col(3, bl::QN3, bl::KP3);
+  fence_async_smem();
+  tc_fence_before();
+  __syncthreads();
+  if (*s_abort) return 7;
+  if (tid == 0) {
+    tc_fence_after();
+    issue_col(2, bl::QN2, bl::KP2);
+    issue_col(3, bl::QN3, bl::KP3);
+    umma_commit(&bar[6]);
+  }
+  tc_mark(p, 11);
+  if (!mbar_wait(&bar[6], 0)) *s_abort = 1;
+  tc_fence_after();
+  tc_mark(p, 12);
+
+  // ---- final epilogue: six accumulators, 16 rows at a time; thread = channel L ------------------------
+  //   DQ: dq_inter^T   DVB: dq_intra^T   DKS: dks^T   DKG: dkgb^T   X: X1^T   DW: dk2^T
+  // pass 1: sum_i k dks (needed by the last row of dG) and everything that does not depend on it
+  {
+    float kdk = 0.f;
+#pragma unroll 1
+    for (int part = 0; part < 2; ++part) {
+      const int r0 = i0 + 16 * part;
+      float a[16];
+      tmem_ld16(tl + tc::DKS + r0, a);
+#pragma unroll
+      for (int ii = 0; ii < 16; ++ii) {
+        const int i = r0 + ii;
+        kdk += ld_bf(sm + bl::K, 8192, i, L) * a[ii] * fexp2(glast - gfix(i));
+      }
+    }
+    s_kdk[hf * 128 + L] = kdk;
+  }
+  __syncthreads();
+  {
+    const float hdv = (s_hd[L] + s_hd[128 + L]) * fexp2(glast) + s_kdk[L] + s_kdk[128 + L];
+#pragma unroll 1
+    for (int part = 0; part < 2; ++part) {
+      const int r0 = i0 + 16 * part;
+      float a[16], g[16], e[16], dkr[16], dgr[16], pb[16], kr[16];
+      const float gfirst = gfix(r0);                // r0 is the first row of its 16-row block
+#pragma unroll
+      for (int ii = 0; ii < 16; ++ii) {
+        g[ii] = gfix(r0 + ii);
+        e[ii] = fexp2(g[ii] - gfirst);              // row factor 2^{G_i - R_ri}
+        kr[ii] = ld_bf(sm + bl::K, 8192, r0 + ii, L);
+      }
+      // dq = scale 2^G dq_inter + e dq_intra ;  dG = q dq
+      tmem_ld16(tl + tc::DQ + r0, a);
+#pragma unroll
+      for (int ii = 0; ii < 16; ++ii) dkr[ii] = a[ii] * p.scale * fexp2(g[ii]);
+      tmem_ld16(tl + tc::DVB + r0, a);
+#pragma unroll
+      for (int ii = 0; ii < 16; ++ii) {
+        const int i = r0 + ii;
+        const float dqv = dkr[ii] + a[ii] * e[ii];
+        const float qv = ld_bf(sm + bl::Q, 8192, i, L);
+        dgr[ii] = qv * dqv;
+        if (i < valid) p.dq[((cw.token0 + i) * H + head) * 128 + L] = __float2bfloat16(dqv);
+      }
+      // dk = r dks + beta 2^G dkgb + beta e X1 + f dk2
+      tmem_ld16(tl + tc::DKS + r0, a);
+#pragma unroll
+      for (int ii = 0; ii < 16; ++ii) {
+        const int i = r0 + ii;
+        const float kv = kr[ii];
+        const float x = a[ii] * fexp2(glast - g[ii]);
+        dkr[ii] = x;
+        dgr[ii] -= kv * x;
+      }
+      tmem_ld16(tl + tc::DKG + r0, a);
+#pragma unroll
+      for (int ii = 0; ii < 16; ++ii) {
+        const int i = r0 + ii;
+        const float gam = fexp2(g[ii]);
+        const float kgm = (ld_bf(sm + bl::K, 8192, i, L)) * gam;   // k 2^G
+        const float b = s_beta[i];
+        dkr[ii] += b * gam * a[ii];
+        dgr[ii] += b * kgm * a[ii];
+        pb[ii] = a[ii] * kgm;
+      }
+      tmem_ld16(tl + tc::X + r0, a);
+#pragma unroll
+      for (int ii = 0; ii < 16; ++ii) {
+        const int i = r0 + ii;
+        const float kv = kr[ii];
+        const float xi = a[ii] * e[ii];
+        const float b = s_beta[i];
+        dkr[ii] += b * xi;
+        dgr[ii] += kv * b * xi;
+        pb[ii] += kv * xi;
+      }
+      {
+        const float tot = warp_transpose_reduce16(pb, lid);
+        if ((lid & 1) == 0) atomicAdd(&s_db[r0 + (lid >> 1)], tot);
+      }
+      tmem_ld16(tl + tc::DW + r0, a);
+      const float rlast = gfix(r0 + 15);            // column factor 2^{R'_cj - G_j}
+#pragma unroll
+      for (int ii = 0; ii < 16; ++ii) {
+        const int i = r0 + ii;
+        const float kv = kr[ii];
+        const float x = a[ii] * fexp2(rlast - g[ii]);
+        float gsum = dgr[ii] - kv * x;
+        if (i == valid - 1) gsum += hdv;
+        if (i < valid) {
+          const int64_t gi = ((cw.token0 + i) * H + head) * 128 + L;
+          p.dk[gi] = __float2bfloat16(dkr[ii] + x);
+          p.dg[gi] = gsum * kLn2;
+        }
+      }
+    }
+  }
+  tc_mark(p, 13);
+  __syncthreads();
+  if (tid < valid) p.db[(cw.token0 + tid) * H + head] = s_db[tid];
+  tc_mark(p, 14);
+  return 0;
+  };
+  const int rc = body();
+  if (rc && tid == 0 && p.error) atomicExch(p.error, rc);
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem_slot[0], 512);
+}
+
+static __device__ int g_bwd_tc_error = 0;
+
+int launch_bwd_chunk_tc(const bf16* q, const bf16* k, const bf16* v, const float* g, const float* beta,
+                        const bf16* akk, const bf16* h, const bf16* dh, const bf16* vnew,
+                        const bf16* dv2, const bf16* dout, bf16* dq, bf16* dk, bf16* dv, float* dg,
+                        float* db, const int32_t* cu, const int32_t* co, int nseq, int H,
+                        int64_t tokens, int chunks, long long* prof, cudaStream_t s) {
+  if (chunks == 0) return KDA_OK;
+  BwdTcParams p;
+  p.prof = prof;
+  const int64_t cols = (int64_t)H * 128, hrows = (int64_t)chunks * H * 128;
+  bool ok = make_tensor_map(&p.tm_h, h, hrows, 128, 128) && make_tensor_map(&p.tm_dh, dh, hrows, 128, 128) &&
+            make_tensor_map(&p.tm_do, dout, tokens, cols, 64) && make_tensor_map(&p.tm_vn, vnew, tokens, cols, 64) &&
+            make_tensor_map(&p.tm_dv2, dv2, tokens, cols, 64) && make_tensor_map(&p.tm_v, v, tokens, cols, 64) &&
+            make_tensor_map(&p.tm_k, k, tokens, cols, 64) && make_tensor_map(&p.tm_q, q, tokens, cols, 64) &&
+            make_tensor_map(&p.tm_a, akk, tokens, (int64_t)H * 64, 64) &&
+            make_tensor_map(&p.tm_g, g, tokens, cols, 64, true);
+  if (!ok) return KDA_ERR_LAUNCH;
+  p.beta = beta; p.dq = dq; p.dk = dk; p.dv = dv; p.dg = dg; p.db = db;
+  p.cu_seqlens = cu; p.chunk_offsets = co; p.nseq = nseq; p.H = H;
+  p.scale = 0.08838834764831845f;
+  if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p.error), g_bwd_tc_error) != cudaSuccess)
+    return KDA_ERR_LAUNCH;
+  const int smem = bl::TOTAL + 1024;
+  if (cudaFuncSetAttribute(kda_bwd_chunk_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
+      cudaSuccess)
+    return KDA_ERR_LAUNCH;
+  StageScope timing(kStageBwdWy, s);
+  kda_bwd_chunk_tc_kernel<<<dim3(chunks, H), 256, smem, s>>>(p);
+  return cudaGetLastError() == cudaSuccess ? KDA_OK : KDA_ERR_LAUNCH;
+}
+
+int bwd_chunk_tc_error_word() {
+  int v = 0, zero = 0;
+  if (cudaMemcpyFromSymbol(&v, g_bwd_tc_error, sizeof(int)) != cudaSuccess) return -1;
+  cudaMemcpyToSymbol(g_bwd_tc_error, &zero, sizeof(int));
+  return v;
+}
+
+}  // namespace kda

@@ -17,6 +17,7 @@
 // in the last stage.
 #include "kda_common.cuh"
 #include "kda_timing.cuh"
+#include <cstdlib>
 
 namespace kda {
 
@@ -38,7 +39,16 @@ struct BwdParams {
   const int32_t* cu_seqlens; const int32_t* chunk_offsets;
   int nseq, H;
   float scale;
+  long long* prof;   // optional per-phase timestamps (debugging aid), null in normal use
 };
+
+__device__ __forceinline__ void prof_mark(const BwdParams& p, int slot) {
+  if (p.prof && threadIdx.x == 0 && blockIdx.y == 0 && blockIdx.x < 64) {
+    long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    p.prof[blockIdx.x * 32 + slot] = t;
+  }
+}
 
 // ------------------------------------------------------------------------------------------
 // state_bwd
@@ -211,6 +221,7 @@ __global__ void __launch_bounds__(32 * NW) kda_bwd_wy_kernel(const BwdParams p) 
   const int64_t hbase = (((int64_t)blockIdx.x * H + head) * D) * D;
   const int g8 = lane >> 2, t2 = 2 * (lane & 3);
 
+  prof_mark(p, 0);
   load_tile_b16<D, D, LDD, THREADS>(sm.hh, p.h + hbase, D, D, tid);
   load_tile_b16<D, D, LDD, THREADS>(sm.dh, p.dh + hbase, D, D, tid);
   load_tile_b16<64, D, LDD, THREADS>(sm.dO, p.dout + rowD, gld, valid, tid);
@@ -228,6 +239,7 @@ __global__ void __launch_bounds__(32 * NW) kda_bwd_wy_kernel(const BwdParams p) 
   if (tid < D) sm.kdk[tid] = 0.f;
   cp_async_wait<0>();
   __syncthreads();
+  prof_mark(p, 1);
 
   // this thread's q and raw-k elements of its (mt, nh) accumulator tile, fetched before any global
   // store so the loads overlap instead of serialising behind possibly-aliasing stores
@@ -267,6 +279,7 @@ __global__ void __launch_bounds__(32 * NW) kda_bwd_wy_kernel(const BwdParams p) 
   }
   __syncthreads();
 
+  prof_mark(p, 2);
   const float* glast = sm.g + (valid - 1) * D;
   const int mt = warp & 3, nh = warp >> 2;
   float dgacc[NTN][4], dkacc[NTN][4];
@@ -290,6 +303,7 @@ __global__ void __launch_bounds__(32 * NW) kda_bwd_wy_kernel(const BwdParams p) 
       dgacc[nt][2 * hh] = qv.x * x0;
       dgacc[nt][2 * hh + 1] = qv.y * x1;
     }
+  prof_mark(p, 3);
   // ---- dk_s = (v_new dh^T) 2^{G_last - G} -----------------------------------------------------
   zero_acc<1, NTN>(acc);
   warp_gemm<1, NTN / 2, false, false>(acc, sm.vn, LDD, 16 * mt, 0, sm.dh, LDD, 0, CW * nh, 8, lane);
@@ -320,6 +334,7 @@ __global__ void __launch_bounds__(32 * NW) kda_bwd_wy_kernel(const BwdParams p) 
       atomicAdd(&sm.kdk[c + 1], cs1);
     }
   }
+  prof_mark(p, 4);
   // ---- dw = -(dv2 h^T) ------------------------------------------------------------------------
   zero_acc<1, NTN>(acc);
   warp_gemm<1, NTN / 2, false, false>(acc, sm.dv2, LDD, 16 * mt, 0, sm.hh, LDD, 0, CW * nh, 8, lane);
@@ -337,6 +352,7 @@ __global__ void __launch_bounds__(32 * NW) kda_bwd_wy_kernel(const BwdParams p) 
     }
   __syncthreads();
 
+  prof_mark(p, 5);
   // ---- dvb = A^T dv2 ; dv = beta dvb ; dbeta += <dvb, v> --------------------------------------
   zero_acc<1, NTN>(acc);
   warp_gemm<1, NTN / 2, true, true>(acc, sm.a, LD64, 16 * mt, 0, sm.dv2, LDD, 0, CW * nh, 4, lane);
@@ -357,6 +373,7 @@ __global__ void __launch_bounds__(32 * NW) kda_bwd_wy_kernel(const BwdParams p) 
     dbp += __shfl_xor_sync(0xffffffffu, dbp, 2);
     if ((lane & 3) == 0) atomicAdd(&sm.db[r], dbp);
   }
+  prof_mark(p, 6);
   // ---- dkgb = A^T dw ; dk += beta 2^G dkgb ; dG += beta k 2^G dkgb ; dbeta += <dkgb, k 2^G> ----
   zero_acc<1, NTN>(acc);
   warp_gemm<1, NTN / 2, true, true>(acc, sm.a, LD64, 16 * mt, 0, s_dw, LDD, 0, CW * nh, 4, lane);
@@ -389,6 +406,7 @@ __global__ void __launch_bounds__(32 * NW) kda_bwd_wy_kernel(const BwdParams p) 
     if ((lane & 3) == 0) atomicAdd(&sm.db[r], dbp);
   }
 
+  prof_mark(p, 7);
   // ---- X = stril(dv2 v^T + dw (k 2^G)^T) diag(beta) -------------------------------------------
   const int nq = warp >> 2;
   float acs[1][NTQ][4];
@@ -405,6 +423,7 @@ __global__ void __launch_bounds__(32 * NW) kda_bwd_wy_kernel(const BwdParams p) 
       *reinterpret_cast<uint32_t*>(&s_x[r * LD64 + c]) = pack_bf16(x0, x1);
     }
   __syncthreads();
+  prof_mark(p, 8);
   // ---- Y = A^T X ------------------------------------------------------------------------------
   zero_acc<1, NTQ>(acs);
   warp_gemm<1, NTQ / 2, true, true>(acs, sm.a, LD64, 16 * mt, 0, s_x, LD64, 0, CQ * nq, 4, lane);
@@ -417,6 +436,7 @@ __global__ void __launch_bounds__(32 * NW) kda_bwd_wy_kernel(const BwdParams p) 
           pack_bf16(acs[0][nt][2 * hh], acs[0][nt][2 * hh + 1]);
     }
   __syncthreads();
+  prof_mark(p, 9);
   // ---- dL = -stril(Y A^T) ---------------------------------------------------------------------
   zero_acc<1, NTQ>(acs);
   warp_gemm<1, NTQ / 2, false, false>(acs, s_y, LD64, 16 * mt, 0, sm.a, LD64, 0, CQ * nq, 4, lane);
@@ -430,6 +450,7 @@ __global__ void __launch_bounds__(32 * NW) kda_bwd_wy_kernel(const BwdParams p) 
             make_float2((r > c) ? -acs[0][nt][2 * hh] : 0.f,
                         (r > c + 1) ? -acs[0][nt][2 * hh + 1] : 0.f);
     }
+  prof_mark(p, 10);
   // ---- dAqk = scale tril(do v_new^T) ----------------------------------------------------------
   zero_acc<1, NTQ>(acs);
   warp_gemm<1, NTQ / 2, false, false>(acs, sm.dO, LDD, 16 * mt, 0, sm.vn, LDD, 0, CQ * nq, 8, lane);
@@ -444,6 +465,7 @@ __global__ void __launch_bounds__(32 * NW) kda_bwd_wy_kernel(const BwdParams p) 
                         (r >= c + 1) ? acs[0][nt][2 * hh + 1] * p.scale : 0.f);
     }
   if (tid < valid) p.db_p[(cw.token0 + tid) * H + head] = sm.db[tid];
+  prof_mark(p, 11);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -486,6 +508,7 @@ __global__ void __launch_bounds__(512) kda_bwd_intra_kernel(const BwdParams p) {
   bf16* kn = sm.kn[group];
   bf16* qn = sm.qn[group];
 
+  prof_mark(p, 16);
   load_tile_b16<64, D, LDD, 512>(sm.q, p.q + rowD, gld, valid, tid);
   load_tile_b16<64, D, LDD, 512>(sm.k, p.k + rowD, gld, valid, tid);
   load_tile_f32<64, D, D, 512>(sm.g, p.g + rowD, gld, valid, tid);
@@ -518,6 +541,7 @@ __global__ void __launch_bounds__(512) kda_bwd_intra_kernel(const BwdParams p) {
   }
 
   float dq[2][2][4], dk[2][2][4], dg[2][2][4];
+  prof_mark(p, 17);
 
   // ---- row phase: dq_i, dk_i, dbeta_i from sum_j (.)_ij 2^{G_i - G_j} k_j ----------------------
 #pragma unroll
@@ -565,6 +589,7 @@ __global__ void __launch_bounds__(512) kda_bwd_intra_kernel(const BwdParams p) {
     group_sync(group);
   }
 
+  prof_mark(p, 18);
   // ---- column phase: dk_j from sum_i (.)_ij 2^{G_i - G_j} {q_i, beta_i k_i} --------------------
 #pragma unroll
   for (int bi = 0; bi < 2; ++bi) {
@@ -604,6 +629,7 @@ __global__ void __launch_bounds__(512) kda_bwd_intra_kernel(const BwdParams p) {
     group_sync(group);
   }
 
+  prof_mark(p, 19);
   // ---- combine with the wy partials: all loads first, then the stores -------------------------
   float2 pa[2][2][2], pb[2][2][2], pc[2][2][2];
 #pragma unroll
@@ -645,7 +671,14 @@ __global__ void __launch_bounds__(512) kda_bwd_intra_kernel(const BwdParams p) {
     int64_t bi = (cw.token0 + tid) * H + head;
     p.db[bi] = p.db_p[bi] + sm.db[tid];
   }
+  prof_mark(p, 20);
 }
+
+int launch_bwd_chunk_tc(const bf16* q, const bf16* k, const bf16* v, const float* g, const float* beta,
+                        const bf16* akk, const bf16* h, const bf16* dh, const bf16* vnew,
+                        const bf16* dv2, const bf16* dout, bf16* dq, bf16* dk, bf16* dv, float* dg,
+                        float* db, const int32_t* cu, const int32_t* co, int nseq, int H,
+                        int64_t tokens, int chunks, long long* prof, cudaStream_t s);
 
 static int check_launch() { return cudaGetLastError() == cudaSuccess ? KDA_OK : KDA_ERR_LAUNCH; }
 template <typename Kern>
@@ -663,6 +696,14 @@ int launch_recompute(const void* q, const void* k, const void* v, const float* g
 }  // namespace kda
 
 using kda::bf16;
+
+static long long* g_prof_buffer = nullptr;
+// Debugging aid: device buffer of 64 x 32 int64 that receives per-phase timestamps of the first
+// 64 chunks of head 0 from the backward chunk kernels (NULL switches it off).
+extern "C" int kda_debug_set_profile_buffer(void* buffer) {
+  g_prof_buffer = reinterpret_cast<long long*>(buffer);
+  return KDA_OK;
+}
 
 extern "C" int64_t kda_chunk_bwd_workspace_bytes(int64_t tokens, int heads, int64_t num_chunks) {
   const int64_t nd = tokens * heads * 128;
@@ -715,6 +756,7 @@ extern "C" int kda_chunk_bwd(const void* q, const void* k, const void* v, const 
   p.dq = (bf16*)dq; p.dk = (bf16*)dk; p.dv = (bf16*)dv; p.dg = dg; p.db = dbeta;
   p.cu_seqlens = cu_seqlens; p.chunk_offsets = chunk_offsets; p.nseq = nseq; p.H = heads;
   p.scale = 0.08838834764831845f;
+  p.prof = g_prof_buffer;
 
   if (kda::set_smem(kda::kda_state_bwd_kernel, sizeof(kda::BStateSmem))) return KDA_ERR_LAUNCH;
   {
@@ -723,6 +765,12 @@ extern "C" int kda_chunk_bwd(const void* q, const void* k, const void* v, const 
   }
   if ((rc = kda::check_launch())) return rc;
   if (num_chunks == 0) return KDA_OK;
+  if (const char* e = getenv("KDA_BWD_TC")) {
+    if (e[0] == '1')
+      return kda::launch_bwd_chunk_tc(p.q, p.k, p.v, p.g, p.beta, p.akk, p.h, p.dh, p.vnew, p.dv2,
+                                      p.dout, p.dq, p.dk, p.dv, p.dg, p.db, cu_seqlens, chunk_offsets,
+                                      nseq, heads, tokens, num_chunks, g_prof_buffer, s);
+  }
   if (kda::set_smem(kda::kda_bwd_wy_kernel<16>, sizeof(kda::WySmem))) return KDA_ERR_LAUNCH;
   {
     kda::StageScope timing(kda::kStageBwdWy, s);

@@ -50,8 +50,8 @@ __device__ __forceinline__ void pack8(const float* x, uint4& o) {
 
 __global__ void __launch_bounds__(128) kda_state_fwd_tc_kernel(const __grid_constant__ StateTcParams p) {
   extern __shared__ unsigned char smem_dyn[];
-  unsigned char* smem = reinterpret_cast<unsigned char*>(
-      (reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~(uintptr_t)1023);
+  // 1024-byte alignment by offset, so the compiler still knows this is shared memory
+  unsigned char* smem = smem_dyn + ((1024u - (saddr(smem_dyn) & 1023u)) & 1023u);
   uint64_t* bar_full = reinterpret_cast<uint64_t*>(smem + StateTcLayout::BAR);        // [2]
   uint64_t* bar_mma1 = bar_full + 2;
   uint64_t* bar_mma2 = bar_full + 3;
@@ -286,36 +286,6 @@ __global__ void __launch_bounds__(128) kda_state_fwd_tc_kernel(const __grid_cons
 static __device__ int g_state_tc_error = 0;
 
 // ---- host side: tensor maps --------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
-                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
-                                  CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  if (!fn) {
-    void* ptr = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(ptr);
-  }
-  return fn;
-}
-
-// [rows x cols] bf16 row-major tensor, boxes of [64 rows x 64 cols], 128-byte swizzle
-static bool make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols) {
-  EncodeTiledFn fn = encode_fn();
-  if (!fn) return false;
-  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
-  cuuint32_t box[2] = {64, 64};
-  cuuint32_t estr[2] = {1, 1};
-  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
-            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
-
 int launch_state_fwd_tc(const bf16* w, const bf16* u, const bf16* kg, const bf16* qg, const bf16* aqk,
                         const float* g, const float* h0, float* ht, bf16* o, bf16* h_out,
                         bf16* vnew_out, const int32_t* cu, const int32_t* co, int nseq, int H,
@@ -326,9 +296,10 @@ int launch_state_fwd_tc(const bf16* w, const bf16* u, const bf16* kg, const bf16
   if (cudaGetSymbolAddress(reinterpret_cast<void**>(&error), g_state_tc_error) != cudaSuccess)
     return KDA_ERR_LAUNCH;
   const int64_t cols = (int64_t)H * D;
-  if (!make_map(&p.tm_w, w, tokens, cols) || !make_map(&p.tm_kg, kg, tokens, cols) ||
-      !make_map(&p.tm_qg, qg, tokens, cols) || !make_map(&p.tm_u, u ? u : w, tokens, cols) ||
-      !make_map(&p.tm_aqk, aqk, tokens, (int64_t)H * 64))
+  if (!make_tensor_map(&p.tm_w, w, tokens, cols, 64) || !make_tensor_map(&p.tm_kg, kg, tokens, cols, 64) ||
+      !make_tensor_map(&p.tm_qg, qg, tokens, cols, 64) ||
+      !make_tensor_map(&p.tm_u, u ? u : w, tokens, cols, 64) ||
+      !make_tensor_map(&p.tm_aqk, aqk, tokens, (int64_t)H * 64, 64))
     return KDA_ERR_LAUNCH;
   p.g = g; p.h0 = h0; p.ht = ht; p.o = o; p.h_out = h_out; p.vnew_out = vnew_out;
   p.cu_seqlens = cu; p.chunk_offsets = co; p.error = error; p.nseq = nseq; p.H = H;
@@ -346,9 +317,11 @@ int launch_state_fwd_tc(const bf16* w, const bf16* u, const bf16* kg, const bf16
 
 // 1 if a tensor-memory kernel gave up on a barrier wait since the last call (clears the flag).
 // Synchronises the device; meant for tests and debugging.
+namespace kda { int bwd_chunk_tc_error_word(); }
+
 extern "C" int kda_device_error_word(void) {
   int v = 0, zero = 0;
   if (cudaMemcpyFromSymbol(&v, kda::g_state_tc_error, sizeof(int)) != cudaSuccess) return -1;
   cudaMemcpyToSymbol(kda::g_state_tc_error, &zero, sizeof(int));
-  return v;
+  return v | (kda::bwd_chunk_tc_error_word() << 8);
 }

@@ -21,6 +21,7 @@ SOURCES = [
     "kda_chunk_fwd.cu",
     "kda_state_tc.cu",
     "kda_chunk_bwd.cu",
+    "kda_bwd_chunk_tc.cu",
     "kda_cp.cu",
 ]
 NVCC_FLAGS = [

@@ -47,6 +47,9 @@ int kda_b200_version(void);
 /* 1 if a tensor-memory kernel abandoned a bounded barrier wait since the last call (clears the
  * flag); synchronises the device.  For tests and debugging; no reference counterpart. */
 int kda_device_error_word(void);
+/* Debugging aid: a device buffer of 64 x 32 int64 that receives per-phase %globaltimer stamps from
+ * the backward chunk kernels (first 64 chunks of head 0); NULL switches it off. */
+int kda_debug_set_profile_buffer(void* buffer);
 int kda_stage_count(void);
 const char* kda_stage_name(int stage);
 int kda_stage_timing_enable(int on);
