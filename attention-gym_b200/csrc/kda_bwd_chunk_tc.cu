@@ -665,7 +665,7 @@ int launch_bwd_chunk_tc(const bf16* q, const bf16* k, const bf16* v, const float
   if (cudaFuncSetAttribute(kda_bwd_chunk_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
       cudaSuccess)
     return KDA_ERR_LAUNCH;
-  StageScope timing(kStageBwdWy, s);
+  StageScope timing(kStageBwdChunk, s);
   kda_bwd_chunk_tc_kernel<<<dim3(chunks, H), 256, smem, s>>>(p);
   return cudaGetLastError() == cudaSuccess ? KDA_OK : KDA_ERR_LAUNCH;
 }

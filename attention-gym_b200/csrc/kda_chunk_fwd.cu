@@ -1,6 +1,6 @@
 // Chunked KDA forward for K = V = 128, chunk = 64, bf16 operands, fp32 state and accumulation.
 //
-// Three kernels replace the reference's seven forward launches
+// Three kernels (two here, the state walk in kda_state_tc.cu) replace the reference's seven forward launches
 // (attn_gym/linear/kda/fwd/cute/chunk_kda_fwd.py:79-131):
 //
 //  intra_solve  per (chunk, head): the gated pairwise products and the WY solve
@@ -9,10 +9,9 @@
 //                fwd/cute/chunk_kda_k3b_offdiag_cutedsl.py:177, fwd/cute/chunk_kda_k4b_inverse_cutedsl.py:188)
 //  wu           per (chunk, head): w = A (beta k 2^G), u = A (beta v), kg = k 2^{G_last-G},
 //               qg = scale q 2^G   (reference: fwd/triton/recompute_w_u.py:257); reused by backward
-//  state_fwd    per (sequence, head, V half), serial over chunks with the fp32 state in registers:
-//               v_new = u - w h;  o = qg h + Aqk v_new;  h <- diag(2^{G_last}) h + kg^T v_new
-//               (fuses reference fwd/triton/chunk_delta_h.py:40-162 and fwd/triton/chunk_gla_fwd_o.py:202-226,
-//                so the per-chunk state never goes to HBM in the forward pass)
+//  state_fwd    per (sequence, head), serial over chunks with the fp32 state in tensor memory
+//               (kda_state_tc.cu): v_new = u - w h;  o = qg h + Aqk v_new;
+//               h <- diag(2^{G_last}) h + kg^T v_new
 //
 // Gate rebasing: 2^{G_i - G_j} is split as 2^{G_i - R} * 2^{R - G_j} with R the gate of the first
 // row of the 16-row block that holds i, so the row factor is <= 1 and the column factor is <= 1
@@ -20,7 +19,6 @@
 // the same exponent budget as the reference (fwd/triton/gate_fwd.py:619-631).
 #include "kda_common.cuh"
 #include "kda_timing.cuh"
-#include <cstdlib>
 
 namespace kda {
 
@@ -273,156 +271,6 @@ __global__ void __launch_bounds__(256) kda_wu_kernel(const ChunkParams p) {
   store_tile_b16<64, D, LDD, 256>(p.u + rowD, gld, sm.v, valid, tid);
 }
 
-// ------------------------------------------------------------------------------------------
-// state_fwd: serial over the chunks of one sequence; one CTA per (sequence, head, V half)
-// ------------------------------------------------------------------------------------------
-struct StateStage {
-  bf16 w[64 * LDD];
-  bf16 qg[64 * LDD];
-  bf16 kg[64 * LDD];
-  bf16 u[64 * LD64];
-  bf16 aqk[64 * LD64];
-  float dec[D];
-};
-struct StateSmem {
-  StateStage st[2];
-  bf16 h[D * LD64];
-  bf16 vn[64 * LD64];
-};
-
-__device__ __forceinline__ void state_load_stage(StateStage& s, const ChunkParams& p, int64_t token0,
-                                                 int valid, int head, int vh, int tid) {
-  const int H = p.H;
-  const int64_t rowD = (token0 * H + head) * D;
-  const int64_t gld = (int64_t)H * D;
-  load_tile_b16<64, D, LDD, 256>(s.w, p.w + rowD, gld, valid, tid);
-  load_tile_b16<64, D, LDD, 256>(s.kg, p.kg + rowD, gld, valid, tid);
-  load_tile_b16<64, 64, LD64, 256>(s.u, p.u ? p.u + rowD + 64 * vh : p.w, gld, p.u ? valid : 0,
-                                   tid);
-  if (p.o) {  // the output terms need qg and Aqk; the recompute / transition passes do not
-    load_tile_b16<64, D, LDD, 256>(s.qg, p.qg + rowD, gld, valid, tid);
-    load_tile_b16<64, 64, LD64, 256>(s.aqk, p.aqk + (token0 * H + head) * 64, (int64_t)H * 64,
-                                     valid, tid);
-  }
-  if (tid < D / 4)
-    cp_async16(s.dec + tid * 4, p.g + rowD + (int64_t)(valid - 1) * gld + tid * 4, true);
-}
-
-__global__ void __launch_bounds__(256) kda_state_fwd_kernel(const ChunkParams p) {
-  extern __shared__ __align__(16) unsigned char smem_raw[];
-  StateSmem& sm = *reinterpret_cast<StateSmem*>(smem_raw);
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int H = p.H;
-  const int vh = blockIdx.x & 1;
-  const int head = (blockIdx.x >> 1) % H;
-  const int seq = (blockIdx.x >> 1) / H;
-  const int64_t bos = p.cu_seqlens[seq], eos = p.cu_seqlens[seq + 1];
-  const int chunk0 = p.chunk_offsets[seq];
-  const int nchunks = p.chunk_offsets[seq + 1] - chunk0;
-  const int g8 = lane >> 2, t2 = 2 * (lane & 3);
-
-  // state rows 16*warp + {g8, g8+8}, columns 64*vh + 8*nt + t2 + {0,1}
-  float h[1][8][4];
-  const int64_t sbase = ((int64_t)seq * H + head) * D * D + 64 * vh;
-#pragma unroll
-  for (int nt = 0; nt < 8; ++nt)
-#pragma unroll
-    for (int hh = 0; hh < 2; ++hh) {
-      int r = 16 * warp + g8 + 8 * hh, c = 8 * nt + t2;
-      float2 x = make_float2(0.f, 0.f);
-      if (p.h0) x = *reinterpret_cast<const float2*>(p.h0 + sbase + (int64_t)r * D + c);
-      h[0][nt][2 * hh] = x.x;
-      h[0][nt][2 * hh + 1] = x.y;
-    }
-
-  auto chunk_valid = [&](int c) {
-    int64_t rem = eos - (bos + (int64_t)c * 64);
-    return rem >= 64 ? 64 : (int)rem;
-  };
-  if (nchunks > 0) state_load_stage(sm.st[0], p, bos, chunk_valid(0), head, vh, tid);
-  cp_async_commit();
-  if (nchunks > 1) state_load_stage(sm.st[1], p, bos + 64, chunk_valid(1), head, vh, tid);
-  cp_async_commit();
-
-  const int mt = warp & 3, nq = warp >> 2;
-  for (int c = 0; c < nchunks; ++c) {
-    StateStage& st = sm.st[c & 1];
-    const int64_t token0 = bos + (int64_t)c * 64;
-    const int valid = chunk_valid(c);
-    cp_async_wait<1>();
-    __syncthreads();
-#pragma unroll
-    for (int nt = 0; nt < 8; ++nt)
-#pragma unroll
-      for (int hh = 0; hh < 2; ++hh)
-        *reinterpret_cast<uint32_t*>(&sm.h[(16 * warp + g8 + 8 * hh) * LD64 + 8 * nt + t2]) =
-            pack_bf16(h[0][nt][2 * hh], h[0][nt][2 * hh + 1]);
-    __syncthreads();
-    if (p.h_out)
-      store_tile_b16<D, 64, LD64, 256>(
-          p.h_out + (((int64_t)(chunk0 + c) * H + head) * D) * D + 64 * vh, D, sm.h, D, tid);
-
-    float accv[1][4][4], acco[1][4][4];
-    zero_acc<1, 4>(accv);
-    zero_acc<1, 4>(acco);
-    warp_gemm<1, 2, false, true>(accv, st.w, LDD, 16 * mt, 0, sm.h, LD64, 0, 32 * nq, 8, lane);
-    if (p.o)
-      warp_gemm<1, 2, false, true>(acco, st.qg, LDD, 16 * mt, 0, sm.h, LD64, 0, 32 * nq, 8, lane);
-#pragma unroll
-    for (int nt = 0; nt < 4; ++nt)
-#pragma unroll
-      for (int hh = 0; hh < 2; ++hh) {
-        int r = 16 * mt + g8 + 8 * hh, cc = 32 * nq + 8 * nt + t2;
-        float2 uu = unpack_bf16(*reinterpret_cast<uint32_t*>(&st.u[r * LD64 + cc]));
-        *reinterpret_cast<uint32_t*>(&sm.vn[r * LD64 + cc]) =
-            pack_bf16(uu.x - accv[0][nt][2 * hh], uu.y - accv[0][nt][2 * hh + 1]);
-      }
-    __syncthreads();
-    if (p.vnew_out)
-      store_tile_b16<64, 64, LD64, 256>(p.vnew_out + (token0 * H + head) * D + 64 * vh,
-                                        (int64_t)H * D, sm.vn, valid, tid);
-    if (p.o)
-      warp_gemm<1, 2, false, true>(acco, st.aqk, LD64, 16 * mt, 0, sm.vn, LD64, 0, 32 * nq, 4, lane);
-    {
-      float d0 = fexp2(st.dec[16 * warp + g8]), d1 = fexp2(st.dec[16 * warp + g8 + 8]);
-#pragma unroll
-      for (int nt = 0; nt < 8; ++nt) {
-        h[0][nt][0] *= d0; h[0][nt][1] *= d0; h[0][nt][2] *= d1; h[0][nt][3] *= d1;
-      }
-    }
-    warp_gemm<1, 4, true, true>(h, st.kg, LDD, 16 * warp, 0, sm.vn, LD64, 0, 0, 4, lane);
-    if (p.o) {
-#pragma unroll
-      for (int nt = 0; nt < 4; ++nt)
-#pragma unroll
-        for (int hh = 0; hh < 2; ++hh) {
-          int r = 16 * mt + g8 + 8 * hh, cc = 32 * nq + 8 * nt + t2;
-          *reinterpret_cast<uint32_t*>(&st.u[r * LD64 + cc]) =
-              pack_bf16(acco[0][nt][2 * hh], acco[0][nt][2 * hh + 1]);
-        }
-    }
-    __syncthreads();
-    if (p.o)
-      store_tile_b16<64, 64, LD64, 256>(p.o + (token0 * H + head) * D + 64 * vh, (int64_t)H * D,
-                                        st.u, valid, tid);
-    __syncthreads();
-    if (c + 2 < nchunks)
-      state_load_stage(st, p, token0 + 128, chunk_valid(c + 2), head, vh, tid);
-    cp_async_commit();
-  }
-  cp_async_wait<0>();
-  if (p.ht) {
-#pragma unroll
-    for (int nt = 0; nt < 8; ++nt)
-#pragma unroll
-      for (int hh = 0; hh < 2; ++hh) {
-        int r = 16 * warp + g8 + 8 * hh, c = 8 * nt + t2;
-        *reinterpret_cast<float2*>(p.ht + sbase + (int64_t)r * D + c) =
-            make_float2(h[0][nt][2 * hh], h[0][nt][2 * hh + 1]);
-      }
-  }
-}
-
 static int check_launch() { return cudaGetLastError() == cudaSuccess ? KDA_OK : KDA_ERR_LAUNCH; }
 
 template <typename Kern>
@@ -446,16 +294,8 @@ int launch_wu(const ChunkParams& p, int chunks, cudaStream_t s) {
   return check_launch();
 }
 int launch_state_fwd(const ChunkParams& p, cudaStream_t s) {
-  if (p.nseq == 0) return KDA_OK;
-  if (const char* e = getenv("KDA_STATE_TC")) {
-    if (e[0] == '1')
-      return launch_state_fwd_tc(p.w, p.u, p.kg, p.qg, p.aqk, p.g, p.h0, p.ht, p.o, p.h_out,
-                                 p.vnew_out, p.cu_seqlens, p.chunk_offsets, p.nseq, p.H, p.tokens, s);
-  }
-  if (set_smem(kda_state_fwd_kernel, sizeof(StateSmem))) return KDA_ERR_LAUNCH;
-  StageScope timing(kStageStateFwd, s);
-  kda_state_fwd_kernel<<<(unsigned)(p.nseq * p.H * 2), 256, sizeof(StateSmem), s>>>(p);
-  return check_launch();
+  return launch_state_fwd_tc(p.w, p.u, p.kg, p.qg, p.aqk, p.g, p.h0, p.ht, p.o, p.h_out, p.vnew_out,
+                             p.cu_seqlens, p.chunk_offsets, p.nseq, p.H, p.tokens, s);
 }
 
 // Backward's recompute leg: w, u, kg, qg from the stored A, then the chunk-entry states h[c]

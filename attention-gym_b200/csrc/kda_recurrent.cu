@@ -11,7 +11,6 @@
 // The decode step is pure state streaming: 2*K*V*4 bytes per (sequence, head) per step.
 #include "kda_common.cuh"
 #include "kda_timing.cuh"
-#include <cstdlib>
 
 namespace kda {
 
@@ -223,18 +222,6 @@ extern "C" int kda_recurrent_fwd(const void* q, const void* k, const void* v, co
   bool vec4 = (value_dim % 4 == 0) && (slot_stride % 4 == 0) &&
               ((int64_t)nseq * heads * ((value_dim + 127) / 128) >= 296 || value_dim > 1024);
   int kr = (key_dim + 7) / 8;
-  if (const char* mode = getenv("KDA_SCAN_MODE")) {  // tuning hook for the K <= 128 decode shapes
-    if (kr <= 16 && value_dim % 4 == 0 && slot_stride % 4 == 0) {
-      switch (atoi(mode)) {
-        case 0: return launch_scan<16, 4, 1>(p, s);
-        case 1: return launch_scan<16, 4, 2>(p, s);
-        case 2: return launch_scan<16, 2, 2>(p, s);
-        case 3: return launch_scan<16, 2, 3>(p, s);
-        case 4: return launch_scan<16, 1, 4>(p, s);
-        default: break;
-      }
-    }
-  }
   if (vec4) {
     if (kr <= 4) return launch_scan<4, 4>(p, s);
     if (kr <= 8) return launch_scan<8, 4>(p, s);

@@ -313,6 +313,256 @@ int launch_state_fwd_tc(const bf16* w, const bf16* u, const bf16* kg, const bf16
   return cudaGetLastError() == cudaSuccess ? KDA_OK : KDA_ERR_LAUNCH;
 }
 
+
+// ------------------------------------------------------------------------------------------------
+// Reverse state-gradient recurrence on tcgen05:
+//   dv2 = kg dh + Aqk^T dO ;  dh <- diag(2^{G_last}) dh + qg^T dO - w^T dv2 ;  dh0 at the end.
+// Same structure as the forward walk: dh [128 x 128] fp32 lives in tensor memory, one CTA per
+// (sequence, head), chunks in reverse order, TMA two-stage ring.  Replaces the reference's
+// bwd/triton/chunk_kda_bwd_dav.py:73-93 + bwd/cute/chunk_delta_h_bwd_v1.py:1147-1276.
+// ------------------------------------------------------------------------------------------------
+struct StateBwdTcParams {
+  CUtensorMap tm_w, tm_qg, tm_kg, tm_do, tm_aqk;
+  const float* g; const float* dht; float* dh0;
+  bf16* dh_out; bf16* dv2_out;
+  const int32_t* cu_seqlens; const int32_t* chunk_offsets;
+  int* error;
+  int nseq, H;
+};
+
+constexpr int kBStageBytes = 4 * 16384 + 8192;   // KG, W, QG, DO, AQK
+struct StateBwdLayout {
+  static constexpr int KG = 0, W = 16384, QG = 32768, DO = 49152, AQK = 65536;
+  static constexpr int DH = 2 * kBStageBytes;            // 147456
+  static constexpr int DV2 = DH + 32768;                 // 180224
+  static constexpr int BAR = DV2 + 16384;                // 196608
+  static constexpr int TOTAL = BAR + 1024;
+};
+
+__global__ void __launch_bounds__(128) kda_state_bwd_tc_kernel(const __grid_constant__ StateBwdTcParams p) {
+  extern __shared__ unsigned char smem_dyn[];
+  unsigned char* smem = smem_dyn + ((1024u - (saddr(smem_dyn) & 1023u)) & 1023u);
+  uint64_t* bar_full = reinterpret_cast<uint64_t*>(smem + StateBwdLayout::BAR);
+  uint64_t* bar_mma1 = bar_full + 2;
+  uint64_t* bar_mma2 = bar_full + 3;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_full + 4);
+  volatile int* s_abort = reinterpret_cast<volatile int*>(bar_full + 5);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lid = tid & 31;
+  const int H = p.H;
+  const int head = blockIdx.x % H, seq = blockIdx.x / H;
+  const int64_t bos = p.cu_seqlens[seq], eos = p.cu_seqlens[seq + 1];
+  const int chunk0 = p.chunk_offsets[seq];
+  const int nchunks = p.chunk_offsets[seq + 1] - chunk0;
+  const int64_t sbase = ((int64_t)seq * H + head) * D * D;
+
+  if (warp == 0) tmem_alloc(tmem_slot, 256);
+  if (tid == 0) {
+    mbar_init(&bar_full[0], 1); mbar_init(&bar_full[1], 1);
+    mbar_init(bar_mma1, 1); mbar_init(bar_mma2, 1);
+    mbar_init_fence();
+    *s_abort = 0;
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  const uint32_t lane_off = (uint32_t)(32 * warp) << 16;
+  const uint32_t tDh = tmem + lane_off, tDv = tmem + 128 + lane_off;
+
+  auto chunk_valid = [&](int c) {
+    int64_t rem = eos - (bos + (int64_t)c * 64);
+    return rem >= 64 ? 64 : (int)rem;
+  };
+  auto issue_stage = [&](int it) {   // thread 0 only; iteration `it` handles chunk nchunks-1-it
+    const int c = nchunks - 1 - it;
+    unsigned char* st = smem + (it & 1) * kBStageBytes;
+    uint64_t* bar = &bar_full[it & 1];
+    const int y = (int)(bos + (int64_t)c * 64);
+    const int x = head * D;
+    mbar_expect_tx(bar, kBStageBytes);
+    for (int b = 0; b < 2; ++b) {
+      tma_load_2d(st + StateBwdLayout::KG + b * 8192, &p.tm_kg, x + 64 * b, y, bar);
+      tma_load_2d(st + StateBwdLayout::W + b * 8192, &p.tm_w, x + 64 * b, y, bar);
+      tma_load_2d(st + StateBwdLayout::QG + b * 8192, &p.tm_qg, x + 64 * b, y, bar);
+      tma_load_2d(st + StateBwdLayout::DO + b * 8192, &p.tm_do, x + 64 * b, y, bar);
+    }
+    tma_load_2d(st + StateBwdLayout::AQK, &p.tm_aqk, head * 64, y, bar);
+  };
+  if (tid == 0) {
+    if (nchunks > 0) issue_stage(0);
+    if (nchunks > 1) issue_stage(1);
+  }
+  {
+    float x[32];
+#pragma unroll 1
+    for (int cb = 0; cb < 4; ++cb) {
+#pragma unroll
+      for (int i = 0; i < 32; i += 4) {
+        float4 v4 = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (p.dht) v4 = *reinterpret_cast<const float4*>(p.dht + sbase + (int64_t)tid * D + 32 * cb + i);
+        x[i] = v4.x; x[i + 1] = v4.y; x[i + 2] = v4.z; x[i + 3] = v4.w;
+      }
+      tmem_st32(tDh + 32 * cb, x);
+    }
+    tmem_st_wait();
+  }
+  const uint32_t sDH = saddr(smem + StateBwdLayout::DH), sDV2 = saddr(smem + StateBwdLayout::DV2);
+  bool failed = false;
+
+  float glast = 0.f;
+  if (nchunks > 0)
+    glast = p.g[((bos + (int64_t)(nchunks - 1) * 64 + chunk_valid(nchunks - 1) - 1) * H + head) * D + tid];
+
+  for (int it = 0; it < nchunks; ++it) {
+    const int c = nchunks - 1 - it;
+    unsigned char* st = smem + (it & 1) * kBStageBytes;
+    const int64_t token0 = bos + (int64_t)c * 64;
+    const int valid = chunk_valid(c);
+    const float dec = exp2f(glast);
+    if (c > 0) glast = p.g[((token0 - 1) * H + head) * D + tid];   // last row of the previous chunk
+
+    if (!mbar_wait(&bar_full[it & 1], (it >> 1) & 1)) *s_abort = 1;
+    if (valid < 64) {
+      // rows past the tail hold another sequence's tokens or unwritten memory: they are contraction
+      // rows of w, qg, dO and Aqk
+      for (int idx = tid; idx < (64 - valid) * 16; idx += 128) {
+        const int r = valid + (idx >> 4), ch = idx & 15;
+        const int off = (ch >> 3) * 8192 + sw128_chunk(r, ch & 7);
+        *reinterpret_cast<uint4*>(st + StateBwdLayout::W + off) = make_uint4(0, 0, 0, 0);
+        *reinterpret_cast<uint4*>(st + StateBwdLayout::QG + off) = make_uint4(0, 0, 0, 0);
+        *reinterpret_cast<uint4*>(st + StateBwdLayout::DO + off) = make_uint4(0, 0, 0, 0);
+        if (ch < 8)
+          *reinterpret_cast<uint4*>(st + StateBwdLayout::AQK + sw128_chunk(r, ch)) = make_uint4(0, 0, 0, 0);
+      }
+    }
+    // ---- a. dh row -> bf16 B tile + global copy; decay in place ---------------------------------
+    {
+      float x[32];
+#pragma unroll 1
+      for (int cb = 0; cb < 4; ++cb) {
+        tmem_ld32(tDh + 32 * cb, x);
+        unsigned char* box = smem + StateBwdLayout::DH + (cb >> 1) * 16384;
+#pragma unroll
+        for (int qd = 0; qd < 4; ++qd) {
+          uint4 v;
+          pack8(x + 8 * qd, v);
+          *reinterpret_cast<uint4*>(box + sw128_chunk(tid, (cb & 1) * 4 + qd)) = v;
+          *reinterpret_cast<uint4*>(p.dh_out + (((int64_t)(chunk0 + c) * H + head) * D + tid) * D +
+                                    32 * cb + 8 * qd) = v;
+        }
+#pragma unroll
+        for (int i = 0; i < 32; ++i) x[i] *= dec;
+        tmem_st32(tDh + 32 * cb, x);
+      }
+      tmem_st_wait();
+    }
+    fence_async_smem();
+    tc_fence_before();
+    __syncthreads();
+    if (*s_abort) { failed = true; break; }
+
+    // ---- b. dv2 = kg dh + Aqk^T dO ;  dh += qg^T dO ------------------------------------------------
+    if (tid == 0) {
+      tc_fence_after();
+      const uint32_t kg = saddr(st + StateBwdLayout::KG), qg = saddr(st + StateBwdLayout::QG),
+                     dO = saddr(st + StateBwdLayout::DO), aqk = saddr(st + StateBwdLayout::AQK);
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks)
+        umma(tmem + 128, desc_kmajor(kg, ks, 8192), desc_mnmajor(sDH, ks, 16384),
+             instr_desc(64, 128, 0, 1), ks > 0);
+#pragma unroll
+      for (int ks = 0; ks < 4; ++ks)
+        umma(tmem + 128, desc_mnmajor(aqk, ks, 0), desc_mnmajor(dO, ks, 8192), instr_desc(64, 128, 1, 1), 1);
+#pragma unroll
+      for (int ks = 0; ks < 4; ++ks)
+        umma(tmem, desc_mnmajor(qg, ks, 8192), desc_mnmajor(dO, ks, 8192), instr_desc(128, 128, 1, 1), 1);
+      umma_commit(bar_mma1);
+    }
+    if (!mbar_wait(bar_mma1, it & 1)) *s_abort = 1;
+    tc_fence_after();
+    // ---- c. dv2 rows (M = 64 accumulator: row j on lane 32 (j / 16) + j % 16) -----------------------
+    {
+      float x[32];
+      const int j = warp * 16 + lid;
+      const bool row = lid < 16;
+#pragma unroll 1
+      for (int cb = 0; cb < 4; ++cb) {
+        tmem_ld32(tDv + 32 * cb, x);
+        if (row) {
+          unsigned char* box = smem + StateBwdLayout::DV2 + (cb >> 1) * 8192;
+#pragma unroll
+          for (int qd = 0; qd < 4; ++qd) {
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (j < valid) pack8(x + 8 * qd, v);
+            *reinterpret_cast<uint4*>(box + sw128_chunk(j, (cb & 1) * 4 + qd)) = v;
+            if (j < valid)
+              *reinterpret_cast<uint4*>(p.dv2_out + ((token0 + j) * H + head) * D + 32 * cb + 8 * qd) = v;
+          }
+        }
+      }
+    }
+    fence_async_smem();
+    tc_fence_before();
+    __syncthreads();
+    if (*s_abort) { failed = true; break; }
+
+    // ---- d. dh -= w^T dv2 ------------------------------------------------------------------------------
+    if (tid == 0) {
+      tc_fence_after();
+      const uint32_t w = saddr(st + StateBwdLayout::W);
+#pragma unroll
+      for (int ks = 0; ks < 4; ++ks)
+        umma(tmem, desc_mnmajor(w, ks, 8192), desc_mnmajor(sDV2, ks, 8192), instr_desc(128, 128, 1, 1, 1), 1);
+      umma_commit(bar_mma2);
+    }
+    if (!mbar_wait(bar_mma2, it & 1)) *s_abort = 1;
+    tc_fence_after();
+    if (tid == 0 && it + 2 < nchunks) issue_stage(it + 2);
+  }
+
+  if (!failed && p.dh0) {
+    float x[32];
+#pragma unroll 1
+    for (int cb = 0; cb < 4; ++cb) {
+      tmem_ld32(tDh + 32 * cb, x);
+#pragma unroll
+      for (int i = 0; i < 32; i += 4)
+        *reinterpret_cast<float4*>(p.dh0 + sbase + (int64_t)tid * D + 32 * cb + i) =
+            make_float4(x[i], x[i + 1], x[i + 2], x[i + 3]);
+    }
+  }
+  if (failed && tid == 0 && p.error) atomicExch(p.error, 16);
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, 256);
+}
+
+int launch_state_bwd_tc(const bf16* w, const bf16* kg, const bf16* qg, const bf16* aqk, const bf16* dout,
+                        const float* g, const float* dht, float* dh0, bf16* dh_out, bf16* dv2_out,
+                        const int32_t* cu, const int32_t* co, int nseq, int H, int64_t tokens,
+                        cudaStream_t s) {
+  if (nseq == 0) return KDA_OK;
+  StateBwdTcParams p;
+  const int64_t cols = (int64_t)H * D;
+  if (!make_tensor_map(&p.tm_w, w, tokens, cols, 64) || !make_tensor_map(&p.tm_kg, kg, tokens, cols, 64) ||
+      !make_tensor_map(&p.tm_qg, qg, tokens, cols, 64) || !make_tensor_map(&p.tm_do, dout, tokens, cols, 64) ||
+      !make_tensor_map(&p.tm_aqk, aqk, tokens, (int64_t)H * 64, 64))
+    return KDA_ERR_LAUNCH;
+  p.g = g; p.dht = dht; p.dh0 = dh0; p.dh_out = dh_out; p.dv2_out = dv2_out;
+  p.cu_seqlens = cu; p.chunk_offsets = co; p.nseq = nseq; p.H = H;
+  p.error = nullptr;
+  if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p.error), g_state_tc_error) != cudaSuccess)
+    return KDA_ERR_LAUNCH;
+  const int smem = StateBwdLayout::TOTAL + 1024;
+  if (cudaFuncSetAttribute(kda_state_bwd_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
+      cudaSuccess)
+    return KDA_ERR_LAUNCH;
+  StageScope timing(kStageStateBwd, s);
+  kda_state_bwd_tc_kernel<<<(unsigned)(nseq * H), 128, smem, s>>>(p);
+  return cudaGetLastError() == cudaSuccess ? KDA_OK : KDA_ERR_LAUNCH;
+}
+
 }  // namespace kda
 
 // 1 if a tensor-memory kernel gave up on a barrier wait since the last call (clears the flag).

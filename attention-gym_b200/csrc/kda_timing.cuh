@@ -10,7 +10,7 @@
 namespace kda {
 
 enum Stage {
-  kStageIntraSolve = 0, kStageWu, kStageStateFwd, kStageStateBwd, kStageBwdWy, kStageBwdIntra,
+  kStageIntraSolve = 0, kStageWu, kStageStateFwd, kStageStateBwd, kStageBwdChunk,
   kStageRecurrent, kStageGateFwd, kStageGateBwd, kStageL2norm, kStageConv, kStageOffsets,
   kStageAffine, kStageCount
 };

@@ -44,8 +44,9 @@ STAGE_BYTES = {
     "state_fwd": 4 * 256 + 128 + 8 + 256,                       # w,u,kg,qg,Aqk,G_last -> o
     "state_fwd_recompute": 4 * 256 + 128 + 8 + 512 + 256,       # ... -> h[c] (bf16) + v_new
     "state_bwd": 3 * 256 + 256 + 128 + 8 + 512 + 256,           # w,kg,qg,dO,Aqk -> dh[c], dv2
-    "bwd_wy": 1024 + 6 * 256 + 512 + 128 + 4 + 3 * 512 + 256 + 2 * 256 + 4,
-    "bwd_intra": 2 * 256 + 512 + 2 * 256 + 3 * 512 + 8 + 2 * 256 + 512 + 4,
+    # h, dh (bf16 [128,128] per chunk = 512 B per token each), dO, v_new, dv2, v, k, q, G, Akk, beta
+    # -> dq, dk, dv, dG, dbeta
+    "bwd_chunk": 1024 + 6 * 256 + 512 + 128 + 4 + 3 * 256 + 512 + 4,
 }
 # the path's algorithmic minimum (inputs once, outputs once), bytes per token per head
 PATH_BYTES_FWD_BWD = 4620
