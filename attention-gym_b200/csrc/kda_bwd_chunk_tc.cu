@@ -18,7 +18,11 @@
 //            forward), UMMAs with N = 16 per row block:
 //              dq_intra^T, X1^T [kappa][i in block ri] = Kn_ri^T {dAqk, dL}[i, j <= 16 ri + 15]
 //              dk2^T [kappa][j in block cj] = Qn_cj^T dAqk[i >= 16 cj, j] + Kn'_cj^T dL[i >= 16 cj, j]
-//   phase 4  epilogue: combine, last-row gate terms, ln 2, stores; dbeta by a warp butterfly.
+//   phase 4  epilogue: combine, last-row gate terms, ln 2; dbeta by a warp butterfly.
+//
+// 512 threads: warp w owns tensor-memory lanes 32 (w % 4) .. +31 (channels) and the 16 chunk rows
+// 16 (w / 4) .. +15.  Outputs are staged in shared memory as swizzled tiles and leave with TMA
+// stores (full chunks) or coalesced 16-byte stores (the partial tail chunk of a sequence).
 //
 // All barrier waits are bounded (error word + early exit instead of a hang).
 #include "kda_common.cuh"
@@ -31,6 +35,7 @@ using namespace sm100;
 
 struct BwdTcParams {
   CUtensorMap tm_h, tm_dh, tm_do, tm_vn, tm_dv2, tm_v, tm_k, tm_q, tm_a, tm_g;
+  CUtensorMap tm_dq, tm_dk, tm_dv, tm_dg;
   const float* beta;
   bf16* dq; bf16* dk; bf16* dv; float* dg; float* db;
   const int32_t* cu_seqlens; const int32_t* chunk_offsets;
@@ -50,7 +55,7 @@ __device__ __forceinline__ void tc_mark(const BwdTcParams& p, int slot) {
 
 namespace bl {  // shared-memory layout (bytes)
 constexpr int HH = 0, DHH = 32768, DO = 65536, VN = 81920, DV2 = 98304, V = 114688, K = 131072,
-              Q = 147456, AK = 163840, G = 172032, MISC = 204800, TOTAL = 206848;
+              Q = 147456, AK = 163840, G = 172032, MISC = 204800, TOTAL = 210944;
 // overlays (valid once their host tiles are dead)
 constexpr int DWT = HH, KGM = HH + 16384;                       // after phase 0
 constexpr int X = DHH, Y = DHH + 8192, DA = DHH + 16384, DL = DHH + 24576;
@@ -59,6 +64,8 @@ constexpr int QN0 = HH, KP0 = HH + 16384;                       // column block 
 constexpr int QN1 = 106496, KP1 = 118784;                       // column block 1 (48 rows)
 constexpr int QN2 = DO, KP2 = DO + 8192;                        // column block 2 (32 rows), after R1
 constexpr int QN3 = DO + 16384, KP3 = DO + 20480;               // column block 3 (16 rows)
+constexpr int DVO = HH;                                         // dv staging (phase 2, h tile is dead)
+constexpr int DQO = HH, DKO = HH + 16384, DGO = DHH;            // dq, dk (bf16), dG (fp32) staging
 }  // namespace bl
 namespace tc {  // tensor-memory columns
 constexpr int DQ = 0, DKS = 64, DW = 128, DVB = 192, DKG = 256, X = 320, Y = 384, DAQK = 448, DL = 448;
@@ -135,7 +142,9 @@ __device__ __forceinline__ float warp_transpose_reduce16(float (&pb)[16], int li
   return pb[0] + __shfl_xor_sync(0xffffffffu, pb[0], 1);
 }
 
-__global__ void __launch_bounds__(256, 1) kda_bwd_chunk_tc_kernel(const __grid_constant__ BwdTcParams p) {
+constexpr int NT = 512;
+
+__global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_constant__ BwdTcParams p) {
   extern __shared__ unsigned char smem_dyn[];
   // 1024-byte alignment by offset, so the compiler still knows this is shared memory
   unsigned char* sm = smem_dyn + ((1024u - (saddr(smem_dyn) & 1023u)) & 1023u);
@@ -144,13 +153,13 @@ __global__ void __launch_bounds__(256, 1) kda_bwd_chunk_tc_kernel(const __grid_c
   volatile int* s_abort = reinterpret_cast<volatile int*>(sm + bl::MISC + 72);
   float* s_beta = reinterpret_cast<float*>(sm + bl::MISC + 128);          // [64]
   float* s_db = s_beta + 64;                                              // [64]
-  float* s_hd = s_db + 64;                                                // [2][128]
-  float* s_kdk = s_hd + 256;                                              // [2][128]
+  float* s_hd = s_db + 64;                                                // [4][128]
+  float* s_kdk = s_hd + 512;                                              // [4][128]
 
   const int tid = threadIdx.x, warp = tid >> 5, lid = tid & 31;
-  const int quad = warp & 3, hf = warp >> 2;
+  const int quad = warp & 3, rq = warp >> 2;
   const int L = quad * 32 + lid;                 // channel owned by this thread (TMEM lane)
-  const int i0 = 32 * hf;                        // first of the 32 chunk rows it handles
+  const int r0 = 16 * rq;                        // first of the 16 chunk rows it handles
   const int head = blockIdx.y, H = p.H;
   const ChunkWork cw = locate_chunk(p.cu_seqlens, p.chunk_offsets, p.nseq, blockIdx.x);
   if (cw.valid == 0) return;
@@ -171,23 +180,25 @@ __global__ void __launch_bounds__(256, 1) kda_bwd_chunk_tc_kernel(const __grid_c
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
   const uint32_t tl = tmem + ((uint32_t)(32 * quad) << 16);    // this warp's lane quadrant
+  const int ty = (int)cw.token0, tx = head * 128;
 
   if (tid == 0) {
-    const int y = (int)cw.token0, x = head * 128;
     const int yh = (blockIdx.x * H + head) * 128;
     mbar_expect_tx(&bar[0], 2 * 32768 + 6 * 16384 + 8192 + 32768);
     for (int b = 0; b < 2; ++b) {
       tma_load_2d(sm + bl::HH + b * 16384, &p.tm_h, 64 * b, yh, &bar[0]);
+      tma_load_2d(sm + bl::DO + b * 8192, &p.tm_do, tx + 64 * b, ty, &bar[0]);
       tma_load_2d(sm + bl::DHH + b * 16384, &p.tm_dh, 64 * b, yh, &bar[0]);
-      tma_load_2d(sm + bl::DO + b * 8192, &p.tm_do, x + 64 * b, y, &bar[0]);
-      tma_load_2d(sm + bl::VN + b * 8192, &p.tm_vn, x + 64 * b, y, &bar[0]);
-      tma_load_2d(sm + bl::DV2 + b * 8192, &p.tm_dv2, x + 64 * b, y, &bar[0]);
-      tma_load_2d(sm + bl::V + b * 8192, &p.tm_v, x + 64 * b, y, &bar[0]);
-      tma_load_2d(sm + bl::K + b * 8192, &p.tm_k, x + 64 * b, y, &bar[0]);
-      tma_load_2d(sm + bl::Q + b * 8192, &p.tm_q, x + 64 * b, y, &bar[0]);
+      tma_load_2d(sm + bl::VN + b * 8192, &p.tm_vn, tx + 64 * b, ty, &bar[0]);
+      tma_load_2d(sm + bl::DV2 + b * 8192, &p.tm_dv2, tx + 64 * b, ty, &bar[0]);
     }
-    tma_load_2d(sm + bl::AK, &p.tm_a, head * 64, y, &bar[0]);
-    for (int b = 0; b < 4; ++b) tma_load_2d(sm + bl::G + b * 8192, &p.tm_g, x + 32 * b, y, &bar[0]);
+    for (int b = 0; b < 2; ++b) {
+      tma_load_2d(sm + bl::V + b * 8192, &p.tm_v, tx + 64 * b, ty, &bar[0]);
+      tma_load_2d(sm + bl::K + b * 8192, &p.tm_k, tx + 64 * b, ty, &bar[0]);
+      tma_load_2d(sm + bl::Q + b * 8192, &p.tm_q, tx + 64 * b, ty, &bar[0]);
+    }
+    tma_load_2d(sm + bl::AK, &p.tm_a, head * 64, ty, &bar[0]);
+    for (int b = 0; b < 4; ++b) tma_load_2d(sm + bl::G + b * 8192, &p.tm_g, tx + 32 * b, ty, &bar[0]);
   }
   auto body = [&]() -> int {
   tc_mark(p, 0);
@@ -198,14 +209,14 @@ __global__ void __launch_bounds__(256, 1) kda_bwd_chunk_tc_kernel(const __grid_c
   // in every token tile and repeat the last gate row, so no later step needs a row guard.
   if (valid < 64) {
     const int tiles[6] = {bl::DO, bl::VN, bl::DV2, bl::V, bl::K, bl::Q};
-    for (int idx = tid; idx < (64 - valid) * 16; idx += 256) {
+    for (int idx = tid; idx < (64 - valid) * 16; idx += NT) {
       const int r = valid + (idx >> 4), ch = idx & 15;
 #pragma unroll
       for (int t = 0; t < 6; ++t)
         *reinterpret_cast<uint4*>(sm + tiles[t] + (ch >> 3) * 8192 + sw128_chunk(r, ch & 7)) = make_uint4(0, 0, 0, 0);
       if (ch < 8) *reinterpret_cast<uint4*>(sm + bl::AK + sw128_chunk(r, ch)) = make_uint4(0, 0, 0, 0);
     }
-    for (int idx = tid; idx < (64 - valid) * 32; idx += 256) {
+    for (int idx = tid; idx < (64 - valid) * 32; idx += NT) {
       const int r = valid + (idx >> 5), ch = idx & 31;        // 32 chunks of 4 floats per row
       const int off = (ch >> 3) * 8192, c = ch & 7;
       *reinterpret_cast<float4*>(sm + bl::G + off + r * 128 + ((c ^ (r & 7)) << 4)) =
@@ -225,20 +236,21 @@ __global__ void __launch_bounds__(256, 1) kda_bwd_chunk_tc_kernel(const __grid_c
                    i64 = instr_desc(64, 64, 0, 0);
 #pragma unroll
     for (int ks = 0; ks < 8; ++ks) {
-      umma(tmem + tc::DQ, desc_kmajor(hh, ks, 16384), desc_kmajor(dO, ks, 8192), i128, ks > 0);
-      umma(tmem + tc::DKS, desc_kmajor(dhh, ks, 16384), desc_kmajor(vn, ks, 8192), i128, ks > 0);
       umma(tmem + tc::DW, desc_kmajor(hh, ks, 16384), desc_kmajor(dv2, ks, 8192), i128n, ks > 0);
       umma(tmem + tc::DAQK, desc_kmajor(dO, ks, 8192), desc_kmajor(vn, ks, 8192), i64, ks > 0);
+      umma(tmem + tc::DQ, desc_kmajor(hh, ks, 16384), desc_kmajor(dO, ks, 8192), i128, ks > 0);
+      umma(tmem + tc::DKS, desc_kmajor(dhh, ks, 16384), desc_kmajor(vn, ks, 8192), i128, ks > 0);
     }
     umma_commit(&bar[1]);
   }
-  // meanwhile: hd[kappa] = sum_v h dh over this thread's v half
+  // meanwhile: hd[kappa] = sum_v h dh over this thread's quarter of v
   {
     float s = 0.f;
-    const unsigned char* hb = sm + bl::HH + hf * 16384;
-    const unsigned char* db = sm + bl::DHH + hf * 16384;
+    const unsigned char* hb = sm + bl::HH + (rq >> 1) * 16384;
+    const unsigned char* db = sm + bl::DHH + (rq >> 1) * 16384;
 #pragma unroll
-    for (int ch = 0; ch < 8; ++ch) {
+    for (int c4 = 0; c4 < 4; ++c4) {
+      const int ch = 4 * (rq & 1) + c4;
       uint4 a = *reinterpret_cast<const uint4*>(hb + sw128_chunk(L, ch));
       uint4 b = *reinterpret_cast<const uint4*>(db + sw128_chunk(L, ch));
       float2 a0 = unpack_bf16(a.x), a1 = unpack_bf16(a.y), a2 = unpack_bf16(a.z), a3 = unpack_bf16(a.w);
@@ -246,11 +258,10 @@ __global__ void __launch_bounds__(256, 1) kda_bwd_chunk_tc_kernel(const __grid_c
       s += a0.x * b0.x + a0.y * b0.y + a1.x * b1.x + a1.y * b1.y + a2.x * b2.x + a2.y * b2.y +
            a3.x * b3.x + a3.y * b3.y;
     }
-    s_hd[hf * 128 + L] = s;
+    s_hd[rq * 128 + L] = s;
   }
   const unsigned char* sG = sm + bl::G;
   const float glast = ld_g(sG, valid - 1, L);
-  auto gfix = [&](int row) { return ld_g(sG, row, L); };
 
   tc_mark(p, 2);
   if (!mbar_wait(&bar[1], 0)) *s_abort = 1;
@@ -261,36 +272,37 @@ __global__ void __launch_bounds__(256, 1) kda_bwd_chunk_tc_kernel(const __grid_c
 
   // ---- phase 1 epilogue: operand tiles for the next products; dq^T and dks^T stay in tensor memory
   {
-    float a[32];
-    tmem_ld32(tl + tc::DW + i0, a);      // dw^T (already negated)
+    float a[16];
+    tmem_ld16(tl + tc::DW + r0, a);      // dw^T (already negated)
 #pragma unroll
-    for (int qd = 0; qd < 4; ++qd) {
+    for (int qd = 0; qd < 2; ++qd) {
       uint4 v;
       pack8v(a + 8 * qd, v);
-      *reinterpret_cast<uint4*>(sm + bl::DWT + sw128_chunk(L, 4 * hf + qd)) = v;
+      *reinterpret_cast<uint4*>(sm + bl::DWT + sw128_chunk(L, 2 * rq + qd)) = v;
     }
     // k 2^G as a K-major tile [s][kappa]
-#pragma unroll 8
-    for (int ii = 0; ii < 32; ++ii) {
-      const int i = i0 + ii;
-      const float kv = ld_bf(sm + bl::K, 8192, i, L);
-      st_bf(sm + bl::KGM, 8192, i, L, kv * fexp2(gfix(i)));
+#pragma unroll
+    for (int task = tid; task < 1024; task += NT) {
+      const int i = task >> 4, c16 = task & 15;
+      float kk[8], gg[8];
+      ld_bf8(sm + bl::K, 8192, i, c16, kk);
+      ld_g8(sG, i, 8 * c16, gg);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) kk[e] *= fexp2(gg[e]);
+      st_bf8(sm + bl::KGM, 8192, i, c16, kk);
     }
     // dAqk (M = 64 accumulator: row r lives on lane 32 (r / 16) + r % 16)
-    tmem_ld32(tl + tc::DAQK + i0, a);
+    tmem_ld16(tl + tc::DAQK + r0, a);
     if (lid < 16) {
       const int r = quad * 16 + lid;
-      float y[32];
+      float y[16];
 #pragma unroll
-      for (int jj = 0; jj < 32; ++jj) {
-        const int j = i0 + jj;
-        y[jj] = (r >= j && r < valid) ? a[jj] * p.scale : 0.f;
-      }
+      for (int jj = 0; jj < 16; ++jj) y[jj] = (r >= r0 + jj && r < valid) ? a[jj] * p.scale : 0.f;
 #pragma unroll
-      for (int qd = 0; qd < 4; ++qd) {
+      for (int qd = 0; qd < 2; ++qd) {
         uint4 v;
         pack8v(y + 8 * qd, v);
-        *reinterpret_cast<uint4*>(sm + bl::DA + sw128_chunk(r, 4 * hf + qd)) = v;
+        *reinterpret_cast<uint4*>(sm + bl::DA + sw128_chunk(r, 2 * rq + qd)) = v;
       }
     }
   }
@@ -321,38 +333,61 @@ __global__ void __launch_bounds__(256, 1) kda_bwd_chunk_tc_kernel(const __grid_c
            instr_desc(64, 64, 1, 0), 1);
     umma_commit(&bar[2]);
   }
+  // Row-type gated tiles  Kn_ri[j][kappa] = k_j 2^{R_ri - G_j},  j < 16 (ri + 1): the four tiles
+  // (16, 32, 48, 64 rows) are one flat list of 2560 eight-channel tasks.  The first three tiles
+  // overlay dO / v_new (dead) and are built while the phase 1 products run; the last one reaches
+  // into the dv2 tile and waits for them.
+  auto build_row_tiles = [&](int begin, int end) {
+    for (int task = begin + tid; task < end; task += NT) {
+      int ri, t0;
+      if (task < 256) { ri = 0; t0 = 0; }
+      else if (task < 768) { ri = 1; t0 = 256; }
+      else if (task < 1536) { ri = 2; t0 = 768; }
+      else { ri = 3; t0 = 1536; }
+      const int rows = 16 * (ri + 1), local = task - t0;
+      const int j = local >> 4, c16 = local & 15;
+      float kk[8], gj[8], rr[8];
+      ld_bf8(sm + bl::K, 8192, j, c16, kk);
+      ld_g8(sG, j, 8 * c16, gj);
+      ld_g8(sG, 16 * ri, 8 * c16, rr);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) kk[e] *= fexp2(fminf(rr[e] - gj[e], 126.f));
+      st_bf8(sm + bl::KN0 + t0 * 16, rows * 128, j, c16, kk);
+    }
+  };
+  build_row_tiles(0, 1536);
   if (!mbar_wait(&bar[2], 0)) *s_abort = 1;
   tc_fence_after();
   tc_mark(p, 5);
 
-  // ---- phase 2 epilogue: dv and its dbeta term; X tile (dkgb^T stays in tensor memory) -------------
+  // ---- phase 2 epilogue: dv (staged) and its dbeta term; X tile (dkgb^T stays in tensor memory) ----
   {
-    float a[32], pb[32];
-    tmem_ld32(tl + tc::DVB + i0, a);      // this thread = value channel v = L
+    float a[16], pb[16];
+    tmem_ld16(tl + tc::DVB + r0, a);      // this thread = value channel v = L
 #pragma unroll
-    for (int ii = 0; ii < 32; ++ii) {
-      const int s = i0 + ii;
-      pb[ii] = 0.f;
-      if (s < valid) {
-        p.dv[((cw.token0 + s) * H + head) * 128 + L] = __float2bfloat16(a[ii] * s_beta[s]);
-        pb[ii] = a[ii] * ld_bf(sm + bl::V, 8192, s, L);
-      }
+    for (int ii = 0; ii < 16; ++ii) {
+      const int s = r0 + ii;
+      st_bf(sm + bl::DVO, 8192, s, L, a[ii] * s_beta[s]);
+      pb[ii] = a[ii] * ld_bf(sm + bl::V, 8192, s, L);
     }
-    atomicAdd(&s_db[i0 + lid], warp_transpose_reduce(pb, lid));
-    tmem_ld32(tl + tc::X + i0, a);
+    {
+      const float tot = warp_transpose_reduce16(pb, lid);
+      if ((lid & 1) == 0) atomicAdd(&s_db[r0 + (lid >> 1)], tot);
+    }
+    tmem_ld16(tl + tc::X + r0, a);
     if (lid < 16) {
       const int t = quad * 16 + lid;
-      float y[32];
+      float y[16];
 #pragma unroll
-      for (int jj = 0; jj < 32; ++jj) {
-        const int s = i0 + jj;
+      for (int jj = 0; jj < 16; ++jj) {
+        const int s = r0 + jj;
         y[jj] = (t > s && t < valid) ? a[jj] * s_beta[s] : 0.f;
       }
 #pragma unroll
-      for (int qd = 0; qd < 4; ++qd) {
+      for (int qd = 0; qd < 2; ++qd) {
         uint4 v;
         pack8v(y + 8 * qd, v);
-        *reinterpret_cast<uint4*>(sm + bl::X + sw128_chunk(t, 4 * hf + qd)) = v;
+        *reinterpret_cast<uint4*>(sm + bl::X + sw128_chunk(t, 2 * rq + qd)) = v;
       }
     }
   }
@@ -362,7 +397,7 @@ __global__ void __launch_bounds__(256, 1) kda_bwd_chunk_tc_kernel(const __grid_c
   if (*s_abort) return 4;
 
   tc_mark(p, 6);
-  // ---- Y = A^T X ------------------------------------------------------------------------------------
+  // ---- Y = A^T X; dv leaves -------------------------------------------------------------------------
   if (tid == 0) {
     tc_fence_after();
     const uint32_t ak = saddr(sm + bl::AK), x = saddr(sm + bl::X);
@@ -370,43 +405,37 @@ __global__ void __launch_bounds__(256, 1) kda_bwd_chunk_tc_kernel(const __grid_c
     for (int ks = 0; ks < 4; ++ks)
       umma(tmem + tc::Y, desc_mnmajor(ak, ks, 0), desc_mnmajor(x, ks, 0), instr_desc(64, 64, 1, 1), ks > 0);
     umma_commit(&bar[3]);
-  }
-  // meanwhile: row-type gated tiles  Kn_ri[j][kappa] = k_j 2^{R_ri - G_j},  j < 16 (ri + 1)
-  {
-    int off = 0;
-#pragma unroll
-    for (int ri = 0; ri < 4; ++ri) {
-      const int rows = 16 * (ri + 1);
-      unsigned char* tile = sm + bl::KN0 + off;
-      for (int task = tid; task < rows * 16; task += 256) {
-        const int j = task >> 4, c16 = task & 15;
-        float kk[8], gj[8], rr[8];
-        ld_bf8(sm + bl::K, 8192, j, c16, kk);
-        ld_g8(sG, j, 8 * c16, gj);
-        ld_g8(sG, 16 * ri, 8 * c16, rr);
-#pragma unroll
-        for (int e = 0; e < 8; ++e) kk[e] *= fexp2(fminf(rr[e] - gj[e], 126.f));
-        st_bf8(tile, rows * 128, j, c16, kk);
-      }
-      off += rows * 256;
+    if (valid == 64) {
+      tma_store_2d(&p.tm_dv, sm + bl::DVO, tx, ty);
+      tma_store_2d(&p.tm_dv, sm + bl::DVO + 8192, tx + 64, ty);
+      tma_store_commit();
     }
   }
+  if (valid < 64) {
+    for (int idx = tid; idx < valid * 16; idx += NT) {
+      const int r = idx >> 4, ch = idx & 15;
+      *reinterpret_cast<uint4*>(p.dv + ((cw.token0 + r) * H + head) * 128 + ch * 8) =
+          *reinterpret_cast<const uint4*>(sm + bl::DVO + (ch >> 3) * 8192 + sw128_chunk(r, ch & 7));
+    }
+  }
+  build_row_tiles(1536, 2560);
   tc_mark(p, 7);
   if (!mbar_wait(&bar[3], 0)) *s_abort = 1;
   tc_fence_after();
   {
-    float a[32];
-    tmem_ld32(tl + tc::Y + i0, a);
+    float a[16];
+    tmem_ld16(tl + tc::Y + r0, a);
     if (lid < 16) {
       const int r = quad * 16 + lid;
 #pragma unroll
-      for (int qd = 0; qd < 4; ++qd) {
+      for (int qd = 0; qd < 2; ++qd) {
         uint4 v;
         pack8v(a + 8 * qd, v);
-        *reinterpret_cast<uint4*>(sm + bl::Y + sw128_chunk(r, 4 * hf + qd)) = v;
+        *reinterpret_cast<uint4*>(sm + bl::Y + sw128_chunk(r, 2 * rq + qd)) = v;
       }
     }
   }
+  if (tid == 0) tma_store_wait_read();      // the dv staging tile is rewritten after the next barrier
   fence_async_smem();
   tc_fence_before();
   __syncthreads();
@@ -432,45 +461,46 @@ __global__ void __launch_bounds__(256, 1) kda_bwd_chunk_tc_kernel(const __grid_c
       off += rows * 256;
     }
   }
-  // meanwhile: column-type gated tiles for blocks 0 and 1
-  auto build_col = [&](int cj, int qoff, int koff) {
+  // meanwhile: column-type gated tiles.  Block cj holds rows 16 cj .. 63 of
+  //   Qn[i][kappa] = q_i 2^{G_i - R'_cj},  Kp[i][kappa] = beta_i k_i 2^{G_i - R'_cj},  R'_cj = G[16 cj + 15]
+  auto build_col = [&](int cj, int local, int qoff, int koff) {
     const int rows = 64 - 16 * cj;
-    for (int task = tid; task < rows * 16; task += 256) {
-      const int r = task >> 4, c16 = task & 15, i = 16 * cj + r;
-      float qq[8], kk[8], gi[8], rr[8];
-      ld_bf8(sm + bl::Q, 8192, i, c16, qq);
-      ld_bf8(sm + bl::K, 8192, i, c16, kk);
-      ld_g8(sG, i, 8 * c16, gi);
-      ld_g8(sG, 16 * cj + 15, 8 * c16, rr);
-      const float b = s_beta[i];
+    const int r = local >> 4, c16 = local & 15, i = 16 * cj + r;
+    float qq[8], kk[8], gi[8], rr[8];
+    ld_bf8(sm + bl::Q, 8192, i, c16, qq);
+    ld_bf8(sm + bl::K, 8192, i, c16, kk);
+    ld_g8(sG, i, 8 * c16, gi);
+    ld_g8(sG, 16 * cj + 15, 8 * c16, rr);
+    const float b = s_beta[i];
 #pragma unroll
-      for (int e = 0; e < 8; ++e) {
-        const float ex = fexp2(fminf(gi[e] - rr[e], 126.f));
-        qq[e] *= ex;
-        kk[e] *= ex * b;
-      }
-      st_bf8(sm + qoff, rows * 128, r, c16, qq);
-      st_bf8(sm + koff, rows * 128, r, c16, kk);
+    for (int e = 0; e < 8; ++e) {
+      const float ex = fexp2(fminf(gi[e] - rr[e], 126.f));
+      qq[e] *= ex;
+      kk[e] *= ex * b;
     }
+    st_bf8(sm + qoff, rows * 128, r, c16, qq);
+    st_bf8(sm + koff, rows * 128, r, c16, kk);
   };
-  build_col(0, bl::QN0, bl::KP0);
-  build_col(1, bl::QN1, bl::KP1);
+  for (int task = tid; task < 1792; task += NT) {          // blocks 0 (64 rows) and 1 (48 rows)
+    if (task < 1024) build_col(0, task, bl::QN0, bl::KP0);
+    else build_col(1, task - 1024, bl::QN1, bl::KP1);
+  }
   tc_mark(p, 9);
   if (!mbar_wait(&bar[4], 0)) *s_abort = 1;
   tc_fence_after();
   {
-    float a[32];
-    tmem_ld32(tl + tc::DL + i0, a);
+    float a[16];
+    tmem_ld16(tl + tc::DL + r0, a);
     if (lid < 16) {
       const int r = quad * 16 + lid;
-      float y[32];
+      float y[16];
 #pragma unroll
-      for (int jj = 0; jj < 32; ++jj) y[jj] = (r > i0 + jj && r < valid) ? a[jj] : 0.f;
+      for (int jj = 0; jj < 16; ++jj) y[jj] = (r > r0 + jj && r < valid) ? a[jj] : 0.f;
 #pragma unroll
-      for (int qd = 0; qd < 4; ++qd) {
+      for (int qd = 0; qd < 2; ++qd) {
         uint4 v;
         pack8v(y + 8 * qd, v);
-        *reinterpret_cast<uint4*>(sm + bl::DL + sw128_chunk(r, 4 * hf + qd)) = v;
+        *reinterpret_cast<uint4*>(sm + bl::DL + sw128_chunk(r, 2 * rq + qd)) = v;
       }
     }
   }
@@ -510,8 +540,10 @@ __global__ void __launch_bounds__(256, 1) kda_bwd_chunk_tc_kernel(const __grid_c
   tc_mark(p, 10);
   if (!mbar_wait(&bar[5], 0)) *s_abort = 1;   // row-type tiles are free again
   tc_fence_after();
-  build_col(2, bl::QN2, bl::KP2);
-  build_col(3, bl::QN3, bl::KP3);
+  for (int task = tid; task < 768; task += NT) {           // blocks 2 (32 rows) and 3 (16 rows)
+    if (task < 512) build_col(2, task, bl::QN2, bl::KP2);
+    else build_col(3, task - 512, bl::QN3, bl::KP3);
+  }
   fence_async_smem();
   tc_fence_before();
   __syncthreads();
@@ -527,111 +559,119 @@ __global__ void __launch_bounds__(256, 1) kda_bwd_chunk_tc_kernel(const __grid_c
   tc_fence_after();
   tc_mark(p, 12);
 
-  // ---- final epilogue: six accumulators, 16 rows at a time; thread = channel L ------------------------
+  // ---- final epilogue: six accumulators, 8 rows at a time; thread = channel L, rows r0 .. r0 + 15 ------
   //   DQ: dq_inter^T   DVB: dq_intra^T   DKS: dks^T   DKG: dkgb^T   X: X1^T   DW: dk2^T
-  // pass 1: sum_i k dks (needed by the last row of dG) and everything that does not depend on it
+  //   dq = e (scale 2^R dq_inter + dq_intra)              e = 2^{G_i - R},  R  = G[r0]
+  //   dk = 2^{G_last - G_i} dks + beta (2^G dkgb + e X1) + f dk2      f = 2^{R' - G_i}, R' = G[r0 + 15]
+  //   dG = q dq - k (dk - 2 beta (...))  assembled term by term below; dbeta_i = sum_kappa k (2^G dkgb + e X1)
   {
-    float kdk = 0.f;
-#pragma unroll 1
-    for (int part = 0; part < 2; ++part) {
-      const int r0 = i0 + 16 * part;
-      float a[16];
-      tmem_ld16(tl + tc::DKS + r0, a);
+    const int constB = (L >> 6) * 8192 + (L & 7) * 2, cB = (L & 63) >> 3;
+    const int constG = (L >> 5) * 8192 + (L & 3) * 4, cG = (L & 31) >> 2;
+    const float gfirst = ld_g(sG, r0, L), rlast = ld_g(sG, r0 + 15, L);
+    const float E0 = fexp2(gfirst), F0 = fexp2(glast - rlast), sE0 = p.scale * E0;
+    float kdk = 0.f, pb[16];
 #pragma unroll
-      for (int ii = 0; ii < 16; ++ii) {
-        const int i = r0 + ii;
-        kdk += ld_bf(sm + bl::K, 8192, i, L) * a[ii] * fexp2(glast - gfix(i));
+    for (int grp = 0; grp < 2; ++grp) {
+      const int rb = r0 + 8 * grp;
+      unsigned char* rowB = sm + constB + rb * 128;
+      unsigned char* rowG = sm + constG + rb * 128;
+      float a[8], a2[8], e[8], f[8], kr[8], bt[8], dkr[8], dgr[8];
+      int oB[8], oG[8];
+#pragma unroll
+      for (int ii = 0; ii < 8; ++ii) {
+        oB[ii] = ii * 128 + ((cB ^ ii) << 4);
+        oG[ii] = ii * 128 + ((cG ^ ii) << 4);
+        const float g = *reinterpret_cast<const float*>(rowG + bl::G + oG[ii]);
+        e[ii] = fexp2(g - gfirst);
+        f[ii] = fexp2(rlast - g);
+        kr[ii] = __bfloat162float(*reinterpret_cast<const bf16*>(rowB + bl::K + oB[ii]));
+        bt[ii] = s_beta[rb + ii];
       }
-    }
-    s_kdk[hf * 128 + L] = kdk;
-  }
-  __syncthreads();
-  {
-    const float hdv = (s_hd[L] + s_hd[128 + L]) * fexp2(glast) + s_kdk[L] + s_kdk[128 + L];
-#pragma unroll 1
-    for (int part = 0; part < 2; ++part) {
-      const int r0 = i0 + 16 * part;
-      float a[16], g[16], e[16], dkr[16], dgr[16], pb[16], kr[16];
-      const float gfirst = gfix(r0);                // r0 is the first row of its 16-row block
+      tmem_ld8(tl + tc::DQ + rb, a);
+      tmem_ld8(tl + tc::DVB + rb, a2);
 #pragma unroll
-      for (int ii = 0; ii < 16; ++ii) {
-        g[ii] = gfix(r0 + ii);
-        e[ii] = fexp2(g[ii] - gfirst);              // row factor 2^{G_i - R_ri}
-        kr[ii] = ld_bf(sm + bl::K, 8192, r0 + ii, L);
-      }
-      // dq = scale 2^G dq_inter + e dq_intra ;  dG = q dq
-      tmem_ld16(tl + tc::DQ + r0, a);
-#pragma unroll
-      for (int ii = 0; ii < 16; ++ii) dkr[ii] = a[ii] * p.scale * fexp2(g[ii]);
-      tmem_ld16(tl + tc::DVB + r0, a);
-#pragma unroll
-      for (int ii = 0; ii < 16; ++ii) {
-        const int i = r0 + ii;
-        const float dqv = dkr[ii] + a[ii] * e[ii];
-        const float qv = ld_bf(sm + bl::Q, 8192, i, L);
+      for (int ii = 0; ii < 8; ++ii) {
+        const float dqv = e[ii] * fmaf(a[ii], sE0, a2[ii]);
+        const float qv = __bfloat162float(*reinterpret_cast<const bf16*>(rowB + bl::Q + oB[ii]));
         dgr[ii] = qv * dqv;
-        if (i < valid) p.dq[((cw.token0 + i) * H + head) * 128 + L] = __float2bfloat16(dqv);
+        a2[ii] = dqv;
       }
-      // dk = r dks + beta 2^G dkgb + beta e X1 + f dk2
-      tmem_ld16(tl + tc::DKS + r0, a);
+      tmem_ld8(tl + tc::DKS + rb, a);
+      // dq^T staging overlays nothing that is still read: the h tile region is dead since bar[6]
 #pragma unroll
-      for (int ii = 0; ii < 16; ++ii) {
-        const int i = r0 + ii;
-        const float kv = kr[ii];
-        const float x = a[ii] * fexp2(glast - g[ii]);
+      for (int ii = 0; ii < 8; ++ii) {
+        *reinterpret_cast<bf16*>(rowB + bl::DQO + oB[ii]) = __float2bfloat16(a2[ii]);
+        const float x = a[ii] * (f[ii] * F0);
+        const float kx = kr[ii] * x;
         dkr[ii] = x;
-        dgr[ii] -= kv * x;
+        dgr[ii] -= kx;
+        kdk += kx;
       }
-      tmem_ld16(tl + tc::DKG + r0, a);
+      tmem_ld8(tl + tc::DKG + rb, a);
+      tmem_ld8(tl + tc::X + rb, a2);
 #pragma unroll
-      for (int ii = 0; ii < 16; ++ii) {
-        const int i = r0 + ii;
-        const float gam = fexp2(g[ii]);
-        const float kgm = (ld_bf(sm + bl::K, 8192, i, L)) * gam;   // k 2^G
-        const float b = s_beta[i];
-        dkr[ii] += b * gam * a[ii];
-        dgr[ii] += b * kgm * a[ii];
-        pb[ii] = a[ii] * kgm;
+      for (int ii = 0; ii < 8; ++ii) {
+        const float gam = e[ii] * E0;                     // 2^{G_i}
+        const float y = fmaf(a[ii], gam, a2[ii] * e[ii]); // 2^G dkgb + e X1
+        const float ky = kr[ii] * y;
+        pb[8 * grp + ii] = ky;
+        dkr[ii] = fmaf(bt[ii], y, dkr[ii]);
+        dgr[ii] = fmaf(bt[ii], ky, dgr[ii]);
       }
-      tmem_ld16(tl + tc::X + r0, a);
+      tmem_ld8(tl + tc::DW + rb, a);
 #pragma unroll
-      for (int ii = 0; ii < 16; ++ii) {
-        const int i = r0 + ii;
-        const float kv = kr[ii];
-        const float xi = a[ii] * e[ii];
-        const float b = s_beta[i];
-        dkr[ii] += b * xi;
-        dgr[ii] += kv * b * xi;
-        pb[ii] += kv * xi;
-      }
-      {
-        const float tot = warp_transpose_reduce16(pb, lid);
-        if ((lid & 1) == 0) atomicAdd(&s_db[r0 + (lid >> 1)], tot);
-      }
-      tmem_ld16(tl + tc::DW + r0, a);
-      const float rlast = gfix(r0 + 15);            // column factor 2^{R'_cj - G_j}
-#pragma unroll
-      for (int ii = 0; ii < 16; ++ii) {
-        const int i = r0 + ii;
-        const float kv = kr[ii];
-        const float x = a[ii] * fexp2(rlast - g[ii]);
-        float gsum = dgr[ii] - kv * x;
-        if (i == valid - 1) gsum += hdv;
-        if (i < valid) {
-          const int64_t gi = ((cw.token0 + i) * H + head) * 128 + L;
-          p.dk[gi] = __float2bfloat16(dkr[ii] + x);
-          p.dg[gi] = gsum * kLn2;
-        }
+      for (int ii = 0; ii < 8; ++ii) {
+        const float x = a[ii] * f[ii];
+        *reinterpret_cast<bf16*>(rowB + bl::DKO + oB[ii]) = __float2bfloat16(dkr[ii] + x);
+        *reinterpret_cast<float*>(rowG + bl::DGO + oG[ii]) = fmaf(-kr[ii], x, dgr[ii]) * kLn2;
       }
     }
+    {
+      const float tot = warp_transpose_reduce16(pb, lid);
+      if ((lid & 1) == 0) atomicAdd(&s_db[r0 + (lid >> 1)], tot);
+    }
+    s_kdk[rq * 128 + L] = kdk;
   }
   tc_mark(p, 13);
   __syncthreads();
+  if (tid < 128) {    // last valid row of dG: + (sum_v h dh) 2^{G_last} + sum_i k dks 2^{G_last - G_i}
+    const float hdv = (s_hd[L] + s_hd[128 + L] + s_hd[256 + L] + s_hd[384 + L]) * fexp2(glast) +
+                      s_kdk[L] + s_kdk[128 + L] + s_kdk[256 + L] + s_kdk[384 + L];
+    float* cell = reinterpret_cast<float*>(sm + bl::DGO + (L >> 5) * 8192 + (valid - 1) * 128 +
+                                           (((((L & 31) >> 2) ^ ((valid - 1) & 7)) << 4) | ((L & 3) << 2)));
+    *cell += hdv * kLn2;
+  }
+  fence_async_smem();
+  __syncthreads();
+  if (valid == 64) {
+    if (tid == 0) {
+      for (int b = 0; b < 2; ++b) {
+        tma_store_2d(&p.tm_dq, sm + bl::DQO + b * 8192, tx + 64 * b, ty);
+        tma_store_2d(&p.tm_dk, sm + bl::DKO + b * 8192, tx + 64 * b, ty);
+      }
+      for (int b = 0; b < 4; ++b) tma_store_2d(&p.tm_dg, sm + bl::DGO + b * 8192, tx + 32 * b, ty);
+      tma_store_commit();
+    }
+  } else {
+    for (int idx = tid; idx < valid * 16; idx += NT) {
+      const int r = idx >> 4, ch = idx & 15;
+      const int64_t gi = ((cw.token0 + r) * H + head) * 128 + ch * 8;
+      const int so = (ch >> 3) * 8192 + sw128_chunk(r, ch & 7);
+      *reinterpret_cast<uint4*>(p.dq + gi) = *reinterpret_cast<const uint4*>(sm + bl::DQO + so);
+      *reinterpret_cast<uint4*>(p.dk + gi) = *reinterpret_cast<const uint4*>(sm + bl::DKO + so);
+    }
+    for (int idx = tid; idx < valid * 32; idx += NT) {
+      const int r = idx >> 5, ch = idx & 31;
+      *reinterpret_cast<float4*>(p.dg + ((cw.token0 + r) * H + head) * 128 + ch * 4) =
+          *reinterpret_cast<const float4*>(sm + bl::DGO + (ch >> 3) * 8192 + r * 128 + (((ch & 7) ^ (r & 7)) << 4));
+    }
+  }
   if (tid < valid) p.db[(cw.token0 + tid) * H + head] = s_db[tid];
   tc_mark(p, 14);
   return 0;
   };
   const int rc = body();
+  if (tid == 0) tma_store_wait_read();      // staged tiles must outlive the bulk stores' reads
   if (rc && tid == 0 && p.error) atomicExch(p.error, rc);
   tc_fence_before();
   __syncthreads();
@@ -654,7 +694,9 @@ int launch_bwd_chunk_tc(const bf16* q, const bf16* k, const bf16* v, const float
             make_tensor_map(&p.tm_dv2, dv2, tokens, cols, 64) && make_tensor_map(&p.tm_v, v, tokens, cols, 64) &&
             make_tensor_map(&p.tm_k, k, tokens, cols, 64) && make_tensor_map(&p.tm_q, q, tokens, cols, 64) &&
             make_tensor_map(&p.tm_a, akk, tokens, (int64_t)H * 64, 64) &&
-            make_tensor_map(&p.tm_g, g, tokens, cols, 64, true);
+            make_tensor_map(&p.tm_g, g, tokens, cols, 64, true) &&
+            make_tensor_map(&p.tm_dq, dq, tokens, cols, 64) && make_tensor_map(&p.tm_dk, dk, tokens, cols, 64) &&
+            make_tensor_map(&p.tm_dv, dv, tokens, cols, 64) && make_tensor_map(&p.tm_dg, dg, tokens, cols, 64, true);
   if (!ok) return KDA_ERR_LAUNCH;
   p.beta = beta; p.dq = dq; p.dk = dk; p.dv = dv; p.dg = dg; p.db = db;
   p.cu_seqlens = cu; p.chunk_offsets = co; p.nseq = nseq; p.H = H;
@@ -666,7 +708,7 @@ int launch_bwd_chunk_tc(const bf16* q, const bf16* k, const bf16* v, const float
       cudaSuccess)
     return KDA_ERR_LAUNCH;
   StageScope timing(kStageBwdChunk, s);
-  kda_bwd_chunk_tc_kernel<<<dim3(chunks, H), 256, smem, s>>>(p);
+  kda_bwd_chunk_tc_kernel<<<dim3(chunks, H), NT, smem, s>>>(p);
   return cudaGetLastError() == cudaSuccess ? KDA_OK : KDA_ERR_LAUNCH;
 }
 
