@@ -45,17 +45,21 @@ struct BwdTcParams {
   long long* prof;
 };
 
+// Debugging aid: phase timestamps of 64 chunks from the middle of the grid (steady state, not the
+// first wave) into the buffer set with kda_debug_set_profile_buffer.
 __device__ __forceinline__ void tc_mark(const BwdTcParams& p, int slot) {
-  if (p.prof && threadIdx.x == 0 && blockIdx.y == 0 && blockIdx.x < 64) {
+  const unsigned base = gridDim.x / 2;
+  if (p.prof && threadIdx.x == 0 && blockIdx.y == gridDim.y / 2 && blockIdx.x >= base &&
+      blockIdx.x < base + 64) {
     long long t;
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-    p.prof[blockIdx.x * 32 + slot] = t;
+    p.prof[(blockIdx.x - base) * 32 + slot] = t;
   }
 }
 
 namespace bl {  // shared-memory layout (bytes)
 constexpr int HH = 0, DHH = 32768, DO = 65536, VN = 81920, DV2 = 98304, V = 114688, K = 131072,
-              Q = 147456, AK = 163840, G = 172032, MISC = 204800, TOTAL = 210944;
+              Q = 147456, AK = 163840, G = 172032, MISC = 204800, TOTAL = 212992;
 // overlays (valid once their host tiles are dead)
 constexpr int DWT = HH, KGM = HH + 16384;                       // after phase 0
 constexpr int X = DHH, Y = DHH + 8192, DA = DHH + 16384, DL = DHH + 24576;
@@ -152,8 +156,8 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm + bl::MISC + 64);
   volatile int* s_abort = reinterpret_cast<volatile int*>(sm + bl::MISC + 72);
   float* s_beta = reinterpret_cast<float*>(sm + bl::MISC + 128);          // [64]
-  float* s_db = s_beta + 64;                                              // [64]
-  float* s_hd = s_db + 64;                                                // [4][128]
+  float* s_db = s_beta + 64;                                              // [2 terms][4 quadrants][64]
+  float* s_hd = s_db + 512;                                               // [4][128]
   float* s_kdk = s_hd + 512;                                              // [4][128]
 
   const int tid = threadIdx.x, warp = tid >> 5, lid = tid & 31;
@@ -173,7 +177,6 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
   }
   if (tid < 64) {
     s_beta[tid] = tid < valid ? p.beta[(cw.token0 + tid) * H + head] : 0.f;
-    s_db[tid] = 0.f;
   }
   tc_fence_before();
   __syncthreads();
@@ -370,9 +373,9 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
       st_bf(sm + bl::DVO, 8192, s, L, a[ii] * s_beta[s]);
       pb[ii] = a[ii] * ld_bf(sm + bl::V, 8192, s, L);
     }
-    {
+    {   // dbeta term 0: one slot per (channel quadrant, row), summed in a fixed order at the end
       const float tot = warp_transpose_reduce16(pb, lid);
-      if ((lid & 1) == 0) atomicAdd(&s_db[r0 + (lid >> 1)], tot);
+      if ((lid & 1) == 0) s_db[quad * 64 + r0 + (lid >> 1)] = tot;
     }
     tmem_ld16(tl + tc::X + r0, a);
     if (lid < 16) {
@@ -628,7 +631,7 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
     }
     {
       const float tot = warp_transpose_reduce16(pb, lid);
-      if ((lid & 1) == 0) atomicAdd(&s_db[r0 + (lid >> 1)], tot);
+      if ((lid & 1) == 0) s_db[256 + quad * 64 + r0 + (lid >> 1)] = tot;
     }
     s_kdk[rq * 128 + L] = kdk;
   }
@@ -666,7 +669,12 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
           *reinterpret_cast<const float4*>(sm + bl::DGO + (ch >> 3) * 8192 + r * 128 + (((ch & 7) ^ (r & 7)) << 4));
     }
   }
-  if (tid < valid) p.db[(cw.token0 + tid) * H + head] = s_db[tid];
+  if (tid < valid) {
+    float t = 0.f;
+#pragma unroll
+    for (int part = 0; part < 8; ++part) t += s_db[part * 64 + tid];
+    p.db[(cw.token0 + tid) * H + head] = t;
+  }
   tc_mark(p, 14);
   return 0;
   };

@@ -45,14 +45,14 @@ extern "C" int64_t kda_chunk_bwd_workspace_bytes(int64_t tokens, int heads, int6
   return (6 * nd + 2 * hs) * 2 + 256;   // w, u, kg, qg, v_new, dv2 and h, dh (all bf16)
 }
 
-extern "C" int kda_chunk_bwd(const void* q, const void* k, const void* v, const float* cum_gate,
-                             const float* beta, const void* aqk, const void* akk,
-                             const float* initial_state, const void* d_out,
-                             const float* d_final_state, void* dq, void* dk, void* dv, float* dg,
-                             float* dbeta, float* d_initial_state, const int32_t* cu_seqlens,
-                             const int32_t* chunk_offsets, int nseq, int64_t tokens, int heads,
-                             int key_dim, int value_dim, int num_chunks, void* workspace,
-                             int64_t workspace_bytes, void* stream) {
+static int chunk_bwd_impl(bool saved, const void* q, const void* k, const void* v, const float* cum_gate,
+                          const float* beta, const void* aqk, const void* akk,
+                          const float* initial_state, const void* d_out,
+                          const float* d_final_state, void* dq, void* dk, void* dv, float* dg,
+                          float* dbeta, float* d_initial_state, const int32_t* cu_seqlens,
+                          const int32_t* chunk_offsets, int nseq, int64_t tokens, int heads,
+                          int key_dim, int value_dim, int num_chunks, void* workspace,
+                          int64_t workspace_bytes, void* stream) {
   if (!q || !k || !v || !cum_gate || !beta || !aqk || !akk || !d_out || !dq || !dk || !dv || !dg ||
       !dbeta || !cu_seqlens || !chunk_offsets || !workspace)
     return KDA_ERR_ARG;
@@ -67,9 +67,12 @@ extern "C" int kda_chunk_bwd(const void* q, const void* k, const void* v, const 
        *dv2 = b + 5 * nd, *hbuf = b + 6 * nd, *dhbuf = b + 6 * nd + hs;
   cudaStream_t s = (cudaStream_t)stream;
 
-  int rc = kda::launch_recompute(q, k, v, cum_gate, beta, aqk, akk, initial_state, w, u, kg, qg,
-                                 hbuf, vnew, cu_seqlens, chunk_offsets, nseq, heads, num_chunks, tokens, s);
-  if (rc) return rc;
+  int rc = KDA_OK;
+  if (!saved) {   // reference behaviour: rebuild w, u, kg, qg, h[c], v_new from the stored A
+    rc = kda::launch_recompute(q, k, v, cum_gate, beta, aqk, akk, initial_state, w, u, kg, qg,
+                               hbuf, vnew, cu_seqlens, chunk_offsets, nseq, heads, num_chunks, tokens, s);
+    if (rc) return rc;
+  }
 
   const bf16* qb = (const bf16*)q; const bf16* kb = (const bf16*)k; const bf16* vb = (const bf16*)v;
   rc = kda::launch_state_bwd_tc(w, kg, qg, (const bf16*)aqk, (const bf16*)d_out, cum_gate,
@@ -80,4 +83,22 @@ extern "C" int kda_chunk_bwd(const void* q, const void* k, const void* v, const 
                                   (const bf16*)d_out, (bf16*)dq, (bf16*)dk, (bf16*)dv, dg, dbeta,
                                   cu_seqlens, chunk_offsets, nseq, heads, tokens, num_chunks,
                                   g_prof_buffer, s);
+}
+
+#define KDA_BWD_ARGS                                                                              \
+  const void *q, const void *k, const void *v, const float *cum_gate, const float *beta,           \
+      const void *aqk, const void *akk, const float *initial_state, const void *d_out,             \
+      const float *d_final_state, void *dq, void *dk, void *dv, float *dg, float *dbeta,           \
+      float *d_initial_state, const int32_t *cu_seqlens, const int32_t *chunk_offsets, int nseq,   \
+      int64_t tokens, int heads, int key_dim, int value_dim, int num_chunks
+#define KDA_BWD_PASS                                                                              \
+  q, k, v, cum_gate, beta, aqk, akk, initial_state, d_out, d_final_state, dq, dk, dv, dg, dbeta,   \
+      d_initial_state, cu_seqlens, chunk_offsets, nseq, tokens, heads, key_dim, value_dim, num_chunks
+
+extern "C" int kda_chunk_bwd(KDA_BWD_ARGS, void* workspace, int64_t workspace_bytes, void* stream) {
+  return chunk_bwd_impl(false, KDA_BWD_PASS, workspace, workspace_bytes, stream);
+}
+
+extern "C" int kda_chunk_bwd_saved(KDA_BWD_ARGS, void* saved, int64_t saved_bytes, void* stream) {
+  return chunk_bwd_impl(true, KDA_BWD_PASS, saved, saved_bytes, stream);
 }

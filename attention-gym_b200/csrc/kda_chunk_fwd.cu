@@ -322,7 +322,7 @@ int launch_recompute(const void* q, const void* k, const void* v, const float* g
 
 using kda::bf16;
 
-extern "C" int kda_chunk_fwd(const void* q, const void* k, const void* v, const float* cum_gate,
+static int chunk_fwd_impl(bool keep, const void* q, const void* k, const void* v, const float* cum_gate,
                              const float* beta, const float* initial_state, float* final_state,
                              void* out, void* aqk, void* akk, const int32_t* cu_seqlens,
                              const int32_t* chunk_offsets, int nseq, int64_t tokens, int heads,
@@ -334,7 +334,10 @@ extern "C" int kda_chunk_fwd(const void* q, const void* k, const void* v, const 
   if (key_dim != 128 || value_dim != 128) return KDA_ERR_UNSUPPORTED;
   if (nseq < 1 || heads < 1 || tokens < 1 || num_chunks < 0) return KDA_ERR_ARG;
   if ((int64_t)nseq * heads * 2 > 0x7fffffffLL) return KDA_ERR_UNSUPPORTED;
-  if (workspace_bytes < kda_chunk_fwd_workspace_bytes(tokens, heads)) return KDA_ERR_ARG;
+  if (workspace_bytes < (keep ? kda_chunk_bwd_workspace_bytes(tokens, heads, num_chunks)
+                              : kda_chunk_fwd_workspace_bytes(tokens, heads)))
+    return KDA_ERR_ARG;
+  if (((uintptr_t)workspace & 15) != 0) return KDA_ERR_ARG;
   kda::ChunkParams p{};
   const int64_t nd = tokens * heads * 128;
   bf16* ws = reinterpret_cast<bf16*>(workspace);
@@ -342,7 +345,10 @@ extern "C" int kda_chunk_fwd(const void* q, const void* k, const void* v, const 
   p.aqk = (bf16*)aqk; p.akk = (bf16*)akk;
   p.w = ws; p.u = ws + nd; p.kg = ws + 2 * nd; p.qg = ws + 3 * nd;
   p.h0 = initial_state; p.ht = final_state; p.o = (bf16*)out;
-  p.h_out = nullptr; p.vnew_out = nullptr;
+  // keep: the workspace has the backward layout (w, u, kg, qg, v_new, dv2, h, dh) and the state
+  // walk also leaves v_new and the chunk-entry states there
+  p.vnew_out = keep ? ws + 4 * nd : nullptr;
+  p.h_out = keep ? ws + 6 * nd : nullptr;
   p.cu_seqlens = cu_seqlens; p.chunk_offsets = chunk_offsets; p.nseq = nseq; p.H = heads;
   p.scale = 0.08838834764831845f;  // 128^-0.5
   p.tokens = tokens;
@@ -352,6 +358,28 @@ extern "C" int kda_chunk_fwd(const void* q, const void* k, const void* v, const 
   rc = kda::launch_wu(p, num_chunks, s);
   if (rc) return rc;
   return kda::launch_state_fwd(p, s);
+}
+
+extern "C" int kda_chunk_fwd(const void* q, const void* k, const void* v, const float* cum_gate,
+                             const float* beta, const float* initial_state, float* final_state,
+                             void* out, void* aqk, void* akk, const int32_t* cu_seqlens,
+                             const int32_t* chunk_offsets, int nseq, int64_t tokens, int heads,
+                             int key_dim, int value_dim, int num_chunks, void* workspace,
+                             int64_t workspace_bytes, void* stream) {
+  return chunk_fwd_impl(false, q, k, v, cum_gate, beta, initial_state, final_state, out, aqk, akk,
+                        cu_seqlens, chunk_offsets, nseq, tokens, heads, key_dim, value_dim,
+                        num_chunks, workspace, workspace_bytes, stream);
+}
+
+extern "C" int kda_chunk_fwd_save(const void* q, const void* k, const void* v, const float* cum_gate,
+                                  const float* beta, const float* initial_state, float* final_state,
+                                  void* out, void* aqk, void* akk, const int32_t* cu_seqlens,
+                                  const int32_t* chunk_offsets, int nseq, int64_t tokens, int heads,
+                                  int key_dim, int value_dim, int num_chunks, void* saved,
+                                  int64_t saved_bytes, void* stream) {
+  return chunk_fwd_impl(true, q, k, v, cum_gate, beta, initial_state, final_state, out, aqk, akk,
+                        cu_seqlens, chunk_offsets, nseq, tokens, heads, key_dim, value_dim,
+                        num_chunks, saved, saved_bytes, stream);
 }
 
 extern "C" int64_t kda_chunk_fwd_workspace_bytes(int64_t tokens, int heads) {

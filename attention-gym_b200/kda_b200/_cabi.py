@@ -47,11 +47,15 @@ _SIGNATURES = {
     "kda_chunk_fwd_workspace_bytes": (c_int64, [c_int64, c_int]),
     "kda_chunk_fwd": (c_int, [c_void_p] * 12 + [c_int, c_int64, c_int, c_int, c_int, c_int, c_void_p,
                               c_int64, c_void_p]),
+    "kda_chunk_fwd_save": (c_int, [c_void_p] * 12 + [c_int, c_int64, c_int, c_int, c_int, c_int,
+                                   c_void_p, c_int64, c_void_p]),
     "kda_chunk_fwd_noalloc": (c_int, [c_void_p] * 12 + [c_int, c_int64, c_int, c_int, c_int, c_int,
                                       c_void_p]),
     "kda_chunk_bwd_workspace_bytes": (c_int64, [c_int64, c_int, c_int64]),
     "kda_chunk_bwd": (c_int, [c_void_p] * 18 + [c_int, c_int64, c_int, c_int, c_int, c_int, c_void_p,
                               c_int64, c_void_p]),
+    "kda_chunk_bwd_saved": (c_int, [c_void_p] * 18 + [c_int, c_int64, c_int, c_int, c_int, c_int,
+                                    c_void_p, c_int64, c_void_p]),
     "kda_chunk_fwd_prepare": (c_int, [c_void_p] * 9 + [c_int, c_int64, c_int, c_int, c_void_p,
                                       c_int64, c_void_p]),
     "kda_chunk_fwd_state": (c_int, [c_void_p] * 7 + [c_int, c_int64, c_int, c_void_p, c_int,

@@ -44,7 +44,8 @@ def _per_token_gate(cumulative_gate, cu_seqlens):
 
 
 def chunk_kda(q, k, v, cumulative_gate, beta, initial_state=None, *, cu_seqlens=None,
-              output_final_state=False, fastmath=False, autotune=True, impl=Impl.FUSED):
+              output_final_state=False, fastmath=False, autotune=True, impl=Impl.FUSED,
+              recompute=False):
     """Chunk-parallel KDA.
 
     q, k, cumulative_gate: ``[B, T, H, K]``; v: ``[B, T, H, V]``; beta: ``[B, T, H]``;
@@ -53,7 +54,9 @@ def chunk_kda(q, k, v, cumulative_gate, beta, initial_state=None, *, cu_seqlens=
     per logical sequence; ``cu_seqlens [N + 1]`` packs N sequences into a batch-one input (starts
     at 0, non-decreasing, may repeat, may end before T).  Returns ``(output in q.dtype, fp32
     final state or None)``.  ``fastmath`` and ``autotune`` are accepted for signature
-    compatibility; there is a single kernel configuration.
+    compatibility; there is a single kernel configuration.  ``recompute`` (not in the reference,
+    which always behaves as ``True``) makes the backward pass rebuild the forward intermediates
+    instead of keeping about 1.6 KiB per token and head between the two passes.
     """
     selected = resolve_impl(impl)
     if selected is Impl.REFERENCE and fastmath:
@@ -73,7 +76,7 @@ def chunk_kda(q, k, v, cumulative_gate, beta, initial_state=None, *, cu_seqlens=
                                         output_final_state=output_final_state)
     return _fused_chunk_forward(q, k, v, cumulative_gate, beta, initial_state,
                                 cu_seqlens=cu_seqlens, output_final_state=output_final_state,
-                                fastmath=fastmath, autotune=autotune)
+                                fastmath=fastmath, autotune=autotune, recompute=recompute)
 
 
 def _validate_paged_state(q, v, initial_state, cu_seqlens, state_indices, output_final_state):

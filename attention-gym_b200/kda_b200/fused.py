@@ -5,6 +5,12 @@ _ChunkKDA :35-144): normalise dtypes (q, k, v -> bf16; gate, beta, state -> fp32
 dense or packed operator, save (q, k, v, gate, beta, tape, h0, offsets) and run the first-order
 backward operator.  Dense inputs of any batch size and length go to the kernels as equal-length
 packed sequences, built inside the operator.
+
+One addition: unless ``recompute=True``, a forward pass that will be differentiated keeps its
+intermediates (w, u, kg, qg, v_new and the chunk-entry states, about 1.6 KiB per token and head)
+for the backward pass instead of rebuilding them there as the reference does
+(bwd/cute/chunk_kda_bwd.py:54-85).  The results are identical; ``recompute=True`` gives the
+reference's memory footprint back.
 """
 
 from __future__ import annotations
@@ -28,9 +34,13 @@ def _validate_fused_constraints(q, v):
 class _ChunkKDA(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, gate, beta, initial_state, cu_seqlens, chunk_offsets,
-                output_final_state, fastmath, autotune):
+                output_final_state, fastmath, autotune, recompute):
         state = None
-        if cu_seqlens is None:
+        saved = None
+        if not recompute and any(ctx.needs_input_grad[:6]):
+            out, state, aqk, akk, saved = ops.chunk_fwd_saved_op(
+                q, k, v, gate, beta, initial_state, cu_seqlens, chunk_offsets, output_final_state)
+        elif cu_seqlens is None:
             if output_final_state:
                 out, state, aqk, akk = ops.chunk_fwd_with_state_op(q, k, v, gate, beta,
                                                                    initial_state, autotune)
@@ -43,7 +53,7 @@ class _ChunkKDA(torch.autograd.Function):
             out, aqk, akk = ops.chunk_fwd_ragged_op(q, k, v, gate, beta, initial_state, cu_seqlens,
                                                     chunk_offsets, autotune)
         ctx.save_for_backward(q, k, v, gate, beta, aqk, akk, initial_state, cu_seqlens,
-                              chunk_offsets)
+                              chunk_offsets, saved)
         ctx.fastmath, ctx.autotune = fastmath, autotune
         ctx.set_materialize_grads(False)
         return (out, state) if output_final_state else out
@@ -51,7 +61,15 @@ class _ChunkKDA(torch.autograd.Function):
     @staticmethod
     @torch.autograd.function.once_differentiable
     def backward(ctx, d_output, d_final_state=None):
-        q, k, v, gate, beta, aqk, akk, initial_state, cu_seqlens, chunk_offsets = ctx.saved_tensors
+        (q, k, v, gate, beta, aqk, akk, initial_state, cu_seqlens, chunk_offsets,
+         saved) = ctx.saved_tensors
+        if saved is not None:
+            dq, dk, dv, dg, db, dh0 = ops.chunk_bwd_saved_op(
+                q, k, v, gate, beta, aqk, akk, saved, cu_seqlens, chunk_offsets, d_output,
+                d_final_state, initial_state, initial_state is not None)
+            if initial_state is None:
+                dh0 = None
+            return dq, dk, dv, dg, db, dh0, None, None, None, None, None, None
         args = (q, k, v, gate, beta, aqk, akk, cu_seqlens, chunk_offsets, d_output, d_final_state,
                 initial_state, ctx.fastmath, ctx.autotune)
         if initial_state is not None:
@@ -59,12 +77,12 @@ class _ChunkKDA(torch.autograd.Function):
         else:
             dq, dk, dv, dg, db = ops.chunk_bwd_op(*args)
             dh0 = None
-        return dq, dk, dv, dg, db, dh0, None, None, None, None, None
+        return dq, dk, dv, dg, db, dh0, None, None, None, None, None, None
 
 
 def chunk_forward(q, k, v, cumulative_gate, beta, initial_state=None, *, cu_seqlens=None,
                   metadata: RaggedChunkMetadata | None = None, output_final_state=False,
-                  fastmath=False, autotune=True):
+                  fastmath=False, autotune=True, recompute=False):
     """Normalise inputs and run the fused chunk operators (reference: impl/fused.py:147-216)."""
     if metadata is not None:
         assert cu_seqlens is None
@@ -83,10 +101,10 @@ def chunk_forward(q, k, v, cumulative_gate, beta, initial_state=None, *, cu_seql
     offsets = None if metadata is None else metadata.chunk_offsets
     if output_final_state:
         out, state = _ChunkKDA.apply(q, k, v, cumulative_gate, beta, initial_state, cu, offsets,
-                                     True, fastmath, autotune)
+                                     True, fastmath, autotune, recompute)
     else:
         out = _ChunkKDA.apply(q, k, v, cumulative_gate, beta, initial_state, cu, offsets, False,
-                              fastmath, autotune)
+                              fastmath, autotune, recompute)
         state = None
     return out.reshape(out_shape).to(out_dtype), state
 

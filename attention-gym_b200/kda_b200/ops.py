@@ -42,6 +42,17 @@ _define("kda_chunk_bwd", _BWD.format(state="Tensor? initial_state")
         + " -> (Tensor, Tensor, Tensor, Tensor, Tensor)")
 _define("kda_chunk_bwd_with_state_grad", _BWD.format(state="Tensor initial_state")
         + " -> (Tensor, Tensor, Tensor, Tensor, Tensor, Tensor)")
+# Training pair that keeps the forward intermediates instead of rebuilding them in the backward
+# pass (no reference counterpart: the reference always recomputes, bwd/cute/chunk_kda_bwd.py:54-85).
+_define("kda_chunk_fwd_saved",
+        "(Tensor q, Tensor k, Tensor v, Tensor cumulative_gate, Tensor beta, Tensor? initial_state, "
+        "Tensor? cu_seqlens, Tensor? chunk_offsets, bool want_state) "
+        "-> (Tensor, Tensor, Tensor, Tensor, Tensor)")
+_define("kda_chunk_bwd_saved",
+        "(Tensor q, Tensor k, Tensor v, Tensor cumulative_gate, Tensor beta, Tensor Aqk, Tensor Akk, "
+        "Tensor saved, Tensor? cu_seqlens, Tensor? chunk_offsets, Tensor? d_output, "
+        "Tensor? d_final_state, Tensor? initial_state, bool want_state_grad) "
+        "-> (Tensor, Tensor, Tensor, Tensor, Tensor, Tensor)")
 _define("kda_recurrent_fwd", _REC + " -> (Tensor, Tensor)")
 _define("kda_recurrent_fwd_no_state", _REC + " -> Tensor")
 _define("kda_recurrent_fwd_paged",
@@ -85,7 +96,8 @@ def _dense_offsets(q):
     return steps * tokens, steps * per_row, batch * per_row
 
 
-def _chunk_fwd_impl(q, k, v, gate, beta, initial_state, cu_seqlens, chunk_offsets, want_state):
+def _chunk_fwd_impl(q, k, v, gate, beta, initial_state, cu_seqlens, chunk_offsets, want_state,
+                    keep=False):
     _require_cuda(q, "the fused KDA core")
     if q.shape[-1] != 128 or v.shape[-1] != 128:
         raise ValueError("the fused KDA core requires K=V=128")
@@ -112,13 +124,18 @@ def _chunk_fwd_impl(q, k, v, gate, beta, initial_state, cu_seqlens, chunk_offset
     akk = torch.empty_like(aqk)
     state = (torch.empty(nseq, heads, 128, 128, dtype=torch.float32, device=q.device)
              if want_state else None)
-    ws_bytes = _cabi.lib().kda_chunk_fwd_workspace_bytes(total, heads)
+    if keep:
+        ws_bytes = _cabi.lib().kda_chunk_bwd_workspace_bytes(total, heads, capacity)
+    else:
+        ws_bytes = _cabi.lib().kda_chunk_fwd_workspace_bytes(total, heads)
     workspace = torch.empty(ws_bytes, dtype=torch.uint8, device=q.device)
-    _cabi.call("kda_chunk_fwd", 3, _cabi.ptr(q), _cabi.ptr(k), _cabi.ptr(v), _cabi.ptr(gate),
+    _cabi.call("kda_chunk_fwd_save" if keep else "kda_chunk_fwd", 3, _cabi.ptr(q), _cabi.ptr(k), _cabi.ptr(v), _cabi.ptr(gate),
                _cabi.ptr(beta), _cabi.ptr(initial_state), _cabi.ptr(state), _cabi.ptr(out),
                _cabi.ptr(aqk), _cabi.ptr(akk), _cabi.ptr(cu_seqlens), _cabi.ptr(chunk_offsets),
                nseq, total, heads, 128, 128, capacity, _cabi.ptr(workspace), ws_bytes,
                _cabi.stream())
+    if keep:
+        return out, state, aqk, akk, workspace
     return out, state, aqk, akk
 
 
@@ -147,7 +164,7 @@ def _chunk_fwd_ragged_with_state(q, k, v, gate, beta, initial_state, cu_seqlens,
 
 
 def _chunk_bwd_impl(q, k, v, gate, beta, aqk, akk, cu_seqlens, chunk_offsets, d_output,
-                    d_final_state, initial_state, want_state_grad):
+                    d_final_state, initial_state, want_state_grad, saved=None):
     batch, tokens, heads, _ = q.shape
     if cu_seqlens is None:
         cu_seqlens, chunk_offsets, capacity = _dense_offsets(q)
@@ -174,8 +191,13 @@ def _chunk_bwd_impl(q, k, v, gate, beta, aqk, akk, cu_seqlens, chunk_offsets, d_
     dh0 = (torch.empty(nseq, heads, 128, 128, dtype=torch.float32, device=q.device)
            if want_state_grad else None)
     ws_bytes = _cabi.lib().kda_chunk_bwd_workspace_bytes(total, heads, capacity)
-    workspace = torch.empty(ws_bytes, dtype=torch.uint8, device=q.device)
-    _cabi.call("kda_chunk_bwd", 5, _cabi.ptr(q), _cabi.ptr(k), _cabi.ptr(v), _cabi.ptr(gate),
+    if saved is not None:
+        if saved.numel() < ws_bytes or saved.dtype != torch.uint8 or not saved.is_cuda:
+            raise ValueError("`saved` is not the buffer kda_chunk_fwd_saved returned for these shapes")
+        workspace = saved
+    else:
+        workspace = torch.empty(ws_bytes, dtype=torch.uint8, device=q.device)
+    _cabi.call("kda_chunk_bwd_saved" if saved is not None else "kda_chunk_bwd", 5, _cabi.ptr(q), _cabi.ptr(k), _cabi.ptr(v), _cabi.ptr(gate),
                _cabi.ptr(beta), _cabi.ptr(aqk), _cabi.ptr(akk), _cabi.ptr(initial_state),
                _cabi.ptr(d_output), _cabi.ptr(d_final_state), _cabi.ptr(dq), _cabi.ptr(dk),
                _cabi.ptr(dv), _cabi.ptr(dg), _cabi.ptr(db), _cabi.ptr(dh0), _cabi.ptr(cu_seqlens),
@@ -196,6 +218,26 @@ def _chunk_bwd_with_state_grad(q, k, v, gate, beta, aqk, akk, cu_seqlens, chunk_
                                d_final_state, initial_state, fastmath, autotune):
     return _chunk_bwd_impl(q, k, v, gate, beta, aqk, akk, cu_seqlens, chunk_offsets, d_output,
                            d_final_state, initial_state, True)
+
+
+@torch.library.impl(_lib, "kda_chunk_fwd_saved", "CUDA")
+def _chunk_fwd_saved(q, k, v, gate, beta, initial_state, cu_seqlens, chunk_offsets, want_state):
+    out, state, aqk, akk, saved = _chunk_fwd_impl(q, k, v, gate, beta, initial_state, cu_seqlens,
+                                                  chunk_offsets, want_state, keep=True)
+    if state is None:
+        state = torch.empty(0, dtype=torch.float32, device=q.device)
+    return out, state, aqk, akk, saved
+
+
+@torch.library.impl(_lib, "kda_chunk_bwd_saved", "CUDA")
+def _chunk_bwd_saved(q, k, v, gate, beta, aqk, akk, saved, cu_seqlens, chunk_offsets, d_output,
+                     d_final_state, initial_state, want_state_grad):
+    dq, dk, dv, dg, db, dh0 = _chunk_bwd_impl(q, k, v, gate, beta, aqk, akk, cu_seqlens,
+                                              chunk_offsets, d_output, d_final_state, initial_state,
+                                              want_state_grad, saved=saved)
+    if dh0 is None:
+        dh0 = torch.empty(0, dtype=torch.float32, device=q.device)
+    return dq, dk, dv, dg, db, dh0
 
 
 def _tape(q):
@@ -242,6 +284,28 @@ def _(q, k, v, gate, beta, aqk, akk, cu_seqlens, chunk_offsets, d_output, d_fina
       initial_state, fastmath, autotune):
     return (*_bwd_fake(q, k, v, gate, beta),
             torch.empty_like(initial_state, dtype=torch.float32))
+
+
+@torch.library.register_fake(f"{_NS}::kda_chunk_fwd_saved")
+def _(q, k, v, gate, beta, initial_state, cu_seqlens, chunk_offsets, want_state):
+    nseq = q.shape[0] if cu_seqlens is None else cu_seqlens.shape[0] - 1
+    state = (q.new_empty((nseq, q.shape[2], q.shape[3], v.shape[-1]), dtype=torch.float32)
+             if want_state else q.new_empty((0,), dtype=torch.float32))
+    total, heads = q.shape[0] * q.shape[1], q.shape[2]
+    chunks = (q.shape[0] * ((q.shape[1] + _CHUNK - 1) // _CHUNK) if cu_seqlens is None
+              else chunk_capacity(q.shape[1], nseq, _CHUNK))
+    nbytes = (6 * total * heads * 128 + 2 * chunks * heads * 128 * 128) * 2 + 256
+    return (v.new_empty(v.shape), state, _tape(q), _tape(q),
+            q.new_empty((nbytes,), dtype=torch.uint8))
+
+
+@torch.library.register_fake(f"{_NS}::kda_chunk_bwd_saved")
+def _(q, k, v, gate, beta, aqk, akk, saved, cu_seqlens, chunk_offsets, d_output, d_final_state,
+      initial_state, want_state_grad):
+    nseq = q.shape[0] if cu_seqlens is None else cu_seqlens.shape[0] - 1
+    dh0 = (q.new_empty((nseq, q.shape[2], q.shape[3], v.shape[-1]), dtype=torch.float32)
+           if want_state_grad else q.new_empty((0,), dtype=torch.float32))
+    return (*_bwd_fake(q, k, v, gate, beta), dh0)
 
 
 # --------------------------------------------------------------------------------------------
@@ -499,6 +563,8 @@ chunk_fwd_op = _ops.kda_chunk_fwd.default
 chunk_fwd_with_state_op = _ops.kda_chunk_fwd_with_state.default
 chunk_fwd_ragged_op = _ops.kda_chunk_fwd_ragged.default
 chunk_fwd_ragged_with_state_op = _ops.kda_chunk_fwd_ragged_with_state.default
+chunk_fwd_saved_op = _ops.kda_chunk_fwd_saved.default
+chunk_bwd_saved_op = _ops.kda_chunk_bwd_saved.default
 chunk_bwd_op = _ops.kda_chunk_bwd.default
 chunk_bwd_with_state_grad_op = _ops.kda_chunk_bwd_with_state_grad.default
 recurrent_fwd_op = _ops.kda_recurrent_fwd.default

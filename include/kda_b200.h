@@ -151,6 +151,29 @@ int kda_chunk_bwd(const void* q, const void* k, const void* v, const float* cum_
                   int value_dim, int num_chunks, void* workspace, int64_t workspace_bytes,
                   void* stream);
 
+/* Training pair that trades memory for time.  kda_chunk_fwd_save is kda_chunk_fwd that also keeps
+ * its intermediates (w, u, kg, qg, v_new and the chunk-entry states h[c], all bf16) in `saved`,
+ * a caller-owned buffer of kda_chunk_bwd_workspace_bytes() bytes, 16-byte aligned;
+ * kda_chunk_bwd_saved is kda_chunk_bwd that reads them from the same, untouched buffer instead of
+ * rebuilding them (it also uses the buffer's remaining part as its workspace).  Results are those
+ * of kda_chunk_fwd / kda_chunk_bwd bit for bit.  The reference always rebuilds in the backward
+ * pass (bwd/cute/chunk_kda_bwd.py:54-85, the recompute_w_u and delta_h legs); with 180 GB of HBM
+ * per GPU keeping 1.5 KiB + 8 KiB / 64 per (token, head) is the cheaper choice by default. */
+int kda_chunk_fwd_save(const void* q, const void* k, const void* v, const float* cum_gate,
+                       const float* beta, const float* initial_state, float* final_state,
+                       void* out, void* aqk, void* akk, const int32_t* cu_seqlens,
+                       const int32_t* chunk_offsets, int nseq, int64_t tokens, int heads,
+                       int key_dim, int value_dim, int num_chunks, void* saved, int64_t saved_bytes,
+                       void* stream);
+int kda_chunk_bwd_saved(const void* q, const void* k, const void* v, const float* cum_gate,
+                        const float* beta, const void* aqk, const void* akk,
+                        const float* initial_state, const void* d_out, const float* d_final_state,
+                        void* dq, void* dk, void* dv, float* dg, float* dbeta,
+                        float* d_initial_state, const int32_t* cu_seqlens,
+                        const int32_t* chunk_offsets, int nseq, int64_t tokens, int heads,
+                        int key_dim, int value_dim, int num_chunks, void* saved, int64_t saved_bytes,
+                        void* stream);
+
 /* The two halves of kda_chunk_fwd: `prepare` = the chunk-parallel part (fills aqk, akk and the
  * workspace), `state` = the serial state recurrence over the workspace (writes out and final_state,
  * either may be NULL).  use_u == 0 runs the homogeneous recurrence: with identity matrices as

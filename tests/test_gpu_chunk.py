@@ -24,13 +24,14 @@ def _case(batch, tokens, heads, seed, lengths=None, with_state=True):
     return inp
 
 
-def _run_fused(inp, do=None, dst=None, grad=False):
+def _run_fused(inp, do=None, dst=None, grad=False, recompute=False):
     q, k, v = (inp[n].cuda().requires_grad_(grad) for n in ("q", "k", "v"))
     g = inp["cum_gate"].cuda().requires_grad_(grad)
     beta = inp["beta"].cuda().requires_grad_(grad)
     h0 = None if inp["h0"] is None else inp["h0"].cuda().requires_grad_(grad)
     cu = None if inp["cu_seqlens"] is None else inp["cu_seqlens"].cuda()
-    o, st = kda_b200.chunk_kda(q, k, v, g, beta, h0, cu_seqlens=cu, output_final_state=True)
+    o, st = kda_b200.chunk_kda(q, k, v, g, beta, h0, cu_seqlens=cu, output_final_state=True,
+                               recompute=recompute)
     res = {"o": o, "state": st}
     if grad:
         loss = (o.float() * do.cuda()).sum()
@@ -98,6 +99,21 @@ def test_backward(case):
         lens = inp["cu_seqlens"][1:] - inp["cu_seqlens"][:-1]
         for s in (lens == 0).nonzero().flatten().tolist():
             assert torch.equal(res["dh0"][s].cpu(), dst[s]), "empty sequence state gradient"
+
+
+@pytest.mark.parametrize("case", [CASES[1], CASES[4]], ids=["dense", "packed"])
+def test_kept_intermediates_equal_recompute(case):
+    """The default training path keeps the forward intermediates; recompute=True rebuilds them in
+    the backward pass as the reference does (bwd/cute/chunk_kda_bwd.py:54-85).  Same kernels on
+    the same values: every result is bitwise equal."""
+    inp = _case(**case)
+    gen = torch.Generator().manual_seed(99)
+    do = torch.randn(inp["v"].shape, generator=gen)
+    dst = torch.randn(inp["h0"].shape, generator=gen)
+    kept = _run_fused(inp, do, dst, grad=True)
+    again = _run_fused(inp, do, dst, grad=True, recompute=True)
+    for name in kept:
+        assert torch.equal(kept[name], again[name]), name
 
 
 def test_dense_batch_equals_packed():
