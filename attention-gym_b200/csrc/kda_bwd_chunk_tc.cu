@@ -40,20 +40,18 @@ struct BwdTcParams {
   bf16* dq; bf16* dk; bf16* dv; float* dg; float* db;
   const int32_t* cu_seqlens; const int32_t* chunk_offsets;
   int* error;
-  int nseq, H;
+  int nseq, H, total;          // total = chunk capacity x heads work items
   float scale;
   long long* prof;
 };
 
-// Debugging aid: phase timestamps of 64 chunks from the middle of the grid (steady state, not the
-// first wave) into the buffer set with kda_debug_set_profile_buffer.
-__device__ __forceinline__ void tc_mark(const BwdTcParams& p, int slot) {
-  const unsigned base = gridDim.x / 2;
-  if (p.prof && threadIdx.x == 0 && blockIdx.y == gridDim.y / 2 && blockIdx.x >= base &&
-      blockIdx.x < base + 64) {
+// Debugging aid: phase timestamps of the 20th work item of the first 64 CTAs (steady state) into
+// the buffer set with kda_debug_set_profile_buffer.
+__device__ __forceinline__ void tc_mark(const BwdTcParams& p, int it, int slot) {
+  if (p.prof && it == 20 && threadIdx.x == 0 && blockIdx.x < 64) {
     long long t;
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-    p.prof[(blockIdx.x - base) * 32 + slot] = t;
+    p.prof[blockIdx.x * 32 + slot] = t;
   }
 }
 
@@ -69,7 +67,7 @@ constexpr int QN1 = 106496, KP1 = 118784;                       // column block 
 constexpr int QN2 = DO, KP2 = DO + 8192;                        // column block 2 (32 rows), after R1
 constexpr int QN3 = DO + 16384, KP3 = DO + 20480;               // column block 3 (16 rows)
 constexpr int DVO = HH;                                         // dv staging (phase 2, h tile is dead)
-constexpr int DQO = HH, DKO = HH + 16384, DGO = DHH;            // dq, dk (bf16), dG (fp32) staging
+constexpr int DQO = DO, DKO = DO + 16384, DGO = DO + 32768;     // dq, dk (bf16), dG (fp32) staging
 }  // namespace bl
 namespace tc {  // tensor-memory columns
 constexpr int DQ = 0, DKS = 64, DW = 128, DVB = 192, DKG = 256, X = 320, Y = 384, DAQK = 448, DL = 448;
@@ -164,10 +162,7 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
   const int quad = warp & 3, rq = warp >> 2;
   const int L = quad * 32 + lid;                 // channel owned by this thread (TMEM lane)
   const int r0 = 16 * rq;                        // first of the 16 chunk rows it handles
-  const int head = blockIdx.y, H = p.H;
-  const ChunkWork cw = locate_chunk(p.cu_seqlens, p.chunk_offsets, p.nseq, blockIdx.x);
-  if (cw.valid == 0) return;
-  const int valid = cw.valid;
+  const int H = p.H;
 
   if (warp == 0) tmem_alloc(tmem_slot, 512);
   if (tid == 0) {
@@ -175,38 +170,80 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
     mbar_init_fence();
     *s_abort = 0;
   }
-  if (tid < 64) {
-    s_beta[tid] = tid < valid ? p.beta[(cw.token0 + tid) * H + head] : 0.f;
-  }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
   const uint32_t tl = tmem + ((uint32_t)(32 * quad) << 16);    // this warp's lane quadrant
-  const int ty = (int)cw.token0, tx = head * 128;
+  const unsigned char* sG = sm + bl::G;
 
+  // Loads of one work item, in three parts so that the next item's tiles can start arriving as
+  // soon as their shared-memory regions die:  A = h, dh (arms the barrier for all three parts);
+  // B = k, q, G, A;  C = dO, v_new, dv2, v.   Thread 0 only.
+  auto issue_loads = [&](int part, int chunk, int head, int64_t token0) {
+    const int ty = (int)token0, tx = head * 128;
+    if (part == 0) {
+      const int yh = (chunk * H + head) * 128;
+      mbar_expect_tx(&bar[0], 2 * 32768 + 6 * 16384 + 8192 + 32768);
+      for (int b = 0; b < 2; ++b) {
+        tma_load_2d(sm + bl::HH + b * 16384, &p.tm_h, 64 * b, yh, &bar[0]);
+        tma_load_2d(sm + bl::DHH + b * 16384, &p.tm_dh, 64 * b, yh, &bar[0]);
+      }
+    } else if (part == 1) {
+      for (int b = 0; b < 2; ++b) {
+        tma_load_2d(sm + bl::K + b * 8192, &p.tm_k, tx + 64 * b, ty, &bar[0]);
+        tma_load_2d(sm + bl::Q + b * 8192, &p.tm_q, tx + 64 * b, ty, &bar[0]);
+      }
+      tma_load_2d(sm + bl::AK, &p.tm_a, head * 64, ty, &bar[0]);
+      for (int b = 0; b < 4; ++b) tma_load_2d(sm + bl::G + b * 8192, &p.tm_g, tx + 32 * b, ty, &bar[0]);
+    } else {
+      for (int b = 0; b < 2; ++b) {
+        tma_load_2d(sm + bl::DO + b * 8192, &p.tm_do, tx + 64 * b, ty, &bar[0]);
+        tma_load_2d(sm + bl::VN + b * 8192, &p.tm_vn, tx + 64 * b, ty, &bar[0]);
+        tma_load_2d(sm + bl::DV2 + b * 8192, &p.tm_dv2, tx + 64 * b, ty, &bar[0]);
+        tma_load_2d(sm + bl::V + b * 8192, &p.tm_v, tx + 64 * b, ty, &bar[0]);
+      }
+    }
+  };
+
+  // persistent walk over the (chunk, head) work items
+  uint32_t ph = 0;              // parity of this item's barrier phases
+  int it = 0, rc = 0;
+  bool pre = false;             // parts A and B of this item's loads were issued by the previous item
+  ChunkWork cw_next{};
+  float beta_next = 0.f;
+  for (int w = blockIdx.x; w < p.total; w += gridDim.x) {
+  const int chunk = w / H, head = w - chunk * H;
+  const ChunkWork cw = pre ? cw_next : locate_chunk(p.cu_seqlens, p.chunk_offsets, p.nseq, chunk);
+  if (cw.valid == 0) continue;              // capacity slot past the last active chunk
+  const int valid = cw.valid;
+  const int ty = (int)cw.token0, tx = head * 128;
+  if (tid < 64)
+    s_beta[tid] = pre ? beta_next : (tid < valid ? p.beta[(cw.token0 + tid) * H + head] : 0.f);
+  __syncthreads();     // the previous item's staging tiles have been read; beta is in place
   if (tid == 0) {
-    const int yh = (blockIdx.x * H + head) * 128;
-    mbar_expect_tx(&bar[0], 2 * 32768 + 6 * 16384 + 8192 + 32768);
-    for (int b = 0; b < 2; ++b) {
-      tma_load_2d(sm + bl::HH + b * 16384, &p.tm_h, 64 * b, yh, &bar[0]);
-      tma_load_2d(sm + bl::DO + b * 8192, &p.tm_do, tx + 64 * b, ty, &bar[0]);
-      tma_load_2d(sm + bl::DHH + b * 16384, &p.tm_dh, 64 * b, yh, &bar[0]);
-      tma_load_2d(sm + bl::VN + b * 8192, &p.tm_vn, tx + 64 * b, ty, &bar[0]);
-      tma_load_2d(sm + bl::DV2 + b * 8192, &p.tm_dv2, tx + 64 * b, ty, &bar[0]);
+    if (!pre) {
+      issue_loads(0, chunk, head, cw.token0);
+      issue_loads(1, chunk, head, cw.token0);
     }
-    for (int b = 0; b < 2; ++b) {
-      tma_load_2d(sm + bl::V + b * 8192, &p.tm_v, tx + 64 * b, ty, &bar[0]);
-      tma_load_2d(sm + bl::K + b * 8192, &p.tm_k, tx + 64 * b, ty, &bar[0]);
-      tma_load_2d(sm + bl::Q + b * 8192, &p.tm_q, tx + 64 * b, ty, &bar[0]);
-    }
-    tma_load_2d(sm + bl::AK, &p.tm_a, head * 64, ty, &bar[0]);
-    for (int b = 0; b < 4; ++b) tma_load_2d(sm + bl::G + b * 8192, &p.tm_g, tx + 32 * b, ty, &bar[0]);
+    issue_loads(2, chunk, head, cw.token0);
+  }
+  // the next item: located (and its beta fetched) now, its loads issued as this item's tiles die
+  const int wn = w + (int)gridDim.x;
+  int chunk_n = 0, head_n = 0;
+  bool next_ok = false;
+  if (wn < p.total) {
+    chunk_n = wn / H;
+    head_n = wn - chunk_n * H;
+    cw_next = locate_chunk(p.cu_seqlens, p.chunk_offsets, p.nseq, chunk_n);
+    next_ok = cw_next.valid > 0;
+    if (tid < 64)
+      beta_next = (next_ok && tid < cw_next.valid) ? p.beta[(cw_next.token0 + tid) * H + head_n] : 0.f;
   }
   auto body = [&]() -> int {
-  tc_mark(p, 0);
-  if (!mbar_wait(&bar[0], 0)) *s_abort = 1;
-  tc_mark(p, 1);
+  tc_mark(p, it, 0);
+  if (!mbar_wait(&bar[0], ph)) *s_abort = 1;
+  tc_mark(p, it, 1);
 
   // partial tail chunk: rows >= valid hold another sequence's tokens or unwritten memory.  Zero them
   // in every token tile and repeat the last gate row, so no later step needs a row guard.
@@ -263,14 +300,13 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
     }
     s_hd[rq * 128 + L] = s;
   }
-  const unsigned char* sG = sm + bl::G;
   const float glast = ld_g(sG, valid - 1, L);
 
-  tc_mark(p, 2);
-  if (!mbar_wait(&bar[1], 0)) *s_abort = 1;
+  tc_mark(p, it, 2);
+  if (!mbar_wait(&bar[1], ph)) *s_abort = 1;
   tc_fence_after();
   __syncthreads();
-  tc_mark(p, 3);      // every thread is done with the raw h / dh tiles
+  tc_mark(p, it, 3);      // every thread is done with the raw h / dh tiles
   if (*s_abort) return 3;
 
   // ---- phase 1 epilogue: operand tiles for the next products; dq^T and dks^T stay in tensor memory
@@ -313,7 +349,7 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
   tc_fence_before();
   __syncthreads();
 
-  tc_mark(p, 4);
+  tc_mark(p, it, 4);
   // ---- phase 1 UMMAs: dvb^T, dkgb^T, X -----------------------------------------------------------
   if (tid == 0) {
     tc_fence_after();
@@ -359,9 +395,9 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
     }
   };
   build_row_tiles(0, 1536);
-  if (!mbar_wait(&bar[2], 0)) *s_abort = 1;
+  if (!mbar_wait(&bar[2], ph)) *s_abort = 1;
   tc_fence_after();
-  tc_mark(p, 5);
+  tc_mark(p, it, 5);
 
   // ---- phase 2 epilogue: dv (staged) and its dbeta term; X tile (dkgb^T stays in tensor memory) ----
   {
@@ -399,7 +435,7 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
   __syncthreads();
   if (*s_abort) return 4;
 
-  tc_mark(p, 6);
+  tc_mark(p, it, 6);
   // ---- Y = A^T X; dv leaves -------------------------------------------------------------------------
   if (tid == 0) {
     tc_fence_after();
@@ -422,8 +458,8 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
     }
   }
   build_row_tiles(1536, 2560);
-  tc_mark(p, 7);
-  if (!mbar_wait(&bar[3], 0)) *s_abort = 1;
+  tc_mark(p, it, 7);
+  if (!mbar_wait(&bar[3], ph)) *s_abort = 1;
   tc_fence_after();
   {
     float a[16];
@@ -444,7 +480,7 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
   __syncthreads();
   if (*s_abort) return 5;
 
-  tc_mark(p, 8);
+  tc_mark(p, it, 8);
   // ---- dL = -(Y A^T), and the dAqk half of the row-type products -------------------------------------
   if (tid == 0) {
     tc_fence_after();
@@ -488,8 +524,8 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
     if (task < 1024) build_col(0, task, bl::QN0, bl::KP0);
     else build_col(1, task - 1024, bl::QN1, bl::KP1);
   }
-  tc_mark(p, 9);
-  if (!mbar_wait(&bar[4], 0)) *s_abort = 1;
+  tc_mark(p, it, 9);
+  if (!mbar_wait(&bar[4], ph)) *s_abort = 1;
   tc_fence_after();
   {
     float a[16];
@@ -540,8 +576,8 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
     issue_col(0, bl::QN0, bl::KP0);
     issue_col(1, bl::QN1, bl::KP1);
   }
-  tc_mark(p, 10);
-  if (!mbar_wait(&bar[5], 0)) *s_abort = 1;   // row-type tiles are free again
+  tc_mark(p, it, 10);
+  if (!mbar_wait(&bar[5], ph)) *s_abort = 1;   // row-type tiles are free again
   tc_fence_after();
   for (int task = tid; task < 768; task += NT) {           // blocks 2 (32 rows) and 3 (16 rows)
     if (task < 512) build_col(2, task, bl::QN2, bl::KP2);
@@ -557,10 +593,12 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
     issue_col(3, bl::QN3, bl::KP3);
     umma_commit(&bar[6]);
   }
-  tc_mark(p, 11);
-  if (!mbar_wait(&bar[6], 0)) *s_abort = 1;
+  tc_mark(p, it, 11);
+  if (!mbar_wait(&bar[6], ph)) *s_abort = 1;
   tc_fence_after();
-  tc_mark(p, 12);
+  tc_mark(p, it, 12);
+  // h / dh regions are dead from here on: the next item's states start arriving
+  if (tid == 0 && next_ok) issue_loads(0, chunk_n, head_n, cw_next.token0);
 
   // ---- final epilogue: six accumulators, 8 rows at a time; thread = channel L, rows r0 .. r0 + 15 ------
   //   DQ: dq_inter^T   DVB: dq_intra^T   DKS: dks^T   DKG: dkgb^T   X: X1^T   DW: dk2^T
@@ -600,7 +638,7 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
         a2[ii] = dqv;
       }
       tmem_ld8(tl + tc::DKS + rb, a);
-      // dq^T staging overlays nothing that is still read: the h tile region is dead since bar[6]
+      // the staging tiles overlay the gated operand tiles, dead since the last products completed
 #pragma unroll
       for (int ii = 0; ii < 8; ++ii) {
         *reinterpret_cast<bf16*>(rowB + bl::DQO + oB[ii]) = __float2bfloat16(a2[ii]);
@@ -635,8 +673,9 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
     }
     s_kdk[rq * 128 + L] = kdk;
   }
-  tc_mark(p, 13);
+  tc_mark(p, it, 13);
   __syncthreads();
+  if (tid == 0 && next_ok) issue_loads(1, chunk_n, head_n, cw_next.token0);   // k, q, G, A are dead
   if (tid < 128) {    // last valid row of dG: + (sum_v h dh) 2^{G_last} + sum_i k dks 2^{G_last - G_i}
     const float hdv = (s_hd[L] + s_hd[128 + L] + s_hd[256 + L] + s_hd[384 + L]) * fexp2(glast) +
                       s_kdk[L] + s_kdk[128 + L] + s_kdk[256 + L] + s_kdk[384 + L];
@@ -675,11 +714,16 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
     for (int part = 0; part < 8; ++part) t += s_db[part * 64 + tid];
     p.db[(cw.token0 + tid) * H + head] = t;
   }
-  tc_mark(p, 14);
+  tc_mark(p, it, 14);
   return 0;
   };
-  const int rc = body();
+  rc = body();
   if (tid == 0) tma_store_wait_read();      // staged tiles must outlive the bulk stores' reads
+  if (rc) break;
+  pre = next_ok;
+  ph ^= 1;
+  ++it;
+  }  // work items
   if (rc && tid == 0 && p.error) atomicExch(p.error, rc);
   tc_fence_before();
   __syncthreads();
@@ -708,7 +752,12 @@ int launch_bwd_chunk_tc(const bf16* q, const bf16* k, const bf16* v, const float
   if (!ok) return KDA_ERR_LAUNCH;
   p.beta = beta; p.dq = dq; p.dk = dk; p.dv = dv; p.dg = dg; p.db = db;
   p.cu_seqlens = cu; p.chunk_offsets = co; p.nseq = nseq; p.H = H;
+  p.total = chunks * H;
   p.scale = 0.08838834764831845f;
+  int dev = 0, sms = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess ||
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms < 1)
+    return KDA_ERR_LAUNCH;
   if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p.error), g_bwd_tc_error) != cudaSuccess)
     return KDA_ERR_LAUNCH;
   const int smem = bl::TOTAL + 1024;
@@ -716,7 +765,7 @@ int launch_bwd_chunk_tc(const bf16* q, const bf16* k, const bf16* v, const float
       cudaSuccess)
     return KDA_ERR_LAUNCH;
   StageScope timing(kStageBwdChunk, s);
-  kda_bwd_chunk_tc_kernel<<<dim3(chunks, H), NT, smem, s>>>(p);
+  kda_bwd_chunk_tc_kernel<<<(unsigned)(p.total < sms ? p.total : sms), NT, smem, s>>>(p);
   return cudaGetLastError() == cudaSuccess ? KDA_OK : KDA_ERR_LAUNCH;
 }
 
