@@ -67,7 +67,6 @@ constexpr int QN1 = 106496, KP1 = 118784;                       // column block 
 constexpr int QN2 = DO, KP2 = DO + 8192;                        // column block 2 (32 rows), after R1
 constexpr int QN3 = DO + 16384, KP3 = DO + 20480;               // column block 3 (16 rows)
 constexpr int DVO = HH;                                         // dv staging (phase 2, h tile is dead)
-constexpr int DQO = DO, DKO = DO + 16384, DGO = DO + 32768;     // dq, dk (bf16), dG (fp32) staging
 }  // namespace bl
 namespace tc {  // tensor-memory columns
 constexpr int DQ = 0, DKS = 64, DW = 128, DVB = 192, DKG = 256, X = 320, Y = 384, DAQK = 448, DL = 448;
@@ -150,7 +149,7 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
   extern __shared__ unsigned char smem_dyn[];
   // 1024-byte alignment by offset, so the compiler still knows this is shared memory
   unsigned char* sm = smem_dyn + ((1024u - (saddr(smem_dyn) & 1023u)) & 1023u);
-  uint64_t* bar = reinterpret_cast<uint64_t*>(sm + bl::MISC);    // [0] TMA, [1..6] UMMA groups
+  uint64_t* bar = reinterpret_cast<uint64_t*>(sm + bl::MISC);    // [0], [7] TMA; [1..6] UMMA groups
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm + bl::MISC + 64);
   volatile int* s_abort = reinterpret_cast<volatile int*>(sm + bl::MISC + 72);
   float* s_beta = reinterpret_cast<float*>(sm + bl::MISC + 128);          // [64]
@@ -166,7 +165,9 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
 
   if (warp == 0) tmem_alloc(tmem_slot, 512);
   if (tid == 0) {
-    for (int i = 0; i < 7; ++i) mbar_init(&bar[i], 1);
+    // arrival counts = number of threads that issue (and commit) products of that group
+    const int counts[8] = {1, 4, 3, 1, 1, 2, 4, 1};
+    for (int i = 0; i < 8; ++i) mbar_init(&bar[i], counts[i]);
     mbar_init_fence();
     *s_abort = 0;
   }
@@ -177,42 +178,40 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
   const uint32_t tl = tmem + ((uint32_t)(32 * quad) << 16);    // this warp's lane quadrant
   const unsigned char* sG = sm + bl::G;
 
-  // Loads of one work item, in three parts so that the next item's tiles can start arriving as
-  // soon as their shared-memory regions die:  A = h, dh (arms the barrier for all three parts);
-  // B = k, q, G, A;  C = dO, v_new, dv2, v.   Thread 0 only.
+  // Loads of one work item, in two parts so that the next item's tiles start arriving as soon as
+  // their shared-memory regions die.  Part 0 (barrier 0): h, dh, dO, v_new, dv2, v, A -- dead once
+  // the last products of the current item have completed.  Part 1 (barrier 7): k, q, G, whose
+  // tiles stage dk, dq, dG until the current item's stores have read them.  Thread 0 only.
   auto issue_loads = [&](int part, int chunk, int head, int64_t token0) {
     const int ty = (int)token0, tx = head * 128;
     if (part == 0) {
       const int yh = (chunk * H + head) * 128;
-      mbar_expect_tx(&bar[0], 2 * 32768 + 6 * 16384 + 8192 + 32768);
+      mbar_expect_tx(&bar[0], 2 * 32768 + 4 * 16384 + 8192);
       for (int b = 0; b < 2; ++b) {
         tma_load_2d(sm + bl::HH + b * 16384, &p.tm_h, 64 * b, yh, &bar[0]);
-        tma_load_2d(sm + bl::DHH + b * 16384, &p.tm_dh, 64 * b, yh, &bar[0]);
-      }
-    } else if (part == 1) {
-      for (int b = 0; b < 2; ++b) {
-        tma_load_2d(sm + bl::K + b * 8192, &p.tm_k, tx + 64 * b, ty, &bar[0]);
-        tma_load_2d(sm + bl::Q + b * 8192, &p.tm_q, tx + 64 * b, ty, &bar[0]);
-      }
-      tma_load_2d(sm + bl::AK, &p.tm_a, head * 64, ty, &bar[0]);
-      for (int b = 0; b < 4; ++b) tma_load_2d(sm + bl::G + b * 8192, &p.tm_g, tx + 32 * b, ty, &bar[0]);
-    } else {
-      for (int b = 0; b < 2; ++b) {
         tma_load_2d(sm + bl::DO + b * 8192, &p.tm_do, tx + 64 * b, ty, &bar[0]);
-        tma_load_2d(sm + bl::VN + b * 8192, &p.tm_vn, tx + 64 * b, ty, &bar[0]);
         tma_load_2d(sm + bl::DV2 + b * 8192, &p.tm_dv2, tx + 64 * b, ty, &bar[0]);
-        tma_load_2d(sm + bl::V + b * 8192, &p.tm_v, tx + 64 * b, ty, &bar[0]);
+        tma_load_2d(sm + bl::DHH + b * 16384, &p.tm_dh, 64 * b, yh, &bar[0]);
+        tma_load_2d(sm + bl::VN + b * 8192, &p.tm_vn, tx + 64 * b, ty, &bar[0]);
       }
+      for (int b = 0; b < 2; ++b) tma_load_2d(sm + bl::V + b * 8192, &p.tm_v, tx + 64 * b, ty, &bar[0]);
+      tma_load_2d(sm + bl::AK, &p.tm_a, head * 64, ty, &bar[0]);
+    } else {
+      mbar_expect_tx(&bar[7], 2 * 16384 + 32768);
+      for (int b = 0; b < 2; ++b) tma_load_2d(sm + bl::K + b * 8192, &p.tm_k, tx + 64 * b, ty, &bar[7]);
+      for (int b = 0; b < 4; ++b) tma_load_2d(sm + bl::G + b * 8192, &p.tm_g, tx + 32 * b, ty, &bar[7]);
+      for (int b = 0; b < 2; ++b) tma_load_2d(sm + bl::Q + b * 8192, &p.tm_q, tx + 64 * b, ty, &bar[7]);
     }
   };
 
   // persistent walk over the (chunk, head) work items
   uint32_t ph = 0;              // parity of this item's barrier phases
   int it = 0, rc = 0;
-  bool pre = false;             // parts A and B of this item's loads were issued by the previous item
+  bool pre = false;             // part 0 of this item's loads was issued by the previous item
   ChunkWork cw_next{};
   float beta_next = 0.f;
   for (int w = blockIdx.x; w < p.total; w += gridDim.x) {
+  tc_mark(p, it, 15);
   const int chunk = w / H, head = w - chunk * H;
   const ChunkWork cw = pre ? cw_next : locate_chunk(p.cu_seqlens, p.chunk_offsets, p.nseq, chunk);
   if (cw.valid == 0) continue;              // capacity slot past the last active chunk
@@ -221,28 +220,21 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
   if (tid < 64)
     s_beta[tid] = pre ? beta_next : (tid < valid ? p.beta[(cw.token0 + tid) * H + head] : 0.f);
   __syncthreads();     // the previous item's staging tiles have been read; beta is in place
+  tc_mark(p, it, 16);
   if (tid == 0) {
-    if (!pre) {
-      issue_loads(0, chunk, head, cw.token0);
+    if (!pre) issue_loads(0, chunk, head, cw.token0);
+    if (valid < 64) {          // the fix-up of a partial chunk needs every tile before the first product
+      tma_store_wait_read();
       issue_loads(1, chunk, head, cw.token0);
     }
-    issue_loads(2, chunk, head, cw.token0);
   }
-  // the next item: located (and its beta fetched) now, its loads issued as this item's tiles die
-  const int wn = w + (int)gridDim.x;
   int chunk_n = 0, head_n = 0;
   bool next_ok = false;
-  if (wn < p.total) {
-    chunk_n = wn / H;
-    head_n = wn - chunk_n * H;
-    cw_next = locate_chunk(p.cu_seqlens, p.chunk_offsets, p.nseq, chunk_n);
-    next_ok = cw_next.valid > 0;
-    if (tid < 64)
-      beta_next = (next_ok && tid < cw_next.valid) ? p.beta[(cw_next.token0 + tid) * H + head_n] : 0.f;
-  }
+  tc_mark(p, it, 17);
   auto body = [&]() -> int {
   tc_mark(p, it, 0);
   if (!mbar_wait(&bar[0], ph)) *s_abort = 1;
+  if (valid < 64 && !mbar_wait(&bar[7], ph)) *s_abort = 1;     // the fix-up below touches every tile
   tc_mark(p, it, 1);
 
   // partial tail chunk: rows >= valid hold another sequence's tokens or unwritten memory.  Zero them
@@ -267,21 +259,37 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
   __syncthreads();
   if (*s_abort) return 2;
 
-  // ---- phase 0 UMMAs --------------------------------------------------------------------------
-  if (tid == 0) {
+  // ---- phase 0 UMMAs: one issuing thread per accumulator (lane 0 of warps 0..3) -------------------
+  if (lid == 0 && warp < 4) {
     tc_fence_after();
     const uint32_t hh = saddr(sm + bl::HH), dhh = saddr(sm + bl::DHH), dO = saddr(sm + bl::DO),
                    vn = saddr(sm + bl::VN), dv2 = saddr(sm + bl::DV2);
-    const uint32_t i128 = instr_desc(128, 64, 0, 0), i128n = instr_desc(128, 64, 0, 0, 1),
-                   i64 = instr_desc(64, 64, 0, 0);
+    if (warp == 0) {
 #pragma unroll
-    for (int ks = 0; ks < 8; ++ks) {
-      umma(tmem + tc::DW, desc_kmajor(hh, ks, 16384), desc_kmajor(dv2, ks, 8192), i128n, ks > 0);
-      umma(tmem + tc::DAQK, desc_kmajor(dO, ks, 8192), desc_kmajor(vn, ks, 8192), i64, ks > 0);
-      umma(tmem + tc::DQ, desc_kmajor(hh, ks, 16384), desc_kmajor(dO, ks, 8192), i128, ks > 0);
-      umma(tmem + tc::DKS, desc_kmajor(dhh, ks, 16384), desc_kmajor(vn, ks, 8192), i128, ks > 0);
+      for (int ks = 0; ks < 8; ++ks)
+        umma(tmem + tc::DW, desc_kmajor(hh, ks, 16384), desc_kmajor(dv2, ks, 8192),
+             instr_desc(128, 64, 0, 0, 1), ks > 0);
+    } else if (warp == 1) {
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks)
+        umma(tmem + tc::DAQK, desc_kmajor(dO, ks, 8192), desc_kmajor(vn, ks, 8192),
+             instr_desc(64, 64, 0, 0), ks > 0);
+    } else if (warp == 2) {
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks)
+        umma(tmem + tc::DQ, desc_kmajor(hh, ks, 16384), desc_kmajor(dO, ks, 8192),
+             instr_desc(128, 64, 0, 0), ks > 0);
+    } else {
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks)
+        umma(tmem + tc::DKS, desc_kmajor(dhh, ks, 16384), desc_kmajor(vn, ks, 8192),
+             instr_desc(128, 64, 0, 0), ks > 0);
     }
     umma_commit(&bar[1]);
+    if (warp == 0 && valid == 64) {   // k, q, G: their tiles staged the previous item's dk, dq, dG
+      tma_store_wait_read();
+      issue_loads(1, chunk, head, cw.token0);
+    }
   }
   // meanwhile: hd[kappa] = sum_v h dh over this thread's quarter of v
   {
@@ -300,9 +308,21 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
     }
     s_hd[rq * 128 + L] = s;
   }
-  const float glast = ld_g(sG, valid - 1, L);
-
+  // the next work item: located (and its beta fetched) while the first products run
+  {
+    const int wn = w + (int)gridDim.x;
+    if (wn < p.total) {
+      chunk_n = wn / H;
+      head_n = wn - chunk_n * H;
+      cw_next = locate_chunk(p.cu_seqlens, p.chunk_offsets, p.nseq, chunk_n);
+      next_ok = cw_next.valid > 0;
+      if (tid < 64)
+        beta_next = (next_ok && tid < cw_next.valid) ? p.beta[(cw_next.token0 + tid) * H + head_n] : 0.f;
+    }
+  }
   tc_mark(p, it, 2);
+  if (!mbar_wait(&bar[7], ph)) *s_abort = 1;       // k, q, A, G, v have landed
+  const float glast = ld_g(sG, valid - 1, L);
   if (!mbar_wait(&bar[1], ph)) *s_abort = 1;
   tc_fence_after();
   __syncthreads();
@@ -350,26 +370,31 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
   __syncthreads();
 
   tc_mark(p, it, 4);
-  // ---- phase 1 UMMAs: dvb^T, dkgb^T, X -----------------------------------------------------------
-  if (tid == 0) {
+  // ---- phase 1 UMMAs: dvb^T, dkgb^T, X (three issuing threads) ------------------------------------
+  if (lid == 0 && warp < 3) {
     tc_fence_after();
     const uint32_t dv2 = saddr(sm + bl::DV2), ak = saddr(sm + bl::AK), dwt = saddr(sm + bl::DWT),
                    v = saddr(sm + bl::V), kgm = saddr(sm + bl::KGM);
+    if (warp == 0) {
 #pragma unroll
-    for (int ks = 0; ks < 4; ++ks) {
-      umma(tmem + tc::DVB, desc_mnmajor(dv2, ks, 8192), desc_mnmajor(ak, ks, 0),
-           instr_desc(128, 64, 1, 1), ks > 0);
-      umma(tmem + tc::DKG, desc_kmajor(dwt, ks, 0), desc_mnmajor(ak, ks, 0),
-           instr_desc(128, 64, 0, 1), ks > 0);
+      for (int ks = 0; ks < 4; ++ks)
+        umma(tmem + tc::DVB, desc_mnmajor(dv2, ks, 8192), desc_mnmajor(ak, ks, 0),
+             instr_desc(128, 64, 1, 1), ks > 0);
+    } else if (warp == 1) {
+#pragma unroll
+      for (int ks = 0; ks < 4; ++ks)
+        umma(tmem + tc::DKG, desc_kmajor(dwt, ks, 0), desc_mnmajor(ak, ks, 0),
+             instr_desc(128, 64, 0, 1), ks > 0);
+    } else {
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks)
+        umma(tmem + tc::X, desc_kmajor(dv2, ks, 8192), desc_kmajor(v, ks, 8192),
+             instr_desc(64, 64, 0, 0), ks > 0);
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks)
+        umma(tmem + tc::X, desc_mnmajor(dwt, ks, 0), desc_kmajor(kgm, ks, 8192),
+             instr_desc(64, 64, 1, 0), 1);
     }
-#pragma unroll
-    for (int ks = 0; ks < 8; ++ks)
-      umma(tmem + tc::X, desc_kmajor(dv2, ks, 8192), desc_kmajor(v, ks, 8192),
-           instr_desc(64, 64, 0, 0), ks > 0);
-#pragma unroll
-    for (int ks = 0; ks < 8; ++ks)
-      umma(tmem + tc::X, desc_mnmajor(dwt, ks, 0), desc_kmajor(kgm, ks, 8192),
-           instr_desc(64, 64, 1, 0), 1);
     umma_commit(&bar[2]);
   }
   // Row-type gated tiles  Kn_ri[j][kappa] = k_j 2^{R_ri - G_j},  j < 16 (ri + 1): the four tiles
@@ -395,6 +420,15 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
     }
   };
   build_row_tiles(0, 1536);
+  // sum_i k dks 2^{G_last - G_i} over this thread's rows: the last row of dG needs the block-wide sum
+  {
+    float a[16], kdk = 0.f;
+    tmem_ld16(tl + tc::DKS + r0, a);
+#pragma unroll
+    for (int ii = 0; ii < 16; ++ii)
+      kdk += ld_bf(sm + bl::K, 8192, r0 + ii, L) * a[ii] * fexp2(glast - ld_g(sG, r0 + ii, L));
+    s_kdk[rq * 128 + L] = kdk;
+  }
   if (!mbar_wait(&bar[2], ph)) *s_abort = 1;
   tc_fence_after();
   tc_mark(p, it, 5);
@@ -481,23 +515,28 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
   if (*s_abort) return 5;
 
   tc_mark(p, it, 8);
-  // ---- dL = -(Y A^T), and the dAqk half of the row-type products -------------------------------------
-  if (tid == 0) {
+  // ---- dL = -(Y A^T) (warp 0), and the dAqk half of the row-type products (warp 1) --------------------
+  if (lid == 0 && warp < 2) {
     tc_fence_after();
-    const uint32_t ak = saddr(sm + bl::AK), y = saddr(sm + bl::Y), da = saddr(sm + bl::DA);
+    if (warp == 0) {
+      const uint32_t ak = saddr(sm + bl::AK), y = saddr(sm + bl::Y);
 #pragma unroll
-    for (int ks = 0; ks < 4; ++ks)
-      umma(tmem + tc::DL, desc_kmajor(y, ks, 0), desc_kmajor(ak, ks, 0), instr_desc(64, 64, 0, 0, 1), ks > 0);
-    umma_commit(&bar[4]);
-    int off = 0;
+      for (int ks = 0; ks < 4; ++ks)
+        umma(tmem + tc::DL, desc_kmajor(y, ks, 0), desc_kmajor(ak, ks, 0), instr_desc(64, 64, 0, 0, 1), ks > 0);
+      umma_commit(&bar[4]);
+    } else {      // committed together with the dL half, on barrier 5
+      const uint32_t da = saddr(sm + bl::DA);
+      int off = 0;
 #pragma unroll
-    for (int ri = 0; ri < 4; ++ri) {
-      const int rows = 16 * (ri + 1);
-      const uint32_t kn = saddr(sm + bl::KN0 + off);
-      for (int ks = 0; ks <= ri; ++ks)
-        umma(tmem + tc::DVB + 16 * ri, desc_mnmajor(kn, ks, rows * 128), desc_kmajor(da + 2048 * ri, ks, 0),
-             instr_desc(128, 16, 1, 0), ks > 0);
-      off += rows * 256;
+      for (int ri = 0; ri < 4; ++ri) {
+        const int rows = 16 * (ri + 1);
+        const uint32_t kn = saddr(sm + bl::KN0 + off);
+#pragma unroll
+        for (int ks = 0; ks <= ri; ++ks)
+          umma(tmem + tc::DVB + 16 * ri, desc_mnmajor(kn, ks, rows * 128), desc_kmajor(da + 2048 * ri, ks, 0),
+               instr_desc(128, 16, 1, 0), ks > 0);
+        off += rows * 256;
+      }
     }
   }
   // meanwhile: column-type gated tiles.  Block cj holds rows 16 cj .. 63 of
@@ -548,7 +587,7 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
   __syncthreads();
   if (*s_abort) return 6;
 
-  auto issue_col = [&](int cj, int qoff, int koff) {   // thread 0
+  auto issue_col = [&](int cj, int qoff, int koff) {   // one issuing thread per column block
     const int rows = 64 - 16 * cj;
     const uint32_t qn = saddr(sm + qoff), kp = saddr(sm + koff);
     const uint32_t da = saddr(sm + bl::DA) + 2048 * cj + 32 * cj;
@@ -558,23 +597,31 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
       umma(tmem + tc::DW + 16 * cj, desc_mnmajor(qn, ks, rows * 128), smem_desc(da + ks * 2048, 0, 1024), id, ks > 0);
     for (int ks = 0; ks < 4 - cj; ++ks)
       umma(tmem + tc::DW + 16 * cj, desc_mnmajor(kp, ks, rows * 128), smem_desc(dl + ks * 2048, 0, 1024), id, 1);
+    umma_commit(&bar[6]);
   };
-  if (tid == 0) {
+  if (lid == 0 && warp < 4) {
     tc_fence_after();
-    const uint32_t dl = saddr(sm + bl::DL);
-    int off = 0;
+    if (warp == 0) {     // the dL half of the row-type products
+      const uint32_t dl = saddr(sm + bl::DL);
+      int off = 0;
 #pragma unroll
-    for (int ri = 0; ri < 4; ++ri) {     // the dL half of the row-type products
-      const int rows = 16 * (ri + 1);
-      const uint32_t kn = saddr(sm + bl::KN0 + off);
-      for (int ks = 0; ks <= ri; ++ks)
-        umma(tmem + tc::X + 16 * ri, desc_mnmajor(kn, ks, rows * 128), desc_kmajor(dl + 2048 * ri, ks, 0),
-             instr_desc(128, 16, 1, 0), ks > 0);
-      off += rows * 256;
+      for (int ri = 0; ri < 4; ++ri) {
+        const int rows = 16 * (ri + 1);
+        const uint32_t kn = saddr(sm + bl::KN0 + off);
+#pragma unroll
+        for (int ks = 0; ks <= ri; ++ks)
+          umma(tmem + tc::X + 16 * ri, desc_mnmajor(kn, ks, rows * 128), desc_kmajor(dl + 2048 * ri, ks, 0),
+               instr_desc(128, 16, 1, 0), ks > 0);
+        off += rows * 256;
+      }
+      umma_commit(&bar[5]);
+    } else if (warp == 1) {
+      umma_commit(&bar[5]);          // its dAqk half, issued one step earlier
+    } else if (warp == 2) {
+      issue_col(0, bl::QN0, bl::KP0);
+    } else {
+      issue_col(1, bl::QN1, bl::KP1);
     }
-    umma_commit(&bar[5]);
-    issue_col(0, bl::QN0, bl::KP0);
-    issue_col(1, bl::QN1, bl::KP1);
   }
   tc_mark(p, it, 10);
   if (!mbar_wait(&bar[5], ph)) *s_abort = 1;   // row-type tiles are free again
@@ -587,17 +634,16 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
   tc_fence_before();
   __syncthreads();
   if (*s_abort) return 7;
-  if (tid == 0) {
+  if (lid == 0 && warp < 2) {
     tc_fence_after();
-    issue_col(2, bl::QN2, bl::KP2);
-    issue_col(3, bl::QN3, bl::KP3);
-    umma_commit(&bar[6]);
+    if (warp == 0) issue_col(2, bl::QN2, bl::KP2);
+    else issue_col(3, bl::QN3, bl::KP3);
   }
   tc_mark(p, it, 11);
   if (!mbar_wait(&bar[6], ph)) *s_abort = 1;
   tc_fence_after();
   tc_mark(p, it, 12);
-  // h / dh regions are dead from here on: the next item's states start arriving
+  // every tile but k, q, G is dead from here on: the next item's tiles start arriving
   if (tid == 0 && next_ok) issue_loads(0, chunk_n, head_n, cw_next.token0);
 
   // ---- final epilogue: six accumulators, 8 rows at a time; thread = channel L, rows r0 .. r0 + 15 ------
@@ -605,12 +651,19 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
   //   dq = e (scale 2^R dq_inter + dq_intra)              e = 2^{G_i - R},  R  = G[r0]
   //   dk = 2^{G_last - G_i} dks + beta (2^G dkgb + e X1) + f dk2      f = 2^{R' - G_i}, R' = G[r0 + 15]
   //   dG = q dq - k (dk - 2 beta (...))  assembled term by term below; dbeta_i = sum_kappa k (2^G dkgb + e X1)
+  // Results are staged in place: dq over the q tile, dk over the k tile, dG over the G tile (every
+  // element of those tiles is read only by the thread that overwrites it).
   {
     const int constB = (L >> 6) * 8192 + (L & 7) * 2, cB = (L & 63) >> 3;
     const int constG = (L >> 5) * 8192 + (L & 3) * 4, cG = (L & 31) >> 2;
     const float gfirst = ld_g(sG, r0, L), rlast = ld_g(sG, r0 + 15, L);
     const float E0 = fexp2(gfirst), F0 = fexp2(glast - rlast), sE0 = p.scale * E0;
-    float kdk = 0.f, pb[16];
+    // last valid row of dG: + (sum_v h dh) 2^{G_last} + sum_i k dks 2^{G_last - G_i}
+    float hdv = 0.f;
+    if (rq == ((valid - 1) >> 4))
+      hdv = ((s_hd[L] + s_hd[128 + L] + s_hd[256 + L] + s_hd[384 + L]) * fexp2(glast) +
+             s_kdk[L] + s_kdk[128 + L] + s_kdk[256 + L] + s_kdk[384 + L]) * kLn2;
+    float pb[16];
 #pragma unroll
     for (int grp = 0; grp < 2; ++grp) {
       const int rb = r0 + 8 * grp;
@@ -633,20 +686,16 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
 #pragma unroll
       for (int ii = 0; ii < 8; ++ii) {
         const float dqv = e[ii] * fmaf(a[ii], sE0, a2[ii]);
-        const float qv = __bfloat162float(*reinterpret_cast<const bf16*>(rowB + bl::Q + oB[ii]));
-        dgr[ii] = qv * dqv;
-        a2[ii] = dqv;
+        bf16* cell = reinterpret_cast<bf16*>(rowB + bl::Q + oB[ii]);
+        dgr[ii] = __bfloat162float(*cell) * dqv;
+        *cell = __float2bfloat16(dqv);
       }
       tmem_ld8(tl + tc::DKS + rb, a);
-      // the staging tiles overlay the gated operand tiles, dead since the last products completed
 #pragma unroll
       for (int ii = 0; ii < 8; ++ii) {
-        *reinterpret_cast<bf16*>(rowB + bl::DQO + oB[ii]) = __float2bfloat16(a2[ii]);
         const float x = a[ii] * (f[ii] * F0);
-        const float kx = kr[ii] * x;
         dkr[ii] = x;
-        dgr[ii] -= kx;
-        kdk += kx;
+        dgr[ii] = fmaf(-kr[ii], x, dgr[ii]);
       }
       tmem_ld8(tl + tc::DKG + rb, a);
       tmem_ld8(tl + tc::X + rb, a2);
@@ -663,35 +712,27 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
 #pragma unroll
       for (int ii = 0; ii < 8; ++ii) {
         const float x = a[ii] * f[ii];
-        *reinterpret_cast<bf16*>(rowB + bl::DKO + oB[ii]) = __float2bfloat16(dkr[ii] + x);
-        *reinterpret_cast<float*>(rowG + bl::DGO + oG[ii]) = fmaf(-kr[ii], x, dgr[ii]) * kLn2;
+        *reinterpret_cast<bf16*>(rowB + bl::K + oB[ii]) = __float2bfloat16(dkr[ii] + x);
+        float dgv = fmaf(-kr[ii], x, dgr[ii]) * kLn2;
+        if (rb + ii == valid - 1) dgv += hdv;
+        *reinterpret_cast<float*>(rowG + bl::G + oG[ii]) = dgv;
       }
     }
     {
       const float tot = warp_transpose_reduce16(pb, lid);
       if ((lid & 1) == 0) s_db[256 + quad * 64 + r0 + (lid >> 1)] = tot;
     }
-    s_kdk[rq * 128 + L] = kdk;
   }
   tc_mark(p, it, 13);
-  __syncthreads();
-  if (tid == 0 && next_ok) issue_loads(1, chunk_n, head_n, cw_next.token0);   // k, q, G, A are dead
-  if (tid < 128) {    // last valid row of dG: + (sum_v h dh) 2^{G_last} + sum_i k dks 2^{G_last - G_i}
-    const float hdv = (s_hd[L] + s_hd[128 + L] + s_hd[256 + L] + s_hd[384 + L]) * fexp2(glast) +
-                      s_kdk[L] + s_kdk[128 + L] + s_kdk[256 + L] + s_kdk[384 + L];
-    float* cell = reinterpret_cast<float*>(sm + bl::DGO + (L >> 5) * 8192 + (valid - 1) * 128 +
-                                           (((((L & 31) >> 2) ^ ((valid - 1) & 7)) << 4) | ((L & 3) << 2)));
-    *cell += hdv * kLn2;
-  }
   fence_async_smem();
   __syncthreads();
   if (valid == 64) {
     if (tid == 0) {
       for (int b = 0; b < 2; ++b) {
-        tma_store_2d(&p.tm_dq, sm + bl::DQO + b * 8192, tx + 64 * b, ty);
-        tma_store_2d(&p.tm_dk, sm + bl::DKO + b * 8192, tx + 64 * b, ty);
+        tma_store_2d(&p.tm_dq, sm + bl::Q + b * 8192, tx + 64 * b, ty);
+        tma_store_2d(&p.tm_dk, sm + bl::K + b * 8192, tx + 64 * b, ty);
       }
-      for (int b = 0; b < 4; ++b) tma_store_2d(&p.tm_dg, sm + bl::DGO + b * 8192, tx + 32 * b, ty);
+      for (int b = 0; b < 4; ++b) tma_store_2d(&p.tm_dg, sm + bl::G + b * 8192, tx + 32 * b, ty);
       tma_store_commit();
     }
   } else {
@@ -699,13 +740,13 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
       const int r = idx >> 4, ch = idx & 15;
       const int64_t gi = ((cw.token0 + r) * H + head) * 128 + ch * 8;
       const int so = (ch >> 3) * 8192 + sw128_chunk(r, ch & 7);
-      *reinterpret_cast<uint4*>(p.dq + gi) = *reinterpret_cast<const uint4*>(sm + bl::DQO + so);
-      *reinterpret_cast<uint4*>(p.dk + gi) = *reinterpret_cast<const uint4*>(sm + bl::DKO + so);
+      *reinterpret_cast<uint4*>(p.dq + gi) = *reinterpret_cast<const uint4*>(sm + bl::Q + so);
+      *reinterpret_cast<uint4*>(p.dk + gi) = *reinterpret_cast<const uint4*>(sm + bl::K + so);
     }
     for (int idx = tid; idx < valid * 32; idx += NT) {
       const int r = idx >> 5, ch = idx & 31;
       *reinterpret_cast<float4*>(p.dg + ((cw.token0 + r) * H + head) * 128 + ch * 4) =
-          *reinterpret_cast<const float4*>(sm + bl::DGO + (ch >> 3) * 8192 + r * 128 + (((ch & 7) ^ (r & 7)) << 4));
+          *reinterpret_cast<const float4*>(sm + bl::G + (ch >> 3) * 8192 + r * 128 + (((ch & 7) ^ (r & 7)) << 4));
     }
   }
   if (tid < valid) {
@@ -718,12 +759,13 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
   return 0;
   };
   rc = body();
-  if (tid == 0) tma_store_wait_read();      // staged tiles must outlive the bulk stores' reads
+  tc_mark(p, it, 18);
   if (rc) break;
   pre = next_ok;
   ph ^= 1;
   ++it;
   }  // work items
+  if (tid == 0) tma_store_wait_read();      // staged tiles must outlive the bulk stores' reads
   if (rc && tid == 0 && p.error) atomicExch(p.error, rc);
   tc_fence_before();
   __syncthreads();

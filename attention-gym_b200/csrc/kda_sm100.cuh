@@ -187,13 +187,15 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes,
   d |= (uint64_t)2 << 61;
   return d;
 }
-// K-major operand: k-step `ks` (16 elements) of a tile whose boxes are `box_bytes` apart
+// K-major operand: k-step `ks` (16 elements) of a tile whose boxes are `box_bytes` apart.  The step
+// is added to the finished descriptor of the tile start (shared-memory addresses stay below
+// 2^18, so the 14-bit address field cannot carry): with a compile-time `ks` this is one add.
 __device__ __forceinline__ uint64_t desc_kmajor(uint32_t tile, int ks, uint32_t box_bytes) {
-  return smem_desc(tile + (ks >> 2) * box_bytes + (ks & 3) * 32, 16, 1024);
+  return smem_desc(tile, 16, 1024) + (uint64_t)(((ks >> 2) * box_bytes + (ks & 3) * 32) >> 4);
 }
 // MN-major operand: k-step `ks` (16 rows of 128 bytes); boxes (64 MN elements) `box_bytes` apart
 __device__ __forceinline__ uint64_t desc_mnmajor(uint32_t tile, int ks, uint32_t box_bytes) {
-  return smem_desc(tile + ks * 2048, box_bytes, 1024);
+  return smem_desc(tile, box_bytes, 1024) + (uint64_t)((ks * 2048) >> 4);
 }
 // instruction descriptor: bf16 x bf16 -> fp32
 __host__ __device__ __forceinline__ uint32_t instr_desc(int m, int n, int a_mn, int b_mn,
