@@ -16,7 +16,7 @@ namespace kda {
 int launch_state_bwd_tc(const bf16* w, const bf16* kg, const bf16* qg, const bf16* aqk, const bf16* dout,
                         const float* g, const float* dht, float* dh0, bf16* dh_out, bf16* dv2_out,
                         const int32_t* cu, const int32_t* co, int nseq, int H, int64_t tokens,
-                        cudaStream_t s);
+                        int chunks, cudaStream_t s);
 int launch_bwd_chunk_tc(const bf16* q, const bf16* k, const bf16* v, const float* g, const float* beta,
                         const bf16* akk, const bf16* h, const bf16* dh, const bf16* vnew,
                         const bf16* dv2, const bf16* dout, bf16* dq, bf16* dk, bf16* dv, float* dg,
@@ -32,6 +32,7 @@ int launch_recompute(const void* q, const void* k, const void* v, const float* g
 using kda::bf16;
 
 static long long* g_prof_buffer = nullptr;
+namespace kda { long long* debug_profile_buffer() { return g_prof_buffer; } }
 // Debugging aid: device buffer of 64 x 32 int64 that receives per-phase timestamps of the first
 // 64 chunks of head 0 from the backward chunk kernel (NULL switches it off).
 extern "C" int kda_debug_set_profile_buffer(void* buffer) {
@@ -77,7 +78,7 @@ static int chunk_bwd_impl(bool saved, const void* q, const void* k, const void* 
   const bf16* qb = (const bf16*)q; const bf16* kb = (const bf16*)k; const bf16* vb = (const bf16*)v;
   rc = kda::launch_state_bwd_tc(w, kg, qg, (const bf16*)aqk, (const bf16*)d_out, cum_gate,
                                 d_final_state, d_initial_state, dhbuf, dv2, cu_seqlens, chunk_offsets,
-                                nseq, heads, tokens, s);
+                                nseq, heads, tokens, num_chunks, s);
   if (rc) return rc;
   return kda::launch_bwd_chunk_tc(qb, kb, vb, cum_gate, beta, (const bf16*)akk, hbuf, dhbuf, vnew, dv2,
                                   (const bf16*)d_out, (bf16*)dq, (bf16*)dk, (bf16*)dv, dg, dbeta,

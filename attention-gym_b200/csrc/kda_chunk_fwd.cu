@@ -37,12 +37,13 @@ struct ChunkParams {
   int nseq, H;
   float scale;
   int64_t tokens;   // rows of the token-major buffers (bounds of the TMA tensor maps)
+  int chunks;       // chunk capacity: h_out holds chunks * H states (needed only with h_out)
 };
 
 int launch_state_fwd_tc(const bf16* w, const bf16* u, const bf16* kg, const bf16* qg, const bf16* aqk,
                         const float* g, const float* h0, float* ht, bf16* o, bf16* h_out,
                         bf16* vnew_out, const int32_t* cu, const int32_t* co, int nseq, int H,
-                        int64_t tokens, cudaStream_t s);
+                        int64_t tokens, int chunks, cudaStream_t s);
 
 // ------------------------------------------------------------------------------------------
 // intra_solve
@@ -295,7 +296,7 @@ int launch_wu(const ChunkParams& p, int chunks, cudaStream_t s) {
 }
 int launch_state_fwd(const ChunkParams& p, cudaStream_t s) {
   return launch_state_fwd_tc(p.w, p.u, p.kg, p.qg, p.aqk, p.g, p.h0, p.ht, p.o, p.h_out, p.vnew_out,
-                             p.cu_seqlens, p.chunk_offsets, p.nseq, p.H, p.tokens, s);
+                             p.cu_seqlens, p.chunk_offsets, p.nseq, p.H, p.tokens, p.chunks, s);
 }
 
 // Backward's recompute leg: w, u, kg, qg from the stored A, then the chunk-entry states h[c]
@@ -313,6 +314,7 @@ int launch_recompute(const void* q, const void* k, const void* v, const float* g
   p.cu_seqlens = cu; p.chunk_offsets = co; p.nseq = nseq; p.H = H;
   p.scale = 0.08838834764831845f;
   p.tokens = tokens;
+  p.chunks = chunks;
   int rc = launch_wu(p, chunks, s);
   if (rc) return rc;
   return launch_state_fwd(p, s);
@@ -349,6 +351,7 @@ static int chunk_fwd_impl(bool keep, const void* q, const void* k, const void* v
   // walk also leaves v_new and the chunk-entry states there
   p.vnew_out = keep ? ws + 4 * nd : nullptr;
   p.h_out = keep ? ws + 6 * nd : nullptr;
+  p.chunks = num_chunks;
   p.cu_seqlens = cu_seqlens; p.chunk_offsets = chunk_offsets; p.nseq = nseq; p.H = heads;
   p.scale = 0.08838834764831845f;  // 128^-0.5
   p.tokens = tokens;

@@ -2,16 +2,17 @@
 //
 //   v_new = u - w h ;  o = qg h + Aqk v_new ;  h <- diag(2^{G_last}) h + kg^T v_new
 //
-// One CTA (128 threads) walks the chunks of one (sequence, head).  The fp32 state h [128 x 128]
+// One CTA (256 threads) walks the chunks of one (sequence, head).  The fp32 state h [128 x 128]
 // lives in tensor memory for the whole walk (128 lanes x 128 columns) and never goes to HBM in
-// the forward pass; a second 128-column accumulator holds [w h ; qg h + Aqk v_new].
+// the forward pass; two more 128-column accumulators alternate as D1 = [w h ; qg h + Aqk v_new].
+// Warp w works on tensor-memory lanes 32 (w % 4) .. +31 and on the 64-column half w / 4.
 // Per chunk:
-//   a. every thread (= state row kappa = TMEM lane) reads its row of h, writes it as bf16 into the
-//      swizzled MN-major B tile, multiplies by the chunk decay and stores it back to TMEM;
+//   a. every thread reads its half row of h, writes it as bf16 into the swizzled MN-major B tile,
+//      multiplies by the chunk decay and stores it back to tensor memory;
 //   b. UMMA 128x128x128:  D1 = [w ; qg] h          (A: TMA tile, K-major; B: the h tile)
-//   c. threads 0..63 read D1 rows 0..63, form v_new = u - w h, write it as the bf16 B tile;
-//   d. UMMA 128x128x64:   D1 += [0 ; Aqk] v_new    and   h += kg^T v_new  (A: kg, MN-major)
-//   e. threads 64..127 read D1 rows 64..127 and store o.
+//   c. lane quadrants 0, 1 read D1 rows 0..63, form v_new = u - w h and write it as the bf16 B
+//      tile; meanwhile quadrants 2, 3 store the output rows (D1 rows 64..127) of the previous chunk;
+//   d. UMMA 128x128x64:   D1 += [0 ; Aqk] v_new    and   h += kg^T v_new  (A: kg, MN-major).
 // w, qg, kg, u, Aqk tiles arrive by TMA (128-byte swizzle) into a two-stage ring, one chunk ahead.
 // Replaces the reference's fwd/triton/chunk_delta_h.py:40-162 + fwd/triton/chunk_gla_fwd_o.py:202-226.
 // Every barrier wait is bounded; a wait that runs out raises the error word and the CTA leaves.
@@ -26,20 +27,33 @@ constexpr int D = 128;
 
 struct StateTcParams {
   CUtensorMap tm_w, tm_qg, tm_kg, tm_u, tm_aqk;
+  CUtensorMap tm_hout, tm_vnew, tm_o;      // result tiles leave shared memory with TMA stores
   const float* g; const float* h0; float* ht;
   bf16* o; bf16* h_out; bf16* vnew_out;
   const int32_t* cu_seqlens; const int32_t* chunk_offsets;
   int* error;
   int nseq, H;
   int use_u, use_o;
+  long long* prof;      // debugging aid: phase timestamps of chunk 10 of the first 64 CTAs (rows 32..63)
 };
+
+long long* debug_profile_buffer();
+
+__device__ __forceinline__ void st_mark(long long* prof, int c, int slot) {
+  if (prof && c == 10 && threadIdx.x == 0 && blockIdx.x < 64) {
+    long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    prof[blockIdx.x * 32 + 20 + slot] = t;
+  }
+}
 
 constexpr int kStageBytes = 32768 + 16384 + 16384 + 16384;   // A1, KG, U, A2
 struct StateTcLayout {
   static constexpr int A1 = 0, KG = 32768, U = 49152, A2 = 65536;
   static constexpr int H = 2 * kStageBytes;              // 163840
   static constexpr int VN = H + 32768;                   // 196608
-  static constexpr int BAR = VN + 16384;                 // 212992
+  static constexpr int OST = VN + 16384;                 // 212992: staging of one chunk's output rows
+  static constexpr int BAR = OST + 16384;                // 229376
   static constexpr int TOTAL = BAR + 1024;
 };
 
@@ -48,7 +62,9 @@ __device__ __forceinline__ void pack8(const float* x, uint4& o) {
   o.z = pack_bf16(x[4], x[5]); o.w = pack_bf16(x[6], x[7]);
 }
 
-__global__ void __launch_bounds__(128) kda_state_fwd_tc_kernel(const __grid_constant__ StateTcParams p) {
+constexpr int kStateThreads = 256;
+
+__global__ void __launch_bounds__(kStateThreads) kda_state_fwd_tc_kernel(const __grid_constant__ StateTcParams p) {
   extern __shared__ unsigned char smem_dyn[];
   // 1024-byte alignment by offset, so the compiler still knows this is shared memory
   unsigned char* smem = smem_dyn + ((1024u - (saddr(smem_dyn) & 1023u)) & 1023u);
@@ -58,7 +74,9 @@ __global__ void __launch_bounds__(128) kda_state_fwd_tc_kernel(const __grid_cons
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_full + 4);
   volatile int* s_abort = reinterpret_cast<volatile int*>(bar_full + 5);
 
-  const int tid = threadIdx.x, warp = tid >> 5;
+  const int tid = threadIdx.x, warp = tid >> 5, lid = tid & 31;
+  const int quad = warp & 3, half = warp >> 2;     // TMEM lane quadrant; 64-column half of the tiles
+  const int row = 32 * quad + lid;                 // TMEM lane = state row kappa / D1 row
   const int H = p.H;
   const int head = blockIdx.x % H, seq = blockIdx.x / H;
   const int64_t bos = p.cu_seqlens[seq], eos = p.cu_seqlens[seq + 1];
@@ -66,17 +84,18 @@ __global__ void __launch_bounds__(128) kda_state_fwd_tc_kernel(const __grid_cons
   const int nchunks = p.chunk_offsets[seq + 1] - chunk0;
   const int64_t sbase = ((int64_t)seq * H + head) * D * D;
 
-  if (warp == 0) tmem_alloc(tmem_slot, 256);
+  if (warp == 0) tmem_alloc(tmem_slot, 512);
   if (tid == 0) {
     mbar_init(&bar_full[0], 1); mbar_init(&bar_full[1], 1);
-    mbar_init(bar_mma1, 1); mbar_init(bar_mma2, 1);
+    mbar_init(bar_mma1, 1);
+    mbar_init(bar_mma2, p.use_o ? 2 : 1);          // one arrival per issuing thread
     mbar_init_fence();
     *s_abort = 0;
     tma_prefetch_desc(&p.tm_w); tma_prefetch_desc(&p.tm_qg); tma_prefetch_desc(&p.tm_kg);
     tma_prefetch_desc(&p.tm_u); tma_prefetch_desc(&p.tm_aqk);
   }
   // rows 0..63 of both A2 tiles stay zero: [0 ; Aqk] keeps the UMMA at M = 128
-  for (int idx = tid; idx < 2 * 512; idx += 128) {
+  for (int idx = tid; idx < 2 * 512; idx += kStateThreads) {
     int st = idx >> 9, off = (idx & 511) * 16;
     *reinterpret_cast<uint4*>(smem + st * kStageBytes + StateTcLayout::A2 + off) = make_uint4(0, 0, 0, 0);
   }
@@ -85,8 +104,11 @@ __global__ void __launch_bounds__(128) kda_state_fwd_tc_kernel(const __grid_cons
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
-  const uint32_t lane_off = (uint32_t)(32 * warp) << 16;
-  const uint32_t tDh = tmem + lane_off, tD1 = tmem + 128 + lane_off;
+  const uint32_t lane_off = (uint32_t)(32 * quad) << 16;
+  // state: columns 0..127; D1 = [w h ; qg h + Aqk v_new]: two buffers at columns 128 and 256, so the
+  // output rows of chunk c leave while the products of chunk c + 1 run
+  const uint32_t tDh = tmem + lane_off + 64 * half;
+  auto tD1 = [&](int c) { return tmem + 128 + 128 * (c & 1) + lane_off + 64 * half; };
 
   auto chunk_valid = [&](int c) {
     int64_t rem = eos - (bos + (int64_t)c * 64);
@@ -110,19 +132,20 @@ __global__ void __launch_bounds__(128) kda_state_fwd_tc_kernel(const __grid_cons
     if (p.use_o) tma_load_2d(st + StateTcLayout::A2 + 8192, &p.tm_aqk, head * 64, y, bar);
   };
 
-  if (tid == 0) {
+  if (tid == 64) {      // the TMA producer: lane 0 of a warp that is off the critical v_new path
     if (nchunks > 0) issue_stage(0);
     if (nchunks > 1) issue_stage(1);
   }
-  // initial state -> tensor memory (this thread owns state row `tid`)
+  // initial state -> tensor memory (this thread owns 64 columns of state row `row`)
   {
     float x[32];
 #pragma unroll 1
-    for (int cb = 0; cb < 4; ++cb) {
+    for (int cb = 0; cb < 2; ++cb) {
 #pragma unroll
       for (int i = 0; i < 32; i += 4) {
         float4 v4 = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (p.h0) v4 = *reinterpret_cast<const float4*>(p.h0 + sbase + (int64_t)tid * D + 32 * cb + i);
+        if (p.h0)
+          v4 = *reinterpret_cast<const float4*>(p.h0 + sbase + (int64_t)row * D + 64 * half + 32 * cb + i);
         x[i] = v4.x; x[i + 1] = v4.y; x[i + 2] = v4.z; x[i + 3] = v4.w;
       }
       tmem_st32(tDh + 32 * cb, x);
@@ -134,9 +157,28 @@ __global__ void __launch_bounds__(128) kda_state_fwd_tc_kernel(const __grid_cons
   const uint32_t sH = saddr(smem + StateTcLayout::H), sVN = saddr(smem + StateTcLayout::VN);
   bool failed = false;
 
+  // Output rows of chunk c (threads of lane quadrants 2, 3 = D1 rows 64..127), 64 columns each:
+  // into the staging tile (a full chunk, which then leaves with a TMA store) or straight to global
+  // memory (the last chunk of the sequence, which may be partial).
+  auto store_o = [&](int c, bool staged) {
+    const int64_t token0 = bos + (int64_t)c * 64;
+    const bool live = row - 64 < chunk_valid(c);
+    bf16* orow = p.o + ((token0 + (live ? row - 64 : 0)) * H + head) * D + 64 * half;
+    unsigned char* obox = smem + StateTcLayout::OST + half * 8192;
+    float x[64];
+    tmem_ld64(tD1(c), x);
+#pragma unroll
+    for (int qd = 0; qd < 8; ++qd) {
+      uint4 v;
+      pack8(x + 8 * qd, v);
+      if (staged) *reinterpret_cast<uint4*>(obox + sw128_chunk(row - 64, qd)) = v;
+      else if (live) *reinterpret_cast<uint4*>(orow + 8 * qd) = v;
+    }
+  };
+
   float glast = 0.f;
   if (nchunks > 0)
-    glast = p.g[((bos + chunk_valid(0) - 1) * H + head) * D + tid];
+    glast = p.g[((bos + chunk_valid(0) - 1) * H + head) * D + row];
 
   for (int c = 0; c < nchunks; ++c) {
     unsigned char* st = smem + (c & 1) * kStageBytes;
@@ -144,143 +186,157 @@ __global__ void __launch_bounds__(128) kda_state_fwd_tc_kernel(const __grid_cons
     const int valid = chunk_valid(c);
     const float dec = exp2f(glast);
     if (c + 1 < nchunks)
-      glast = p.g[((token0 + 64 + chunk_valid(c + 1) - 1) * H + head) * D + tid];
+      glast = p.g[((token0 + 64 + chunk_valid(c + 1) - 1) * H + head) * D + row];
 
+    st_mark(p.prof, c, 0);
     // ---- a. h row -> bf16 B tile (MN-major: rows kappa, boxes = 64-wide v halves); decay in place
     {
-      float x[32];
-#pragma unroll 1
-      for (int cb = 0; cb < 4; ++cb) {
-        tmem_ld32(tDh + 32 * cb, x);
-        unsigned char* box = smem + StateTcLayout::H + (cb >> 1) * 16384;
+      float x[64];
+      unsigned char* box = smem + StateTcLayout::H + half * 16384;
+      tmem_ld64(tDh, x);
 #pragma unroll
-        for (int qd = 0; qd < 4; ++qd) {
-          uint4 v;
-          pack8(x + 8 * qd, v);
-          *reinterpret_cast<uint4*>(box + sw128_chunk(tid, (cb & 1) * 4 + qd)) = v;
-          if (p.h_out)
-            *reinterpret_cast<uint4*>(p.h_out + (((int64_t)(chunk0 + c) * H + head) * D + tid) * D +
-                                      32 * cb + 8 * qd) = v;
-        }
-#pragma unroll
-        for (int i = 0; i < 32; ++i) x[i] *= dec;
-        tmem_st32(tDh + 32 * cb, x);
+      for (int qd = 0; qd < 8; ++qd) {
+        uint4 v;
+        pack8(x + 8 * qd, v);
+        *reinterpret_cast<uint4*>(box + sw128_chunk(row, qd)) = v;
       }
+#pragma unroll
+      for (int i = 0; i < 64; ++i) x[i] *= dec;
+      tmem_st64(tDh, x);
       tmem_st_wait();
     }
+    st_mark(p.prof, c, 1);
+    if (tid == 0) tma_store_wait_read();    // v_new / output staging of the previous chunk are free again
     fence_async_smem();
     tc_fence_before();
     __syncthreads();
+    st_mark(p.prof, c, 2);
     if (*s_abort) { failed = true; break; }
 
-    // ---- b. D1 = [w ; qg] h ----------------------------------------------------------------
+    // ---- b. D1 = [w ; qg] h ;  the bf16 state tile also leaves as h[c] (kept for the backward pass)
     if (tid == 0) {
+      if (p.h_out) {
+        const int yh = ((chunk0 + c) * H + head) * D;
+        tma_store_2d(&p.tm_hout, smem + StateTcLayout::H, 0, yh);
+        tma_store_2d(&p.tm_hout, smem + StateTcLayout::H + 16384, 64, yh);
+        tma_store_commit();
+      }
+      st_mark(p.prof, c, 10);
       if (!mbar_wait(&bar_full[c & 1], (c >> 1) & 1)) *s_abort = 1;
       tc_fence_after();
+      st_mark(p.prof, c, 11);
       const uint32_t a1 = saddr(st + StateTcLayout::A1);
 #pragma unroll
       for (int ks = 0; ks < 8; ++ks)
-        umma(tmem + 128, desc_kmajor(a1, ks, 16384), desc_mnmajor(sH, ks, 16384), idesc_kmn, ks > 0);
+        umma(tmem + 128 + 128 * (c & 1), desc_kmajor(a1, ks, 16384), desc_mnmajor(sH, ks, 16384),
+             idesc_kmn, ks > 0);
       umma_commit(bar_mma1);
     }
+    st_mark(p.prof, c, 3);
 
-    // ---- c. v_new = u - w h (threads 0..63); zero the kg rows past a partial chunk (64..127) ---
+    // ---- c. v_new = u - w h (lane quadrants 0, 1);  meanwhile quadrants 2, 3 store the output rows of
+    //         the previous chunk and zero the kg rows past a partial chunk
     if (!mbar_wait(&bar_full[c & 1], (c >> 1) & 1)) *s_abort = 1;
-    if (tid < 64) {
+    if (quad < 2) {
       if (!mbar_wait(bar_mma1, c & 1)) *s_abort = 1;
       tc_fence_after();
-      float x[32];
-#pragma unroll 1
-      for (int cb = 0; cb < 4; ++cb) {
-        tmem_ld32(tD1 + 32 * cb, x);
-        const unsigned char* ubox = st + StateTcLayout::U + (cb >> 1) * 8192;
-        unsigned char* vbox = smem + StateTcLayout::VN + (cb >> 1) * 8192;
+      st_mark(p.prof, c, 4);
+      float x[64];
+      const unsigned char* ubox = st + StateTcLayout::U + half * 8192;
+      unsigned char* vbox = smem + StateTcLayout::VN + half * 8192;
+      tmem_ld64(tD1(c), x);
 #pragma unroll
-        for (int qd = 0; qd < 4; ++qd) {
-          const int off = sw128_chunk(tid, (cb & 1) * 4 + qd);
-          float y[8];
-          if (p.use_u) {
-            uint4 u4 = *reinterpret_cast<const uint4*>(ubox + off);
-            float2 a = unpack_bf16(u4.x), b = unpack_bf16(u4.y), cc = unpack_bf16(u4.z),
-                   d = unpack_bf16(u4.w);
-            y[0] = a.x; y[1] = a.y; y[2] = b.x; y[3] = b.y; y[4] = cc.x; y[5] = cc.y; y[6] = d.x; y[7] = d.y;
-          } else {
+      for (int qd = 0; qd < 8; ++qd) {
+        const int off = sw128_chunk(row, qd);
+        float y[8];
+        if (p.use_u) {
+          uint4 u4 = *reinterpret_cast<const uint4*>(ubox + off);
+          float2 a = unpack_bf16(u4.x), b = unpack_bf16(u4.y), cc = unpack_bf16(u4.z),
+                 d = unpack_bf16(u4.w);
+          y[0] = a.x; y[1] = a.y; y[2] = b.x; y[3] = b.y; y[4] = cc.x; y[5] = cc.y; y[6] = d.x; y[7] = d.y;
+        } else {
 #pragma unroll
-            for (int i = 0; i < 8; ++i) y[i] = 0.f;
-          }
+          for (int i = 0; i < 8; ++i) y[i] = 0.f;
+        }
 #pragma unroll
-          for (int i = 0; i < 8; ++i) y[i] = tid < valid ? y[i] - x[8 * qd + i] : 0.f;
-          uint4 v;
-          pack8(y, v);
-          *reinterpret_cast<uint4*>(vbox + off) = v;
-          if (p.vnew_out && tid < valid)
-            *reinterpret_cast<uint4*>(p.vnew_out + ((token0 + tid) * H + head) * D + 32 * cb + 8 * qd) = v;
+        for (int i = 0; i < 8; ++i) y[i] = row < valid ? y[i] - x[8 * qd + i] : 0.f;
+        uint4 v;
+        pack8(y, v);
+        *reinterpret_cast<uint4*>(vbox + off) = v;
+        if (p.vnew_out && valid < 64 && row < valid)     // a partial chunk cannot use the tile store
+          *reinterpret_cast<uint4*>(p.vnew_out + ((token0 + row) * H + head) * D + 64 * half + 8 * qd) = v;
+      }
+    } else {
+      if (valid < 64) {
+        // rows >= valid of the kg tile hold another sequence's tokens (or unwritten memory)
+        for (int idx = (quad - 2) * 32 + lid + 64 * half; idx < (64 - valid) * 16; idx += 128) {
+          int r = valid + (idx >> 4), ch = idx & 15;
+          *reinterpret_cast<uint4*>(st + StateTcLayout::KG + (ch >> 3) * 8192 + sw128_chunk(r, ch & 7)) =
+              make_uint4(0, 0, 0, 0);
         }
       }
-    } else if (valid < 64) {
-      // rows >= valid of the kg tile hold another sequence's tokens (or unwritten memory)
-      for (int idx = tid - 64; idx < (64 - valid) * 16; idx += 64) {
-        int r = valid + (idx >> 4), ch = idx & 15;
-        *reinterpret_cast<uint4*>(st + StateTcLayout::KG + (ch >> 3) * 8192 + sw128_chunk(r, ch & 7)) =
-            make_uint4(0, 0, 0, 0);
-      }
+      if (p.use_o && c > 0) store_o(c - 1, true);
     }
+    st_mark(p.prof, c, 5);
+    if (tid == 0) tma_store_wait_read();    // the state tile is rewritten after the next barrier
     fence_async_smem();
     tc_fence_before();
     __syncthreads();
+    st_mark(p.prof, c, 6);
     if (*s_abort) { failed = true; break; }
 
-    // ---- d. D1 += [0 ; Aqk] v_new ;  h += kg^T v_new ----------------------------------------
+    // ---- d. h += kg^T v_new (thread 0);  D1 += [0 ; Aqk] v_new (thread 32); v_new and the previous
+    //         chunk's output rows leave
     if (tid == 0) {
-      tc_fence_after();
-      const uint32_t a2 = saddr(st + StateTcLayout::A2), kg = saddr(st + StateTcLayout::KG);
-      if (p.use_o) {
-#pragma unroll
-        for (int ks = 0; ks < 4; ++ks)
-          umma(tmem + 128, desc_kmajor(a2, ks, 0), desc_mnmajor(sVN, ks, 8192), idesc_kmn, 1);
+      const int x0 = head * D;
+      if (p.vnew_out && valid == 64) {
+        tma_store_2d(&p.tm_vnew, smem + StateTcLayout::VN, x0, (int)token0);
+        tma_store_2d(&p.tm_vnew, smem + StateTcLayout::VN + 8192, x0 + 64, (int)token0);
       }
+      if (p.use_o && c > 0) {
+        tma_store_2d(&p.tm_o, smem + StateTcLayout::OST, x0, (int)token0 - 64);
+        tma_store_2d(&p.tm_o, smem + StateTcLayout::OST + 8192, x0 + 64, (int)token0 - 64);
+      }
+      tma_store_commit();
+      tc_fence_after();
+      const uint32_t kg = saddr(st + StateTcLayout::KG);
 #pragma unroll
       for (int ks = 0; ks < 4; ++ks)
         umma(tmem, desc_mnmajor(kg, ks, 8192), desc_mnmajor(sVN, ks, 8192), idesc_mnmn, 1);
       umma_commit(bar_mma2);
+      st_mark(p.prof, c, 7);
+    } else if (tid == 32 && p.use_o) {
+      tc_fence_after();
+      const uint32_t a2 = saddr(st + StateTcLayout::A2);
+#pragma unroll
+      for (int ks = 0; ks < 4; ++ks)
+        umma(tmem + 128 + 128 * (c & 1), desc_kmajor(a2, ks, 0), desc_mnmajor(sVN, ks, 8192), idesc_kmn, 1);
+      umma_commit(bar_mma2);
     }
     if (!mbar_wait(bar_mma2, c & 1)) *s_abort = 1;
     tc_fence_after();
-    if (tid == 0 && c + 2 < nchunks) issue_stage(c + 2);
-
-    // ---- e. o rows (threads 64..127) ----------------------------------------------------------
-    if (p.use_o && tid >= 64) {   // warp-uniform: tensor-memory loads are whole-warp operations
-      float x[32];
-      const bool live = tid - 64 < valid;
-      bf16* orow = p.o + ((token0 + (live ? tid - 64 : 0)) * H + head) * D;
-#pragma unroll 1
-      for (int cb = 0; cb < 4; ++cb) {
-        tmem_ld32(tD1 + 32 * cb, x);
-#pragma unroll
-        for (int qd = 0; qd < 4; ++qd) {
-          uint4 v;
-          pack8(x + 8 * qd, v);
-          if (live) *reinterpret_cast<uint4*>(orow + 32 * cb + 8 * qd) = v;
-        }
-      }
-    }
+    st_mark(p.prof, c, 8);
+    if (tid == 64 && c + 2 < nchunks) issue_stage(c + 2);
+    st_mark(p.prof, c, 9);
   }
+  if (!failed && p.use_o && nchunks > 0 && quad >= 2) store_o(nchunks - 1, false);
+  if (tid == 0) tma_store_wait_read();
 
   if (!failed && p.ht) {
     float x[32];
 #pragma unroll 1
-    for (int cb = 0; cb < 4; ++cb) {
+    for (int cb = 0; cb < 2; ++cb) {
       tmem_ld32(tDh + 32 * cb, x);
 #pragma unroll
       for (int i = 0; i < 32; i += 4)
-        *reinterpret_cast<float4*>(p.ht + sbase + (int64_t)tid * D + 32 * cb + i) =
+        *reinterpret_cast<float4*>(p.ht + sbase + (int64_t)row * D + 64 * half + 32 * cb + i) =
             make_float4(x[i], x[i + 1], x[i + 2], x[i + 3]);
     }
   }
   if (failed && tid == 0 && p.error) atomicExch(p.error, 1);
   tc_fence_before();
   __syncthreads();
-  if (warp == 0) tmem_dealloc(tmem, 256);
+  if (warp == 0) tmem_dealloc(tmem, 512);
 }
 
 static __device__ int g_state_tc_error = 0;
@@ -289,7 +345,7 @@ static __device__ int g_state_tc_error = 0;
 int launch_state_fwd_tc(const bf16* w, const bf16* u, const bf16* kg, const bf16* qg, const bf16* aqk,
                         const float* g, const float* h0, float* ht, bf16* o, bf16* h_out,
                         bf16* vnew_out, const int32_t* cu, const int32_t* co, int nseq, int H,
-                        int64_t tokens, cudaStream_t s) {
+                        int64_t tokens, int chunks, cudaStream_t s) {
   if (nseq == 0) return KDA_OK;
   StateTcParams p;
   int* error = nullptr;
@@ -301,15 +357,23 @@ int launch_state_fwd_tc(const bf16* w, const bf16* u, const bf16* kg, const bf16
       !make_tensor_map(&p.tm_u, u ? u : w, tokens, cols, 64) ||
       !make_tensor_map(&p.tm_aqk, aqk, tokens, (int64_t)H * 64, 64))
     return KDA_ERR_LAUNCH;
+  // tensor maps of absent results are built over `w` and never used
+  if (!make_tensor_map(&p.tm_vnew, vnew_out ? vnew_out : w, tokens, cols, 64) ||
+      !make_tensor_map(&p.tm_o, o ? o : w, tokens, cols, 64))
+    return KDA_ERR_LAUNCH;
+  if (!make_tensor_map(&p.tm_hout, h_out ? h_out : w, h_out ? (int64_t)chunks * H * D : tokens,
+                       h_out ? D : cols, 128))
+    return KDA_ERR_LAUNCH;
   p.g = g; p.h0 = h0; p.ht = ht; p.o = o; p.h_out = h_out; p.vnew_out = vnew_out;
   p.cu_seqlens = cu; p.chunk_offsets = co; p.error = error; p.nseq = nseq; p.H = H;
   p.use_u = u != nullptr; p.use_o = o != nullptr;
+  p.prof = debug_profile_buffer();
   const int smem = StateTcLayout::TOTAL + 1024;
   if (cudaFuncSetAttribute(kda_state_fwd_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
       cudaSuccess)
     return KDA_ERR_LAUNCH;
   StageScope timing(kStageStateFwd, s);
-  kda_state_fwd_tc_kernel<<<(unsigned)(nseq * H), 128, smem, s>>>(p);
+  kda_state_fwd_tc_kernel<<<(unsigned)(nseq * H), kStateThreads, smem, s>>>(p);
   return cudaGetLastError() == cudaSuccess ? KDA_OK : KDA_ERR_LAUNCH;
 }
 
@@ -323,6 +387,7 @@ int launch_state_fwd_tc(const bf16* w, const bf16* u, const bf16* kg, const bf16
 // ------------------------------------------------------------------------------------------------
 struct StateBwdTcParams {
   CUtensorMap tm_w, tm_qg, tm_kg, tm_do, tm_aqk;
+  CUtensorMap tm_dhout, tm_dv2out;          // result tiles leave shared memory with TMA stores
   const float* g; const float* dht; float* dh0;
   bf16* dh_out; bf16* dv2_out;
   const int32_t* cu_seqlens; const int32_t* chunk_offsets;
@@ -339,7 +404,7 @@ struct StateBwdLayout {
   static constexpr int TOTAL = BAR + 1024;
 };
 
-__global__ void __launch_bounds__(128) kda_state_bwd_tc_kernel(const __grid_constant__ StateBwdTcParams p) {
+__global__ void __launch_bounds__(kStateThreads) kda_state_bwd_tc_kernel(const __grid_constant__ StateBwdTcParams p) {
   extern __shared__ unsigned char smem_dyn[];
   unsigned char* smem = smem_dyn + ((1024u - (saddr(smem_dyn) & 1023u)) & 1023u);
   uint64_t* bar_full = reinterpret_cast<uint64_t*>(smem + StateBwdLayout::BAR);
@@ -349,6 +414,8 @@ __global__ void __launch_bounds__(128) kda_state_bwd_tc_kernel(const __grid_cons
   volatile int* s_abort = reinterpret_cast<volatile int*>(bar_full + 5);
 
   const int tid = threadIdx.x, warp = tid >> 5, lid = tid & 31;
+  const int quad = warp & 3, half = warp >> 2;     // TMEM lane quadrant; 64-column half of the tiles
+  const int row = 32 * quad + lid;                 // TMEM lane = state row kappa
   const int H = p.H;
   const int head = blockIdx.x % H, seq = blockIdx.x / H;
   const int64_t bos = p.cu_seqlens[seq], eos = p.cu_seqlens[seq + 1];
@@ -359,7 +426,7 @@ __global__ void __launch_bounds__(128) kda_state_bwd_tc_kernel(const __grid_cons
   if (warp == 0) tmem_alloc(tmem_slot, 256);
   if (tid == 0) {
     mbar_init(&bar_full[0], 1); mbar_init(&bar_full[1], 1);
-    mbar_init(bar_mma1, 1); mbar_init(bar_mma2, 1);
+    mbar_init(bar_mma1, 2); mbar_init(bar_mma2, 1);      // one arrival per issuing thread
     mbar_init_fence();
     *s_abort = 0;
   }
@@ -367,8 +434,8 @@ __global__ void __launch_bounds__(128) kda_state_bwd_tc_kernel(const __grid_cons
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
-  const uint32_t lane_off = (uint32_t)(32 * warp) << 16;
-  const uint32_t tDh = tmem + lane_off, tDv = tmem + 128 + lane_off;
+  const uint32_t lane_off = (uint32_t)(32 * quad) << 16;
+  const uint32_t tDh = tmem + lane_off + 64 * half, tDv = tmem + 128 + lane_off + 64 * half;
 
   auto chunk_valid = [&](int c) {
     int64_t rem = eos - (bos + (int64_t)c * 64);
@@ -389,18 +456,19 @@ __global__ void __launch_bounds__(128) kda_state_bwd_tc_kernel(const __grid_cons
     }
     tma_load_2d(st + StateBwdLayout::AQK, &p.tm_aqk, head * 64, y, bar);
   };
-  if (tid == 0) {
+  if (tid == 64) {      // the TMA producer: lane 0 of a warp of its own
     if (nchunks > 0) issue_stage(0);
     if (nchunks > 1) issue_stage(1);
   }
   {
     float x[32];
 #pragma unroll 1
-    for (int cb = 0; cb < 4; ++cb) {
+    for (int cb = 0; cb < 2; ++cb) {
 #pragma unroll
       for (int i = 0; i < 32; i += 4) {
         float4 v4 = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (p.dht) v4 = *reinterpret_cast<const float4*>(p.dht + sbase + (int64_t)tid * D + 32 * cb + i);
+        if (p.dht)
+          v4 = *reinterpret_cast<const float4*>(p.dht + sbase + (int64_t)row * D + 64 * half + 32 * cb + i);
         x[i] = v4.x; x[i + 1] = v4.y; x[i + 2] = v4.z; x[i + 3] = v4.w;
       }
       tmem_st32(tDh + 32 * cb, x);
@@ -412,7 +480,7 @@ __global__ void __launch_bounds__(128) kda_state_bwd_tc_kernel(const __grid_cons
 
   float glast = 0.f;
   if (nchunks > 0)
-    glast = p.g[((bos + (int64_t)(nchunks - 1) * 64 + chunk_valid(nchunks - 1) - 1) * H + head) * D + tid];
+    glast = p.g[((bos + (int64_t)(nchunks - 1) * 64 + chunk_valid(nchunks - 1) - 1) * H + head) * D + row];
 
   for (int it = 0; it < nchunks; ++it) {
     const int c = nchunks - 1 - it;
@@ -420,13 +488,13 @@ __global__ void __launch_bounds__(128) kda_state_bwd_tc_kernel(const __grid_cons
     const int64_t token0 = bos + (int64_t)c * 64;
     const int valid = chunk_valid(c);
     const float dec = exp2f(glast);
-    if (c > 0) glast = p.g[((token0 - 1) * H + head) * D + tid];   // last row of the previous chunk
+    if (c > 0) glast = p.g[((token0 - 1) * H + head) * D + row];   // last row of the previous chunk
 
     if (!mbar_wait(&bar_full[it & 1], (it >> 1) & 1)) *s_abort = 1;
     if (valid < 64) {
       // rows past the tail hold another sequence's tokens or unwritten memory: they are contraction
       // rows of w, qg, dO and Aqk
-      for (int idx = tid; idx < (64 - valid) * 16; idx += 128) {
+      for (int idx = tid; idx < (64 - valid) * 16; idx += kStateThreads) {
         const int r = valid + (idx >> 4), ch = idx & 15;
         const int off = (ch >> 3) * 8192 + sw128_chunk(r, ch & 7);
         *reinterpret_cast<uint4*>(st + StateBwdLayout::W + off) = make_uint4(0, 0, 0, 0);
@@ -436,37 +504,37 @@ __global__ void __launch_bounds__(128) kda_state_bwd_tc_kernel(const __grid_cons
           *reinterpret_cast<uint4*>(st + StateBwdLayout::AQK + sw128_chunk(r, ch)) = make_uint4(0, 0, 0, 0);
       }
     }
-    // ---- a. dh row -> bf16 B tile + global copy; decay in place ---------------------------------
+    // ---- a. dh row -> bf16 B tile; decay in place ------------------------------------------------
     {
-      float x[32];
-#pragma unroll 1
-      for (int cb = 0; cb < 4; ++cb) {
-        tmem_ld32(tDh + 32 * cb, x);
-        unsigned char* box = smem + StateBwdLayout::DH + (cb >> 1) * 16384;
+      float x[64];
+      unsigned char* box = smem + StateBwdLayout::DH + half * 16384;
+      tmem_ld64(tDh, x);
 #pragma unroll
-        for (int qd = 0; qd < 4; ++qd) {
-          uint4 v;
-          pack8(x + 8 * qd, v);
-          *reinterpret_cast<uint4*>(box + sw128_chunk(tid, (cb & 1) * 4 + qd)) = v;
-          *reinterpret_cast<uint4*>(p.dh_out + (((int64_t)(chunk0 + c) * H + head) * D + tid) * D +
-                                    32 * cb + 8 * qd) = v;
-        }
-#pragma unroll
-        for (int i = 0; i < 32; ++i) x[i] *= dec;
-        tmem_st32(tDh + 32 * cb, x);
+      for (int qd = 0; qd < 8; ++qd) {
+        uint4 v;
+        pack8(x + 8 * qd, v);
+        *reinterpret_cast<uint4*>(box + sw128_chunk(row, qd)) = v;
       }
+#pragma unroll
+      for (int i = 0; i < 64; ++i) x[i] *= dec;
+      tmem_st64(tDh, x);
       tmem_st_wait();
     }
+    if (tid == 0) tma_store_wait_read();    // the dv2 tile of the previous step is free again
     fence_async_smem();
     tc_fence_before();
     __syncthreads();
     if (*s_abort) { failed = true; break; }
 
-    // ---- b. dv2 = kg dh + Aqk^T dO ;  dh += qg^T dO ------------------------------------------------
+    // ---- b. dv2 = kg dh + Aqk^T dO ;  dh += qg^T dO ;  the bf16 dh tile leaves as dh[c] ------------------
     if (tid == 0) {
+      const int yh = ((chunk0 + c) * H + head) * D;
+      tma_store_2d(&p.tm_dhout, smem + StateBwdLayout::DH, 0, yh);
+      tma_store_2d(&p.tm_dhout, smem + StateBwdLayout::DH + 16384, 64, yh);
+      tma_store_commit();
       tc_fence_after();
-      const uint32_t kg = saddr(st + StateBwdLayout::KG), qg = saddr(st + StateBwdLayout::QG),
-                     dO = saddr(st + StateBwdLayout::DO), aqk = saddr(st + StateBwdLayout::AQK);
+      const uint32_t kg = saddr(st + StateBwdLayout::KG), dO = saddr(st + StateBwdLayout::DO),
+                     aqk = saddr(st + StateBwdLayout::AQK);
 #pragma unroll
       for (int ks = 0; ks < 8; ++ks)
         umma(tmem + 128, desc_kmajor(kg, ks, 8192), desc_mnmajor(sDH, ks, 16384),
@@ -474,6 +542,10 @@ __global__ void __launch_bounds__(128) kda_state_bwd_tc_kernel(const __grid_cons
 #pragma unroll
       for (int ks = 0; ks < 4; ++ks)
         umma(tmem + 128, desc_mnmajor(aqk, ks, 0), desc_mnmajor(dO, ks, 8192), instr_desc(64, 128, 1, 1), 1);
+      umma_commit(bar_mma1);
+    } else if (tid == 32) {
+      tc_fence_after();
+      const uint32_t qg = saddr(st + StateBwdLayout::QG), dO = saddr(st + StateBwdLayout::DO);
 #pragma unroll
       for (int ks = 0; ks < 4; ++ks)
         umma(tmem, desc_mnmajor(qg, ks, 8192), desc_mnmajor(dO, ks, 8192), instr_desc(128, 128, 1, 1), 1);
@@ -483,32 +555,34 @@ __global__ void __launch_bounds__(128) kda_state_bwd_tc_kernel(const __grid_cons
     tc_fence_after();
     // ---- c. dv2 rows (M = 64 accumulator: row j on lane 32 (j / 16) + j % 16) -----------------------
     {
-      float x[32];
-      const int j = warp * 16 + lid;
-      const bool row = lid < 16;
-#pragma unroll 1
-      for (int cb = 0; cb < 4; ++cb) {
-        tmem_ld32(tDv + 32 * cb, x);
-        if (row) {
-          unsigned char* box = smem + StateBwdLayout::DV2 + (cb >> 1) * 8192;
+      float x[64];
+      const int j = quad * 16 + lid;
+      unsigned char* box = smem + StateBwdLayout::DV2 + half * 8192;
+      tmem_ld64(tDv, x);
+      if (lid < 16) {
 #pragma unroll
-          for (int qd = 0; qd < 4; ++qd) {
-            uint4 v = make_uint4(0, 0, 0, 0);
-            if (j < valid) pack8(x + 8 * qd, v);
-            *reinterpret_cast<uint4*>(box + sw128_chunk(j, (cb & 1) * 4 + qd)) = v;
-            if (j < valid)
-              *reinterpret_cast<uint4*>(p.dv2_out + ((token0 + j) * H + head) * D + 32 * cb + 8 * qd) = v;
-          }
+        for (int qd = 0; qd < 8; ++qd) {
+          uint4 v = make_uint4(0, 0, 0, 0);
+          if (j < valid) pack8(x + 8 * qd, v);
+          *reinterpret_cast<uint4*>(box + sw128_chunk(j, qd)) = v;
+          if (valid < 64 && j < valid)        // a partial chunk cannot use the tile store
+            *reinterpret_cast<uint4*>(p.dv2_out + ((token0 + j) * H + head) * D + 64 * half + 8 * qd) = v;
         }
       }
     }
+    if (tid == 0) tma_store_wait_read();    // the dh tile is rewritten after the next barrier
     fence_async_smem();
     tc_fence_before();
     __syncthreads();
     if (*s_abort) { failed = true; break; }
 
-    // ---- d. dh -= w^T dv2 ------------------------------------------------------------------------------
+    // ---- d. dh -= w^T dv2 ;  dv2 leaves -----------------------------------------------------------------
     if (tid == 0) {
+      if (valid == 64) {
+        tma_store_2d(&p.tm_dv2out, smem + StateBwdLayout::DV2, head * D, (int)token0);
+        tma_store_2d(&p.tm_dv2out, smem + StateBwdLayout::DV2 + 8192, head * D + 64, (int)token0);
+        tma_store_commit();
+      }
       tc_fence_after();
       const uint32_t w = saddr(st + StateBwdLayout::W);
 #pragma unroll
@@ -518,17 +592,18 @@ __global__ void __launch_bounds__(128) kda_state_bwd_tc_kernel(const __grid_cons
     }
     if (!mbar_wait(bar_mma2, it & 1)) *s_abort = 1;
     tc_fence_after();
-    if (tid == 0 && it + 2 < nchunks) issue_stage(it + 2);
+    if (tid == 64 && it + 2 < nchunks) issue_stage(it + 2);
   }
+  if (tid == 0) tma_store_wait_read();
 
   if (!failed && p.dh0) {
     float x[32];
 #pragma unroll 1
-    for (int cb = 0; cb < 4; ++cb) {
+    for (int cb = 0; cb < 2; ++cb) {
       tmem_ld32(tDh + 32 * cb, x);
 #pragma unroll
       for (int i = 0; i < 32; i += 4)
-        *reinterpret_cast<float4*>(p.dh0 + sbase + (int64_t)tid * D + 32 * cb + i) =
+        *reinterpret_cast<float4*>(p.dh0 + sbase + (int64_t)row * D + 64 * half + 32 * cb + i) =
             make_float4(x[i], x[i + 1], x[i + 2], x[i + 3]);
     }
   }
@@ -541,13 +616,15 @@ __global__ void __launch_bounds__(128) kda_state_bwd_tc_kernel(const __grid_cons
 int launch_state_bwd_tc(const bf16* w, const bf16* kg, const bf16* qg, const bf16* aqk, const bf16* dout,
                         const float* g, const float* dht, float* dh0, bf16* dh_out, bf16* dv2_out,
                         const int32_t* cu, const int32_t* co, int nseq, int H, int64_t tokens,
-                        cudaStream_t s) {
+                        int chunks, cudaStream_t s) {
   if (nseq == 0) return KDA_OK;
   StateBwdTcParams p;
   const int64_t cols = (int64_t)H * D;
   if (!make_tensor_map(&p.tm_w, w, tokens, cols, 64) || !make_tensor_map(&p.tm_kg, kg, tokens, cols, 64) ||
       !make_tensor_map(&p.tm_qg, qg, tokens, cols, 64) || !make_tensor_map(&p.tm_do, dout, tokens, cols, 64) ||
-      !make_tensor_map(&p.tm_aqk, aqk, tokens, (int64_t)H * 64, 64))
+      !make_tensor_map(&p.tm_aqk, aqk, tokens, (int64_t)H * 64, 64) ||
+      !make_tensor_map(&p.tm_dhout, dh_out, (int64_t)chunks * H * D, D, 128) ||
+      !make_tensor_map(&p.tm_dv2out, dv2_out, tokens, cols, 64))
     return KDA_ERR_LAUNCH;
   p.g = g; p.dht = dht; p.dh0 = dh0; p.dh_out = dh_out; p.dv2_out = dv2_out;
   p.cu_seqlens = cu; p.chunk_offsets = co; p.nseq = nseq; p.H = H;
@@ -559,7 +636,7 @@ int launch_state_bwd_tc(const bf16* w, const bf16* kg, const bf16* qg, const bf1
       cudaSuccess)
     return KDA_ERR_LAUNCH;
   StageScope timing(kStageStateBwd, s);
-  kda_state_bwd_tc_kernel<<<(unsigned)(nseq * H), 128, smem, s>>>(p);
+  kda_state_bwd_tc_kernel<<<(unsigned)(nseq * H), kStateThreads, smem, s>>>(p);
   return cudaGetLastError() == cudaSuccess ? KDA_OK : KDA_ERR_LAUNCH;
 }
 
