@@ -32,6 +32,17 @@ __device__ __forceinline__ float load_as_float(const void* p, int dtype, int64_t
   if (dtype == KDA_F16) return __half2float(reinterpret_cast<const __half*>(p)[i]);
   return reinterpret_cast<const float*>(p)[i];
 }
+// The same access split in two, for software prefetch: the raw bits are loaded now and turned into
+// a float only when they are needed, so the warp does not stall on the load in between.
+__device__ __forceinline__ uint32_t load_raw(const void* p, int dtype, int64_t i) {
+  if (dtype == KDA_F32) return reinterpret_cast<const uint32_t*>(p)[i];
+  return reinterpret_cast<const unsigned short*>(p)[i];
+}
+__device__ __forceinline__ float raw_to_float(uint32_t raw, int dtype) {
+  if (dtype == KDA_BF16) return __uint_as_float(raw << 16);
+  if (dtype == KDA_F16) return __half2float(__ushort_as_half((unsigned short)raw));
+  return __uint_as_float(raw);
+}
 __device__ __forceinline__ void store_from_float(void* p, int dtype, int64_t i, float x) {
   if (dtype == KDA_BF16) reinterpret_cast<bf16*>(p)[i] = __float2bfloat16(x);
   else if (dtype == KDA_F16) reinterpret_cast<__half*>(p)[i] = __float2half(x);

@@ -91,6 +91,34 @@ def test_decode_paged_pool():
     assert torch.equal(pool_gpu[untouched].cpu(), pool[untouched])
 
 
+def test_decode_ring_many_items():
+    """More (sequence, head) states than SMs: every persistent CTA walks several states through its
+    shared-memory ring, with padding slots in between; three steps in a row on the same pool."""
+    n, h, slots = 150, 4, 160
+    gen = torch.Generator().manual_seed(11)
+    pool = 0.02 * torch.randn(slots, h, 128, 128, generator=gen)
+    idx = torch.randperm(slots - 1, generator=gen)[:n].to(torch.int32) + 1
+    idx[::7] = 0                                            # padding rows
+    pool_gpu, ref_pool = pool.cuda(), pool.clone()
+    for step in range(3):
+        inp = orc.make_inputs(n, 1, h, 128, 128, seed=20 + step)
+        q, k, v, g = (inp[x].bfloat16() for x in ("q", "k", "v", "gate_log2"))
+        beta = inp["beta"].bfloat16()
+        o, _ = kda_b200.recurrent_kda(q.cuda(), k.cuda(), v.cuda(), g.cuda(), beta.cuda(), pool_gpu,
+                                      state_indices=idx.cuda())
+        live = (idx > 0).nonzero().flatten()
+        sl = idx[live].long()
+        ro, rs = orc.recurrent_kda_ref(q[live].float(), k[live].float(), v[live].float(),
+                                       g[live].float(), beta[live].float(), ref_pool[sl])
+        ref_pool[sl] = rs
+        assert o[(idx <= 0).nonzero().flatten().cuda()].abs().max() == 0
+        assert_normalised(o[live.cuda()].float(), ro, 2e-2, f"step {step} output")
+        assert_normalised(pool_gpu[sl.cuda()], rs, 1e-4, f"step {step} state")
+    spare = torch.ones(slots, dtype=torch.bool)
+    spare[idx[idx > 0].long()] = False
+    assert torch.equal(pool_gpu[spare.cuda()].cpu(), pool[spare])
+
+
 def test_decode_steps_match_chunk_core():
     """64 decode steps == one chunk of the chunked core (reference: test_kda_recurrent.py:173-204)."""
     inp = orc.make_inputs(2, 64, 2, 128, 128, seed=4)
