@@ -48,6 +48,9 @@ STAGE_BYTES = {
     # -> dq, dk, dv, dG, dbeta
     "bwd_chunk": 1024 + 6 * 256 + 512 + 128 + 4 + 3 * 256 + 512 + 4,
 }
+# DRAM bytes per (token, head) and launch that ncu measured (dram__bytes_read + dram__bytes_write on
+# the B=2 case, which grows in proportion to the units; see profiles/)
+NCU_TRAFFIC = {"bwd_chunk": 4369, "state_fwd": 2023, "state_bwd": 1779, "intra_solve": 1225, "wu": 2289}
 # the path's algorithmic minimum (inputs once, outputs once), bytes per token per head
 PATH_BYTES_FWD_BWD = 4620
 PATH_FLOP_FWD_BWD = 576171
@@ -258,15 +261,13 @@ def run_ours(args):
         per_launch_ms = tot / n
         units = tokens_per_step * H
         key = top
-        if top in ("state_fwd", "wu"):  # two launches per step with different traffic: average
-            per_unit = (STAGE_BYTES["state_fwd"] + STAGE_BYTES["state_fwd_recompute"]) / 2 \
-                if top == "state_fwd" else STAGE_BYTES["wu"]
-        else:
-            per_unit = STAGE_BYTES.get(key, 0)
+        # the default path keeps the forward intermediates: state_fwd also writes h[c] and v_new
+        per_unit = STAGE_BYTES["state_fwd_recompute"] if top == "state_fwd" else STAGE_BYTES.get(key, 0)
         achieved = per_unit * units / (per_launch_ms * 1e-3) / 1e9
         roofline = {"kernel": top, "bound": "hbm", "achieved": round(achieved, 1),
                     "peak": peaks["hbm_gbs"], "peak_source": peaks["source"], "unit": "GB/s",
-                    "frac": round(achieved / peaks["hbm_gbs"], 4), "traffic": None,
+                    "frac": round(achieved / peaks["hbm_gbs"], 4),
+                    "traffic": NCU_TRAFFIC[top] * units if top in NCU_TRAFFIC else None,
                     "bytes_per_token_head": per_unit, "ms_per_launch": round(per_launch_ms, 4)}
     path = {"hbm_frac": round(value * H * PATH_BYTES_FWD_BWD / 1e9 / world / peaks["hbm_gbs"], 4),
             "tensor_frac": round(value * H * PATH_FLOP_FWD_BWD / 1e12 / world / peaks["bf16_tflops"], 4),
