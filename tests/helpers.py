@@ -5,6 +5,10 @@ import torch
 
 def norm_err(actual, ref):
     """max |actual - ref| divided by max |ref| (errors are judged on normalised tensors)."""
+    if actual.is_cuda and ref.is_cuda and actual.numel() > (1 << 24):
+        # large tensors stay on the GPU (fp32 is ample for a max-norm of bf16-sized errors)
+        a, r = actual.detach().float(), ref.detach().float()
+        return float((a - r).abs().max() / max(float(r.abs().max()), 1e-12))
     a, r = actual.detach().double().cpu(), ref.detach().double().cpu()
     return float((a - r).abs().max() / max(float(r.abs().max()), 1e-12))
 
