@@ -69,6 +69,23 @@ __device__ __forceinline__ void block_mm16(float* dst, int ldd, const float* A, 
   dst[i * ldd + j] = sign * s;
 }
 
+// eight adjacent bf16 / fp32 values of a row-major shared-memory tile (16-byte accesses)
+__device__ __forceinline__ void ld8_bf(const bf16* p, float (&o)[8]) {
+  const uint4 u = *reinterpret_cast<const uint4*>(p);
+  const float2 a = unpack_bf16(u.x), b = unpack_bf16(u.y), c = unpack_bf16(u.z), d = unpack_bf16(u.w);
+  o[0] = a.x; o[1] = a.y; o[2] = b.x; o[3] = b.y; o[4] = c.x; o[5] = c.y; o[6] = d.x; o[7] = d.y;
+}
+__device__ __forceinline__ uint4 pack8_bf(const float (&x)[8]) {
+  uint4 u;
+  u.x = pack_bf16(x[0], x[1]); u.y = pack_bf16(x[2], x[3]);
+  u.z = pack_bf16(x[4], x[5]); u.w = pack_bf16(x[6], x[7]);
+  return u;
+}
+__device__ __forceinline__ void ld8_f(const float* p, float (&o)[8]) {
+  const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+  o[0] = a.x; o[1] = a.y; o[2] = a.z; o[3] = a.w; o[4] = b.x; o[5] = b.y; o[6] = b.z; o[7] = b.w;
+}
+
 __global__ void __launch_bounds__(256) kda_intra_solve_kernel(const ChunkParams p) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   IntraSmem& sm = *reinterpret_cast<IntraSmem*>(smem_raw);
@@ -99,23 +116,33 @@ __global__ void __launch_bounds__(256) kda_intra_solve_kernel(const ChunkParams 
   for (int ri = 0; ri < 4; ++ri) {
     const int ncol = 16 * (ri + 1);
     const float* R = sm.g + (16 * ri) * D;
-    // row operands (in place for q, separate for k): x_i 2^{G_i - R}
-    for (int idx = tid; idx < 16 * (D / 2); idx += 256) {
-      int r = idx / (D / 2), c = (idx % (D / 2)) * 2;
-      int i = 16 * ri + r;
-      float e0 = fexp2(sm.g[i * D + c] - R[c]), e1 = fexp2(sm.g[i * D + c + 1] - R[c + 1]);
-      float2 qv = unpack_bf16(*reinterpret_cast<uint32_t*>(&sm.q[i * LDD + c]));
-      float2 kv = unpack_bf16(*reinterpret_cast<uint32_t*>(&sm.k[i * LDD + c]));
-      *reinterpret_cast<uint32_t*>(&sm.q[i * LDD + c]) = pack_bf16(qv.x * e0, qv.y * e1);
-      *reinterpret_cast<uint32_t*>(&sm.rk[r * LDD + c]) = pack_bf16(kv.x * e0, kv.y * e1);
+    // row operands (in place for q, separate for k): x_i 2^{G_i - R}; one 8-channel piece per thread
+    {
+      const int r = tid >> 4, c = (tid & 15) * 8, i = 16 * ri + r;
+      float gi[8], rr[8], qq[8], kk[8];
+      ld8_f(sm.g + i * D + c, gi);
+      ld8_f(R + c, rr);
+      ld8_bf(sm.q + i * LDD + c, qq);
+      ld8_bf(sm.k + i * LDD + c, kk);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const float ex = fexp2(gi[e] - rr[e]);
+        qq[e] *= ex;
+        kk[e] *= ex;
+      }
+      *reinterpret_cast<uint4*>(sm.q + i * LDD + c) = pack8_bf(qq);
+      *reinterpret_cast<uint4*>(sm.rk + r * LDD + c) = pack8_bf(kk);
     }
     // column operand: k_j 2^{R - G_j}, j < ncol (entries with j > i are masked after the product)
-    for (int idx = tid; idx < ncol * (D / 2); idx += 256) {
-      int j = idx / (D / 2), c = (idx % (D / 2)) * 2;
-      float e0 = fexp2(fminf(R[c] - sm.g[j * D + c], 126.f));
-      float e1 = fexp2(fminf(R[c + 1] - sm.g[j * D + c + 1], 126.f));
-      float2 kv = unpack_bf16(*reinterpret_cast<uint32_t*>(&sm.k[j * LDD + c]));
-      *reinterpret_cast<uint32_t*>(&sm.kn[j * LDD + c]) = pack_bf16(kv.x * e0, kv.y * e1);
+    for (int task = tid; task < ncol * 16; task += 256) {
+      const int j = task >> 4, c = (task & 15) * 8;
+      float gj[8], rr[8], kk[8];
+      ld8_f(sm.g + j * D + c, gj);
+      ld8_f(R + c, rr);
+      ld8_bf(sm.k + j * LDD + c, kk);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) kk[e] *= fexp2(fminf(rr[e] - gj[e], 126.f));
+      *reinterpret_cast<uint4*>(sm.kn + j * LDD + c) = pack8_bf(kk);
     }
     __syncthreads();
     {
@@ -232,22 +259,30 @@ __global__ void __launch_bounds__(256) kda_wu_kernel(const ChunkParams p) {
   __syncthreads();
 
   const float* glast = sm.g + (valid - 1) * D;
-  for (int idx = tid; idx < 64 * (D / 2); idx += 256) {
-    int r = idx / (D / 2), c = (idx % (D / 2)) * 2;
-    float g0 = sm.g[r * D + c], g1 = sm.g[r * D + c + 1];
-    float e0 = fexp2(g0), e1 = fexp2(g1);
-    float2 kv = unpack_bf16(*reinterpret_cast<uint32_t*>(&sm.k[r * LDD + c]));
-    float2 vv = unpack_bf16(*reinterpret_cast<uint32_t*>(&sm.v[r * LDD + c]));
-    float b = sm.beta[r];
-    if (r < valid) {
-      int64_t gi = rowD + (int64_t)r * gld + c;
-      float2 qv = unpack_bf16(*reinterpret_cast<uint32_t*>(&sm.q[r * LDD + c]));
-      *reinterpret_cast<uint32_t*>(p.qg + gi) = pack_bf16(qv.x * e0 * p.scale, qv.y * e1 * p.scale);
-      *reinterpret_cast<uint32_t*>(p.kg + gi) =
-          pack_bf16(kv.x * fexp2(glast[c] - g0), kv.y * fexp2(glast[c + 1] - g1));
+  for (int task = tid; task < 64 * 16; task += 256) {      // one 8-channel piece of one row per task
+    const int r = task >> 4, c = (task & 15) * 8;
+    float g[8], gl[8], kk[8], vv[8], qq[8], kgv[8];
+    ld8_f(sm.g + r * D + c, g);
+    ld8_f(glast + c, gl);
+    ld8_bf(sm.k + r * LDD + c, kk);
+    ld8_bf(sm.v + r * LDD + c, vv);
+    ld8_bf(sm.q + r * LDD + c, qq);
+    const float b = sm.beta[r];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const float ex = fexp2(g[e]);
+      qq[e] = qq[e] * ex * p.scale;
+      kgv[e] = kk[e] * fexp2(gl[e] - g[e]);
+      kk[e] = kk[e] * ex * b;
+      vv[e] *= b;
     }
-    *reinterpret_cast<uint32_t*>(&sm.k[r * LDD + c]) = pack_bf16(kv.x * e0 * b, kv.y * e1 * b);
-    *reinterpret_cast<uint32_t*>(&sm.v[r * LDD + c]) = pack_bf16(vv.x * b, vv.y * b);
+    if (r < valid) {
+      const int64_t gi = rowD + (int64_t)r * gld + c;
+      *reinterpret_cast<uint4*>(p.qg + gi) = pack8_bf(qq);
+      *reinterpret_cast<uint4*>(p.kg + gi) = pack8_bf(kgv);
+    }
+    *reinterpret_cast<uint4*>(sm.k + r * LDD + c) = pack8_bf(kk);
+    *reinterpret_cast<uint4*>(sm.v + r * LDD + c) = pack8_bf(vv);
   }
   __syncthreads();
   const int mt = warp & 3, nh = warp >> 2;

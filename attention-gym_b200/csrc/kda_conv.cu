@@ -14,7 +14,7 @@
 namespace kda {
 
 constexpr int WMAX = 8;     // widest supported filter
-constexpr int CONV_TT = 32; // tokens per thread run
+constexpr int CONV_TT = 64; // tokens per thread run
 
 template <typename T> struct VecOf { static constexpr int N = 16 / sizeof(T); };
 
@@ -103,19 +103,172 @@ __device__ __forceinline__ void conv_walk(const ConvParams& p, int64_t t0, int64
   }
 }
 
+// raw 16-byte vector of adjacent channels (converted only when used, so loads can be issued ahead)
+template <typename T, int N>
+__device__ __forceinline__ void cvt_raw(const uint4& raw, float (&x)[N]) {
+  const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+  for (int i = 0; i < N; ++i) x[i] = (float)e[i];
+}
+// the same for N adjacent channels of any vector width (8 or 16 bytes)
+// two adjacent channels of a shared-memory tile / of the output
 template <typename T>
-__global__ void __launch_bounds__(128) conv_fwd_kernel(const ConvParams p) {
+__device__ __forceinline__ float2 unpack2(const T* p) {
+  if constexpr (sizeof(T) == 4) return *reinterpret_cast<const float2*>(p);
+  else return make_float2((float)p[0], (float)p[1]);
+}
+template <typename T>
+__device__ __forceinline__ void pack2(T* p, float a, float b) {
+  if constexpr (sizeof(T) == 4) *reinterpret_cast<float2*>(p) = make_float2(a, b);
+  else {
+    T v[2] = {(T)a, (T)b};
+    *reinterpret_cast<uint32_t*>(p) = *reinterpret_cast<uint32_t*>(v);
+  }
+}
+template <typename T, int N> struct RawVec { uint32_t w[N * sizeof(T) / 4]; };
+template <typename T, int N>
+__device__ __forceinline__ RawVec<T, N> ld_raw(const T* p) {
+  RawVec<T, N> r;
+  if constexpr (N * sizeof(T) == 16) {
+    const uint4 u = *reinterpret_cast<const uint4*>(p);
+    r.w[0] = u.x; r.w[1] = u.y; r.w[2] = u.z; r.w[3] = u.w;
+  } else if constexpr (N * sizeof(T) == 8) {
+    const uint2 u = *reinterpret_cast<const uint2*>(p);
+    r.w[0] = u.x; r.w[1] = u.y;
+  } else {
+    static_assert(N * sizeof(T) == 4, "4-, 8- or 16-byte vectors");
+    r.w[0] = *reinterpret_cast<const uint32_t*>(p);
+  }
+  return r;
+}
+template <typename T, int N>
+__device__ __forceinline__ void cvt_rawv(const RawVec<T, N>& raw, float (&x)[N]) {
+  const T* e = reinterpret_cast<const T*>(raw.w);
+#pragma unroll
+  for (int i = 0; i < N; ++i) x[i] = (float)e[i];
+}
+template <typename T, int N>
+__device__ __forceinline__ void st_vec(T* p, const float (&x)[N]) {
+  RawVec<T, N> r;
+  T* e = reinterpret_cast<T*>(r.w);
+#pragma unroll
+  for (int i = 0; i < N; ++i) e[i] = (T)x[i];
+  if constexpr (N * sizeof(T) == 16) *reinterpret_cast<uint4*>(p) = make_uint4(r.w[0], r.w[1], r.w[2], r.w[3]);
+  else if constexpr (N * sizeof(T) == 8) *reinterpret_cast<uint2*>(p) = make_uint2(r.w[0], r.w[1]);
+  else *reinterpret_cast<uint32_t*>(p) = r.w[0];
+}
+
+// Sequence that holds a run starting at token t0.  Returns true when the whole run [t0, t1) lies in
+// that sequence: the fast kernels then handle it, reading the history (or zeros) before the sequence
+// start and nothing past its end.  Runs that straddle a packed sequence boundary, and first runs
+// when the history gradient is wanted, go to the general kernels.
+__device__ __forceinline__ bool conv_run_simple(const ConvParams& p, int64_t t0, int64_t t1, int& seq,
+                                                int64_t& bos, int64_t& eos) {
+  if (p.cu_seqlens) {
+    if (t0 >= p.cu_seqlens[p.nseq]) return false;
+    seq = find_seq(p.cu_seqlens, p.nseq, t0);
+    bos = p.cu_seqlens[seq]; eos = p.cu_seqlens[seq + 1];
+  } else {
+    seq = (int)(t0 / p.T); bos = (int64_t)seq * p.T; eos = bos + p.T;
+  }
+  if (t1 > eos) return false;
+  return !(p.dstate && t0 - (p.W - 1) < bos);
+}
+
+// y for tokens [t0, t1) of a run inside one sequence, filter width W known at compile time: the
+// inputs are fetched four tokens ahead as raw vectors, the window slides through registers.
+template <typename T, int W>
+__device__ __forceinline__ void conv_fwd_run(const ConvParams& p, int64_t t0, int64_t t1, int c0, int seq,
+                                             int64_t bos) {
+  constexpr int N = VecOf<T>::N, B = 4;
+  const T* x = reinterpret_cast<const T*>(p.x);
+  const T* w = reinterpret_cast<const T*>(p.w);
+  const T* st = reinterpret_cast<const T*>(p.state);
+  T* y = reinterpret_cast<T*>(p.y);
+  const int64_t C = p.C;
+  float wr[N][W], win[W][N];
+#pragma unroll
+  for (int i = 0; i < N; ++i)
+#pragma unroll
+    for (int j = 0; j < W; ++j) wr[i][j] = (float)w[(int64_t)(c0 + i) * W + j];
+#pragma unroll
+  for (int j = 0; j < W - 1; ++j) {
+    const int64_t pos = t0 - (W - 1) + j;
+    if (pos >= bos) ldv<T, N>(x + pos * C + c0, win[j]);
+    else if (st) ldv<T, N>(st + ((int64_t)seq * (W - 1) + (pos - bos + W - 1)) * C + c0, win[j]);
+    else {
+#pragma unroll
+      for (int i = 0; i < N; ++i) win[j][i] = 0.f;
+    }
+  }
+  uint4 nxt[B];
+#pragma unroll
+  for (int b = 0; b < B; ++b)
+    if (t0 + b < t1) nxt[b] = *reinterpret_cast<const uint4*>(x + (t0 + b) * C + c0);
+  for (int64_t tb = t0; tb < t1; tb += B) {
+    uint4 cur[B];
+#pragma unroll
+    for (int b = 0; b < B; ++b) cur[b] = nxt[b];
+#pragma unroll
+    for (int b = 0; b < B; ++b)
+      if (tb + B + b < t1) nxt[b] = *reinterpret_cast<const uint4*>(x + (tb + B + b) * C + c0);
+#pragma unroll
+    for (int b = 0; b < B; ++b) {
+      if (tb + b < t1) {
+        cvt_raw<T, N>(cur[b], win[W - 1]);
+        float o[N];
+#pragma unroll
+        for (int i = 0; i < N; ++i) {
+          float acc = 0.f;
+#pragma unroll
+          for (int j = 0; j < W; ++j) acc = fmaf(wr[i][j], win[j][i], acc);
+          o[i] = p.act ? __fdividef(acc, 1.f + __expf(-acc)) : acc;
+        }
+        stv<T, N>(y + (tb + b) * C + c0, o);
+#pragma unroll
+        for (int j = 0; j < W - 1; ++j)
+#pragma unroll
+          for (int i = 0; i < N; ++i) win[j][i] = win[j + 1][i];
+      }
+    }
+  }
+}
+
+// token run of block bx: CONV_TT tokens; runs never straddle dense rows
+__device__ __forceinline__ void conv_run_of(const ConvParams& p, int bx, int64_t& t0, int64_t& t1) {
+  const int64_t total = (int64_t)p.batch * p.T;
+  if (p.cu_seqlens) { t0 = (int64_t)bx * CONV_TT; t1 = min(t0 + CONV_TT, total); }
+  else {
+    int rpr = (p.T + CONV_TT - 1) / CONV_TT;
+    int row = bx / rpr, rb = bx % rpr;
+    t0 = (int64_t)row * p.T + (int64_t)rb * CONV_TT;
+    t1 = min(t0 + CONV_TT, (int64_t)(row + 1) * p.T);
+  }
+}
+
+// width-4 filter, every run that lies inside one sequence
+template <typename T>
+__global__ void __launch_bounds__(128, 4) conv_fwd_fast_kernel(const ConvParams p) {
   constexpr int N = VecOf<T>::N;
   const int c0 = (blockIdx.y * 128 + threadIdx.x) * N;
   if (c0 >= p.C) return;
-  const int64_t total = (int64_t)p.batch * p.T;
+  int64_t t0, t1, bos, eos;
+  int seq;
+  conv_run_of(p, blockIdx.x, t0, t1);
+  if (t0 < t1 && conv_run_simple(p, t0, t1, seq, bos, eos)) conv_fwd_run<T, 4>(p, t0, t1, c0, seq, bos);
+}
+
+// any width, sequence starts, histories; with skip_interior != 0 only the runs the fast kernel left
+template <typename T>
+__global__ void __launch_bounds__(128) conv_fwd_kernel(const ConvParams p, int skip_interior) {
+  constexpr int N = VecOf<T>::N;
+  const int c0 = (blockIdx.y * 128 + threadIdx.x) * N;
+  if (c0 >= p.C) return;
   int64_t t0, t1;
-  if (p.cu_seqlens) { t0 = (int64_t)blockIdx.x * CONV_TT; t1 = min(t0 + CONV_TT, total); }
-  else {  // runs never straddle dense rows
-    int rpr = (p.T + CONV_TT - 1) / CONV_TT;
-    int row = blockIdx.x / rpr, rb = blockIdx.x % rpr;
-    t0 = (int64_t)row * p.T + (int64_t)rb * CONV_TT;
-    t1 = min(t0 + CONV_TT, (int64_t)(row + 1) * p.T);
+  conv_run_of(p, blockIdx.x, t0, t1);
+  {
+    int seq; int64_t bos, eos;
+    if (skip_interior && (t0 >= t1 || conv_run_simple(p, t0, t1, seq, bos, eos))) return;
   }
   const T* w = reinterpret_cast<const T*>(p.w);
   float wr[N][WMAX];
@@ -139,8 +292,10 @@ __global__ void __launch_bounds__(128) conv_fwd_kernel(const ConvParams p) {
 }
 
 // backward pass A: dpre = dy * act'(pre) (fp32 scratch), weight-gradient partials, history gradient
+// With edge_only != 0 (width-4 filters) only the runs the fast kernel left are processed, nothing is
+// written to the fp32 scratch, and the partials go to the second half of dw_part.
 template <typename T>
-__global__ void __launch_bounds__(256) conv_bwd_pre_kernel(const ConvParams p) {
+__global__ void __launch_bounds__(256) conv_bwd_pre_kernel(const ConvParams p, int edge_only) {
   constexpr int N = VecOf<T>::N;
   __shared__ float s_red[8][32][N];
   const int cx = threadIdx.x & 31, ty = threadIdx.x >> 5;
@@ -160,7 +315,8 @@ __global__ void __launch_bounds__(256) conv_bwd_pre_kernel(const ConvParams p) {
   for (int i = 0; i < N; ++i)
 #pragma unroll
     for (int j = 0; j < WMAX; ++j) dwacc[i][j] = 0.f;
-  if (live && t0 < t1) {
+  int seq_; int64_t bos_, eos_;
+  if (live && t0 < t1 && !(edge_only && conv_run_simple(p, t0, t1, seq_, bos_, eos_))) {
     const T* w = reinterpret_cast<const T*>(p.w);
     const T* dy = reinterpret_cast<const T*>(p.dy);
     float wr[N][WMAX];
@@ -184,9 +340,11 @@ __global__ void __launch_bounds__(256) conv_bwd_pre_kernel(const ConvParams p) {
         for (int j = 0; j < WMAX; ++j)
           if (j < p.W) dwacc[i][j] += d[i] * win[j][i];
       }
+      if (!edge_only) {
 #pragma unroll
-      for (int i = 0; i < N; i += 4)
-        *reinterpret_cast<float4*>(p.dpre + t * p.C + c0 + i) = make_float4(d[i], d[i + 1], d[i + 2], d[i + 3]);
+        for (int i = 0; i < N; i += 4)
+          *reinterpret_cast<float4*>(p.dpre + t * p.C + c0 + i) = make_float4(d[i], d[i + 1], d[i + 2], d[i + 3]);
+      }
       if (p.dstate && t - bos < p.W - 1) {  // window slots that fall before the sequence start
 #pragma unroll
         for (int j = 0; j < WMAX - 1; ++j) {
@@ -217,7 +375,7 @@ __global__ void __launch_bounds__(256) conv_bwd_pre_kernel(const ConvParams p) {
         float s = 0.f;
 #pragma unroll
         for (int y = 0; y < 8; ++y) s += s_red[y][cx][i];
-        p.dw_part[((int64_t)blockIdx.x * p.C + c0 + i) * p.W + j] = s;
+        p.dw_part[((int64_t)(blockIdx.x + (edge_only ? gridDim.x : 0)) * p.C + c0 + i) * p.W + j] = s;
       }
     }
     __syncthreads();
@@ -312,6 +470,209 @@ __global__ void __launch_bounds__(128) conv_decode_kernel(const void* x_, const 
   stv<T, N>(y + (int64_t)seq * C + c0, o);
 }
 
+// ------------------------------------------------------------------------------------------
+// Width-4 backward in one pass for every run that lies inside one sequence:
+//   pre[s] = sum_j w[j] x[s-3+j];  dpre[s] = dy[s] act'(pre[s]);  dx[t] = sum_j w[j] dpre[t+3-j]
+//   dw[j] += dpre[s] x[s-3+j]
+// A block walks the 8 runs of its 512-token span.  Per run it stages the x and dy tiles
+// ([64 + halo tokens] x 128 channels) in shared memory with 16-byte asynchronous copies; thread
+// (channel pair, token quarter) then slides the x and dpre windows through registers over its 16
+// tokens plus 3 recomputed ones past them, so no dpre ever goes to memory.  Tokens before the
+// sequence start read the history (or zeros), tokens past its end contribute nothing.
+// ------------------------------------------------------------------------------------------
+constexpr int kBwdCh = 128;                 // channels per block
+template <typename T>
+__global__ void __launch_bounds__(256) conv_bwd_fast_kernel(const ConvParams p) {
+  constexpr int W = 4, HALO = W - 1, XR = CONV_TT + 2 * HALO, YR = CONV_TT + HALO;
+  __shared__ __align__(16) T s_x[XR][kBwdCh];      // tokens t0-3 .. t1+2
+  __shared__ __align__(16) T s_y[YR][kBwdCh];      // tokens t0 .. t1+2
+  __shared__ float s_dw[4][kBwdCh][W];
+  const int tid = threadIdx.x, cp = tid & 63, qt = tid >> 6;
+  const int cb = blockIdx.y * kBwdCh;              // first channel of the block
+  const int64_t C = p.C, total = (int64_t)p.batch * p.T;
+  const T* x = reinterpret_cast<const T*>(p.x);
+  const T* dy = reinterpret_cast<const T*>(p.dy);
+  const T* st = reinterpret_cast<const T*>(p.state);
+  const T* w = reinterpret_cast<const T*>(p.w);
+  T* dx = reinterpret_cast<T*>(p.dx);
+  const int c0 = cb + 2 * cp;                      // this thread's two channels
+  const bool live = c0 < p.C;                      // C is even
+  float wr[2][W], dwacc[2][W];
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int j = 0; j < W; ++j) {
+      wr[i][j] = live ? (float)w[(int64_t)(c0 + i) * W + j] : 0.f;
+      dwacc[i][j] = 0.f;
+    }
+  constexpr int VPR = kBwdCh * sizeof(T) / 16;     // 16-byte vectors per tile row
+  constexpr int EPV = 16 / sizeof(T);              // elements per vector
+
+  for (int r = 0; r < 8; ++r) {
+    int64_t t0, t1;
+    if (p.cu_seqlens) { t0 = ((int64_t)blockIdx.x * 8 + r) * CONV_TT; t1 = min(t0 + CONV_TT, total); }
+    else {
+      int rpr = (p.T + 8 * CONV_TT - 1) / (8 * CONV_TT);
+      int row = blockIdx.x / rpr, rb = blockIdx.x % rpr;
+      t0 = (int64_t)row * p.T + ((int64_t)rb * 8 + r) * CONV_TT;
+      t1 = min(t0 + CONV_TT, (int64_t)(row + 1) * p.T);
+    }
+    int seq; int64_t bos, eos;
+    if (t0 >= t1 || !conv_run_simple(p, t0, t1, seq, bos, eos)) continue;   // uniform over the block
+    const int64_t send = min(t1 + HALO, eos);      // dpre exists for s < send
+    // ---- stage the tiles (rows outside the sequence: history or zeros) ----
+    for (int v = tid; v < XR * VPR; v += 256) {
+      const int row = v / VPR, col = (v % VPR) * EPV;
+      const int64_t pos = t0 - HALO + row;
+      T* dst = &s_x[row][col];
+      const bool ch_ok = cb + col < p.C;
+      if (ch_ok && pos >= bos && pos < send) cp_async16(dst, x + pos * C + cb + col, true);
+      else if (ch_ok && pos < bos && st)
+        cp_async16(dst, st + ((int64_t)seq * HALO + (pos - bos + HALO)) * C + cb + col, true);
+      else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+    }
+    for (int v = tid; v < YR * VPR; v += 256) {
+      const int row = v / VPR, col = (v % VPR) * EPV;
+      const int64_t pos = t0 + row;
+      T* dst = &s_y[row][col];
+      if (cb + col < p.C && pos < send) cp_async16(dst, dy + pos * C + cb + col, true);
+      else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+    }
+    cp_async_commit();
+    cp_async_wait<0>();
+    __syncthreads();
+    // ---- this thread: tokens [16 qt, 16 qt + 16) of the run, two channels ----
+    {
+      const int l0 = 16 * qt, owned = (int)(t1 - t0);   // local token index; rows of s_x are shifted by 3
+      float xw[W][2], dp[W][2];                         // circular: slot = local index & 3
+#pragma unroll
+      for (int j = 0; j < HALO; ++j) {
+        const float2 v = unpack2<T>(&s_x[l0 + j][2 * cp]);          // tokens l0-3 .. l0-1
+        xw[(l0 + j + 1) & 3][0] = v.x; xw[(l0 + j + 1) & 3][1] = v.y;
+        dp[(l0 + j + 1) & 3][0] = 0.f; dp[(l0 + j + 1) & 3][1] = 0.f;
+      }
+#pragma unroll
+      for (int k = 0; k < 16 + HALO; ++k) {             // l0 is a multiple of 4: slot = k & 3
+        const int l = l0 + k, b = k & 3;
+        const float2 xv = unpack2<T>(&s_x[l + HALO][2 * cp]);
+        const float2 gv = unpack2<T>(&s_y[l < YR ? l : YR - 1][2 * cp]);
+        xw[b][0] = xv.x; xw[b][1] = xv.y;
+        const float g[2] = {gv.x, gv.y};
+        const bool own = k < 16 && l < owned;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          float pre = 0.f;
+#pragma unroll
+          for (int j = 0; j < W; ++j) pre = fmaf(wr[i][j], xw[(b + 1 + j) & 3][i], pre);
+          float dact = 1.f;
+          if (p.act) {
+            const float sg = __fdividef(1.f, 1.f + __expf(-pre));
+            dact = sg * fmaf(pre, 1.f - sg, 1.f);
+          }
+          const float d = (l < YR) ? g[i] * dact : 0.f;
+          dp[b][i] = d;
+          if (own) {
+#pragma unroll
+            for (int j = 0; j < W; ++j) dwacc[i][j] = fmaf(d, xw[(b + 1 + j) & 3][i], dwacc[i][j]);
+          }
+        }
+        if (k >= HALO) {                                // dx[l-3] = w0 dpre[l] + ... + w3 dpre[l-3]
+          const int lt = l - HALO;
+          float o[2];
+#pragma unroll
+          for (int i = 0; i < 2; ++i) {
+            float acc = 0.f;
+#pragma unroll
+            for (int j = 0; j < W; ++j) acc = fmaf(wr[i][j], dp[(b + 4 - j) & 3][i], acc);
+            o[i] = acc;
+          }
+          if (live && lt < owned) pack2<T>(dx + (t0 + lt) * C + c0, o[0], o[1]);
+        }
+      }
+    }
+    __syncthreads();       // the tiles are rewritten by the next run
+  }
+  // reduce the four token quarters, then one partial per (block, channel, tap)
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int j = 0; j < W; ++j) s_dw[qt][2 * cp + i][j] = dwacc[i][j];
+  __syncthreads();
+  for (int e = tid; e < kBwdCh * W; e += 256) {
+    const int ch = e / W, j = e % W;
+    if (cb + ch < p.C)
+      p.dw_part[((int64_t)blockIdx.x * C + cb + ch) * W + j] =
+          s_dw[0][ch][j] + s_dw[1][ch][j] + s_dw[2][ch][j] + s_dw[3][ch][j];
+  }
+}
+
+// dx for the runs the fast kernel left (first and last run of a sequence): dpre is rebuilt on the
+// fly from x and dy, with the history or zeros before the sequence start.  Any width.
+template <typename T>
+__global__ void __launch_bounds__(128) conv_bwd_dx_edge_kernel(const ConvParams p) {
+  constexpr int N = VecOf<T>::N;
+  const int c0 = (blockIdx.y * 128 + threadIdx.x) * N;
+  if (c0 >= p.C) return;
+  int64_t t0, t1;
+  conv_run_of(p, blockIdx.x, t0, t1);
+  if (p.cu_seqlens) t1 = min(t1, (int64_t)p.cu_seqlens[p.nseq]);
+  {
+    int seq_; int64_t bos_, eos_;
+    if (t0 >= t1 || conv_run_simple(p, t0, t1, seq_, bos_, eos_)) return;
+  }
+  const T* x = reinterpret_cast<const T*>(p.x);
+  const T* w = reinterpret_cast<const T*>(p.w);
+  const T* dy = reinterpret_cast<const T*>(p.dy);
+  const T* st = reinterpret_cast<const T*>(p.state);
+  T* dx = reinterpret_cast<T*>(p.dx);
+  const int W = p.W;
+  const int64_t C = p.C;
+  float wr[N][WMAX];
+#pragma unroll
+  for (int i = 0; i < N; ++i)
+#pragma unroll
+    for (int j = 0; j < WMAX; ++j) wr[i][j] = j < W ? (float)w[(int64_t)(c0 + i) * W + j] : 0.f;
+  int seq; int64_t bos, eos;
+  if (p.cu_seqlens) { seq = find_seq(p.cu_seqlens, p.nseq, t0); bos = p.cu_seqlens[seq]; eos = p.cu_seqlens[seq + 1]; }
+  else { seq = (int)(t0 / p.T); bos = (int64_t)seq * p.T; eos = bos + p.T; }
+  for (int64_t t = t0; t < t1; ++t) {
+    while (t >= eos) { ++seq; bos = eos; eos = p.cu_seqlens ? p.cu_seqlens[seq + 1] : bos + p.T; }
+    float o[N];
+#pragma unroll
+    for (int i = 0; i < N; ++i) o[i] = 0.f;
+    for (int j = 0; j < W; ++j) {
+      const int64_t src = t + (W - 1) - j;
+      if (src >= eos) continue;
+      float pre[N], g[N];
+#pragma unroll
+      for (int i = 0; i < N; ++i) pre[i] = 0.f;
+      for (int jj = 0; jj < W; ++jj) {
+        const int64_t pos = src - (W - 1) + jj;
+        float xv[N];
+        if (pos >= bos) ldv<T, N>(x + pos * C + c0, xv);
+        else if (st) ldv<T, N>(st + ((int64_t)seq * (W - 1) + (pos - bos + W - 1)) * C + c0, xv);
+        else {
+#pragma unroll
+          for (int i = 0; i < N; ++i) xv[i] = 0.f;
+        }
+#pragma unroll
+        for (int i = 0; i < N; ++i)
+#pragma unroll
+          for (int q = 0; q < WMAX; ++q) if (q == jj) pre[i] += wr[i][q] * xv[i];
+      }
+      ldv<T, N>(dy + src * C + c0, g);
+#pragma unroll
+      for (int i = 0; i < N; ++i) {
+        float dact = 1.f;
+        if (p.act) { const float sg = 1.f / (1.f + expf(-pre[i])); dact = sg * (1.f + pre[i] * (1.f - sg)); }
+#pragma unroll
+        for (int q = 0; q < WMAX; ++q) if (q == j) o[i] += wr[i][q] * g[i] * dact;
+      }
+    }
+    stv<T, N>(dx + t * C + c0, o);
+  }
+}
+
 static int conv_check(const ConvParams& p) {
   if (!p.x || !p.w || p.C <= 0 || p.W < 1 || p.W > WMAX || p.batch < 1 || p.T < 1) return KDA_ERR_ARG;
   if (p.cu_seqlens && p.batch != 1) return KDA_ERR_ARG;
@@ -326,7 +687,9 @@ static int conv_fwd_launch(const ConvParams& p, cudaStream_t s) {
   int64_t runs = p.cu_seqlens ? (total + CONV_TT - 1) / CONV_TT
                               : (int64_t)p.batch * ((p.T + CONV_TT - 1) / CONV_TT);
   dim3 grid((unsigned)runs, (unsigned)((p.C / N + 127) / 128));
-  conv_fwd_kernel<T><<<grid, 128, 0, s>>>(p);
+  const int fast = p.W == 4;
+  if (fast) conv_fwd_fast_kernel<T><<<grid, 128, 0, s>>>(p);
+  conv_fwd_kernel<T><<<grid, 128, 0, s>>>(p, fast);
   return cudaGetLastError() == cudaSuccess ? KDA_OK : KDA_ERR_LAUNCH;
 }
 
@@ -334,10 +697,26 @@ template <typename T>
 static int conv_bwd_launch(const ConvParams& p, int64_t blocks, cudaStream_t s) {
   constexpr int N = VecOf<T>::N;
   if (p.C % N) return KDA_ERR_UNSUPPORTED;
+  // dw_part holds 2 * blocks partial slots: [0, blocks) and [blocks, 2 blocks)
   dim3 grid((unsigned)blocks, (unsigned)((p.C / N + 31) / 32));
-  conv_bwd_pre_kernel<T><<<grid, 256, 0, s>>>(p);
-  if (cudaGetLastError() != cudaSuccess) return KDA_ERR_LAUNCH;
   int64_t total = (int64_t)p.batch * p.T;
+  if constexpr (sizeof(T) == 2) if (p.W == 4) {
+    // one-pass kernel for the runs inside one sequence, the general kernels for the other runs
+    if (p.C % 8) return KDA_ERR_UNSUPPORTED;
+    dim3 gridf((unsigned)blocks, (unsigned)((p.C + kBwdCh - 1) / kBwdCh));
+    conv_bwd_fast_kernel<T><<<gridf, 256, 0, s>>>(p);
+    conv_bwd_pre_kernel<T><<<grid, 256, 0, s>>>(p, 1);
+    int64_t runs = p.cu_seqlens ? (total + CONV_TT - 1) / CONV_TT
+                                : (int64_t)p.batch * ((p.T + CONV_TT - 1) / CONV_TT);
+    dim3 grid3((unsigned)runs, (unsigned)((p.C / N + 127) / 128));
+    conv_bwd_dx_edge_kernel<T><<<grid3, 128, 0, s>>>(p);
+    return cudaGetLastError() == cudaSuccess ? KDA_OK : KDA_ERR_LAUNCH;
+  }
+  if (!p.dpre) return KDA_ERR_ARG;
+  if (cudaMemsetAsync(p.dw_part + blocks * p.C * p.W, 0, sizeof(float) * blocks * p.C * p.W, s) != cudaSuccess)
+    return KDA_ERR_LAUNCH;
+  conv_bwd_pre_kernel<T><<<grid, 256, 0, s>>>(p, 0);
+  if (cudaGetLastError() != cudaSuccess) return KDA_ERR_LAUNCH;
   dim3 grid2((unsigned)((total + CONV_TT - 1) / CONV_TT), (unsigned)((p.C / N + 127) / 128));
   conv_bwd_dx_kernel<T><<<grid2, 128, 0, s>>>(p);
   return cudaGetLastError() == cudaSuccess ? KDA_OK : KDA_ERR_LAUNCH;
@@ -360,10 +739,15 @@ extern "C" int kda_conv1d_fwd(const void* x, const void* weight, const void* ini
   return kda::conv_fwd_launch<float>(p, s);
 }
 
-extern "C" int64_t kda_conv1d_bwd_blocks(int batch, int tokens, int packed) {
+// launch blocks of the backward kernels (each covers 8 runs of CONV_TT tokens)
+static int64_t conv_bwd_launch_blocks(int batch, int tokens, int packed) {
   const int64_t span = 8 * kda::CONV_TT;
   if (packed) return ((int64_t)batch * tokens + span - 1) / span;
   return (int64_t)batch * ((tokens + span - 1) / span);
+}
+// partial slots of dw_partial: two per launch block (interior runs, sequence-edge runs)
+extern "C" int64_t kda_conv1d_bwd_blocks(int batch, int tokens, int packed) {
+  return 2 * conv_bwd_launch_blocks(batch, tokens, packed);
 }
 
 extern "C" int kda_conv1d_bwd(const void* x, const void* weight, const void* initial_state,
@@ -375,10 +759,10 @@ extern "C" int kda_conv1d_bwd(const void* x, const void* weight, const void* ini
   p.x = x; p.w = weight; p.state = initial_state; p.dy = dy; p.dx = dx; p.dpre = dpre_scratch;
   p.dw_part = dw_partial; p.dstate = dstate; p.cu_seqlens = cu_seqlens; p.nseq = nseq;
   p.batch = batch; p.T = tokens; p.C = channels; p.W = width; p.act = activation;
-  if (!dy || !dx || !dw_partial || !dpre_scratch) return KDA_ERR_ARG;
+  if (!dy || !dx || !dw_partial) return KDA_ERR_ARG;     // dpre_scratch is needed only when width != 4
   int rc = kda::conv_check(p);
   if (rc) return rc;
-  int64_t blocks = kda_conv1d_bwd_blocks(batch, tokens, cu_seqlens != nullptr);
+  int64_t blocks = conv_bwd_launch_blocks(batch, tokens, cu_seqlens != nullptr);
   cudaStream_t s = (cudaStream_t)stream;
   if (dtype == KDA_BF16) return kda::conv_bwd_launch<__nv_bfloat16>(p, blocks, s);
   if (dtype == KDA_F16) return kda::conv_bwd_launch<__half>(p, blocks, s);

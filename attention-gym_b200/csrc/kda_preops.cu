@@ -127,6 +127,26 @@ __device__ __forceinline__ void store4(void* p, int dt, int64_t i, const float (
   }
 }
 
+// load4 split in two for software prefetch: raw bits now (8 bytes for 16-bit types, 16 for fp32),
+// floats when they are needed, so the warp does not wait on the load in between
+__device__ __forceinline__ uint4 load4_raw(const void* p, int dt, int64_t i) {
+  if (dt == KDA_F32) return *reinterpret_cast<const uint4*>(reinterpret_cast<const float*>(p) + i);
+  const uint2 u = *reinterpret_cast<const uint2*>(reinterpret_cast<const unsigned short*>(p) + i);
+  return make_uint4(u.x, u.y, 0u, 0u);
+}
+__device__ __forceinline__ void raw4_to_float(const uint4& r, int dt, float (&x)[4]) {
+  if (dt == KDA_BF16) {
+    float2 a = unpack_bf16(r.x), b = unpack_bf16(r.y);
+    x[0] = a.x; x[1] = a.y; x[2] = b.x; x[3] = b.y;
+  } else if (dt == KDA_F16) {
+    __half2 a = *reinterpret_cast<const __half2*>(&r.x), b = *reinterpret_cast<const __half2*>(&r.y);
+    x[0] = __low2float(a); x[1] = __high2float(a); x[2] = __low2float(b); x[3] = __high2float(b);
+  } else {
+    x[0] = __uint_as_float(r.x); x[1] = __uint_as_float(r.y);
+    x[2] = __uint_as_float(r.z); x[3] = __uint_as_float(r.w);
+  }
+}
+
 __global__ void __launch_bounds__(128) gate_cumsum_fwd_kernel(const GateParams p) {
   const int HK = p.H * p.K;
   const int f0 = (blockIdx.y * 128 + threadIdx.x) * 4;
@@ -137,18 +157,34 @@ __global__ void __launch_bounds__(128) gate_cumsum_fwd_kernel(const GateParams p
   const float4 b4 = *reinterpret_cast<const float4*>(p.dt_bias + f0);
   const float bias[4] = {b4.x, b4.y, b4.z, b4.w};
   float acc[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll 4
-  for (int r = 0; r < valid; ++r) {
-    int64_t idx = (token0 + r) * HK + f0;
-    float x[4], o[4];
-    load4(p.raw, p.dt_raw, idx, x);
+  // rows are fetched eight ahead as raw bits (converted when used): the prefix sum is serial over
+  // the rows, the loads are not
+  constexpr int B = 8;
+  uint4 nxt[B];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      float z = a * (x[j] + bias[j]);
-      acc[j] += p.lower_bound / (1.f + expf(-z));
-      o[j] = acc[j] * kLog2e;
+  for (int b = 0; b < B; ++b)
+    if (b < valid) nxt[b] = load4_raw(p.raw, p.dt_raw, (token0 + b) * HK + f0);
+  for (int r0 = 0; r0 < valid; r0 += B) {
+    uint4 cur[B];
+#pragma unroll
+    for (int b = 0; b < B; ++b) cur[b] = nxt[b];
+#pragma unroll
+    for (int b = 0; b < B; ++b)
+      if (r0 + B + b < valid) nxt[b] = load4_raw(p.raw, p.dt_raw, (token0 + r0 + B + b) * HK + f0);
+#pragma unroll
+    for (int b = 0; b < B; ++b) {
+      if (r0 + b < valid) {
+        float x[4], o[4];
+        raw4_to_float(cur[b], p.dt_raw, x);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float z = a * (x[j] + bias[j]);
+          acc[j] += __fdividef(p.lower_bound, 1.f + __expf(-z));   // 2-ulp intrinsics: 1e-6 relative
+          o[j] = acc[j] * kLog2e;
+        }
+        store4(p.out, KDA_F32, (token0 + r0 + b) * HK + f0, o);
+      }
     }
-    store4(p.out, KDA_F32, idx, o);
   }
 }
 
@@ -163,22 +199,45 @@ __global__ void __launch_bounds__(128) gate_cumsum_bwd_kernel(const GateParams p
     const float4 b4 = *reinterpret_cast<const float4*>(p.dt_bias + f0);
     const float bias[4] = {b4.x, b4.y, b4.z, b4.w};
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll 4
-    for (int r = valid - 1; r >= 0; --r) {
-      int64_t idx = (token0 + r) * HK + f0;
-      float x[4], d[4], o[4];
-      load4(p.raw, p.dt_raw, idx, x);
-      load4(p.d_cum, KDA_F32, idx, d);
+    // reverse walk, rows fetched four ahead as raw bits (see the forward kernel)
+    constexpr int B = 4;
+    uint4 nx[B], nd[B];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        acc[j] += d[j];
-        float z = x[j] + bias[j];
-        float s = 1.f / (1.f + expf(-a * z));
-        o[j] = acc[j] * kLog2e * p.lower_bound * a * s * (1.f - s);
-        pa[j] += o[j] * z;
-        pb[j] += o[j];
+    for (int b = 0; b < B; ++b)
+      if (valid - 1 - b >= 0) {
+        const int64_t idx = (token0 + valid - 1 - b) * HK + f0;
+        nx[b] = load4_raw(p.raw, p.dt_raw, idx);
+        nd[b] = load4_raw(p.d_cum, KDA_F32, idx);
       }
-      store4(p.d_raw, p.dt_raw, idx, o);
+    for (int r0 = valid - 1; r0 >= 0; r0 -= B) {
+      uint4 cx[B], cd[B];
+#pragma unroll
+      for (int b = 0; b < B; ++b) { cx[b] = nx[b]; cd[b] = nd[b]; }
+#pragma unroll
+      for (int b = 0; b < B; ++b)
+        if (r0 - B - b >= 0) {
+          const int64_t idx = (token0 + r0 - B - b) * HK + f0;
+          nx[b] = load4_raw(p.raw, p.dt_raw, idx);
+          nd[b] = load4_raw(p.d_cum, KDA_F32, idx);
+        }
+#pragma unroll
+      for (int b = 0; b < B; ++b) {
+        if (r0 - b >= 0) {
+          float x[4], d[4], o[4];
+          raw4_to_float(cx[b], p.dt_raw, x);
+          raw4_to_float(cd[b], KDA_F32, d);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            acc[j] += d[j];
+            float z = x[j] + bias[j];
+            float s = __fdividef(1.f, 1.f + __expf(-a * z));
+            o[j] = acc[j] * kLog2e * p.lower_bound * a * s * (1.f - s);
+            pa[j] += o[j] * z;
+            pb[j] += o[j];
+          }
+          store4(p.d_raw, p.dt_raw, (token0 + r0 - b) * HK + f0, o);
+        }
+      }
     }
   }
   int64_t pidx = (int64_t)blockIdx.x * HK + f0;
@@ -186,8 +245,28 @@ __global__ void __launch_bounds__(128) gate_cumsum_bwd_kernel(const GateParams p
   store4(p.dbias_part, KDA_F32, pidx, pb);
 }
 
+// eight 16-bit values <-> floats
+__device__ __forceinline__ void raw8_to_float(const uint4& r, int dt, float (&x)[8]) {
+  const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    if (dt == KDA_BF16) { float2 a = unpack_bf16(w[i]); x[2 * i] = a.x; x[2 * i + 1] = a.y; }
+    else { __half2 h = *reinterpret_cast<const __half2*>(&w[i]); x[2 * i] = __low2float(h); x[2 * i + 1] = __high2float(h); }
+  }
+}
+__device__ __forceinline__ uint4 float8_to_raw(const float (&x)[8], int dt) {
+  uint32_t w[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    if (dt == KDA_BF16) w[i] = pack_bf16(x[2 * i], x[2 * i + 1]);
+    else { __half2 h = __floats2half2_rn(x[2 * i], x[2 * i + 1]); w[i] = *reinterpret_cast<uint32_t*>(&h); }
+  }
+  return make_uint4(w[0], w[1], w[2], w[3]);
+}
+
 // ------------------------------------------------------------------------------------------
-// L2 row normalisation: one warp per row
+// L2 row normalisation: one warp per row (any width and dtype); vector kernels for 16-bit rows of
+// 64 / 128 / 256 elements further down
 // ------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) l2norm_fwd_kernel(const void* x, int dt, void* y,
                                                          float* rstd, int64_t rows, int D,
@@ -237,6 +316,84 @@ __global__ void __launch_bounds__(256) l2norm_bwd_kernel(const void* y, const fl
 #pragma unroll
     for (int j = 0; j < 4; ++j) o[j] = r * (b[j] - a[j] * dot);
     store4(dx, dt, row * D + c, o);
+  }
+}
+
+// 16-bit rows of 64 / 128 / 256 elements: LPR = D / 8 lanes share a row (one 16-byte vector each), a
+// warp holds 32 / LPR rows per slot and four slots in flight; every element is read once and stays
+// in registers between the reduction and the scaling.
+template <int LPR>
+__global__ void __launch_bounds__(256) l2norm_fwd_vec_kernel(const uint4* __restrict__ x, int dt,
+                                                             uint4* __restrict__ y, float* rstd,
+                                                             int64_t rows, float eps) {
+  constexpr int RPS = 32 / LPR, SLOTS = 4;
+  const int lane = threadIdx.x & 31;
+  const int64_t row0 = ((int64_t)blockIdx.x * 8 + (threadIdx.x >> 5)) * (RPS * SLOTS) + lane / LPR;
+  uint4 v[SLOTS];
+#pragma unroll
+  for (int s = 0; s < SLOTS; ++s) {
+    const int64_t row = row0 + s * RPS;
+    if (row < rows) v[s] = x[row * LPR + lane % LPR];
+  }
+#pragma unroll
+  for (int s = 0; s < SLOTS; ++s) {
+    const int64_t row = row0 + s * RPS;
+    float f[8];
+    float ss = 0.f;
+    if (row < rows) {
+      raw8_to_float(v[s], dt, f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss = fmaf(f[j], f[j], ss);
+    }
+#pragma unroll
+    for (int d = LPR / 2; d > 0; d >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, d);
+    if (row < rows) {
+      const float r = rsqrtf(ss + eps);
+      if (lane % LPR == 0 && rstd) rstd[row] = r;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) f[j] *= r;
+      y[row * LPR + lane % LPR] = float8_to_raw(f, dt);
+    }
+  }
+}
+
+template <int LPR>
+__global__ void __launch_bounds__(256) l2norm_bwd_vec_kernel(const uint4* __restrict__ y,
+                                                             const float* __restrict__ rstd,
+                                                             const uint4* __restrict__ dy, int dt,
+                                                             uint4* __restrict__ dx, int64_t rows) {
+  constexpr int RPS = 32 / LPR, SLOTS = 4;
+  const int lane = threadIdx.x & 31;
+  const int64_t row0 = ((int64_t)blockIdx.x * 8 + (threadIdx.x >> 5)) * (RPS * SLOTS) + lane / LPR;
+  uint4 a[SLOTS], b[SLOTS];
+  float rs[SLOTS];
+#pragma unroll
+  for (int s = 0; s < SLOTS; ++s) {
+    const int64_t row = row0 + s * RPS;
+    if (row < rows) {
+      a[s] = y[row * LPR + lane % LPR];
+      b[s] = dy[row * LPR + lane % LPR];
+      rs[s] = rstd[row];
+    }
+  }
+#pragma unroll
+  for (int s = 0; s < SLOTS; ++s) {
+    const int64_t row = row0 + s * RPS;
+    float fy[8], fd[8];
+    float dot = 0.f;
+    if (row < rows) {
+      raw8_to_float(a[s], dt, fy);
+      raw8_to_float(b[s], dt, fd);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) dot = fmaf(fy[j], fd[j], dot);
+    }
+#pragma unroll
+    for (int d = LPR / 2; d > 0; d >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, d);
+    if (row < rows) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) fd[j] = rs[s] * (fd[j] - fy[j] * dot);
+      dx[row * LPR + lane % LPR] = float8_to_raw(fd, dt);
+    }
   }
 }
 
@@ -309,8 +466,20 @@ extern "C" int kda_l2norm_fwd(const void* x, int dtype, void* y, float* rstd, in
                               int dim, float eps, void* stream) {
   if (!x || !y || rows < 0 || dim <= 0 || dim % 4) return KDA_ERR_ARG;
   if (rows == 0) return KDA_OK;
-  kda::l2norm_fwd_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, (cudaStream_t)stream>>>(
-      x, dtype, y, rstd, rows, dim, eps);
+  cudaStream_t s = (cudaStream_t)stream;
+  const bool vec = dtype != KDA_F32 && (dim == 64 || dim == 128 || dim == 256) &&
+                   ((uintptr_t)x & 15) == 0 && ((uintptr_t)y & 15) == 0;
+  if (vec) {
+    const int lpr = dim / 8, rows_per_block = 8 * (32 / lpr) * 4;
+    const unsigned blocks = (unsigned)((rows + rows_per_block - 1) / rows_per_block);
+    const uint4* xv = reinterpret_cast<const uint4*>(x);
+    uint4* yv = reinterpret_cast<uint4*>(y);
+    if (lpr == 8) kda::l2norm_fwd_vec_kernel<8><<<blocks, 256, 0, s>>>(xv, dtype, yv, rstd, rows, eps);
+    else if (lpr == 16) kda::l2norm_fwd_vec_kernel<16><<<blocks, 256, 0, s>>>(xv, dtype, yv, rstd, rows, eps);
+    else kda::l2norm_fwd_vec_kernel<32><<<blocks, 256, 0, s>>>(xv, dtype, yv, rstd, rows, eps);
+    return kda::check_launch();
+  }
+  kda::l2norm_fwd_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, s>>>(x, dtype, y, rstd, rows, dim, eps);
   return kda::check_launch();
 }
 
@@ -318,7 +487,20 @@ extern "C" int kda_l2norm_bwd(const void* y, const float* rstd, const void* dy, 
                               int64_t rows, int dim, void* stream) {
   if (!y || !rstd || !dy || !dx || rows < 0 || dim <= 0 || dim % 4) return KDA_ERR_ARG;
   if (rows == 0) return KDA_OK;
-  kda::l2norm_bwd_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, (cudaStream_t)stream>>>(
-      y, rstd, dy, dtype, dx, rows, dim);
+  cudaStream_t s = (cudaStream_t)stream;
+  const bool vec = dtype != KDA_F32 && (dim == 64 || dim == 128 || dim == 256) &&
+                   ((uintptr_t)y & 15) == 0 && ((uintptr_t)dy & 15) == 0 && ((uintptr_t)dx & 15) == 0;
+  if (vec) {
+    const int lpr = dim / 8, rows_per_block = 8 * (32 / lpr) * 4;
+    const unsigned blocks = (unsigned)((rows + rows_per_block - 1) / rows_per_block);
+    const uint4* yv = reinterpret_cast<const uint4*>(y);
+    const uint4* dv = reinterpret_cast<const uint4*>(dy);
+    uint4* xv = reinterpret_cast<uint4*>(dx);
+    if (lpr == 8) kda::l2norm_bwd_vec_kernel<8><<<blocks, 256, 0, s>>>(yv, rstd, dv, dtype, xv, rows);
+    else if (lpr == 16) kda::l2norm_bwd_vec_kernel<16><<<blocks, 256, 0, s>>>(yv, rstd, dv, dtype, xv, rows);
+    else kda::l2norm_bwd_vec_kernel<32><<<blocks, 256, 0, s>>>(yv, rstd, dv, dtype, xv, rows);
+    return kda::check_launch();
+  }
+  kda::l2norm_bwd_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, s>>>(y, rstd, dy, dtype, dx, rows, dim);
   return kda::check_launch();
 }

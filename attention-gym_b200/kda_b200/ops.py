@@ -520,7 +520,10 @@ def _short_conv_bwd(x, weight, grad_output, cu_seqlens=None, initial_state=None,
     dw_part = torch.empty(blocks, channels, width, dtype=torch.float32, device=x.device)
     dstate = (torch.zeros(nseq, max(width - 1, 0), channels, dtype=torch.float32, device=x.device)
               if state_grad else None)
-    scratch = torch.empty(batch * tokens, channels, dtype=torch.float32, device=x.device)
+    # the width-4 kernels for 16-bit tensors need no scratch; every other case keeps dpre in fp32
+    # between its two passes
+    scratch = (None if width == 4 and x.element_size() == 2 else
+               torch.empty(batch * tokens, channels, dtype=torch.float32, device=x.device))
     _cabi.call("kda_conv1d_bwd", 2, _cabi.ptr(x), _cabi.ptr(weight), _cabi.ptr(initial_state),
                _cabi.ptr(grad_output), _cabi.ptr(dx), _cabi.ptr(dw_part), _cabi.ptr(dstate),
                _cabi.ptr(scratch), _cabi.dt(x), _cabi.ptr(cu_seqlens), nseq, batch, tokens,

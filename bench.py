@@ -42,7 +42,7 @@ STAGE_BYTES = {
     "intra_solve": 2 * 256 + 512 + 4 + 2 * 128,                 # q,k bf16 + G fp32 + beta -> Aqk, Akk
     "wu": 3 * 256 + 512 + 4 + 128 + 4 * 256,                    # q,k,v,G,beta,Akk -> w,u,kg,qg
     "state_fwd": 4 * 256 + 128 + 8 + 256,                       # w,u,kg,qg,Aqk,G_last -> o
-    "state_fwd_recompute": 4 * 256 + 128 + 8 + 512 + 256,       # ... -> h[c] (bf16) + v_new
+    "state_fwd_recompute": 4 * 256 + 128 + 8 + 256 + 512 + 256, # ... -> o, h[c] (bf16) and v_new (kept)
     "state_bwd": 3 * 256 + 256 + 128 + 8 + 512 + 256,           # w,kg,qg,dO,Aqk -> dh[c], dv2
     # h, dh (bf16 [128,128] per chunk = 512 B per token each), dO, v_new, dv2, v, k, q, G, Akk, beta
     # -> dq, dk, dv, dG, dbeta
@@ -186,6 +186,7 @@ def run_ours(args):
     launches = _cabi.launch_count - launches0
 
     decode = None if args.skip_decode else bench_decode(kda_b200, _cabi, device, load_peaks())
+    preops = None if (args.skip_decode or rank != 0) else bench_preops(device, load_peaks(), batch, tokens)
     # ---- end to end: pinned host buffers in, pinned host buffers out, every copy inside the timed
     # region.  Three streams (H2D, compute, D2H) with double-buffered device inputs and host
     # outputs, so the copies of neighbouring steps overlap the kernels the way a host-buffer caller
@@ -291,6 +292,7 @@ def run_ours(args):
         "kernels": breakdown,
         "cpu_baseline": cpu,
         "decode": decode,
+        "preops": preops,
     }
     print(json.dumps(line), flush=True)
     if world > 1:
@@ -340,6 +342,49 @@ def bench_decode(kda_b200, _cabi, device, peaks, nseq=256, steps=200):
             "roofline": {"bound": "hbm", "achieved": round(gbs, 1), "peak": peaks["hbm_gbs"],
                          "unit": "GB/s", "frac": round(gbs / peaks["hbm_gbs"], 4),
                          "bytes_per_step": bytes_per_step}}
+
+
+def bench_preops(device, peaks, batch=8, tokens=4096, iters=20):
+    """The bandwidth-bound pre-ops at the config-1 shapes: achieved HBM GB/s of each kernel
+    (algorithmic bytes: what its interface must read + write) with CUDA events."""
+    ops = torch.ops.kda_b200
+    gen = torch.Generator().manual_seed(9)
+    n = batch * tokens * H * D
+    raw = torch.randn(batch, tokens, H, D, generator=gen).bfloat16().to(device)
+    a_log = torch.randn(H, generator=gen).to(device) * 0.1
+    dt_bias = torch.randn(H, D, generator=gen).to(device) * 0.1
+    dcum = torch.randn(batch, tokens, H, D, generator=gen).to(device)
+    x = torch.randn(batch, tokens, H, D, generator=gen).bfloat16().to(device)
+    dy = torch.randn(batch, tokens, H, D, generator=gen).bfloat16().to(device)
+    y, rstd = ops.kda_l2norm_fwd(x, 1e-6)
+    xc = x.view(batch, tokens, H * D)
+    dyc = dy.view(batch, tokens, H * D)
+    w = (torch.randn(H * D, 4, generator=gen) * 0.5).bfloat16().to(device)
+    cases = {
+        "gate_cumsum_fwd": (lambda: ops.kda_bounded_gate_fwd_dense(raw, a_log, dt_bias, CHUNK, -5.0), 6),
+        "gate_cumsum_bwd": (lambda: ops.kda_bounded_gate_bwd(raw, a_log, dt_bias, dcum, None, None,
+                                                             CHUNK, -5.0), 8),
+        "l2norm_fwd": (lambda: ops.kda_l2norm_fwd(x, 1e-6), 4),
+        "l2norm_bwd": (lambda: ops.kda_l2norm_bwd(y, rstd, dy), 6),
+        "short_conv_fwd": (lambda: ops.short_conv_fwd(xc, w, activation="silu"), 4),
+        "short_conv_bwd": (lambda: ops.short_conv_bwd(xc, w, dyc, activation="silu"), 6),
+    }
+    out = {}
+    for name, (fn, bytes_per_elem) in cases.items():
+        for _ in range(3):
+            fn()
+        a, z = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        a.record()
+        for _ in range(iters):
+            fn()
+        z.record()
+        torch.cuda.synchronize()
+        us = a.elapsed_time(z) * 1e3 / iters
+        gbs = n * bytes_per_elem / (us * 1e-6) / 1e9
+        out[name] = {"us": round(us, 1), "bytes_per_elem": bytes_per_elem, "achieved_gbs": round(gbs, 1),
+                     "frac": round(gbs / peaks["hbm_gbs"], 4)}
+    return out
 
 
 def cpu_sample_step(threads):

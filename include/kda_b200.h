@@ -207,7 +207,8 @@ int kda_conv1d_fwd(const void* x, const void* weight, const void* initial_state,
 
 /* Backward of kda_conv1d_fwd.  dx like x; dw_partial fp32 [kda_conv1d_bwd_blocks(), C, W] (sum over
  * the first axis gives dw); dstate fp32 [nseq, W-1, C] zero-initialised by the caller, or NULL;
- * dpre_scratch fp32 [batch * tokens, C].
+ * dpre_scratch fp32 [batch * tokens, C]; may be NULL for W == 4 with bf16 / fp16 tensors, whose
+ * one-pass kernel keeps the pre-activation gradient in registers.
  * Replaces attn_gym::_cute_short_conv_bwd (kda/ops.py:106-110; short_conv/cute.py:582, :791, :1960). */
 int64_t kda_conv1d_bwd_blocks(int batch, int tokens, int packed);
 int kda_conv1d_bwd(const void* x, const void* weight, const void* initial_state, const void* dy,
