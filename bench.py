@@ -448,12 +448,19 @@ def main():
     ap.add_argument("--skip-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--skip-e2e", action="store_true", help="skip the host-buffer leg")
     ap.add_argument("--skip-decode", action="store_true", help="skip the decode-step measurement")
+    ap.add_argument("--preops-only", action="store_true",
+                    help="measure only the gate / l2norm / short-conv pre-ops (for profiler captures)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
         return
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback of the fused path)")
+    if args.preops_only:
+        import kda_b200  # noqa: F401  (registers the operators)
+        torch.cuda.set_device(0)
+        print(json.dumps({"preops": bench_preops(torch.device("cuda", 0), load_peaks(), iters=3)}), flush=True)
+        return
     run_ours(args)
 
 
