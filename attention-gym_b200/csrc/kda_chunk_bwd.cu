@@ -43,7 +43,8 @@ extern "C" int kda_debug_set_profile_buffer(void* buffer) {
 extern "C" int64_t kda_chunk_bwd_workspace_bytes(int64_t tokens, int heads, int64_t num_chunks) {
   const int64_t nd = tokens * heads * 128;
   const int64_t hs = num_chunks * heads * 128 * 128;
-  return (6 * nd + 2 * hs) * 2 + 256;   // w, u, kg, qg, v_new, dv2 and h, dh (all bf16)
+  // w, u, kg, qg, v_new, dv2 and h, dh (all bf16); a scratch tape [2][tokens, H, 64] for the rebuild
+  return (6 * nd + 2 * hs + nd) * 2 + 256;
 }
 
 static int chunk_bwd_impl(bool saved, const void* q, const void* k, const void* v, const float* cum_gate,
@@ -65,12 +66,12 @@ static int chunk_bwd_impl(bool saved, const void* q, const void* k, const void* 
   const int64_t hs = (int64_t)num_chunks * heads * 128 * 128;
   bf16* b = reinterpret_cast<bf16*>(workspace);
   bf16 *w = b, *u = b + nd, *kg = b + 2 * nd, *qg = b + 3 * nd, *vnew = b + 4 * nd,
-       *dv2 = b + 5 * nd, *hbuf = b + 6 * nd, *dhbuf = b + 6 * nd + hs;
+       *dv2 = b + 5 * nd, *hbuf = b + 6 * nd, *dhbuf = b + 6 * nd + hs, *tape = b + 6 * nd + 2 * hs;
   cudaStream_t s = (cudaStream_t)stream;
 
   int rc = KDA_OK;
   if (!saved) {   // reference behaviour: rebuild w, u, kg, qg, h[c], v_new from the stored A
-    rc = kda::launch_recompute(q, k, v, cum_gate, beta, aqk, akk, initial_state, w, u, kg, qg,
+    rc = kda::launch_recompute(q, k, v, cum_gate, beta, tape, tape + nd / 2, initial_state, w, u, kg, qg,
                                hbuf, vnew, cu_seqlens, chunk_offsets, nseq, heads, num_chunks, tokens, s);
     if (rc) return rc;
   }

@@ -644,11 +644,11 @@ int launch_state_bwd_tc(const bf16* w, const bf16* kg, const bf16* qg, const bf1
 
 // 1 if a tensor-memory kernel gave up on a barrier wait since the last call (clears the flag).
 // Synchronises the device; meant for tests and debugging.
-namespace kda { int bwd_chunk_tc_error_word(); }
+namespace kda { int bwd_chunk_tc_error_word(); int prepare_tc_error_word(); }
 
 extern "C" int kda_device_error_word(void) {
   int v = 0, zero = 0;
   if (cudaMemcpyFromSymbol(&v, kda::g_state_tc_error, sizeof(int)) != cudaSuccess) return -1;
   cudaMemcpyToSymbol(kda::g_state_tc_error, &zero, sizeof(int));
-  return v | (kda::bwd_chunk_tc_error_word() << 8);
+  return v | (kda::bwd_chunk_tc_error_word() << 8) | (kda::prepare_tc_error_word() << 16);
 }

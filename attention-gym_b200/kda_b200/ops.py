@@ -294,7 +294,7 @@ def _(q, k, v, gate, beta, initial_state, cu_seqlens, chunk_offsets, want_state)
     total, heads = q.shape[0] * q.shape[1], q.shape[2]
     chunks = (q.shape[0] * ((q.shape[1] + _CHUNK - 1) // _CHUNK) if cu_seqlens is None
               else chunk_capacity(q.shape[1], nseq, _CHUNK))
-    nbytes = (6 * total * heads * 128 + 2 * chunks * heads * 128 * 128) * 2 + 256
+    nbytes = (7 * total * heads * 128 + 2 * chunks * heads * 128 * 128) * 2 + 256
     return (v.new_empty(v.shape), state, _tape(q), _tape(q),
             q.new_empty((nbytes,), dtype=torch.uint8))
 
