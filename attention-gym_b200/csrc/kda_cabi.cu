@@ -8,7 +8,7 @@
 namespace kda {
 
 static const char* kStageNames[kStageCount] = {
-    "intra_solve", "wu", "state_fwd", "state_bwd", "bwd_chunk", "recurrent",
+    "prepare", "state_fwd", "state_bwd", "bwd_chunk", "recurrent",
     "gate_fwd", "gate_bwd", "l2norm", "conv", "chunk_offsets", "state_affine"};
 
 struct Pair { cudaEvent_t a, b; };

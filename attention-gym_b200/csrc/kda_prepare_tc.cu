@@ -361,33 +361,53 @@ __global__ void __launch_bounds__(NT, 1) kda_prepare_tc_kernel(const __grid_cons
   pr_mark(p, it, 6);
   // A[r][c] = -A[r][r] * sum_{c <= m < r} L[r][m] A[m][c], one block diagonal at a time; the inner
   // loops are unrolled so that all shared-memory loads of a product are in flight together
+  // Each thread owns a 2 x 2 tile of a 16 x 16 result block: 16-byte loads along k for the row
+  // operand, 8-byte loads for the column operand (the plain one-output-per-thread form is bound by
+  // shared-memory load issue).
   auto round = [&](auto dist_tag) {
     constexpr int DIST = decltype(dist_tag)::value;
     constexpr int pairs = 4 - DIST;
-    for (int o = tid; o < pairs * 256; o += NT) {
-      const int c = o >> 8, r = c + DIST, i = (o >> 4) & 15, j = o & 15;
-      const float* A_ = Lf + (16 * r + i) * pl::LP + 16 * c;      // L[r][c .. r-1] row i
-      const float* B_ = Af + (16 * c) * pl::LP + 16 * c + j;      // A[c .. r-1][c] column j
-      float s0 = 0.f, s1 = 0.f;
+    if (tid < pairs * 64) {
+      const int c = tid >> 6, r = c + DIST, i = 2 * ((tid >> 3) & 7), j = 2 * (tid & 7);
+      const float* A0 = Lf + (16 * r + i) * pl::LP + 16 * c;      // L[r][c .. r-1], rows i, i + 1
+      const float* B_ = Af + (16 * c) * pl::LP + 16 * c + j;      // A[c .. r-1][c], columns j, j + 1
+      float s00 = 0.f, s01 = 0.f, s10 = 0.f, s11 = 0.f;
 #pragma unroll
-      for (int k = 0; k < 16 * DIST; k += 2) {
-        s0 = fmaf(A_[k], B_[k * pl::LP], s0);
-        s1 = fmaf(A_[k + 1], B_[(k + 1) * pl::LP], s1);
+      for (int k = 0; k < 16 * DIST; k += 4) {
+        const float4 a0 = *reinterpret_cast<const float4*>(A0 + k);
+        const float4 a1 = *reinterpret_cast<const float4*>(A0 + pl::LP + k);
+        const float av0[4] = {a0.x, a0.y, a0.z, a0.w}, av1[4] = {a1.x, a1.y, a1.z, a1.w};
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) {
+          const float2 bv = *reinterpret_cast<const float2*>(B_ + (k + kk) * pl::LP);
+          s00 = fmaf(av0[kk], bv.x, s00); s01 = fmaf(av0[kk], bv.y, s01);
+          s10 = fmaf(av1[kk], bv.x, s10); s11 = fmaf(av1[kk], bv.y, s11);
+        }
       }
-      s_tmp[o] = s0 + s1;
+      *reinterpret_cast<float2*>(s_tmp + (c << 8) + i * 16 + j) = make_float2(s00, s01);
+      *reinterpret_cast<float2*>(s_tmp + (c << 8) + (i + 1) * 16 + j) = make_float2(s10, s11);
     }
     __syncthreads();
-    for (int o = tid; o < pairs * 256; o += NT) {
-      const int c = o >> 8, r = c + DIST, i = (o >> 4) & 15, j = o & 15;
-      const float* A_ = Af + (16 * r + i) * pl::LP + 16 * r;      // A[r][r] row i
+    if (tid < pairs * 64) {
+      const int c = tid >> 6, r = c + DIST, i = 2 * ((tid >> 3) & 7), j = 2 * (tid & 7);
+      const float* A0 = Af + (16 * r + i) * pl::LP + 16 * r;      // A[r][r], rows i, i + 1
       const float* B_ = s_tmp + (c << 8) + j;
-      float s0 = 0.f, s1 = 0.f;
+      float s00 = 0.f, s01 = 0.f, s10 = 0.f, s11 = 0.f;
 #pragma unroll
-      for (int k = 0; k < 16; k += 2) {
-        s0 = fmaf(A_[k], B_[k * 16], s0);
-        s1 = fmaf(A_[k + 1], B_[(k + 1) * 16], s1);
+      for (int k = 0; k < 16; k += 4) {
+        const float4 a0 = *reinterpret_cast<const float4*>(A0 + k);
+        const float4 a1 = *reinterpret_cast<const float4*>(A0 + pl::LP + k);
+        const float av0[4] = {a0.x, a0.y, a0.z, a0.w}, av1[4] = {a1.x, a1.y, a1.z, a1.w};
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) {
+          const float2 bv = *reinterpret_cast<const float2*>(B_ + (k + kk) * 16);
+          s00 = fmaf(av0[kk], bv.x, s00); s01 = fmaf(av0[kk], bv.y, s01);
+          s10 = fmaf(av1[kk], bv.x, s10); s11 = fmaf(av1[kk], bv.y, s11);
+        }
       }
-      Af[(16 * r + i) * pl::LP + 16 * c + j] = -(s0 + s1);
+      float* dst = Af + (16 * r + i) * pl::LP + 16 * c + j;
+      *reinterpret_cast<float2*>(dst) = make_float2(-s00, -s01);
+      *reinterpret_cast<float2*>(dst + pl::LP) = make_float2(-s10, -s11);
     }
     __syncthreads();
   };
@@ -533,7 +553,7 @@ int launch_prepare_tc(const bf16* q, const bf16* k, const bf16* v, const float* 
   if (cudaFuncSetAttribute(kda_prepare_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
       cudaSuccess)
     return KDA_ERR_LAUNCH;
-  StageScope timing(kStageIntraSolve, s);
+  StageScope timing(kStagePrepare, s);
   kda_prepare_tc_kernel<<<(unsigned)(p.total < sms ? p.total : sms), NT, smem, s>>>(p);
   return cudaGetLastError() == cudaSuccess ? KDA_OK : KDA_ERR_LAUNCH;
 }

@@ -10,7 +10,7 @@
 namespace kda {
 
 enum Stage {
-  kStageIntraSolve = 0, kStageWu, kStageStateFwd, kStageStateBwd, kStageBwdChunk,
+  kStagePrepare = 0, kStageStateFwd, kStageStateBwd, kStageBwdChunk,
   kStageRecurrent, kStageGateFwd, kStageGateBwd, kStageL2norm, kStageConv, kStageOffsets,
   kStageAffine, kStageCount
 };

@@ -39,8 +39,8 @@ H, D, CHUNK = 32, 128, 64
 
 # algorithmic HBM bytes per (token, head) of each kernel: what its interface must read + write
 STAGE_BYTES = {
-    "intra_solve": 2 * 256 + 512 + 4 + 2 * 128,                 # q,k bf16 + G fp32 + beta -> Aqk, Akk
-    "wu": 3 * 256 + 512 + 4 + 128 + 4 * 256,                    # q,k,v,G,beta,Akk -> w,u,kg,qg
+    # q,k,v bf16 + G fp32 + beta -> Aqk, Akk, w, u, kg, qg
+    "prepare": 3 * 256 + 512 + 4 + 2 * 128 + 4 * 256,
     "state_fwd": 4 * 256 + 128 + 8 + 256,                       # w,u,kg,qg,Aqk,G_last -> o
     "state_fwd_recompute": 4 * 256 + 128 + 8 + 256 + 512 + 256, # ... -> o, h[c] (bf16) and v_new (kept)
     "state_bwd": 3 * 256 + 256 + 128 + 8 + 512 + 256,           # w,kg,qg,dO,Aqk -> dh[c], dv2
@@ -50,7 +50,7 @@ STAGE_BYTES = {
 }
 # DRAM bytes per (token, head) and launch that ncu measured (dram__bytes_read + dram__bytes_write on
 # the B=2 case, which grows in proportion to the units; see profiles/)
-NCU_TRAFFIC = {"bwd_chunk": 4369, "state_fwd": 2023, "state_bwd": 1779, "intra_solve": 1225, "wu": 2289}
+NCU_TRAFFIC = {"bwd_chunk": 4369, "state_fwd": 2023, "state_bwd": 1779}
 # the path's algorithmic minimum (inputs once, outputs once), bytes per token per head
 PATH_BYTES_FWD_BWD = 4620
 PATH_FLOP_FWD_BWD = 576171
