@@ -50,7 +50,7 @@ STAGE_BYTES = {
 }
 # DRAM bytes per (token, head) and launch that ncu measured (dram__bytes_read + dram__bytes_write on
 # the B=2 case, which grows in proportion to the units; see profiles/)
-NCU_TRAFFIC = {"bwd_chunk": 4369, "state_fwd": 2023, "state_bwd": 1779}
+NCU_TRAFFIC = {"bwd_chunk": 4367, "state_fwd": 2017, "state_bwd": 1788, "prepare": 2376}
 # the path's algorithmic minimum (inputs once, outputs once), bytes per token per head
 PATH_BYTES_FWD_BWD = 4620
 PATH_FLOP_FWD_BWD = 576171
