@@ -19,10 +19,6 @@
 namespace kda {
 
 constexpr int D = 128;     // K = V
-constexpr int LDD = 136;   // padded row stride of a [*, 128] bf16 tile (272 B: conflict-free ldmatrix)
-constexpr int LD64 = 72;   // padded row stride of a [*, 64] bf16 tile
-constexpr int LDP = 68;    // padded row stride of a [64, 64] fp32 tile
-
 struct ChunkParams {
   const bf16* q; const bf16* k; const bf16* v; const float* g; const float* beta;
   bf16* aqk; bf16* akk;                 // tape [N, H, 64]
@@ -43,14 +39,6 @@ int launch_state_fwd_tc(const bf16* w, const bf16* u, const bf16* kg, const bf16
                         const float* g, const float* h0, float* ht, bf16* o, bf16* h_out,
                         bf16* vnew_out, const int32_t* cu, const int32_t* co, int nseq, int H,
                         int64_t tokens, int chunks, cudaStream_t s);
-
-static int check_launch() { return cudaGetLastError() == cudaSuccess ? KDA_OK : KDA_ERR_LAUNCH; }
-
-template <typename Kern>
-static int set_smem(Kern kern, size_t bytes) {
-  return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes) ==
-                 cudaSuccess ? KDA_OK : KDA_ERR_LAUNCH;
-}
 
 // forward: the whole chunk-parallel part (tape, w, u, kg, qg) in one tcgen05 kernel
 int launch_prepare(const ChunkParams& p, int chunks, cudaStream_t s) {

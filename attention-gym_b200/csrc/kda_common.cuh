@@ -118,138 +118,4 @@ __device__ __forceinline__ void cp_async_wait() {
   asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
 }
 
-// Copy a [rows x COLS] tile of 2-byte elements (row stride `gld` elements in global memory) into
-// shared memory with row stride LDS elements; rows >= valid_rows are zero-filled.
-template <int ROWS, int COLS, int LDS, int THREADS>
-__device__ __forceinline__ void load_tile_b16(bf16* smem, const bf16* gmem, int64_t gld,
-                                              int valid_rows, int tid) {
-  constexpr int VPR = COLS / 8;  // 16-byte vectors per row
-  for (int idx = tid; idx < ROWS * VPR; idx += THREADS) {
-    int r = idx / VPR, c = (idx % VPR) * 8;
-    bool ok = r < valid_rows;
-    const bf16* src = gmem + (ok ? (int64_t)r * gld + c : 0);
-    cp_async16(smem + r * LDS + c, src, ok);
-  }
-}
-// Same for fp32 tiles.
-template <int ROWS, int COLS, int LDS, int THREADS>
-__device__ __forceinline__ void load_tile_f32(float* smem, const float* gmem, int64_t gld,
-                                              int valid_rows, int tid) {
-  constexpr int VPR = COLS / 4;
-  for (int idx = tid; idx < ROWS * VPR; idx += THREADS) {
-    int r = idx / VPR, c = (idx % VPR) * 4;
-    bool ok = r < valid_rows;
-    const float* src = gmem + (ok ? (int64_t)r * gld + c : 0);
-    cp_async16(smem + r * LDS + c, src, ok);
-  }
-}
-// Coalesced copy of a [rows x COLS] 2-byte tile from shared to global memory (rows < valid_rows).
-template <int ROWS, int COLS, int LDS, int THREADS>
-__device__ __forceinline__ void store_tile_b16(bf16* gmem, int64_t gld, const bf16* smem,
-                                               int valid_rows, int tid) {
-  constexpr int VPR = COLS / 8;
-  for (int idx = tid; idx < ROWS * VPR; idx += THREADS) {
-    int r = idx / VPR, c = (idx % VPR) * 8;
-    if (r < valid_rows)
-      *reinterpret_cast<uint4*>(gmem + (int64_t)r * gld + c) =
-          *reinterpret_cast<const uint4*>(smem + r * LDS + c);
-  }
-}
-
-// ------------------------------------------------------------------------------------------
-// warp-level bf16 tensor-core tiles (mma.sync m16n8k16, fp32 accumulate) fed by ldmatrix
-// ------------------------------------------------------------------------------------------
-__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const void* p) {
-  uint32_t a = smem_u32(p);
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a) : "memory");
-}
-__device__ __forceinline__ void ldsm_x4_t(uint32_t (&r)[4], const void* p) {
-  uint32_t a = smem_u32(p);
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a) : "memory");
-}
-__device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0,
-                                         uint32_t b1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
-      "{%8,%9}, {%0,%1,%2,%3};\n"
-      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-
-// A fragment (16 x 16) of the logical matrix A[m][k].
-//   AT == false: shared memory holds A[m][k] with k contiguous (row stride lda)
-//   AT == true : shared memory holds A^T, i.e. element (m, k) lives at smem[k * lda + m]
-template <bool AT>
-__device__ __forceinline__ void load_a_frag(uint32_t (&a)[4], const bf16* A, int lda, int m0,
-                                            int k0, int lane) {
-  if (!AT) {
-    ldsm_x4(a, A + (m0 + (lane & 15)) * lda + k0 + (lane >> 4) * 8);
-  } else {
-    ldsm_x4_t(a, A + (k0 + (lane & 7) + ((lane >> 4) & 1) * 8) * lda + m0 + ((lane >> 3) & 1) * 8);
-  }
-}
-// B fragments for two adjacent n-tiles (16 k x 16 n) of the logical matrix B[k][n].
-//   BT == false: shared memory holds element (k, n) at smem[n * ldb + k]  (k contiguous)
-//   BT == true : shared memory holds element (k, n) at smem[k * ldb + n]  (n contiguous)
-// b[0], b[1] feed n-tile n0..n0+7; b[2], b[3] feed n-tile n0+8..n0+15.
-template <bool BT>
-__device__ __forceinline__ void load_b_frag(uint32_t (&b)[4], const bf16* B, int ldb, int k0,
-                                            int n0, int lane) {
-  if (!BT) {
-    ldsm_x4(b, B + (n0 + (lane & 7) + ((lane >> 4) & 1) * 8) * ldb + k0 + ((lane >> 3) & 1) * 8);
-  } else {
-    ldsm_x4_t(b, B + (k0 + (lane & 7) + ((lane >> 3) & 1) * 8) * ldb + n0 + ((lane >> 4) & 1) * 8);
-  }
-}
-
-// acc[mt][nt][4] += A[m0 + 16 mt .., ka0 ..] * B[kb0 .., n0 + 8 nt ..] over KS k-steps of 16.
-// NEG negates the A operand (flips the sign bits of the packed bf16 pairs).
-template <int MT, int NT2, bool AT, bool BT, bool NEG = false>
-__device__ __forceinline__ void warp_gemm(float (&acc)[MT][NT2 * 2][4], const bf16* A, int lda,
-                                          int m0, int ka0, const bf16* B, int ldb, int kb0, int n0,
-                                          int ksteps, int lane) {
-  for (int ks = 0; ks < ksteps; ++ks) {
-    uint32_t a[MT][4];
-#pragma unroll
-    for (int mt = 0; mt < MT; ++mt) {
-      load_a_frag<AT>(a[mt], A, lda, m0 + 16 * mt, ka0 + 16 * ks, lane);
-      if (NEG) {
-#pragma unroll
-        for (int i = 0; i < 4; ++i) a[mt][i] ^= 0x80008000u;
-      }
-    }
-#pragma unroll
-    for (int np = 0; np < NT2; ++np) {
-      uint32_t b[4];
-      load_b_frag<BT>(b, B, ldb, kb0 + 16 * ks, n0 + 16 * np, lane);
-#pragma unroll
-      for (int mt = 0; mt < MT; ++mt) {
-        mma16816(acc[mt][2 * np], a[mt], b[0], b[1]);
-        mma16816(acc[mt][2 * np + 1], a[mt], b[2], b[3]);
-      }
-    }
-  }
-}
-
-template <int MT, int NT>
-__device__ __forceinline__ void zero_acc(float (&acc)[MT][NT][4]) {
-#pragma unroll
-  for (int m = 0; m < MT; ++m)
-#pragma unroll
-    for (int n = 0; n < NT; ++n)
-#pragma unroll
-      for (int i = 0; i < 4; ++i) acc[m][n][i] = 0.f;
-}
-
-// Accumulator element (mt, nt, i) of a warp tile anchored at (m0, n0) sits at
-//   row = m0 + 16 mt + (lane >> 2) + 8 (i >> 1),  col = n0 + 8 nt + 2 (lane & 3) + (i & 1).
-__device__ __forceinline__ int acc_row(int m0, int mt, int i, int lane) {
-  return m0 + 16 * mt + (lane >> 2) + 8 * (i >> 1);
-}
-__device__ __forceinline__ int acc_col(int n0, int nt, int i, int lane) {
-  return n0 + 8 * nt + 2 * (lane & 3) + (i & 1);
-}
-
 }  // namespace kda
