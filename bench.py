@@ -75,12 +75,13 @@ class ClockSampler:
 
     def __init__(self, index: int):
         self.index, self.samples, self.proc = index, [], None
+        self.window = None          # (t0, t1) of the timed region, time.monotonic()
 
     def __enter__(self):
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-i", str(self.index), "-lms", "50"],
+                 "-i", str(self.index), "-lms", "20"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -92,7 +93,7 @@ class ClockSampler:
         for line in self.proc.stdout:
             parts = [p.strip() for p in line.split(",")]
             if len(parts) >= 6:
-                self.samples.append(parts)
+                self.samples.append((time.monotonic(), parts))
 
     def __exit__(self, *exc):
         if self.proc is not None:
@@ -102,15 +103,31 @@ class ClockSampler:
             except subprocess.TimeoutExpired:
                 self.proc.kill()
 
+    def mark(self, t0, t1):
+        self.window = (t0, t1)
+
     def summary(self):
-        if not self.samples:
+        # samples taken inside the timed region; a region shorter than the sampling period widens
+        # the window by 100 ms on both sides (the same kernels run in the warm-up before it)
+        picked = self.samples
+        if self.window is not None:
+            t0, t1 = self.window
+            picked = [s for s in self.samples if t0 <= s[0] <= t1]
+            if not picked:
+                picked = [s for s in self.samples if t0 - 0.1 <= s[0] <= t1 + 0.1]
+        picked = [s[1] for s in picked]
+        if not picked:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unavailable"]}
-        mhz = sorted(int(s[0]) for s in self.samples if s[0].isdigit())
+        return self._summarise(picked)
+
+    @staticmethod
+    def _summarise(samples):
+        mhz = sorted(int(s[0]) for s in samples if s[0].isdigit())
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = [n for i, n in enumerate(names) if any(s[2 + i] == "Active" for s in self.samples)]
-        mx = [int(s[1]) for s in self.samples if s[1].isdigit()]
+        reasons = [n for i, n in enumerate(names) if any(s[2 + i] == "Active" for s in samples)]
+        mx = [int(s[1]) for s in samples if s[1].isdigit()]
         return {"sm_mhz": mhz[len(mhz) // 2] if mhz else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": reasons, "samples": len(self.samples)}
+                "reasons": reasons, "samples": len(samples)}
 
 
 def make_host_inputs(batch, tokens, seed, pin):
@@ -166,20 +183,29 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(args.warmup):
-        step_device(kda_b200, dev)
-    barrier()
-    _cabi.stage_timing(True)
-    _cabi.read_stage_timing(reset=True)
-    launches0 = _cabi.launch_count
-    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    # the sampler starts before the warm-up so that nvidia-smi is already reporting when the timed
+    # region begins; only samples whose timestamps fall inside the region are summarised
     with ClockSampler(local_rank) as clocks:
+        for _ in range(args.warmup):
+            step_device(kda_b200, dev)
+        for _ in range(30):                      # keep the GPU under the same load until samples arrive
+            if clocks.samples:
+                break
+            step_device(kda_b200, dev)
+            torch.cuda.synchronize()
         barrier()
+        _cabi.stage_timing(True)
+        _cabi.read_stage_timing(reset=True)
+        launches0 = _cabi.launch_count
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        t_begin = time.monotonic()
         start.record()
         for _ in range(args.steps):
             step_device(kda_b200, dev)
         stop.record()
         barrier()
+        clocks.mark(t_begin, time.monotonic())
     ms = start.elapsed_time(stop)
     stages = _cabi.read_stage_timing(reset=True)
     _cabi.stage_timing(False)
