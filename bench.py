@@ -51,6 +51,14 @@ STAGE_BYTES = {
 # DRAM bytes per (token, head) and launch that ncu measured (dram__bytes_read + dram__bytes_write on
 # the B=2 case, which grows in proportion to the units; see profiles/)
 NCU_TRAFFIC = {"bwd_chunk": 4367, "state_fwd": 2017, "state_bwd": 1788, "prepare": 2376}
+# algorithmic FLOP per (token, head) of each kernel (dense 64-wide tiles, no causal discount;
+# P = 2*64*128 = 16384, S = 2*128*128 = 32768); they add up to PATH_FLOP_FWD_BWD
+STAGE_FLOP = {
+    "prepare": 4 * 16384 + 2731,            # K~K~^T, Q~K~^T, w, u + the triangular solve
+    "state_fwd": 3 * 32768 + 16384,         # w h, kg^T v_new, qg h + Aqk v_new
+    "state_bwd": 3 * 32768 + 16384,         # kg dh, qg^T dO, w^T dv2 + Aqk^T dO
+    "bwd_chunk": 3 * 32768 + 16384 + 4 * 16384 + 16384 + 5 * 16384,
+}
 # the path's algorithmic minimum (inputs once, outputs once), bytes per token per head
 PATH_BYTES_FWD_BWD = 4620
 PATH_FLOP_FWD_BWD = 576171
@@ -280,8 +288,13 @@ def run_ours(args):
     roofline, breakdown = None, {}
     total_stage_ms = sum(v[1] for v in stages.values()) or 1.0
     for name, (n, tot) in stages.items():
+        sec = tot / n * 1e-3
+        units_ = tokens_per_step * H
+        b_unit = STAGE_BYTES["state_fwd_recompute"] if name == "state_fwd" else STAGE_BYTES.get(name, 0)
         breakdown[name] = {"launches": n, "ms_per_launch": round(tot / n, 4),
-                           "share": round(tot / total_stage_ms, 4)}
+                           "share": round(tot / total_stage_ms, 4),
+                           "algorithmic_gbs": round(b_unit * units_ / sec / 1e9, 1),
+                           "algorithmic_tflops": round(STAGE_FLOP.get(name, 0) * units_ / sec / 1e12, 1)}
     if stages:
         top = max(stages, key=lambda n: stages[n][1])
         n, tot = stages[top]

@@ -177,7 +177,7 @@ def test_config4_one_million_tokens_prefix_and_context_parallel_chain():
         v[0, lo:lo + piece] = torch.randn(piece, H, D, generator=gen, device="cuda").bfloat16()
         g2 = _gate((piece, H, D), gen)
         if lo == 0:
-            g_head = g2[:256].clone()
+            g_head = g2[:2048].clone()
         cum[0, lo:lo + piece] = g2.view(piece // 64, 64, H, D).cumsum(1).view(piece, H, D)
         del g2
     beta = torch.sigmoid(torch.randn(1, T, H, generator=gen, device="cuda"))
@@ -189,8 +189,8 @@ def test_config4_one_million_tokens_prefix_and_context_parallel_chain():
         op, _ = kda_b200.chunk_kda(q[:, :m], k[:, :m], v[:, :m], cum[:, :m], beta[:, :m])
         assert torch.equal(o[:, :m], op), "prefix alone differs"
         del op
-        ro, _ = _oracle_slice(q[0, :256], k[0, :256], v[0, :256], g_head, beta[0, :256], None, (0, 2))
-        assert_normalised(o[0, :256, 0:2].float(), ro[0], 2e-2, "config 4 output vs oracle")
+        ro, _ = _oracle_slice(q[0, :2048], k[0, :2048], v[0, :2048], g_head, beta[0, :2048], None, (0, 2))
+        assert_normalised(o[0, :2048, 0:2].float(), ro[0], 2e-2, "config 4 output vs oracle")
         # the boundary-state chain of 8 contiguous slices, ranks run one after another
         world, per, mailbox, last_state = 8, T // 8, {}, None
         for rank in range(world):
