@@ -188,13 +188,16 @@ __global__ void __launch_bounds__(128) gate_cumsum_fwd_kernel(const GateParams p
   }
 }
 
-__global__ void __launch_bounds__(128) gate_cumsum_bwd_kernel(const GateParams p) {
+constexpr int kGateBwdGroup = 4;   // chunks per block of the backward kernel = chunks per partial row
+
+__global__ void __launch_bounds__(128) gate_cumsum_bwd_kernel(const GateParams p, int num_chunks) {
   const int HK = p.H * p.K;
   const int f0 = (blockIdx.y * 128 + threadIdx.x) * 4;
   if (f0 >= HK) return;
-  int64_t token0; int valid;
   float pa[4] = {0.f, 0.f, 0.f, 0.f}, pb[4] = {0.f, 0.f, 0.f, 0.f};
-  if (gate_locate(p, blockIdx.x, token0, valid)) {
+  for (int gc = blockIdx.x * kGateBwdGroup; gc < min(num_chunks, (int)(blockIdx.x + 1) * kGateBwdGroup); ++gc) {
+  int64_t token0; int valid;
+  if (gate_locate(p, gc, token0, valid)) {
     const float a = expf(p.A_log[f0 / p.K]);
     const float4 b4 = *reinterpret_cast<const float4*>(p.dt_bias + f0);
     const float bias[4] = {b4.x, b4.y, b4.z, b4.w};
@@ -239,6 +242,7 @@ __global__ void __launch_bounds__(128) gate_cumsum_bwd_kernel(const GateParams p
         }
       }
     }
+  }
   }
   int64_t pidx = (int64_t)blockIdx.x * HK + f0;
   store4(p.dA_part, KDA_F32, pidx, pa);
@@ -439,6 +443,10 @@ extern "C" int kda_gate_cumsum_fwd(const void* raw_gate, int dt_raw, const float
   return kda::check_launch();
 }
 
+extern "C" int64_t kda_gate_bwd_partial_rows(int64_t num_chunks) {
+  return (num_chunks + kda::kGateBwdGroup - 1) / kda::kGateBwdGroup;
+}
+
 extern "C" int kda_gate_cumsum_bwd(const void* raw_gate, int dt_raw, const float* A_log,
                                    const float* dt_bias, const float* d_cumulative, void* d_raw,
                                    float* dA_partial, float* dbias_partial,
@@ -456,9 +464,9 @@ extern "C" int kda_gate_cumsum_bwd(const void* raw_gate, int dt_raw, const float
   p.raw = raw_gate; p.dt_raw = dt_raw; p.A_log = A_log; p.dt_bias = dt_bias;
   p.d_cum = d_cumulative; p.d_raw = d_raw; p.dA_part = dA_partial; p.dbias_part = dbias_partial;
   p.lower_bound = lower_bound;
-  dim3 grid((unsigned)num_chunks, (unsigned)((heads * dim / 4 + 127) / 128));
+  dim3 grid((unsigned)kda_gate_bwd_partial_rows(num_chunks), (unsigned)((heads * dim / 4 + 127) / 128));
   kda::StageScope timing(kda::kStageGateBwd, (cudaStream_t)stream);
-  kda::gate_cumsum_bwd_kernel<<<grid, 128, 0, (cudaStream_t)stream>>>(p);
+  kda::gate_cumsum_bwd_kernel<<<grid, 128, 0, (cudaStream_t)stream>>>(p, (int)num_chunks);
   return kda::check_launch();
 }
 

@@ -425,7 +425,8 @@ def _gate_bwd(raw, A_log, dt_bias, d_cumulative, cu_seqlens, chunk_offsets, chun
     batch, tokens, heads, dim = raw.shape
     nseq, chunks = _gate_chunks(raw, cu_seqlens, chunk_size)
     d_raw = (torch.zeros_like if cu_seqlens is not None else torch.empty_like)(raw)
-    pa = torch.empty(max(chunks, 1), heads * dim, dtype=torch.float32, device=raw.device)
+    rows = _cabi.lib().kda_gate_bwd_partial_rows(chunks)
+    pa = torch.empty(max(rows, 1), heads * dim, dtype=torch.float32, device=raw.device)
     pb = torch.empty_like(pa)
     if chunks == 0:
         pa.zero_(), pb.zero_()

@@ -87,11 +87,12 @@ int kda_gate_cumsum_fwd(const void* raw_gate, int dt_raw, const float* A_log, co
                         int nseq, int batch, int tokens, int heads, int dim, int chunk_size,
                         float lower_bound, int64_t num_chunks, void* stream);
 
-/* Backward of the above: d_raw (dtype of raw) and per-chunk partial sums
- * dA_partial, dbias_partial: fp32 [num_chunks, H * dim]; dA_log[h] = sum over chunks and dim of
- * dA_partial, d_dt_bias = sum over chunks of dbias_partial.
+/* Backward of the above: d_raw (dtype of raw) and partial sums over groups of chunks
+ * dA_partial, dbias_partial: fp32 [kda_gate_bwd_partial_rows(num_chunks), H * dim]; dA_log[h] = sum
+ * over rows and dim of dA_partial, d_dt_bias = sum over rows of dbias_partial.
  * Replaces attn_gym::kda_fused_gate_bwd (bwd/cute/gate_bwd_fused.py:498-502) and
  * attn_gym::kda_bounded_gate_bwd_ragged (fwd/triton/gate_fwd.py:389-393, bwd/triton/gate_bwd.py:141). */
+int64_t kda_gate_bwd_partial_rows(int64_t num_chunks);
 int kda_gate_cumsum_bwd(const void* raw_gate, int dt_raw, const float* A_log, const float* dt_bias,
                         const float* d_cumulative, void* d_raw, float* dA_partial,
                         float* dbias_partial, const int32_t* cu_seqlens,
