@@ -81,6 +81,14 @@ _define("short_conv_decode",
         "str? activation=None) -> Tensor")
 
 
+# Decode-step preprocessing in one launch (no reference counterpart: the reference runs the conv,
+# the two l2norms and the gate as separate launches, kda/api.py:210-212).
+_define("kda_decode_prep",
+        "(Tensor x, Tensor weight, Tensor(a!) conv_state, Tensor? state_indices, Tensor raw_gate, "
+        "Tensor A_log, Tensor dt_bias, int heads, str? activation, float lower_bound, float eps) "
+        "-> (Tensor, Tensor, Tensor, Tensor)")
+
+
 def _require_cuda(t: torch.Tensor, what: str):
     if not t.is_cuda:
         raise ValueError(f"{what} requires CUDA tensors")
@@ -542,6 +550,30 @@ def _short_conv_decode(x, weight, state, state_indices, *, activation=None):
                _cabi.ptr(state_indices), _cabi.ptr(y), _cabi.dt(x), nseq, state.shape[0], channels,
                weight.shape[1], _act_code(activation), _cabi.stream())
     return y
+
+
+@torch.library.impl(_lib, "kda_decode_prep", "CUDA")
+def _decode_prep(x, weight, conv_state, state_indices, raw_gate, A_log, dt_bias, heads, activation,
+                 lower_bound, eps):
+    nseq = x.shape[0]
+    q = torch.empty(nseq, 1, heads, 128, dtype=x.dtype, device=x.device)
+    k, v = torch.empty_like(q), torch.empty_like(q)
+    gate = torch.empty(nseq, 1, heads, 128, dtype=torch.float32, device=x.device)
+    raw_gate = raw_gate.contiguous()
+    _cabi.call("kda_decode_prep", 1, _cabi.ptr(x), _cabi.ptr(weight), _cabi.ptr(conv_state),
+               _cabi.ptr(state_indices), _cabi.ptr(raw_gate), _cabi.dt(raw_gate),
+               _cabi.ptr(A_log.float().contiguous()), _cabi.ptr(dt_bias.float().contiguous()),
+               _cabi.ptr(q), _cabi.ptr(k), _cabi.ptr(v), _cabi.ptr(gate), _cabi.dt(x), nseq, heads, 128,
+               weight.shape[1], conv_state.shape[0], _act_code(activation), float(lower_bound),
+               float(eps), _cabi.stream())
+    return q, k, v, gate
+
+
+@torch.library.register_fake(f"{_NS}::kda_decode_prep")
+def _(x, weight, conv_state, state_indices, raw_gate, A_log, dt_bias, heads, activation,
+      lower_bound, eps):
+    q = x.new_empty((x.shape[0], 1, heads, 128))
+    return q, torch.empty_like(q), torch.empty_like(q), q.new_empty(q.shape, dtype=torch.float32)
 
 
 @torch.library.register_fake(f"{_NS}::short_conv_fwd")

@@ -224,6 +224,20 @@ int kda_conv1d_decode(const void* x, const void* weight, void* state, const int3
                       void* y, int dtype, int nseq, int num_slots, int channels, int width,
                       int activation, void* stream);
 
+/* Decode-step preprocessing in one launch: the q | k | v projection x [N, 3 * H * 128] goes through the
+ * depthwise causal convolution over the paged history conv_state [num_slots, W-1, 3 * H * 128] (advanced
+ * in place; conv_state_indices as for kda_conv1d_decode, NULL = slot i for sequence i) and the
+ * activation; q and k are L2-normalised per head (rsqrt(sum y^2 + eps)); the per-token log2 gate is
+ * log2(e) * lower_bound * sigmoid(exp(A_log[h]) * (raw_gate + dt_bias[h])).  Writes q, k, v
+ * [N, H, 128] in the dtype of x and gate fp32 [N, H, 128]: the operands of kda_recurrent_fwd.
+ * head_dim must be 128.  The reference runs this as four launches (short_conv/cute.py:3569,
+ * fwd/triton/l2norm_fwd.py:231 twice, fwd/triton/gate_fwd.py:716 with chunk size 1). */
+int kda_decode_prep(const void* x, const void* conv_weight, void* conv_state,
+                    const int32_t* conv_state_indices, const void* raw_gate, int dt_gate,
+                    const float* A_log, const float* dt_bias, void* q, void* k, void* v, float* gate,
+                    int dtype, int nseq, int heads, int head_dim, int width, int num_slots,
+                    int activation, float lower_bound, float eps, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
