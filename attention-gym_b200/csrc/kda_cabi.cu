@@ -9,7 +9,8 @@ namespace kda {
 
 static const char* kStageNames[kStageCount] = {
     "prepare", "state_fwd", "state_bwd", "bwd_chunk", "recurrent",
-    "gate_fwd", "gate_bwd", "l2norm", "conv", "chunk_offsets", "state_affine"};
+    "gate_fwd", "gate_bwd", "l2norm", "conv", "chunk_offsets", "state_affine",
+    "epilogue"};
 
 struct Pair { cudaEvent_t a, b; };
 static bool g_enabled = false;

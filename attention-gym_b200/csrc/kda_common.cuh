@@ -118,4 +118,23 @@ __device__ __forceinline__ void cp_async_wait() {
   asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
 }
 
+// eight 16-bit values <-> floats
+__device__ __forceinline__ void raw8_to_float(const uint4& r, int dt, float (&x)[8]) {
+  const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    if (dt == KDA_BF16) { float2 a = unpack_bf16(w[i]); x[2 * i] = a.x; x[2 * i + 1] = a.y; }
+    else { __half2 h = *reinterpret_cast<const __half2*>(&w[i]); x[2 * i] = __low2float(h); x[2 * i + 1] = __high2float(h); }
+  }
+}
+__device__ __forceinline__ uint4 float8_to_raw(const float (&x)[8], int dt) {
+  uint32_t w[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    if (dt == KDA_BF16) w[i] = pack_bf16(x[2 * i], x[2 * i + 1]);
+    else { __half2 h = __floats2half2_rn(x[2 * i], x[2 * i + 1]); w[i] = *reinterpret_cast<uint32_t*>(&h); }
+  }
+  return make_uint4(w[0], w[1], w[2], w[3]);
+}
+
 }  // namespace kda

@@ -177,10 +177,9 @@ __device__ __forceinline__ bool conv_run_simple(const ConvParams& p, int64_t t0,
 
 // y for tokens [t0, t1) of a run inside one sequence, filter width W known at compile time: the
 // inputs are fetched four tokens ahead as raw vectors, the window slides through registers.
-template <typename T, int W>
+template <typename T, int W, int N, int B>
 __device__ __forceinline__ void conv_fwd_run(const ConvParams& p, int64_t t0, int64_t t1, int c0, int seq,
                                              int64_t bos) {
-  constexpr int N = VecOf<T>::N, B = 4;
   const T* x = reinterpret_cast<const T*>(p.x);
   const T* w = reinterpret_cast<const T*>(p.w);
   const T* st = reinterpret_cast<const T*>(p.state);
@@ -194,28 +193,26 @@ __device__ __forceinline__ void conv_fwd_run(const ConvParams& p, int64_t t0, in
 #pragma unroll
   for (int j = 0; j < W - 1; ++j) {
     const int64_t pos = t0 - (W - 1) + j;
-    if (pos >= bos) ldv<T, N>(x + pos * C + c0, win[j]);
-    else if (st) ldv<T, N>(st + ((int64_t)seq * (W - 1) + (pos - bos + W - 1)) * C + c0, win[j]);
+    if (pos >= bos) cvt_rawv<T, N>(ld_raw<T, N>(x + pos * C + c0), win[j]);
+    else if (st) cvt_rawv<T, N>(ld_raw<T, N>(st + ((int64_t)seq * (W - 1) + (pos - bos + W - 1)) * C + c0), win[j]);
     else {
 #pragma unroll
       for (int i = 0; i < N; ++i) win[j][i] = 0.f;
     }
   }
-  uint4 nxt[B];
+  const int n = (int)(t1 - t0);
+  const T* xl = x + t0 * C + c0;       // next token to fetch
+  T* yp = y + t0 * C + c0;             // next token to write
+  RawVec<T, N> nxt[B];
 #pragma unroll
   for (int b = 0; b < B; ++b)
-    if (t0 + b < t1) nxt[b] = *reinterpret_cast<const uint4*>(x + (t0 + b) * C + c0);
-  for (int64_t tb = t0; tb < t1; tb += B) {
-    uint4 cur[B];
-#pragma unroll
-    for (int b = 0; b < B; ++b) cur[b] = nxt[b];
-#pragma unroll
-    for (int b = 0; b < B; ++b)
-      if (tb + B + b < t1) nxt[b] = *reinterpret_cast<const uint4*>(x + (tb + B + b) * C + c0);
+    if (b < n) { nxt[b] = ld_raw<T, N>(xl); xl += C; }
+  for (int tb = 0; tb < n; tb += B) {
 #pragma unroll
     for (int b = 0; b < B; ++b) {
-      if (tb + b < t1) {
-        cvt_raw<T, N>(cur[b], win[W - 1]);
+      if (tb + b < n) {
+        cvt_rawv<T, N>(nxt[b], win[W - 1]);
+        if (tb + B + b < n) { nxt[b] = ld_raw<T, N>(xl); xl += C; }   // B tokens ahead
         float o[N];
 #pragma unroll
         for (int i = 0; i < N; ++i) {
@@ -224,7 +221,8 @@ __device__ __forceinline__ void conv_fwd_run(const ConvParams& p, int64_t t0, in
           for (int j = 0; j < W; ++j) acc = fmaf(wr[i][j], win[j][i], acc);
           o[i] = p.act ? __fdividef(acc, 1.f + __expf(-acc)) : acc;
         }
-        stv<T, N>(y + (tb + b) * C + c0, o);
+        st_vec<T, N>(yp, o);
+        yp += C;
 #pragma unroll
         for (int j = 0; j < W - 1; ++j)
 #pragma unroll
@@ -246,16 +244,19 @@ __device__ __forceinline__ void conv_run_of(const ConvParams& p, int bx, int64_t
   }
 }
 
-// width-4 filter, every run that lies inside one sequence
+// width-4 filter, every run that lies inside one sequence.  A thread owns kFwdN adjacent channels
+// (8-byte vectors for 16-bit types) and keeps kFwdB tokens of loads in flight: few registers, so
+// that the resident threads together hold enough bytes in flight to cover the DRAM latency.
+constexpr int kFwdN = 4, kFwdB = 8;
 template <typename T>
-__global__ void __launch_bounds__(128, 4) conv_fwd_fast_kernel(const ConvParams p) {
-  constexpr int N = VecOf<T>::N;
-  const int c0 = (blockIdx.y * 128 + threadIdx.x) * N;
+__global__ void __launch_bounds__(128, 8) conv_fwd_fast_kernel(const ConvParams p) {
+  const int c0 = (blockIdx.y * 128 + threadIdx.x) * kFwdN;
   if (c0 >= p.C) return;
   int64_t t0, t1, bos, eos;
   int seq;
   conv_run_of(p, blockIdx.x, t0, t1);
-  if (t0 < t1 && conv_run_simple(p, t0, t1, seq, bos, eos)) conv_fwd_run<T, 4>(p, t0, t1, c0, seq, bos);
+  if (t0 < t1 && conv_run_simple(p, t0, t1, seq, bos, eos))
+    conv_fwd_run<T, 4, kFwdN, (sizeof(T) == 4 ? kFwdB / 2 : kFwdB)>(p, t0, t1, c0, seq, bos);
 }
 
 // any width, sequence starts, histories; with skip_interior != 0 only the runs the fast kernel left
@@ -474,28 +475,29 @@ __global__ void __launch_bounds__(128) conv_decode_kernel(const void* x_, const 
 // Width-4 backward in one pass for every run that lies inside one sequence:
 //   pre[s] = sum_j w[j] x[s-3+j];  dpre[s] = dy[s] act'(pre[s]);  dx[t] = sum_j w[j] dpre[t+3-j]
 //   dw[j] += dpre[s] x[s-3+j]
-// A block walks the 8 runs of its 512-token span.  Per run it stages the x and dy tiles
-// ([64 + halo tokens] x 128 channels) in shared memory with 16-byte asynchronous copies; thread
-// (channel pair, token quarter) then slides the x and dpre windows through registers over its 16
-// tokens plus 3 recomputed ones past them, so no dpre ever goes to memory.  Tokens before the
-// sequence start read the history (or zeros), tokens past its end contribute nothing.
+// A block covers a 512-token span and 64 channels: warp r walks run r of the span, lane l owns the
+// channel pair 2l, 2l+1 (a warp reads one 128-byte row segment per token).  The x and dy words are
+// fetched eight tokens ahead as raw bits; the x and dpre windows slide through registers over the
+// run's 64 tokens plus 3 recomputed ones past them, so no dpre ever goes to memory.  Tokens before
+// the sequence start read the history (or zeros), tokens past its end contribute nothing.  Few
+// registers per thread, no shared-memory staging and no barriers in the loop: 1024 threads per SM
+// keep 64 KB of loads in flight.
 // ------------------------------------------------------------------------------------------
-constexpr int kBwdCh = 128;                 // channels per block
+constexpr int kBwdCh = 64;                  // channels per block
+constexpr int kBwdAhead = 8;                // tokens of loads in flight per thread
 template <typename T>
-__global__ void __launch_bounds__(256) conv_bwd_fast_kernel(const ConvParams p) {
-  constexpr int W = 4, HALO = W - 1, XR = CONV_TT + 2 * HALO, YR = CONV_TT + HALO;
-  __shared__ __align__(16) T s_x[XR][kBwdCh];      // tokens t0-3 .. t1+2
-  __shared__ __align__(16) T s_y[YR][kBwdCh];      // tokens t0 .. t1+2
-  __shared__ float s_dw[4][kBwdCh][W];
-  const int tid = threadIdx.x, cp = tid & 63, qt = tid >> 6;
-  const int cb = blockIdx.y * kBwdCh;              // first channel of the block
+__global__ void __launch_bounds__(256, 3) conv_bwd_fast_kernel(const ConvParams p) {
+  constexpr int W = 4, HALO = W - 1, B = kBwdAhead;
+  static_assert(sizeof(T) == 2, "channel pairs travel as one 32-bit word");
+  __shared__ float s_dw[8][kBwdCh][W];
+  const int tid = threadIdx.x, lane = tid & 31, r = tid >> 5;
   const int64_t C = p.C, total = (int64_t)p.batch * p.T;
   const T* x = reinterpret_cast<const T*>(p.x);
   const T* dy = reinterpret_cast<const T*>(p.dy);
   const T* st = reinterpret_cast<const T*>(p.state);
   const T* w = reinterpret_cast<const T*>(p.w);
   T* dx = reinterpret_cast<T*>(p.dx);
-  const int c0 = cb + 2 * cp;                      // this thread's two channels
+  const int c0 = blockIdx.y * kBwdCh + 2 * lane;   // this thread's two channels
   const bool live = c0 < p.C;                      // C is even
   float wr[2][W], dwacc[2][W];
 #pragma unroll
@@ -505,104 +507,104 @@ __global__ void __launch_bounds__(256) conv_bwd_fast_kernel(const ConvParams p) 
       wr[i][j] = live ? (float)w[(int64_t)(c0 + i) * W + j] : 0.f;
       dwacc[i][j] = 0.f;
     }
-  constexpr int VPR = kBwdCh * sizeof(T) / 16;     // 16-byte vectors per tile row
-  constexpr int EPV = 16 / sizeof(T);              // elements per vector
-
-  for (int r = 0; r < 8; ++r) {
-    int64_t t0, t1;
-    if (p.cu_seqlens) { t0 = ((int64_t)blockIdx.x * 8 + r) * CONV_TT; t1 = min(t0 + CONV_TT, total); }
-    else {
-      int rpr = (p.T + 8 * CONV_TT - 1) / (8 * CONV_TT);
-      int row = blockIdx.x / rpr, rb = blockIdx.x % rpr;
-      t0 = (int64_t)row * p.T + ((int64_t)rb * 8 + r) * CONV_TT;
-      t1 = min(t0 + CONV_TT, (int64_t)(row + 1) * p.T);
-    }
-    int seq; int64_t bos, eos;
-    if (t0 >= t1 || !conv_run_simple(p, t0, t1, seq, bos, eos)) continue;   // uniform over the block
-    const int64_t send = min(t1 + HALO, eos);      // dpre exists for s < send
-    // ---- stage the tiles (rows outside the sequence: history or zeros) ----
-    for (int v = tid; v < XR * VPR; v += 256) {
-      const int row = v / VPR, col = (v % VPR) * EPV;
-      const int64_t pos = t0 - HALO + row;
-      T* dst = &s_x[row][col];
-      const bool ch_ok = cb + col < p.C;
-      if (ch_ok && pos >= bos && pos < send) cp_async16(dst, x + pos * C + cb + col, true);
-      else if (ch_ok && pos < bos && st)
-        cp_async16(dst, st + ((int64_t)seq * HALO + (pos - bos + HALO)) * C + cb + col, true);
-      else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
-    }
-    for (int v = tid; v < YR * VPR; v += 256) {
-      const int row = v / VPR, col = (v % VPR) * EPV;
-      const int64_t pos = t0 + row;
-      T* dst = &s_y[row][col];
-      if (cb + col < p.C && pos < send) cp_async16(dst, dy + pos * C + cb + col, true);
-      else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
-    }
-    cp_async_commit();
-    cp_async_wait<0>();
-    __syncthreads();
-    // ---- this thread: tokens [16 qt, 16 qt + 16) of the run, two channels ----
-    {
-      const int l0 = 16 * qt, owned = (int)(t1 - t0);   // local token index; rows of s_x are shifted by 3
-      float xw[W][2], dp[W][2];                         // circular: slot = local index & 3
+  int64_t t0, t1;
+  if (p.cu_seqlens) { t0 = ((int64_t)blockIdx.x * 8 + r) * CONV_TT; t1 = min(t0 + CONV_TT, total); }
+  else {
+    int rpr = (p.T + 8 * CONV_TT - 1) / (8 * CONV_TT);
+    int row = blockIdx.x / rpr, rb = blockIdx.x % rpr;
+    t0 = (int64_t)row * p.T + ((int64_t)rb * 8 + r) * CONV_TT;
+    t1 = min(t0 + CONV_TT, (int64_t)(row + 1) * p.T);
+  }
+  int seq; int64_t bos, eos;
+  if (live && t0 < t1 && conv_run_simple(p, t0, t1, seq, bos, eos)) {     // uniform over the warp
+    const int owned = (int)(t1 - t0);                                    // tokens whose dx is written
+    const int avail = (int)(min(t1 + HALO, eos) - t0);                   // tokens that have a dpre
+    const int steps = owned + HALO;
+    float xw[W][2], dp[W][2];                        // circular: slot = (token - t0) & 3
 #pragma unroll
-      for (int j = 0; j < HALO; ++j) {
-        const float2 v = unpack2<T>(&s_x[l0 + j][2 * cp]);          // tokens l0-3 .. l0-1
-        xw[(l0 + j + 1) & 3][0] = v.x; xw[(l0 + j + 1) & 3][1] = v.y;
-        dp[(l0 + j + 1) & 3][0] = 0.f; dp[(l0 + j + 1) & 3][1] = 0.f;
+    for (int j = 0; j < HALO; ++j) {                 // tokens t0-3 .. t0-1 -> slots 1, 2, 3
+      const int64_t pos = t0 - HALO + j;
+      uint32_t raw = 0u;
+      if (pos >= bos) raw = *reinterpret_cast<const uint32_t*>(x + pos * C + c0);
+      else if (st) raw = *reinterpret_cast<const uint32_t*>(st + ((int64_t)seq * HALO + (pos - bos + HALO)) * C + c0);
+      const float2 v = unpack2<T>(reinterpret_cast<const T*>(&raw));
+      xw[j + 1][0] = v.x; xw[j + 1][1] = v.y;
+      dp[j + 1][0] = 0.f; dp[j + 1][1] = 0.f;
+    }
+    const T* xl = x + t0 * C + c0;                   // next token to fetch
+    const T* gl = dy + t0 * C + c0;
+    T* dxp = dx + t0 * C + c0;                       // next dx row to write
+    uint32_t nx[B], ng[B];
+#pragma unroll
+    for (int b = 0; b < B; ++b) {
+      nx[b] = 0u; ng[b] = 0u;
+      if (b < avail) {
+        nx[b] = *reinterpret_cast<const uint32_t*>(xl); ng[b] = *reinterpret_cast<const uint32_t*>(gl);
+        xl += C; gl += C;
       }
+    }
+    for (int kb = 0; kb < steps; kb += B) {
 #pragma unroll
-      for (int k = 0; k < 16 + HALO; ++k) {             // l0 is a multiple of 4: slot = k & 3
-        const int l = l0 + k, b = k & 3;
-        const float2 xv = unpack2<T>(&s_x[l + HALO][2 * cp]);
-        const float2 gv = unpack2<T>(&s_y[l < YR ? l : YR - 1][2 * cp]);
-        xw[b][0] = xv.x; xw[b][1] = xv.y;
-        const float g[2] = {gv.x, gv.y};
-        const bool own = k < 16 && l < owned;
-#pragma unroll
-        for (int i = 0; i < 2; ++i) {
-          float pre = 0.f;
-#pragma unroll
-          for (int j = 0; j < W; ++j) pre = fmaf(wr[i][j], xw[(b + 1 + j) & 3][i], pre);
-          float dact = 1.f;
-          if (p.act) {
-            const float sg = __fdividef(1.f, 1.f + __expf(-pre));
-            dact = sg * fmaf(pre, 1.f - sg, 1.f);
+      for (int b8 = 0; b8 < B; ++b8) {
+        const int k = kb + b8, b = b8 & 3;
+        if (k < steps) {
+          const float2 xv = unpack2<T>(reinterpret_cast<const T*>(&nx[b8]));
+          const float2 gv = unpack2<T>(reinterpret_cast<const T*>(&ng[b8]));   // zero past `avail`
+          nx[b8] = 0u; ng[b8] = 0u;
+          if (k + B < avail) {
+            nx[b8] = *reinterpret_cast<const uint32_t*>(xl); ng[b8] = *reinterpret_cast<const uint32_t*>(gl);
+            xl += C; gl += C;
           }
-          const float d = (l < YR) ? g[i] * dact : 0.f;
-          dp[b][i] = d;
-          if (own) {
-#pragma unroll
-            for (int j = 0; j < W; ++j) dwacc[i][j] = fmaf(d, xw[(b + 1 + j) & 3][i], dwacc[i][j]);
-          }
-        }
-        if (k >= HALO) {                                // dx[l-3] = w0 dpre[l] + ... + w3 dpre[l-3]
-          const int lt = l - HALO;
-          float o[2];
+          xw[b][0] = xv.x; xw[b][1] = xv.y;
+          const float g[2] = {gv.x, gv.y};
+          const bool own = k < owned;
 #pragma unroll
           for (int i = 0; i < 2; ++i) {
-            float acc = 0.f;
+            float pre = 0.f;
 #pragma unroll
-            for (int j = 0; j < W; ++j) acc = fmaf(wr[i][j], dp[(b + 4 - j) & 3][i], acc);
-            o[i] = acc;
+            for (int j = 0; j < W; ++j) pre = fmaf(wr[i][j], xw[(b + 1 + j) & 3][i], pre);
+            float dact = 1.f;
+            if (p.act) {
+              const float sg = __fdividef(1.f, 1.f + __expf(-pre));
+              dact = sg * fmaf(pre, 1.f - sg, 1.f);
+            }
+            const float d = g[i] * dact;
+            dp[b][i] = d;
+            if (own) {
+#pragma unroll
+              for (int j = 0; j < W; ++j) dwacc[i][j] = fmaf(d, xw[(b + 1 + j) & 3][i], dwacc[i][j]);
+            }
           }
-          if (live && lt < owned) pack2<T>(dx + (t0 + lt) * C + c0, o[0], o[1]);
+          if (k >= HALO) {                           // dx[k-3] = w0 dpre[k] + ... + w3 dpre[k-3]
+            float o[2];
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+              float acc = 0.f;
+#pragma unroll
+              for (int j = 0; j < W; ++j) acc = fmaf(wr[i][j], dp[(b + 4 - j) & 3][i], acc);
+              o[i] = acc;
+            }
+            pack2<T>(dxp, o[0], o[1]);
+            dxp += C;
+          }
         }
       }
     }
-    __syncthreads();       // the tiles are rewritten by the next run
   }
-  // reduce the four token quarters, then one partial per (block, channel, tap)
+  // reduce the eight runs, then one partial per (block, channel, tap)
 #pragma unroll
   for (int i = 0; i < 2; ++i)
 #pragma unroll
-    for (int j = 0; j < W; ++j) s_dw[qt][2 * cp + i][j] = dwacc[i][j];
+    for (int j = 0; j < W; ++j) s_dw[r][2 * lane + i][j] = dwacc[i][j];
   __syncthreads();
   for (int e = tid; e < kBwdCh * W; e += 256) {
     const int ch = e / W, j = e % W;
-    if (cb + ch < p.C)
-      p.dw_part[((int64_t)blockIdx.x * C + cb + ch) * W + j] =
-          s_dw[0][ch][j] + s_dw[1][ch][j] + s_dw[2][ch][j] + s_dw[3][ch][j];
+    if (blockIdx.y * kBwdCh + ch < p.C) {
+      float acc = 0.f;
+#pragma unroll
+      for (int q = 0; q < 8; ++q) acc += s_dw[q][ch][j];
+      p.dw_part[((int64_t)blockIdx.x * C + blockIdx.y * kBwdCh + ch) * W + j] = acc;
+    }
   }
 }
 
@@ -688,7 +690,10 @@ static int conv_fwd_launch(const ConvParams& p, cudaStream_t s) {
                               : (int64_t)p.batch * ((p.T + CONV_TT - 1) / CONV_TT);
   dim3 grid((unsigned)runs, (unsigned)((p.C / N + 127) / 128));
   const int fast = p.W == 4;
-  if (fast) conv_fwd_fast_kernel<T><<<grid, 128, 0, s>>>(p);
+  if (fast) {
+    dim3 gridf((unsigned)runs, (unsigned)((p.C / kFwdN + 127) / 128));
+    conv_fwd_fast_kernel<T><<<gridf, 128, 0, s>>>(p);
+  }
   conv_fwd_kernel<T><<<grid, 128, 0, s>>>(p, fast);
   return cudaGetLastError() == cudaSuccess ? KDA_OK : KDA_ERR_LAUNCH;
 }

@@ -12,7 +12,7 @@ namespace kda {
 enum Stage {
   kStagePrepare = 0, kStageStateFwd, kStageStateBwd, kStageBwdChunk,
   kStageRecurrent, kStageGateFwd, kStageGateBwd, kStageL2norm, kStageConv, kStageOffsets,
-  kStageAffine, kStageCount
+  kStageAffine, kStageEpilogue, kStageCount
 };
 
 void stage_begin(int stage, cudaStream_t s);

@@ -45,6 +45,9 @@ _SIGNATURES = {
                                     c_int, c_float, c_int64, c_void_p]),
     "kda_l2norm_fwd": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int64, c_int, c_float, c_void_p]),
     "kda_l2norm_bwd": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int64, c_int, c_void_p]),
+    "kda_output_gate_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int64, c_int, c_float, c_void_p]),
+    "kda_output_gate_bwd_partial_rows": (c_int64, [c_int64]),
+    "kda_output_gate_bwd": (c_int, [c_void_p] * 4 + [c_int] + [c_void_p] * 3 + [c_int64, c_int, c_float, c_void_p]),
     "kda_chunk_fwd_workspace_bytes": (c_int64, [c_int64, c_int]),
     "kda_chunk_fwd": (c_int, [c_void_p] * 12 + [c_int, c_int64, c_int, c_int, c_int, c_int, c_void_p,
                               c_int64, c_void_p]),

@@ -21,6 +21,7 @@ SOURCES = [
     "kda_chunk_fwd.cu",
     "kda_prepare_tc.cu",
     "kda_decode_prep.cu",
+    "kda_epilogue.cu",
     "kda_state_tc.cu",
     "kda_chunk_bwd.cu",
     "kda_bwd_chunk_tc.cu",

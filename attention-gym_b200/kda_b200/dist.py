@@ -14,6 +14,13 @@
          sends its true leaving state, the last rank only receives);
       3. every rank, in parallel: the recurrence with the true h_in -> outputs.
 
+The backward pass runs the mirror-image chain (``cp_chunk_backward``): the gradient entering a
+slice from the right, ``dh_out``, maps affinely to the one leaving it on the left,
+``dh_in = M_r^T dh_out + c_r`` with the same transition ``M_r``; ``c_r`` is the slice's own backward
+with ``dh_out = 0``.  So middle ranks compute ``c_r`` in parallel, the [H, K, V] gradient travels
+from the last rank to the first, and every rank then runs its local backward with the true
+``dh_out``.  ``cp_chunk_kda`` ties both chains into one differentiable call.
+
 The reference has no multi-GPU code on this path (docs/linear.md:220-222 leaves context
 parallelism to the caller); the per-slice math is the chunk recurrence of
 attn_gym/linear/kda/naive.py:99-138 applied to an identity initial state.
@@ -104,18 +111,34 @@ class CudaSlice:
         return out
 
 
-def cp_chunk_forward(q, k, v, cumulative_gate, beta, initial_state=None, *, group=None,
+def _cp_forward(q, k, v, cumulative_gate, beta, initial_state=None, *, group=None,
                      slice_factory: Callable = CudaSlice, rank: Optional[int] = None,
                      world: Optional[int] = None, send: Optional[Callable] = None,
                      recv: Optional[Callable] = None):
-    """Context-parallel chunked forward of this rank's slice ``[1, T_local, H, 128]``.
+    """cp_chunk_forward that also returns the entering state and the slice transition (middle ranks)."""
+    rank, world, send, recv = _resolve_p2p(group, rank, world, send, recv)
+    last = rank + 1 == world
+    if not last and q.shape[1] % 64:
+        raise ValueError("every slice but the last must hold whole 64-token chunks")
+    part = slice_factory(q, k, v, cumulative_gate, beta)           # step 1, all ranks in parallel
+    if rank == 0:
+        out, h_out = part.run(initial_state)
+        if not last:
+            send(h_out, 1)
+        return out, h_out, initial_state, None
+    b = trans = None
+    if not last:                                                   # still step 1
+        b, trans = part.zero_state_result(), part.transition()
+    h_in = torch.empty(q.shape[0], q.shape[2], q.shape[3], v.shape[-1], dtype=torch.float32,
+                       device=q.device)
+    recv(h_in, rank - 1)                                           # step 2
+    if not last:
+        send(part.affine(trans, h_in, b), rank + 1)
+    out, h_out = part.run(h_in)                                    # step 3
+    return out, h_out, h_in, trans
 
-    ``T_local`` must be a multiple of 64 on every rank but the last, so that slices hold whole
-    chunks and the chunk-local cumulative gate needs no exchange.  ``initial_state`` is used on rank
-    0 only.  Returns (local output, state leaving this slice); on the last rank the second result is
-    the final state of the whole sequence.  Only boundary states are communicated:
-    ``send(tensor, dst)`` / ``recv(tensor, src)`` default to torch.distributed point-to-point calls.
-    """
+
+def _resolve_p2p(group, rank, world, send, recv):
     if rank is None:
         import torch.distributed as dist
 
@@ -128,25 +151,108 @@ def cp_chunk_forward(q, k, v, cumulative_gate, beta, initial_state=None, *, grou
 
         def recv(t, src):
             dist.recv(t, src, group=group)
+    return rank, world, send, recv
 
+
+def cp_chunk_forward(q, k, v, cumulative_gate, beta, initial_state=None, *, group=None,
+                     slice_factory: Callable = CudaSlice, rank: Optional[int] = None,
+                     world: Optional[int] = None, send: Optional[Callable] = None,
+                     recv: Optional[Callable] = None):
+    """Context-parallel chunked forward of this rank's slice ``[1, T_local, H, 128]``.
+
+    ``T_local`` must be a multiple of 64 on every rank but the last, so that slices hold whole
+    chunks and the chunk-local cumulative gate needs no exchange.  ``initial_state`` is used on rank
+    0 only.  Returns (local output, state leaving this slice); on the last rank the second result is
+    the final state of the whole sequence.  Only boundary states are communicated:
+    ``send(tensor, dst)`` / ``recv(tensor, src)`` default to torch.distributed point-to-point calls.
+    """
+    return _cp_forward(q, k, v, cumulative_gate, beta, initial_state, group=group,
+                       slice_factory=slice_factory, rank=rank, world=world, send=send, recv=recv)[:2]
+
+
+def cuda_slice_grads(q, k, v, cumulative_gate, beta, h_in, d_out, dh_out):
+    """Local backward of one slice on the CUDA kernels: the gradients of (output, leaving state)
+    with cotangents (d_out, dh_out) with respect to q, k, v, gate, beta and the entering state."""
+    from .api import chunk_kda
+
+    batch, heads = q.shape[0], q.shape[2]
+    if h_in is None:
+        h_in = torch.zeros(batch, heads, q.shape[3], v.shape[3], dtype=torch.float32, device=q.device)
+    leaves = [t.detach().requires_grad_() for t in (q, k, v, cumulative_gate, beta, h_in)]
+    with torch.enable_grad():
+        out, h_out = chunk_kda(*leaves, output_final_state=True)
+        return torch.autograd.grad((out, h_out), leaves, (d_out, dh_out))
+
+
+def _transposed_affine(trans, dh_out, c):
+    """M^T dh_out + c for M [B, H, K, K] and states [B, H, K, V] (fp32)."""
+    return torch.baddbmm(c.flatten(0, 1), trans.flatten(0, 1).transpose(1, 2).float(),
+                         dh_out.flatten(0, 1).float()).view_as(c)
+
+
+def cp_chunk_backward(q, k, v, cumulative_gate, beta, h_in, trans, d_out, d_final_state=None, *,
+                      group=None, local_grads: Callable = cuda_slice_grads,
+                      rank: Optional[int] = None, world: Optional[int] = None,
+                      send: Optional[Callable] = None, recv: Optional[Callable] = None):
+    """Context-parallel backward of this rank's slice.
+
+    ``h_in`` is the state that entered the slice in the forward chain and ``trans`` the slice
+    transition (both as returned by the forward chain; ``trans`` is only needed on middle ranks).
+    ``d_out`` is the cotangent of the local output; ``d_final_state`` (last rank only) that of the
+    final state.  Returns (dq, dk, dv, d_gate, d_beta, d_h_in); on rank 0 the last one is the
+    gradient of the initial state.  Only [B, H, K, V] fp32 state gradients are communicated, from
+    rank r + 1 to rank r.
+    """
+    rank, world, send, recv = _resolve_p2p(group, rank, world, send, recv)
     last = rank + 1 == world
-    if not last and q.shape[1] % 64:
-        raise ValueError("every slice but the last must hold whole 64-token chunks")
-    part = slice_factory(q, k, v, cumulative_gate, beta)           # step 1, all ranks in parallel
-    if rank == 0:
-        out, h_out = part.run(initial_state)
-        if not last:
-            send(h_out, 1)
+    shape = (q.shape[0], q.shape[2], q.shape[3], v.shape[3])
+    if last:
+        dh_out = (torch.zeros(shape, dtype=torch.float32, device=q.device)
+                  if d_final_state is None else d_final_state.float())
+        grads = local_grads(q, k, v, cumulative_gate, beta, h_in, d_out, dh_out)
+        if rank > 0:
+            send(grads[5].contiguous(), rank - 1)
+        return grads
+    c = None
+    if rank > 0:      # middle rank, in parallel with the others: c = the backward with dh_out = 0
+        zero = torch.zeros(shape, dtype=torch.float32, device=q.device)
+        c = local_grads(q, k, v, cumulative_gate, beta, h_in, d_out, zero)[5]
+    dh_out = torch.empty(shape, dtype=torch.float32, device=q.device)
+    recv(dh_out, rank + 1)
+    if rank > 0:
+        send(_transposed_affine(trans, dh_out, c.float()).contiguous(), rank - 1)
+    return local_grads(q, k, v, cumulative_gate, beta, h_in, d_out, dh_out)
+
+
+class _CPChunkKDA(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, cumulative_gate, beta, initial_state, group):
+        out, h_out, h_in, trans = _cp_forward(q, k, v, cumulative_gate, beta, initial_state,
+                                              group=group)
+        ctx.group = group
+        # the initial state is read on rank 0 only; elsewhere it gets no gradient
+        ctx.has_h0 = initial_state is not None and _resolve_p2p(group, None, None, None, None)[0] == 0
+        ctx.save_for_backward(q, k, v, cumulative_gate, beta, h_in, trans)
         return out, h_out
-    b = trans = None
-    if not last:                                                   # still step 1
-        b, trans = part.zero_state_result(), part.transition()
-    h_in = torch.empty(q.shape[0], q.shape[2], q.shape[3], v.shape[-1], dtype=torch.float32,
-                       device=q.device)
-    recv(h_in, rank - 1)                                           # step 2
-    if not last:
-        send(part.affine(trans, h_in, b), rank + 1)
-    return part.run(h_in)                                          # step 3
+
+    @staticmethod
+    @torch.autograd.function.once_differentiable
+    def backward(ctx, d_out, d_h_out):
+        q, k, v, gate, beta, h_in, trans = ctx.saved_tensors
+        grads = cp_chunk_backward(q, k, v, gate, beta, h_in, trans, d_out.contiguous(), d_h_out,
+                                  group=ctx.group)
+        dq, dk, dv, dg, db, dh = grads
+        return (dq.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype), dg.to(gate.dtype), db.to(beta.dtype),
+                dh if ctx.has_h0 else None, None)
 
 
-__all__ = ["shard_ranges", "cp_chunk_forward", "CudaSlice"]
+def cp_chunk_kda(q, k, v, cumulative_gate, beta, initial_state=None, *, group=None):
+    """Differentiable context-parallel ``chunk_kda`` of this rank's slice: the forward boundary-state
+    chain and, in backward, the state-gradient chain in the opposite direction.  Returns (local
+    output, state leaving the slice).  The cotangent of the leaving state is used on the last rank
+    only (on the other ranks it arrives through the chain)."""
+    return _CPChunkKDA.apply(q, k, v, cumulative_gate, beta, initial_state, group)
+
+
+__all__ = ["shard_ranges", "cp_chunk_forward", "cp_chunk_backward", "cp_chunk_kda",
+           "cuda_slice_grads", "CudaSlice"]

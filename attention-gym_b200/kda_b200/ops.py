@@ -69,6 +69,10 @@ _define("kda_bounded_gate_bwd",
         "Tensor? chunk_offsets, int chunk_size, float lower_bound) -> (Tensor, Tensor, Tensor)")
 _define("kda_l2norm_fwd", "(Tensor x, float eps) -> (Tensor, Tensor)")
 _define("kda_l2norm_bwd", "(Tensor y, Tensor rstd, Tensor dy) -> Tensor")
+# output epilogue of the layer (examples/kda_training.py:507-539): RMSNorm * weight * sigmoid(gate)
+_define("kda_output_gate_fwd", "(Tensor o, Tensor gate_logits, Tensor weight, float eps) -> Tensor")
+_define("kda_output_gate_bwd",
+        "(Tensor o, Tensor gate_logits, Tensor weight, Tensor dy, float eps) -> (Tensor, Tensor, Tensor)")
 _define("short_conv_fwd",
         "(Tensor x, Tensor weight, Tensor? cu_seqlens=None, Tensor? initial_state=None, *, "
         "str? activation=None) -> Tensor")
@@ -492,6 +496,43 @@ def _(x, eps):
 @torch.library.register_fake(f"{_NS}::kda_l2norm_bwd")
 def _(y, rstd, dy):
     return torch.empty_like(y)
+
+
+@torch.library.impl(_lib, "kda_output_gate_fwd", "CUDA")
+def _output_gate_fwd(o, gate_logits, weight, eps):
+    o = o.contiguous()
+    gate_logits = gate_logits.to(o.dtype).contiguous()
+    dim = o.shape[-1]
+    y = torch.empty_like(o)
+    _cabi.call("kda_output_gate_fwd", 1, _cabi.ptr(o), _cabi.ptr(gate_logits),
+               _cabi.ptr(weight.float().contiguous()), _cabi.dt(o), _cabi.ptr(y), o.numel() // dim,
+               dim, float(eps), _cabi.stream())
+    return y
+
+
+@torch.library.impl(_lib, "kda_output_gate_bwd", "CUDA")
+def _output_gate_bwd(o, gate_logits, weight, dy, eps):
+    o = o.contiguous()
+    gate_logits, dy = gate_logits.to(o.dtype).contiguous(), dy.to(o.dtype).contiguous()
+    dim = o.shape[-1]
+    rows = o.numel() // dim
+    d_o, d_logits = torch.empty_like(o), torch.empty_like(o)
+    partial = torch.empty(_cabi.lib().kda_output_gate_bwd_partial_rows(rows), dim,
+                          dtype=torch.float32, device=o.device)
+    _cabi.call("kda_output_gate_bwd", 1, _cabi.ptr(o), _cabi.ptr(gate_logits), _cabi.ptr(dy),
+               _cabi.ptr(weight.float().contiguous()), _cabi.dt(o), _cabi.ptr(d_o),
+               _cabi.ptr(d_logits), _cabi.ptr(partial), rows, dim, float(eps), _cabi.stream())
+    return d_o, d_logits, partial.sum(0).to(weight.dtype)
+
+
+@torch.library.register_fake(f"{_NS}::kda_output_gate_fwd")
+def _(o, gate_logits, weight, eps):
+    return torch.empty_like(o)
+
+
+@torch.library.register_fake(f"{_NS}::kda_output_gate_bwd")
+def _(o, gate_logits, weight, dy, eps):
+    return torch.empty_like(o), torch.empty_like(o), torch.empty_like(weight)
 
 
 # --------------------------------------------------------------------------------------------

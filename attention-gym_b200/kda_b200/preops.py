@@ -128,6 +128,41 @@ def l2norm(x, eps: float = 1e-6, *, cu_seqlens=None):
     return _L2Norm.apply(x, eps)
 
 
+class _OutputGate(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, o, gate_logits, weight, eps):
+        ctx.eps = eps
+        ctx.save_for_backward(o, gate_logits, weight)
+        return _ops.kda_output_gate_fwd(o, gate_logits, weight, eps)
+
+    @staticmethod
+    @torch.autograd.function.once_differentiable
+    def backward(ctx, dy):
+        o, gate_logits, weight = ctx.saved_tensors
+        d_o, d_logits, d_weight = _ops.kda_output_gate_bwd(o, gate_logits, weight, dy, ctx.eps)
+        return d_o, d_logits.to(gate_logits.dtype), d_weight, None
+
+
+def gated_output_norm(o, gate_logits, weight, eps: float = 1e-5):
+    """``rms_norm(o, weight, eps) * sigmoid(gate_logits)`` over the last (head) dimension in one
+    pass, fp32 arithmetic, result in ``o.dtype``.
+
+    The epilogue the reference module applies to the output of ``chunk_kda`` as three launches
+    (examples/kda_training.py:507-517 ``F.rms_norm``, :519-532 the sigmoid of the gate projection,
+    :535-539 their product).  ``o`` and ``gate_logits``: ``[..., D]`` of one shape; ``weight``:
+    ``[D]``.  Differentiable in all three.
+    """
+    if not o.is_cuda:
+        raise ValueError("gated_output_norm requires CUDA tensors")
+    if o.shape != gate_logits.shape or tuple(weight.shape) != (o.shape[-1],):
+        raise ValueError("gate_logits must have the shape of o and weight must be [D]")
+    if o.shape[-1] % 4 or o.shape[-1] > 512:
+        raise ValueError("gated_output_norm requires the last dimension to be a multiple of 4, at most 512")
+    if o.dtype not in (torch.float32, torch.bfloat16, torch.float16):
+        raise TypeError("gated_output_norm takes float32, bfloat16 or float16 tensors")
+    return _OutputGate.apply(o, gate_logits, weight, float(eps))
+
+
 class _ShortConv(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, weight, cu_seqlens, initial_state, activation):
@@ -244,5 +279,5 @@ def causal_conv1d_decode(x, weight, state, *, activation=None, state_indices=Non
                                   activation=activation)
 
 
-__all__ = ["bounded_gate_cumsum", "l2norm", "causal_conv1d", "causal_conv1d_decode",
+__all__ = ["bounded_gate_cumsum", "l2norm", "gated_output_norm", "causal_conv1d", "causal_conv1d_decode",
            "MAX_GATE_LOWER_BOUND_MAGNITUDE"]

@@ -424,6 +424,7 @@ def bench_preops(device, peaks, batch=8, tokens=4096, iters=20):
     xc = x.view(batch, tokens, H * D)
     dyc = dy.view(batch, tokens, H * D)
     w = (torch.randn(H * D, 4, generator=gen) * 0.5).bfloat16().to(device)
+    norm_w = (1 + 0.1 * torch.randn(D, generator=gen)).to(device)
     cases = {
         "gate_cumsum_fwd": (lambda: ops.kda_bounded_gate_fwd_dense(raw, a_log, dt_bias, CHUNK, -5.0), 6),
         "gate_cumsum_bwd": (lambda: ops.kda_bounded_gate_bwd(raw, a_log, dt_bias, dcum, None, None,
@@ -432,6 +433,8 @@ def bench_preops(device, peaks, batch=8, tokens=4096, iters=20):
         "l2norm_bwd": (lambda: ops.kda_l2norm_bwd(y, rstd, dy), 6),
         "short_conv_fwd": (lambda: ops.short_conv_fwd(xc, w, activation="silu"), 4),
         "short_conv_bwd": (lambda: ops.short_conv_bwd(xc, w, dyc, activation="silu"), 6),
+        "output_gate_fwd": (lambda: ops.kda_output_gate_fwd(x, raw, norm_w, 1e-5), 6),
+        "output_gate_bwd": (lambda: ops.kda_output_gate_bwd(x, raw, norm_w, dy, 1e-5), 10),
     }
     out = {}
     for name, (fn, bytes_per_elem) in cases.items():

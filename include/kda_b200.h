@@ -107,6 +107,19 @@ int kda_l2norm_fwd(const void* x, int dtype, void* y, float* rstd, int64_t rows,
 int kda_l2norm_bwd(const void* y, const float* rstd, const void* dy, int dtype, void* dx,
                    int64_t rows, int dim, void* stream);
 
+/* Output epilogue of the layer in one pass: y = o * rsqrt(mean(o^2) + eps) * weight * sigmoid(gate_logits)
+ * over rows of `dim` elements (o, gate_logits, y in `dtype`; weight fp32 [dim]), and its backward:
+ * d_o, d_logits in `dtype`, and the weight gradient as kda_output_gate_bwd_partial_rows(rows) fp32
+ * rows of [dim] that the caller sums.  dim: a multiple of 4, at most 512.
+ * Replaces the three launches of the reference module after chunk_kda (examples/kda_training.py:
+ * 507-517 F.rms_norm, :519-532 sigmoid of the gate projection, :535-539 their product). */
+int kda_output_gate_fwd(const void* o, const void* gate_logits, const float* weight, int dtype,
+                        void* y, int64_t rows, int dim, float eps, void* stream);
+int64_t kda_output_gate_bwd_partial_rows(int64_t rows);
+int kda_output_gate_bwd(const void* o, const void* gate_logits, const void* dy, const float* weight,
+                        int dtype, void* d_o, void* d_logits, float* dw_partial, int64_t rows,
+                        int dim, float eps, void* stream);
+
 /* Chunked forward, bf16 q/k/v [tokens, H, 128], fp32 cumulative log2 gate and beta, chunk 64.
  * Writes out (bf16 [tokens, H, 128]), the tape aqk / akk (bf16 [tokens, H, 64]) and, when
  * final_state != NULL, the fp32 final states.  workspace: kda_chunk_fwd_workspace_bytes() bytes,

@@ -320,6 +320,16 @@ def l2norm_bwd_ref(y, rstd, dy):
     return (rstd.to(dt) * (dyc - yc * (dyc * yc).sum(-1, keepdim=True))).to(y.dtype)
 
 
+def gated_output_norm_ref(o, gate_logits, weight, eps=1e-5):
+    """``o * rsqrt(mean(o^2) + eps) * weight * sigmoid(gate_logits)`` over the last dim: the
+    layer's output epilogue (examples/kda_training.py:507-517 RMSNorm, :519-539 sigmoid gate and
+    product), in fp32 (fp64 for fp64 input) without intermediate rounding."""
+    dt = _compute_dtype(o)
+    oc = o.to(dt)
+    rstd = torch.rsqrt((oc * oc).mean(-1, keepdim=True) + eps)
+    return (oc * rstd * weight.to(dt) * torch.sigmoid(gate_logits.to(dt))).to(o.dtype)
+
+
 def causal_conv1d_ref(x, weight, activation=None, cu_seqlens=None, initial_state=None):
     """Depthwise causal convolution ``y[t,c] = act(sum_j w[c,j] x[t-(W-1)+j, c])``.
 

@@ -6,6 +6,7 @@ import torch.nn.functional as F
 
 import kda_b200
 from kda_b200.chunk_schedule import chunk_capacity, prepare_ragged_chunk_metadata
+from helpers import assert_normalised
 from oracle import kda_oracle as orc
 
 pytestmark = pytest.mark.gpu
@@ -134,3 +135,29 @@ def test_conv_packed_and_decode():
         torch.testing.assert_close(yd[s].cpu(), want, atol=1e-5, rtol=1e-5)
         torch.testing.assert_close(pool_gpu[slot].cpu(), ext[1:], atol=0, rtol=0)
     assert torch.equal(pool_gpu[[0, 3, 4]].cpu(), pool[[0, 3, 4]])
+
+
+@pytest.mark.parametrize("dtype,dim,rows,tol", [
+    (torch.bfloat16, 128, (3, 37, 4), 2e-2), (torch.float16, 64, (1, 130, 2), 4e-3),
+    (torch.bfloat16, 256, (2, 19, 1), 2e-2), (torch.float32, 128, (2, 33, 4), 2e-5),
+    (torch.float32, 96, (1, 21, 3), 2e-5), (torch.bfloat16, 128, (1, 4099, 8), 2e-2),
+])
+def test_gated_output_norm(dtype, dim, rows, tol):
+    """RMSNorm * weight * sigmoid(gate) epilogue, values and the three gradients, against the fp32
+    oracle evaluated on the same (rounded) inputs."""
+    gen = torch.Generator().manual_seed(dim + rows[1])
+    o = torch.randn(*rows, dim, generator=gen).to(dtype)
+    z = (2 * torch.randn(*rows, dim, generator=gen)).to(dtype)
+    w = 1 + 0.2 * torch.randn(dim, generator=gen)
+    dy = torch.randn(*rows, dim, generator=gen).to(dtype)
+    ro, rz, rw = (t.float().requires_grad_() for t in (o, z, w))
+    ref = orc.gated_output_norm_ref(ro, rz, rw, 1e-5)
+    rgo, rgz, rgw = torch.autograd.grad(ref, (ro, rz, rw), dy.float())
+    go, gz, gw = (t.cuda().requires_grad_() for t in (o, z, w))
+    y = kda_b200.gated_output_norm(go, gz, gw, 1e-5)
+    assert y.dtype == dtype
+    y.backward(dy.cuda())
+    assert_normalised(y.float(), ref.detach(), tol, "epilogue output")
+    assert_normalised(go.grad.float(), rgo, tol, "epilogue d_o")
+    assert_normalised(gz.grad.float(), rgz, tol, "epilogue d_gate_logits")
+    assert_normalised(gw.grad.float(), rgw, max(tol / 4, 2e-5), "epilogue d_weight")

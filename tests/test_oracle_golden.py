@@ -129,3 +129,18 @@ def test_slice_transition_composes():
     _, zero = orc.recurrent_kda_ref(inp["q"], inp["k"], inp["v"], g2, beta, None)
     m = orc.slice_transition_ref(inp["k"][0], g2[0], beta[0])
     torch.testing.assert_close(full[0], m @ h0[0] + zero[0], atol=1e-12, rtol=1e-9)
+
+
+def test_gated_output_norm_matches_torch_composition():
+    """The epilogue oracle against the three torch operations the reference module applies
+    (F.rms_norm, sigmoid, product) in fp64, values and gradients."""
+    gen = torch.Generator().manual_seed(3)
+    o = torch.randn(5, 7, 3, 128, generator=gen, dtype=torch.float64, requires_grad=True)
+    z = torch.randn(5, 7, 3, 128, generator=gen, dtype=torch.float64, requires_grad=True)
+    w = (1 + 0.1 * torch.randn(128, generator=gen, dtype=torch.float64)).requires_grad_()
+    dy = torch.randn(5, 7, 3, 128, generator=gen, dtype=torch.float64)
+    ref = torch.nn.functional.rms_norm(o, (128,), w, eps=1e-5) * z.sigmoid()
+    got = orc.gated_output_norm_ref(o, z, w, 1e-5)
+    _close(got, ref, 1e-12)
+    for a, b in zip(torch.autograd.grad(got, (o, z, w), dy), torch.autograd.grad(ref, (o, z, w), dy)):
+        _close(a, b, 1e-12)
