@@ -9,6 +9,7 @@
 // HBM-bound streaming kernels: a thread owns 16 bytes of adjacent channels and walks a run of
 // consecutive tokens with a W-wide register window, so every element is read once per pass
 // (plus a W-1 halo per run).
+#include <type_traits>
 #include "kda_common.cuh"
 
 namespace kda {
@@ -158,6 +159,43 @@ __device__ __forceinline__ void st_vec(T* p, const float (&x)[N]) {
   else *reinterpret_cast<uint32_t*>(p) = r.w[0];
 }
 
+// two 16-bit values in one register word <-> two floats (bf16: a shift and a mask; no memory trip)
+template <typename T>
+__device__ __forceinline__ float2 word_to_float2(uint32_t u) {
+  if constexpr (std::is_same<T, __nv_bfloat16>::value)
+    return make_float2(__uint_as_float(u << 16), __uint_as_float(u & 0xffff0000u));
+  else return __half22float2(*reinterpret_cast<const __half2*>(&u));
+}
+template <typename T>
+__device__ __forceinline__ uint32_t float2_to_word(float a, float b) {
+  if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<const uint32_t*>(&v);
+  } else {
+    const __half2 v = __floats2half2_rn(a, b);
+    return *reinterpret_cast<const uint32_t*>(&v);
+  }
+}
+template <typename T, int N>
+__device__ __forceinline__ void words_to_float(const RawVec<T, N>& raw, float (&x)[N]) {
+  static_assert(sizeof(T) == 2, "16-bit types");
+#pragma unroll
+  for (int i = 0; i < N / 2; ++i) {
+    const float2 v = word_to_float2<T>(raw.w[i]);
+    x[2 * i] = v.x; x[2 * i + 1] = v.y;
+  }
+}
+template <typename T, int N>
+__device__ __forceinline__ void st_words(T* p, const float (&x)[N]) {
+  static_assert(sizeof(T) == 2, "16-bit types");
+  uint32_t w[N / 2];
+#pragma unroll
+  for (int i = 0; i < N / 2; ++i) w[i] = float2_to_word<T>(x[2 * i], x[2 * i + 1]);
+  if constexpr (N == 8) *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
+  else if constexpr (N == 4) *reinterpret_cast<uint2*>(p) = make_uint2(w[0], w[1]);
+  else *reinterpret_cast<uint32_t*>(p) = w[0];
+}
+
 // Sequence that holds a run starting at token t0.  Returns true when the whole run [t0, t1) lies in
 // that sequence: the fast kernels then handle it, reading the history (or zeros) before the sequence
 // start and nothing past its end.  Runs that straddle a packed sequence boundary, and first runs
@@ -244,19 +282,108 @@ __device__ __forceinline__ void conv_run_of(const ConvParams& p, int bx, int64_t
   }
 }
 
+// The same for 16-bit types and the width-4 filter, written for few instructions per element: the
+// window is circular (token k lives in slot k & 3, so nothing is moved), words are converted in
+// registers, and groups of B tokens that need no bounds checks run without any.
+template <typename T, int N, int B, bool ACT>
+__device__ __forceinline__ void conv_fwd_run16(const ConvParams& p, int64_t t0, int64_t t1, int c0, int seq,
+                                               int64_t bos) {
+  constexpr int W = 4;
+  static_assert(B % 4 == 0, "the window slot of a token is its position in the group");
+  const T* x = reinterpret_cast<const T*>(p.x);
+  const T* w = reinterpret_cast<const T*>(p.w);
+  const T* st = reinterpret_cast<const T*>(p.state);
+  T* y = reinterpret_cast<T*>(p.y);
+  const int64_t C = p.C;
+  float wr[N][W], win[W][N];
+#pragma unroll
+  for (int i = 0; i < N; ++i) {          // the four taps of a channel are one 8-byte word pair
+    RawVec<T, 4> taps = ld_raw<T, 4>(w + (int64_t)(c0 + i) * W);
+    words_to_float<T, 4>(taps, wr[i]);
+  }
+#pragma unroll
+  for (int j = 0; j < W - 1; ++j) {      // tokens t0-3 .. t0-1 -> slots 1, 2, 3
+    const int64_t pos = t0 - (W - 1) + j;
+    if (pos >= bos) words_to_float<T, N>(ld_raw<T, N>(x + pos * C + c0), win[j + 1]);
+    else if (st) words_to_float<T, N>(ld_raw<T, N>(st + ((int64_t)seq * (W - 1) + (pos - bos + W - 1)) * C + c0), win[j + 1]);
+    else {
+#pragma unroll
+      for (int i = 0; i < N; ++i) win[j + 1][i] = 0.f;
+    }
+  }
+  // Channel pairs go through the packed fp32 instructions (two lanes per issue slot); the results are
+  // the same correctly rounded products and sums as the scalar forms.
+  auto token = [&](const RawVec<T, N>& raw, int slot, T* out) {    // slot: constant after unrolling
+    words_to_float<T, N>(raw, win[slot]);
+    const int s1 = (slot + 1) & 3, s2 = (slot + 2) & 3, s3 = (slot + 3) & 3;
+    float o[N];
+#pragma unroll
+    for (int i = 0; i < N; i += 2) {
+      float2 acc = __fmul2_rn(make_float2(wr[i][0], wr[i + 1][0]), make_float2(win[s1][i], win[s1][i + 1]));
+      acc = __ffma2_rn(make_float2(wr[i][1], wr[i + 1][1]), make_float2(win[s2][i], win[s2][i + 1]), acc);
+      acc = __ffma2_rn(make_float2(wr[i][2], wr[i + 1][2]), make_float2(win[s3][i], win[s3][i + 1]), acc);
+      acc = __ffma2_rn(make_float2(wr[i][3], wr[i + 1][3]), make_float2(win[slot][i], win[slot][i + 1]), acc);
+      if (ACT) {                                   // acc / (1 + e^-acc)
+        const float2 e = __fmul2_rn(acc, make_float2(-kLog2e, -kLog2e));
+        const float2 den = __fadd2_rn(make_float2(fexp2(e.x), fexp2(e.y)), make_float2(1.f, 1.f));
+        acc = __fmul2_rn(acc, make_float2(__fdividef(1.f, den.x), __fdividef(1.f, den.y)));
+      }
+      o[i] = acc.x; o[i + 1] = acc.y;
+    }
+    st_words<T, N>(out, o);
+  };
+  const int n = (int)(t1 - t0);
+  const T* xrow = x + t0 * C + c0;
+  T* yrow = y + t0 * C + c0;
+  const uint32_t Cu = (uint32_t)p.C;     // element offsets inside a run fit 32 bits (checked at launch)
+  RawVec<T, N> nxt[B];
+#pragma unroll
+  for (int b = 0; b < B; ++b)
+    if (b < n) nxt[b] = ld_raw<T, N>(xrow + b * Cu);
+  int k = 0;
+  for (; k + 2 * B <= n; k += B) {       // B tokens and the B after them all exist
+    const uint32_t off = (uint32_t)k * Cu;
+#pragma unroll
+    for (int b = 0; b < B; ++b) {
+      const RawVec<T, N> cur = nxt[b];
+      nxt[b] = ld_raw<T, N>(xrow + (off + (B + b) * Cu));
+      token(cur, b & 3, yrow + (off + b * Cu));
+    }
+  }
+  for (; k < n; k += B) {
+#pragma unroll
+    for (int b = 0; b < B; ++b) {
+      if (k + b < n) {
+        const RawVec<T, N> cur = nxt[b];
+        if (k + B + b < n) nxt[b] = ld_raw<T, N>(xrow + (uint32_t)(k + B + b) * Cu);
+        token(cur, b & 3, yrow + (uint32_t)(k + b) * Cu);
+      }
+    }
+  }
+}
+
 // width-4 filter, every run that lies inside one sequence.  A thread owns kFwdN adjacent channels
-// (8-byte vectors for 16-bit types) and keeps kFwdB tokens of loads in flight: few registers, so
-// that the resident threads together hold enough bytes in flight to cover the DRAM latency.
-constexpr int kFwdN = 4, kFwdB = 8;
-template <typename T>
-__global__ void __launch_bounds__(128, 8) conv_fwd_fast_kernel(const ConvParams p) {
-  const int c0 = (blockIdx.y * 128 + threadIdx.x) * kFwdN;
+// (one 8-byte vector of a 16-bit type) and keeps kFwdB tokens of loads in flight; 72 registers, so
+// seven blocks per SM hold about 57 KB of loads in flight.
+constexpr int kFwdN = 4, kFwdB = 8, kFwdMinBlocks = 7;
+template <typename T, int N16, int B, int MINB>
+__global__ void __launch_bounds__(128, MINB) conv_fwd_fast_kernel(const ConvParams p, int chan_blocks) {
+  constexpr int N = sizeof(T) == 2 ? N16 : N16 / 2;
+  // channel block fastest: the blocks resident at one time cover whole token rows
+  const int cblk = blockIdx.x % chan_blocks, run = blockIdx.x / chan_blocks;
+  const int c0 = (cblk * 128 + threadIdx.x) * N;
   if (c0 >= p.C) return;
   int64_t t0, t1, bos, eos;
   int seq;
-  conv_run_of(p, blockIdx.x, t0, t1);
-  if (t0 < t1 && conv_run_simple(p, t0, t1, seq, bos, eos))
-    conv_fwd_run<T, 4, kFwdN, (sizeof(T) == 4 ? kFwdB / 2 : kFwdB)>(p, t0, t1, c0, seq, bos);
+  conv_run_of(p, run, t0, t1);
+  if (t0 < t1 && conv_run_simple(p, t0, t1, seq, bos, eos)) {
+    if constexpr (sizeof(T) == 2) {
+      if (p.act) conv_fwd_run16<T, N, B, true>(p, t0, t1, c0, seq, bos);
+      else conv_fwd_run16<T, N, B, false>(p, t0, t1, c0, seq, bos);
+    } else {
+      conv_fwd_run<T, 4, N, 4>(p, t0, t1, c0, seq, bos);
+    }
+  }
 }
 
 // any width, sequence starts, histories; with skip_interior != 0 only the runs the fast kernel left
@@ -483,35 +610,37 @@ __global__ void __launch_bounds__(128) conv_decode_kernel(const void* x_, const 
 // registers per thread, no shared-memory staging and no barriers in the loop: 1024 threads per SM
 // keep 64 KB of loads in flight.
 // ------------------------------------------------------------------------------------------
-constexpr int kBwdCh = 64;                  // channels per block
-constexpr int kBwdAhead = 8;                // tokens of loads in flight per thread
-template <typename T>
-__global__ void __launch_bounds__(256, 3) conv_bwd_fast_kernel(const ConvParams p) {
-  constexpr int W = 4, HALO = W - 1, B = kBwdAhead;
-  static_assert(sizeof(T) == 2, "channel pairs travel as one 32-bit word");
+constexpr int kBwdN = 4;                    // adjacent channels per thread (one 8-byte vector)
+constexpr int kBwdCh = 32 * kBwdN;          // channels per block
+constexpr int kBwdAhead = 4;                // tokens of loads in flight per thread
+template <typename T, int B, bool ACT>
+__global__ void __launch_bounds__(256, 2) conv_bwd_fast_kernel(const ConvParams p, int chan_blocks) {
+  constexpr int W = 4, HALO = W - 1, N = kBwdN;
+  static_assert(sizeof(T) == 2 && B % 4 == 0, "16-bit types; a token's window slot is its position in the group");
   __shared__ float s_dw[8][kBwdCh][W];
   const int tid = threadIdx.x, lane = tid & 31, r = tid >> 5;
+  // channel block fastest, so that the resident blocks cover whole token rows
+  const int cblk = blockIdx.x % chan_blocks, span = blockIdx.x / chan_blocks;
   const int64_t C = p.C, total = (int64_t)p.batch * p.T;
   const T* x = reinterpret_cast<const T*>(p.x);
   const T* dy = reinterpret_cast<const T*>(p.dy);
   const T* st = reinterpret_cast<const T*>(p.state);
   const T* w = reinterpret_cast<const T*>(p.w);
   T* dx = reinterpret_cast<T*>(p.dx);
-  const int c0 = blockIdx.y * kBwdCh + 2 * lane;   // this thread's two channels
-  const bool live = c0 < p.C;                      // C is even
-  float wr[2][W], dwacc[2][W];
+  const int c0 = cblk * kBwdCh + N * lane;         // this thread's channels
+  const bool live = c0 < p.C;                      // C is a multiple of 8
+  float wr[N][W], dwacc[N][W];
 #pragma unroll
-  for (int i = 0; i < 2; ++i)
+  for (int i = 0; i < N; ++i) {
 #pragma unroll
-    for (int j = 0; j < W; ++j) {
-      wr[i][j] = live ? (float)w[(int64_t)(c0 + i) * W + j] : 0.f;
-      dwacc[i][j] = 0.f;
-    }
+    for (int j = 0; j < W; ++j) { wr[i][j] = 0.f; dwacc[i][j] = 0.f; }
+    if (live) words_to_float<T, 4>(ld_raw<T, 4>(w + (int64_t)(c0 + i) * W), wr[i]);
+  }
   int64_t t0, t1;
-  if (p.cu_seqlens) { t0 = ((int64_t)blockIdx.x * 8 + r) * CONV_TT; t1 = min(t0 + CONV_TT, total); }
+  if (p.cu_seqlens) { t0 = ((int64_t)span * 8 + r) * CONV_TT; t1 = min(t0 + CONV_TT, total); }
   else {
     int rpr = (p.T + 8 * CONV_TT - 1) / (8 * CONV_TT);
-    int row = blockIdx.x / rpr, rb = blockIdx.x % rpr;
+    int row = span / rpr, rb = span % rpr;
     t0 = (int64_t)row * p.T + ((int64_t)rb * 8 + r) * CONV_TT;
     t1 = min(t0 + CONV_TT, (int64_t)(row + 1) * p.T);
   }
@@ -520,90 +649,129 @@ __global__ void __launch_bounds__(256, 3) conv_bwd_fast_kernel(const ConvParams 
     const int owned = (int)(t1 - t0);                                    // tokens whose dx is written
     const int avail = (int)(min(t1 + HALO, eos) - t0);                   // tokens that have a dpre
     const int steps = owned + HALO;
-    float xw[W][2], dp[W][2];                        // circular: slot = (token - t0) & 3
+    float xw[W][N], dp[W][N];                        // circular: slot = (token - t0) & 3
 #pragma unroll
     for (int j = 0; j < HALO; ++j) {                 // tokens t0-3 .. t0-1 -> slots 1, 2, 3
       const int64_t pos = t0 - HALO + j;
-      uint32_t raw = 0u;
-      if (pos >= bos) raw = *reinterpret_cast<const uint32_t*>(x + pos * C + c0);
-      else if (st) raw = *reinterpret_cast<const uint32_t*>(st + ((int64_t)seq * HALO + (pos - bos + HALO)) * C + c0);
-      const float2 v = unpack2<T>(reinterpret_cast<const T*>(&raw));
-      xw[j + 1][0] = v.x; xw[j + 1][1] = v.y;
-      dp[j + 1][0] = 0.f; dp[j + 1][1] = 0.f;
+      RawVec<T, N> raw;
+#pragma unroll
+      for (int q = 0; q < N / 2; ++q) raw.w[q] = 0u;
+      if (pos >= bos) raw = ld_raw<T, N>(x + pos * C + c0);
+      else if (st) raw = ld_raw<T, N>(st + ((int64_t)seq * HALO + (pos - bos + HALO)) * C + c0);
+      words_to_float<T, N>(raw, xw[j + 1]);
+#pragma unroll
+      for (int i = 0; i < N; ++i) dp[j + 1][i] = 0.f;
     }
-    const T* xl = x + t0 * C + c0;                   // next token to fetch
-    const T* gl = dy + t0 * C + c0;
-    T* dxp = dx + t0 * C + c0;                       // next dx row to write
-    uint32_t nx[B], ng[B];
+    const T* xrow = x + t0 * C + c0;
+    const T* grow = dy + t0 * C + c0;
+    T* dxrow = dx + t0 * C + c0;
+    const uint32_t Cu = (uint32_t)p.C;               // element offsets inside a run fit 32 bits
+    RawVec<T, N> nx[B], ng[B];
 #pragma unroll
     for (int b = 0; b < B; ++b) {
-      nx[b] = 0u; ng[b] = 0u;
-      if (b < avail) {
-        nx[b] = *reinterpret_cast<const uint32_t*>(xl); ng[b] = *reinterpret_cast<const uint32_t*>(gl);
-        xl += C; gl += C;
+#pragma unroll
+      for (int q = 0; q < N / 2; ++q) { nx[b].w[q] = 0u; ng[b].w[q] = 0u; }
+      if (b < avail) { nx[b] = ld_raw<T, N>(xrow + b * Cu); ng[b] = ld_raw<T, N>(grow + b * Cu); }
+    }
+    // One token: slot is constant after unrolling; OWN / OUT say whether the token adds to dw and
+    // whether a dx row (three tokens back) is complete.
+    auto token = [&](const RawVec<T, N>& rx, const RawVec<T, N>& rg, int slot, bool own, bool out, T* dxp) {
+      float g[N];
+      words_to_float<T, N>(rx, xw[slot]);
+      words_to_float<T, N>(rg, g);                   // zero past `avail`
+      const int s1 = (slot + 1) & 3, s2 = (slot + 2) & 3, s3 = (slot + 3) & 3;
+      const float2 one = make_float2(1.f, 1.f);
+      float o[N];
+#pragma unroll
+      for (int i = 0; i < N; i += 2) {               // channel pairs on the packed fp32 instructions
+        const float2 w0 = make_float2(wr[i][0], wr[i + 1][0]), w1 = make_float2(wr[i][1], wr[i + 1][1]),
+                     w2 = make_float2(wr[i][2], wr[i + 1][2]), w3 = make_float2(wr[i][3], wr[i + 1][3]);
+        const float2 x1 = make_float2(xw[s1][i], xw[s1][i + 1]), x2 = make_float2(xw[s2][i], xw[s2][i + 1]),
+                     x3 = make_float2(xw[s3][i], xw[s3][i + 1]), x0 = make_float2(xw[slot][i], xw[slot][i + 1]);
+        float2 pre = __fmul2_rn(w0, x1);
+        pre = __ffma2_rn(w1, x2, pre);
+        pre = __ffma2_rn(w2, x3, pre);
+        pre = __ffma2_rn(w3, x0, pre);
+        float2 d = make_float2(g[i], g[i + 1]);
+        if (ACT) {                                   // act'(pre) = s (1 + pre (1 - s)),  s = sigmoid(pre)
+          const float2 e = __fmul2_rn(pre, make_float2(-kLog2e, -kLog2e));
+          const float2 den = __fadd2_rn(make_float2(fexp2(e.x), fexp2(e.y)), one);
+          const float2 sg = make_float2(__fdividef(1.f, den.x), __fdividef(1.f, den.y));
+          const float2 om = __ffma2_rn(sg, make_float2(-1.f, -1.f), one);
+          d = __fmul2_rn(d, __fmul2_rn(sg, __ffma2_rn(pre, om, one)));
+        }
+        dp[slot][i] = d.x; dp[slot][i + 1] = d.y;
+        if (own) {
+          float2 a0 = __ffma2_rn(d, x1, make_float2(dwacc[i][0], dwacc[i + 1][0]));
+          float2 a1 = __ffma2_rn(d, x2, make_float2(dwacc[i][1], dwacc[i + 1][1]));
+          float2 a2 = __ffma2_rn(d, x3, make_float2(dwacc[i][2], dwacc[i + 1][2]));
+          float2 a3 = __ffma2_rn(d, x0, make_float2(dwacc[i][3], dwacc[i + 1][3]));
+          dwacc[i][0] = a0.x; dwacc[i + 1][0] = a0.y; dwacc[i][1] = a1.x; dwacc[i + 1][1] = a1.y;
+          dwacc[i][2] = a2.x; dwacc[i + 1][2] = a2.y; dwacc[i][3] = a3.x; dwacc[i + 1][3] = a3.y;
+        }
+        // dx[k-3] = w0 dpre[k] + w1 dpre[k-1] + w2 dpre[k-2] + w3 dpre[k-3]
+        float2 acc = __fmul2_rn(w0, d);
+        acc = __ffma2_rn(w1, make_float2(dp[s3][i], dp[s3][i + 1]), acc);
+        acc = __ffma2_rn(w2, make_float2(dp[s2][i], dp[s2][i + 1]), acc);
+        acc = __ffma2_rn(w3, make_float2(dp[s1][i], dp[s1][i + 1]), acc);
+        o[i] = acc.x; o[i + 1] = acc.y;
+      }
+      if (out) st_words<T, N>(dxp, o);
+    };
+    const RawVec<T, N> zero = [] { RawVec<T, N> z;
+#pragma unroll
+      for (int q = 0; q < N / 2; ++q) z.w[q] = 0u;
+      return z; }();
+    int k = 0;
+    if (owned >= B && 2 * B <= avail) {              // first group: no dx rows for its first three tokens
+#pragma unroll
+      for (int b = 0; b < B; ++b) {
+        const RawVec<T, N> cx = nx[b], cg = ng[b];
+        nx[b] = ld_raw<T, N>(xrow + (B + b) * Cu);
+        ng[b] = ld_raw<T, N>(grow + (B + b) * Cu);
+        token(cx, cg, b & 3, true, b >= HALO, dxrow + (b >= HALO ? (b - HALO) * Cu : 0u));
+      }
+      k = B;
+    }
+    for (; k > 0 && k + B <= owned && k + 2 * B <= avail; k += B) {   // interior: nothing to check
+      const uint32_t off = (uint32_t)k * Cu;
+#pragma unroll
+      for (int b = 0; b < B; ++b) {
+        const RawVec<T, N> cx = nx[b], cg = ng[b];
+        nx[b] = ld_raw<T, N>(xrow + (off + (B + b) * Cu));
+        ng[b] = ld_raw<T, N>(grow + (off + (B + b) * Cu));
+        token(cx, cg, b & 3, true, true, dxrow + (off + b * Cu - HALO * Cu));
       }
     }
-    for (int kb = 0; kb < steps; kb += B) {
+    for (; k < steps; k += B) {                      // the rest, every condition checked
 #pragma unroll
-      for (int b8 = 0; b8 < B; ++b8) {
-        const int k = kb + b8, b = b8 & 3;
-        if (k < steps) {
-          const float2 xv = unpack2<T>(reinterpret_cast<const T*>(&nx[b8]));
-          const float2 gv = unpack2<T>(reinterpret_cast<const T*>(&ng[b8]));   // zero past `avail`
-          nx[b8] = 0u; ng[b8] = 0u;
-          if (k + B < avail) {
-            nx[b8] = *reinterpret_cast<const uint32_t*>(xl); ng[b8] = *reinterpret_cast<const uint32_t*>(gl);
-            xl += C; gl += C;
+      for (int b = 0; b < B; ++b) {
+        if (k + b < steps) {
+          const RawVec<T, N> cx = nx[b], cg = ng[b];
+          nx[b] = zero; ng[b] = zero;
+          if (k + B + b < avail) {
+            nx[b] = ld_raw<T, N>(xrow + (uint32_t)(k + B + b) * Cu);
+            ng[b] = ld_raw<T, N>(grow + (uint32_t)(k + B + b) * Cu);
           }
-          xw[b][0] = xv.x; xw[b][1] = xv.y;
-          const float g[2] = {gv.x, gv.y};
-          const bool own = k < owned;
-#pragma unroll
-          for (int i = 0; i < 2; ++i) {
-            float pre = 0.f;
-#pragma unroll
-            for (int j = 0; j < W; ++j) pre = fmaf(wr[i][j], xw[(b + 1 + j) & 3][i], pre);
-            float dact = 1.f;
-            if (p.act) {
-              const float sg = __fdividef(1.f, 1.f + __expf(-pre));
-              dact = sg * fmaf(pre, 1.f - sg, 1.f);
-            }
-            const float d = g[i] * dact;
-            dp[b][i] = d;
-            if (own) {
-#pragma unroll
-              for (int j = 0; j < W; ++j) dwacc[i][j] = fmaf(d, xw[(b + 1 + j) & 3][i], dwacc[i][j]);
-            }
-          }
-          if (k >= HALO) {                           // dx[k-3] = w0 dpre[k] + ... + w3 dpre[k-3]
-            float o[2];
-#pragma unroll
-            for (int i = 0; i < 2; ++i) {
-              float acc = 0.f;
-#pragma unroll
-              for (int j = 0; j < W; ++j) acc = fmaf(wr[i][j], dp[(b + 4 - j) & 3][i], acc);
-              o[i] = acc;
-            }
-            pack2<T>(dxp, o[0], o[1]);
-            dxp += C;
-          }
+          token(cx, cg, b & 3, k + b < owned, k + b >= HALO,
+                dxrow + (k + b >= HALO ? (uint32_t)(k + b - HALO) * Cu : 0u));
         }
       }
     }
   }
   // reduce the eight runs, then one partial per (block, channel, tap)
 #pragma unroll
-  for (int i = 0; i < 2; ++i)
+  for (int i = 0; i < N; ++i)
 #pragma unroll
-    for (int j = 0; j < W; ++j) s_dw[r][2 * lane + i][j] = dwacc[i][j];
+    for (int j = 0; j < W; ++j) s_dw[r][N * lane + i][j] = dwacc[i][j];
   __syncthreads();
   for (int e = tid; e < kBwdCh * W; e += 256) {
     const int ch = e / W, j = e % W;
-    if (blockIdx.y * kBwdCh + ch < p.C) {
+    if (cblk * kBwdCh + ch < p.C) {
       float acc = 0.f;
 #pragma unroll
       for (int q = 0; q < 8; ++q) acc += s_dw[q][ch][j];
-      p.dw_part[((int64_t)blockIdx.x * C + blockIdx.y * kBwdCh + ch) * W + j] = acc;
+      p.dw_part[((int64_t)span * C + cblk * kBwdCh + ch) * W + j] = acc;
     }
   }
 }
@@ -691,8 +859,10 @@ static int conv_fwd_launch(const ConvParams& p, cudaStream_t s) {
   dim3 grid((unsigned)runs, (unsigned)((p.C / N + 127) / 128));
   const int fast = p.W == 4;
   if (fast) {
-    dim3 gridf((unsigned)runs, (unsigned)((p.C / kFwdN + 127) / 128));
-    conv_fwd_fast_kernel<T><<<gridf, 128, 0, s>>>(p);
+    if ((int64_t)(CONV_TT + 8) * p.C > 0x7fffffffLL) return KDA_ERR_UNSUPPORTED;
+    const int chan_blocks = (p.C / (sizeof(T) == 2 ? kFwdN : kFwdN / 2) + 127) / 128;
+    if (runs * chan_blocks > 0x7fffffffLL) return KDA_ERR_UNSUPPORTED;
+    conv_fwd_fast_kernel<T, kFwdN, kFwdB, kFwdMinBlocks><<<(unsigned)(runs * chan_blocks), 128, 0, s>>>(p, chan_blocks);
   }
   conv_fwd_kernel<T><<<grid, 128, 0, s>>>(p, fast);
   return cudaGetLastError() == cudaSuccess ? KDA_OK : KDA_ERR_LAUNCH;
@@ -708,8 +878,18 @@ static int conv_bwd_launch(const ConvParams& p, int64_t blocks, cudaStream_t s) 
   if constexpr (sizeof(T) == 2) if (p.W == 4) {
     // one-pass kernel for the runs inside one sequence, the general kernels for the other runs
     if (p.C % 8) return KDA_ERR_UNSUPPORTED;
-    dim3 gridf((unsigned)blocks, (unsigned)((p.C + kBwdCh - 1) / kBwdCh));
-    conv_bwd_fast_kernel<T><<<gridf, 256, 0, s>>>(p);
+    const int chan_blocks = (int)((p.C + kBwdCh - 1) / kBwdCh);
+    if (blocks * chan_blocks > 0x7fffffffLL) return KDA_ERR_UNSUPPORTED;
+    if ((int64_t)(CONV_TT + 16) * p.C > 0x7fffffffLL) return KDA_ERR_UNSUPPORTED;
+    const unsigned nb = (unsigned)(blocks * chan_blocks);
+    if (p.act) conv_bwd_fast_kernel<T, kBwdAhead, true><<<nb, 256, 0, s>>>(p, chan_blocks);
+    else conv_bwd_fast_kernel<T, kBwdAhead, false><<<nb, 256, 0, s>>>(p, chan_blocks);
+    if (!p.cu_seqlens && !p.dstate) {
+      // dense rows without a history gradient: every run went through the one-pass kernel
+      if (cudaMemsetAsync(p.dw_part + blocks * p.C * p.W, 0, sizeof(float) * blocks * p.C * p.W, s) != cudaSuccess)
+        return KDA_ERR_LAUNCH;
+      return cudaGetLastError() == cudaSuccess ? KDA_OK : KDA_ERR_LAUNCH;
+    }
     conv_bwd_pre_kernel<T><<<grid, 256, 0, s>>>(p, 1);
     int64_t runs = p.cu_seqlens ? (total + CONV_TT - 1) / CONV_TT
                                 : (int64_t)p.batch * ((p.T + CONV_TT - 1) / CONV_TT);
@@ -725,6 +905,16 @@ static int conv_bwd_launch(const ConvParams& p, int64_t blocks, cudaStream_t s) 
   dim3 grid2((unsigned)((total + CONV_TT - 1) / CONV_TT), (unsigned)((p.C / N + 127) / 128));
   conv_bwd_dx_kernel<T><<<grid2, 128, 0, s>>>(p);
   return cudaGetLastError() == cudaSuccess ? KDA_OK : KDA_ERR_LAUNCH;
+}
+
+// dw[e] = sum over the partial rows, written in the weight's dtype
+__global__ void __launch_bounds__(256) conv_dw_reduce_kernel(const float* __restrict__ part, int64_t rows,
+                                                             int64_t n, void* dw, int dt) {
+  const int64_t e = (int64_t)blockIdx.x * 256 + threadIdx.x;
+  if (e >= n) return;
+  float acc = 0.f;
+  for (int64_t r = 0; r < rows; ++r) acc += part[r * n + e];
+  store_from_float(dw, dt, e, acc);
 }
 
 }  // namespace kda
@@ -791,5 +981,15 @@ extern "C" int kda_conv1d_decode(const void* x, const void* weight, void* state,
     kda::conv_decode_kernel<__half><<<grid, 128, 0, s>>>(x, weight, state, state_indices, y, nseq, num_slots, channels, width, activation);
   else
     kda::conv_decode_kernel<float><<<grid, 128, 0, s>>>(x, weight, state, state_indices, y, nseq, num_slots, channels, width, activation);
+  return cudaGetLastError() == cudaSuccess ? KDA_OK : KDA_ERR_LAUNCH;
+}
+
+// dw [C, W] in `dtype` = the sum of the `rows` fp32 partial rows kda_conv1d_bwd wrote (fixed order).
+extern "C" int kda_conv1d_dw_reduce(const float* dw_partial, int64_t rows, int64_t channels_times_width,
+                                    void* dw, int dtype, void* stream) {
+  if (!dw_partial || !dw || rows < 0 || channels_times_width < 0) return KDA_ERR_ARG;
+  if (channels_times_width == 0) return KDA_OK;
+  const unsigned blocks = (unsigned)((channels_times_width + 255) / 256);
+  kda::conv_dw_reduce_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(dw_partial, rows, channels_times_width, dw, dtype);
   return cudaGetLastError() == cudaSuccess ? KDA_OK : KDA_ERR_LAUNCH;
 }

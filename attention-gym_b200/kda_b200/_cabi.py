@@ -70,6 +70,7 @@ _SIGNATURES = {
     "kda_conv1d_bwd_blocks": (c_int64, [c_int, c_int, c_int]),
     "kda_conv1d_bwd": (c_int, [c_void_p] * 8 + [c_int, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                c_int, c_void_p]),
+    "kda_conv1d_dw_reduce": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int, c_void_p]),
     "kda_decode_prep": (c_int, [c_void_p] * 5 + [c_int] + [c_void_p] * 6 + [c_int] * 7 + [c_float, c_float,
                                                                                       c_void_p]),
     "kda_conv1d_decode": (c_int, [c_void_p] * 5 + [c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),

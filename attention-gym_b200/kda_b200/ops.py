@@ -578,7 +578,9 @@ def _short_conv_bwd(x, weight, grad_output, cu_seqlens=None, initial_state=None,
                _cabi.ptr(grad_output), _cabi.ptr(dx), _cabi.ptr(dw_part), _cabi.ptr(dstate),
                _cabi.ptr(scratch), _cabi.dt(x), _cabi.ptr(cu_seqlens), nseq, batch, tokens,
                channels, width, _act_code(activation), _cabi.stream())
-    dw = dw_part.sum(0).to(weight.dtype)
+    dw = torch.empty_like(weight, memory_format=torch.contiguous_format)
+    _cabi.call("kda_conv1d_dw_reduce", 1, _cabi.ptr(dw_part), blocks, channels * width, _cabi.ptr(dw),
+               _cabi.dt(dw), _cabi.stream())
     ds = dstate.to(x.dtype) if state_grad else x.new_empty(0)
     return dx, dw, ds
 

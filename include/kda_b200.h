@@ -229,6 +229,9 @@ int kda_conv1d_bwd(const void* x, const void* weight, const void* initial_state,
                    void* dx, float* dw_partial, float* dstate, float* dpre_scratch, int dtype,
                    const int32_t* cu_seqlens, int nseq, int batch, int tokens, int channels,
                    int width, int activation, void* stream);
+/* dw [C, W] in `dtype` = the sum of the `rows` partial rows of dw_partial, in a fixed order. */
+int kda_conv1d_dw_reduce(const float* dw_partial, int64_t rows, int64_t channels_times_width, void* dw,
+                         int dtype, void* stream);
 
 /* One token per sequence over a paged history pool state [num_slots, W-1, C], advanced in place;
  * state_indices NULL means sequence i uses slot i; entries <= 0 are padding (zero output).

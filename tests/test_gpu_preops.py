@@ -150,10 +150,10 @@ def test_gated_output_norm(dtype, dim, rows, tol):
     z = (2 * torch.randn(*rows, dim, generator=gen)).to(dtype)
     w = 1 + 0.2 * torch.randn(dim, generator=gen)
     dy = torch.randn(*rows, dim, generator=gen).to(dtype)
-    ro, rz, rw = (t.float().requires_grad_() for t in (o, z, w))
+    ro, rz, rw = (t.float().clone().requires_grad_() for t in (o, z, w))
     ref = orc.gated_output_norm_ref(ro, rz, rw, 1e-5)
     rgo, rgz, rgw = torch.autograd.grad(ref, (ro, rz, rw), dy.float())
-    go, gz, gw = (t.cuda().requires_grad_() for t in (o, z, w))
+    go, gz, gw = (t.detach().cuda().requires_grad_() for t in (o, z, w))
     y = kda_b200.gated_output_norm(go, gz, gw, 1e-5)
     assert y.dtype == dtype
     y.backward(dy.cuda())
