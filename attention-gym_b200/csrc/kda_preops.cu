@@ -382,6 +382,51 @@ __global__ void __launch_bounds__(256) l2norm_bwd_vec_kernel(const uint4* __rest
   }
 }
 
+// dA_log[h] = sum over partial rows and channels, d_dt_bias[h, c] = sum over partial rows (fixed order).
+// One block per head; when K divides 256 the 256 / K row groups of a block work side by side, each
+// thread keeping eight rows of loads in flight.
+__global__ void __launch_bounds__(256) gate_bwd_reduce_kernel(const float* __restrict__ pa,
+                                                              const float* __restrict__ pb, int64_t rows,
+                                                              int K, float* __restrict__ dA,
+                                                              float* __restrict__ dbias) {
+  __shared__ float s_a[256], s_b[256];
+  const int h = blockIdx.x, tid = threadIdx.x;
+  const int64_t HK = (int64_t)gridDim.x * K;
+  const bool split = K <= 256 && 256 % K == 0;
+  const int groups = split ? 256 / K : 1;
+  float total = 0.f;
+  for (int c0 = 0; c0 < K; c0 += 256) {
+    const int c = split ? tid % K : c0 + tid, g = split ? tid / K : 0;
+    float a = 0.f, b = 0.f;
+    if (c < K) {
+      const float* qa = pa + (int64_t)h * K + c;
+      const float* qb = pb + (int64_t)h * K + c;
+      int64_t r = g;
+      for (; r + 7 * groups < rows; r += 8 * groups) {
+        float va[8], vb[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) { va[u] = qa[(r + u * groups) * HK]; vb[u] = qb[(r + u * groups) * HK]; }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) { a += va[u]; b += vb[u]; }
+      }
+      for (; r < rows; r += groups) { a += qa[r * HK]; b += qb[r * HK]; }
+    }
+    s_a[tid] = a; s_b[tid] = b;
+    __syncthreads();
+    if (c < K && g == 0) {
+      float bs = 0.f;
+      for (int q = 0; q < groups; ++q) bs += s_b[q * K + (split ? c : tid)];
+      dbias[(int64_t)h * K + c] = bs;
+    }
+    if (tid == 0) {
+      const int n = split ? 256 : min(256, K - c0);
+      for (int q = 0; q < n; ++q) total += s_a[q];
+    }
+    __syncthreads();
+  }
+  if (tid == 0) dA[h] = total;
+}
+
 static int check_launch() { return cudaGetLastError() == cudaSuccess ? KDA_OK : KDA_ERR_LAUNCH; }
 
 }  // namespace kda
@@ -448,6 +493,16 @@ extern "C" int kda_gate_cumsum_bwd(const void* raw_gate, int dt_raw, const float
   dim3 grid((unsigned)kda_gate_bwd_partial_rows(num_chunks), (unsigned)((heads * dim / 4 + 127) / 128));
   kda::StageScope timing(kda::kStageGateBwd, (cudaStream_t)stream);
   kda::gate_cumsum_bwd_kernel<<<grid, 128, 0, (cudaStream_t)stream>>>(p, (int)num_chunks);
+  return kda::check_launch();
+}
+
+// Sums the partial rows kda_gate_cumsum_bwd wrote: dA_log [heads], d_dt_bias [heads, dim] (fp32).
+extern "C" int kda_gate_bwd_reduce(const float* dA_partial, const float* dbias_partial, int64_t rows,
+                                   int heads, int dim, float* dA_log, float* d_dt_bias, void* stream) {
+  if (!dA_partial || !dbias_partial || !dA_log || !d_dt_bias || rows < 0 || heads < 1 || dim < 1)
+    return KDA_ERR_ARG;
+  kda::gate_bwd_reduce_kernel<<<(unsigned)heads, 256, 0, (cudaStream_t)stream>>>(
+      dA_partial, dbias_partial, rows, dim, dA_log, d_dt_bias);
   return kda::check_launch();
 }
 

@@ -39,6 +39,7 @@ _SIGNATURES = {
     "kda_gate_cumsum_fwd": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                     c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int64,
                                     c_void_p]),
+    "kda_gate_bwd_reduce": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "kda_gate_bwd_partial_rows": (c_int64, [c_int64]),
     "kda_gate_cumsum_bwd": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                     c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,

@@ -446,8 +446,10 @@ def _gate_bwd(raw, A_log, dt_bias, d_cumulative, cu_seqlens, chunk_offsets, chun
                _cabi.ptr(dt_bias.contiguous()), _cabi.ptr(d_cumulative), _cabi.ptr(d_raw),
                _cabi.ptr(pa), _cabi.ptr(pb), _cabi.ptr(cu_seqlens), _cabi.ptr(chunk_offsets), nseq,
                batch, tokens, heads, dim, chunk_size, float(lower_bound), chunks, _cabi.stream())
-    dA = pa.sum(0).view(heads, dim).sum(-1)
-    dbias = pb.sum(0).view(heads, dim)
+    dA = torch.empty(heads, dtype=torch.float32, device=raw.device)
+    dbias = torch.empty(heads, dim, dtype=torch.float32, device=raw.device)
+    _cabi.call("kda_gate_bwd_reduce", 1, _cabi.ptr(pa), _cabi.ptr(pb), max(rows, 1), heads, dim,
+               _cabi.ptr(dA), _cabi.ptr(dbias), _cabi.stream())
     return d_raw, dA, dbias
 
 

@@ -99,6 +99,11 @@ int kda_gate_cumsum_bwd(const void* raw_gate, int dt_raw, const float* A_log, co
                         const int32_t* chunk_offsets, int nseq, int batch, int tokens, int heads,
                         int dim, int chunk_size, float lower_bound, int64_t num_chunks,
                         void* stream);
+/* dA_log [heads] and d_dt_bias [heads, dim] (fp32) = sums of the partial rows written by
+ * kda_gate_cumsum_bwd (the reference reduces them in its autograd glue,
+ * fwd/triton/gate_fwd.py:518-616). */
+int kda_gate_bwd_reduce(const float* dA_partial, const float* dbias_partial, int64_t rows, int heads,
+                        int dim, float* dA_log, float* d_dt_bias, void* stream);
 
 /* y = x * rsqrt(sum(x^2) + eps) per row of `dim` elements; rstd (fp32 [rows]) may be NULL.
  * Replaces attn_gym::kda_l2norm_fwd / _bwd (fwd/triton/l2norm_fwd.py:84,143; bwd/triton/l2norm_bwd.py:37). */
