@@ -56,7 +56,8 @@ __device__ __forceinline__ void pr_mark(const PrepParams& p, int it, int slot) {
 namespace pl {  // shared-memory layout (bytes)
 constexpr int Q = 0, K = 16384, V = 32768, G = 49152, KR = 81920, KN = 98304, QR = 139264,
               KG = 155648, AT = 172032, AQK = 180224, LF = 188416, AF = 205824, MISC = 223232,
-              TOTAL = 228352;
+              OFFS = 228352, TOTAL = 230400;
+constexpr int kOffCache = 256;          // cu_seqlens / chunk_offsets entries kept in shared memory
 constexpr int TAB = AT;                 // phase 1 table (3 KiB) over the A / Aqk tiles, dead until phase 3
 constexpr int QG = Q;                   // qg is staged in place over q
 constexpr int W = KR, U = KR + 16384;   // result staging over Kr / Kn, dead after phase 2
@@ -113,6 +114,15 @@ __global__ void __launch_bounds__(NT, 1) kda_prepare_tc_kernel(const __grid_cons
   const int quad = warp & 3, wq = warp >> 2;       // TMEM lane quadrant; which of its four warps
   const int H = p.H;
 
+  // Work items are located by a binary search over the sequence offsets: from shared memory when
+  // they fit (a chain of dependent global loads per item would sit on the critical path).
+  int32_t* s_cu = reinterpret_cast<int32_t*>(sm + pl::OFFS);
+  int32_t* s_co = s_cu + pl::kOffCache;
+  const bool cached = p.nseq + 1 <= pl::kOffCache;
+  if (cached)
+    for (int i = tid; i <= p.nseq; i += NT) { s_cu[i] = p.cu_seqlens[i]; s_co[i] = p.chunk_offsets[i]; }
+  const int32_t* cu_off = cached ? s_cu : p.cu_seqlens;
+  const int32_t* ch_off = cached ? s_co : p.chunk_offsets;
   if (warp == 0) tmem_alloc(tmem_slot, 512);
   if (tid == 0) {
     mbar_init(&bar[0], 1);
@@ -151,7 +161,7 @@ __global__ void __launch_bounds__(NT, 1) kda_prepare_tc_kernel(const __grid_cons
   float beta_next = 0.f;
   for (int wi = blockIdx.x; wi < p.total; wi += gridDim.x) {
   const int chunk = wi / H, head = wi - chunk * H;
-  const ChunkWork cw = pre ? cw_next : locate_chunk(p.cu_seqlens, p.chunk_offsets, p.nseq, chunk);
+  const ChunkWork cw = pre ? cw_next : locate_chunk(cu_off, ch_off, p.nseq, chunk);
   if (cw.valid == 0) continue;               // capacity slot past the last active chunk
   const int valid = cw.valid;
   const int ty = (int)cw.token0, tx = head * 128;
@@ -170,7 +180,7 @@ __global__ void __launch_bounds__(NT, 1) kda_prepare_tc_kernel(const __grid_cons
     if (wn < p.total) {
       const int chunk_n = wn / H;
       head_n = wn - chunk_n * H;
-      cw_next = locate_chunk(p.cu_seqlens, p.chunk_offsets, p.nseq, chunk_n);
+      cw_next = locate_chunk(cu_off, ch_off, p.nseq, chunk_n);
       next_ok = cw_next.valid > 0;
       if (tid < 64)
         beta_next = (next_ok && tid < cw_next.valid) ? p.beta[(cw_next.token0 + tid) * H + head_n] : 0.f;
