@@ -36,6 +36,7 @@ import torch  # noqa: E402
 
 METRIC = "KDA fwd+bwd tokens/s (H32,K=V=128,bf16)"
 H, D, CHUNK = 32, 128, 64
+LOG2E = 1.4426950408889634
 
 # algorithmic HBM bytes per (token, head) of each kernel: what its interface must read + write
 STAGE_BYTES = {
@@ -140,7 +141,6 @@ class ClockSampler:
 
 def make_host_inputs(batch, tokens, seed, pin):
     """Synthetic step inputs on the host (pinned when asked), in the dtypes the kernels consume."""
-    from oracle.kda_oracle import LOG2E  # constants only; inputs are generated with torch here
 
     gen = torch.Generator().manual_seed(seed)
     shape = (batch, tokens, H, D)
@@ -221,6 +221,12 @@ def run_ours(args):
 
     decode = None if args.skip_decode else bench_decode(kda_b200, _cabi, device, load_peaks())
     preops = None if (args.skip_decode or rank != 0) else bench_preops(device, load_peaks(), batch, tokens)
+    others = None
+    if args.other_configs and rank == 0:
+        del dev
+        torch.cuda.empty_cache()
+        others = bench_other_configs(kda_b200, _cabi, device)
+        dev = {n: t.to(device, non_blocking=True) for n, t in host.items()}
     # ---- end to end: pinned host buffers in, pinned host buffers out, every copy inside the timed
     # region.  Three streams (H2D, compute, D2H) with double-buffered device inputs and host
     # outputs, so the copies of neighbouring steps overlap the kernels the way a host-buffer caller
@@ -332,6 +338,7 @@ def run_ours(args):
         "cpu_baseline": cpu,
         "decode": decode,
         "preops": preops,
+        "other_configs": others,
     }
     print(json.dumps(line), flush=True)
     if world > 1:
@@ -406,6 +413,105 @@ def bench_decode(kda_b200, _cabi, device, peaks, nseq=256, steps=200):
             "roofline": {"bound": "hbm", "achieved": round(gbs, 1), "peak": peaks["hbm_gbs"],
                          "unit": "GB/s", "frac": round(gbs / peaks["hbm_gbs"], 4),
                          "bytes_per_step": bytes_per_step}}
+
+
+def _device_inputs(batch, tokens, device, seed, cu=None, with_do=True):
+    """Synthetic inputs of the bench distribution generated on the device (large shapes)."""
+    gen = torch.Generator(device=device).manual_seed(seed)
+    shape = (batch, tokens, H, D)
+
+    def rnd(*s):
+        return torch.randn(*s, generator=gen, device=device)
+
+    q = torch.nn.functional.normalize(rnd(*shape), dim=-1).bfloat16()
+    k = torch.nn.functional.normalize(rnd(*shape), dim=-1).bfloat16()
+    v = rnd(*shape).bfloat16()
+    g = torch.nn.functional.logsigmoid(rnd(*shape)).mul_(LOG2E)
+    if cu is None:
+        pad = (-tokens) % CHUNK
+        if pad:
+            raise ValueError("dense bench shapes hold whole chunks")
+        g = g.view(batch, tokens // CHUNK, CHUNK, H, D).cumsum_(2).view(shape)
+    else:   # chunk-local prefix sums restarting at every sequence start
+        out = torch.empty_like(g)
+        bounds = cu.tolist()
+        for a, b in zip(bounds[:-1], bounds[1:]):
+            n = b - a
+            full = n // CHUNK * CHUNK
+            if full:
+                out[0, a:a + full] = g[0, a:a + full].view(full // CHUNK, CHUNK, H, D).cumsum(1).view(full, H, D)
+            if n > full:
+                out[0, a + full:b] = g[0, a + full:b].cumsum(0)
+        g = out
+    beta = torch.sigmoid(rnd(batch, tokens, H))
+    d = {"q": q, "k": k, "v": v, "g": g.contiguous(), "beta": beta}
+    if with_do:
+        d["do"] = rnd(*shape).bfloat16()
+    return d
+
+
+def bench_other_configs(kda_b200, _cabi, device, iters=5):
+    """The two other GPU workloads of the spec, timed with CUDA events (not the headline metric):
+    config 2 = 64 packed sequences of 128..8192 tokens with initial states, forward + backward;
+    config 4 = one sequence of 1,048,576 tokens, forward."""
+    out = {}
+
+    def timed(fn, n):
+        for _ in range(2):
+            fn()
+        torch.cuda.synchronize()
+        _cabi.read_stage_timing(reset=True)
+        _cabi.stage_timing(True)
+        a, z = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(n):
+            fn()
+        z.record()
+        torch.cuda.synchronize()
+        stages = _cabi.read_stage_timing(reset=True)
+        _cabi.stage_timing(False)
+        return a.elapsed_time(z) / n, {k: round(v[1] / max(v[0], 1), 4) for k, v in stages.items()}
+
+    # ---- config 2
+    gen = torch.Generator().manual_seed(77)
+    lengths = torch.randint(128, 8193, (64,), generator=gen)
+    cu_host = torch.cat((torch.zeros(1, dtype=torch.int64), lengths.cumsum(0))).to(torch.int32)
+    total = int(cu_host[-1])
+    cu = cu_host.to(device)
+    d = _device_inputs(1, total, device, 78, cu=cu_host)
+    h0 = 0.02 * torch.randn(64, H, D, D, device=device)
+
+    def ragged_step():
+        leaves = [d[n].detach().requires_grad_() for n in ("q", "k", "v", "g", "beta")]
+        h = h0.detach().requires_grad_()
+        o, s = kda_b200.chunk_kda(*leaves, h, cu_seqlens=cu, output_final_state=True)
+        return torch.autograd.grad((o, s), leaves + [h], (d["do"], torch.ones_like(s)))
+
+    ms, stages = timed(ragged_step, iters)
+    out["config2_ragged_fwd_bwd"] = {
+        "workload": f"64 packed sequences, 128..8192 tokens each ({total} tokens), H{H}, initial and "
+                    "final states with gradients",
+        "ms_per_step": round(ms, 3), "tokens_per_s": round(total / (ms * 1e-3), 1),
+        "ms_per_kernel_launch": stages}
+    del d, h0
+    torch.cuda.empty_cache()
+
+    # ---- config 4
+    tokens = 1 << 20
+    d = _device_inputs(1, tokens, device, 79, with_do=False)
+
+    def long_forward():
+        with torch.no_grad():
+            return kda_b200.chunk_kda(d["q"], d["k"], d["v"], d["g"], d["beta"], output_final_state=True)
+
+    ms, stages = timed(long_forward, 3)
+    out["config4_long_forward"] = {
+        "workload": f"one sequence of {tokens} tokens, H{H}, forward with final state",
+        "ms_per_step": round(ms, 3), "tokens_per_s": round(tokens / (ms * 1e-3), 1),
+        "ms_per_kernel_launch": stages}
+    del d
+    torch.cuda.empty_cache()
+    return out
 
 
 def bench_preops(device, peaks, batch=8, tokens=4096, iters=20):
@@ -515,6 +621,8 @@ def main():
     ap.add_argument("--skip-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--skip-e2e", action="store_true", help="skip the host-buffer leg")
     ap.add_argument("--skip-decode", action="store_true", help="skip the decode-step measurement")
+    ap.add_argument("--other-configs", action="store_true",
+                    help="also time the packed (config 2) and 1M-token (config 4) workloads")
     ap.add_argument("--preops-only", action="store_true",
                     help="measure only the gate / l2norm / short-conv pre-ops (for profiler captures)")
     args = ap.parse_args()
