@@ -9,8 +9,9 @@
 // as a serving limitation (kda/api.py:210-212).  Here the preprocessing is one kernel and the
 // state update (kda_recurrent_fwd) the second.
 //
-// One block of 128 threads per (sequence, head): thread c owns channel c of the head's q, k and v
-// blocks; x and the history are [.., 3 * H * 128] with the q channels first, then k, then v.
+// x and the history are [.., 3 * H * 128] with the q channels first, then k, then v.  Two kernels:
+// the vector kernel further down for 16-bit tensors, and this scalar one (any dtype, W <= 8): one
+// block of 128 threads per (sequence, head), thread c owns channel c of the head's q, k and v blocks.
 #include "kda_common.cuh"
 #include "kda_timing.cuh"
 
@@ -78,6 +79,88 @@ __global__ void __launch_bounds__(128) kda_decode_prep_kernel(const PrepDecodePa
   p.g[orow] = p.lower_bound / (1.f + expf(-z)) * kLog2e;
 }
 
+// 16-bit tensors: a thread owns one 16-byte vector of 8 adjacent channels.  Vector v covers channels
+// 8 v .. 8 v + 7 of the q | k | v row, i.e. part v / (16 H), head (v / 16) % H; the 16 threads of a
+// (part, head) group are adjacent lanes, so the L2 norms are half-warp shuffles and every global
+// access is a coalesced 16-byte vector.  Threads of the q part also evaluate the gate of their
+// eight (head, channel) pairs.
+template <int W>
+__global__ void __launch_bounds__(256) kda_decode_prep_vec_kernel(const PrepDecodeParams p) {
+  const int seq = blockIdx.y, vec = blockIdx.x * 256 + threadIdx.x;
+  const int HD = p.H * 128, C = 3 * HD, nvec = C / 8;
+  const bool in_range = vec < nvec;
+  const int part = in_range ? vec / (p.H * 16) : 3, hv = vec - part * (p.H * 16);   // hv: vector inside the part
+  int64_t slot = seq;
+  bool active = true;
+  if (p.state_indices) {
+    const int si = p.state_indices[seq];
+    active = si > 0 && si < p.num_slots;
+    slot = si;
+  }
+  const int dt = p.dt;
+  float y[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) y[i] = 0.f;
+  if (in_range && active) {
+    const uint4* xr = reinterpret_cast<const uint4*>(p.x) + (int64_t)seq * nvec + vec;
+    uint4* hist = reinterpret_cast<uint4*>(p.conv_state) + slot * (int64_t)(W - 1) * nvec + vec;
+    const uint4* wv = reinterpret_cast<const uint4*>(p.w) + (int64_t)vec * W;    // 8 channels x W taps
+    uint4 raw[W];                                  // history rows 0 .. W-2, then the new token
+#pragma unroll
+    for (int j = 0; j < W - 1; ++j) raw[j] = hist[(int64_t)j * nvec];
+    raw[W - 1] = *xr;
+    uint4 wraw[W];                                 // 8 W weights = W vectors; element i * W + j
+#pragma unroll
+    for (int j = 0; j < W; ++j) wraw[j] = wv[j];
+    const unsigned short* wh = reinterpret_cast<const unsigned short*>(wraw);
+#pragma unroll
+    for (int j = 0; j < W; ++j) {
+      float f[8];
+      raw8_to_float(raw[j], dt, f);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) y[i] = fmaf(raw_to_float(wh[i * W + j], dt), f[i], y[i]);
+    }
+#pragma unroll
+    for (int j = 0; j < W - 1; ++j) hist[(int64_t)j * nvec] = raw[j + 1];      // shift left, append x
+    if (p.act) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) y[i] = y[i] / (1.f + expf(-y[i]));
+    }
+  }
+  // q, k: L2 norm over the 128 channels of the head = 16 adjacent lanes (all lanes take part)
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) ss = fmaf(y[i], y[i], ss);
+#pragma unroll
+  for (int d = 8; d > 0; d >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, d);
+  if (!in_range) return;
+  if (part < 2) {
+    const float r = rsqrtf(ss + p.eps);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) y[i] *= r;
+  }
+  void* dst = part == 0 ? p.q : (part == 1 ? p.k : p.v);
+  reinterpret_cast<uint4*>(dst)[(int64_t)seq * (p.H * 16) + hv] = float8_to_raw(y, dt);   // zeros for padding
+  if (part == 0) {                                 // the gate of the same (head, 8 channels)
+    const int head = hv >> 4, c0 = (hv & 15) * 8;
+    float g[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) g[i] = 0.f;
+    if (active) {
+      const float a = expf(p.A_log[head]);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float z = a * (load_as_float(p.raw_gate, p.dt_gate, ((int64_t)seq * p.H + head) * 128 + c0 + i) +
+                             p.dt_bias[head * 128 + c0 + i]);
+        g[i] = p.lower_bound / (1.f + expf(-z)) * kLog2e;
+      }
+    }
+    float4* go = reinterpret_cast<float4*>(p.g + ((int64_t)seq * p.H + head) * 128 + c0);
+    go[0] = make_float4(g[0], g[1], g[2], g[3]);
+    go[1] = make_float4(g[4], g[5], g[6], g[7]);
+  }
+}
+
 }  // namespace kda
 
 extern "C" int kda_decode_prep(const void* x, const void* conv_weight, void* conv_state,
@@ -98,6 +181,15 @@ extern "C" int kda_decode_prep(const void* x, const void* conv_weight, void* con
   p.dt = dtype; p.dt_gate = dt_gate; p.nseq = nseq; p.H = heads; p.W = width; p.num_slots = num_slots;
   p.act = activation; p.lower_bound = lower_bound; p.eps = eps;
   kda::StageScope timing(kda::kStageConv, (cudaStream_t)stream);
+  const uintptr_t bits = (uintptr_t)x | (uintptr_t)conv_weight | (uintptr_t)conv_state | (uintptr_t)q |
+                         (uintptr_t)k | (uintptr_t)v | (uintptr_t)gate;
+  if (dtype != KDA_F32 && (width == 4 || width == 2 || width == 3) && (bits & 15) == 0 && nseq <= 65535) {
+    dim3 grid((unsigned)((3 * heads * 16 + 255) / 256), (unsigned)nseq);
+    if (width == 4) kda::kda_decode_prep_vec_kernel<4><<<grid, 256, 0, (cudaStream_t)stream>>>(p);
+    else if (width == 3) kda::kda_decode_prep_vec_kernel<3><<<grid, 256, 0, (cudaStream_t)stream>>>(p);
+    else kda::kda_decode_prep_vec_kernel<2><<<grid, 256, 0, (cudaStream_t)stream>>>(p);
+    return cudaGetLastError() == cudaSuccess ? KDA_OK : KDA_ERR_LAUNCH;
+  }
   kda::kda_decode_prep_kernel<<<(unsigned)(nseq * heads), 128, 0, (cudaStream_t)stream>>>(p);
   return cudaGetLastError() == cudaSuccess ? KDA_OK : KDA_ERR_LAUNCH;
 }

@@ -406,10 +406,29 @@ def bench_decode(kda_b200, _cabi, device, peaks, nseq=256, steps=200):
     z.record()
     torch.cuda.synchronize()
     full_us = a.elapsed_time(z) * 1e3 / steps
+    # the same step replayed from a CUDA graph (how a serving loop drives it: no host work per token)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        full_step(0)
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        full_step(0)
+    for _ in range(5):
+        graph.replay()
+    torch.cuda.synchronize()
+    a.record()
+    for _ in range(steps):
+        graph.replay()
+    z.record()
+    torch.cuda.synchronize()
+    graph_us = a.elapsed_time(z) * 1e3 / steps
     return {"workload": f"config3: {nseq} sequences x H{H}, K=V={D}, paged fp32 state, bf16 tokens",
             "us_per_step": round(us, 2), "kernel_us": round(kernel_us, 2),
             "tokens_per_s": round(nseq / (us * 1e-6), 1),
             "decode_step_with_preprocessing_us": round(full_us, 2),
+            "decode_step_graph_replay_us": round(graph_us, 2),
             "roofline": {"bound": "hbm", "achieved": round(gbs, 1), "peak": peaks["hbm_gbs"],
                          "unit": "GB/s", "frac": round(gbs / peaks["hbm_gbs"], 4),
                          "bytes_per_step": bytes_per_step}}
