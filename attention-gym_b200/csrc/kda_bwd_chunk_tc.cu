@@ -85,11 +85,15 @@ __device__ __forceinline__ float ld_g(const unsigned char* g, int row, int c) {
 }
 // 8 consecutive channels kappa0 .. kappa0+7 (kappa0 % 8 == 0) of one row
 __device__ __forceinline__ void ld_g8(const unsigned char* g, int row, int kappa0, float (&o)[8]) {
+  // The eight lanes of a quarter-warp hold kappa0 = 0, 8, .., 56 (+64): two 32-float boxes, the same
+  // four even chunks in each.  Lanes of the odd box fetch their second chunk first, so each 16-byte
+  // load touches eight different chunks (no bank conflict).
   const unsigned char* base = g + (kappa0 >> 5) * 8192 + row * 128;
-  const int c = (kappa0 & 31) >> 2, sw = row & 7;
-  const float4 a = *reinterpret_cast<const float4*>(base + ((c ^ sw) << 4));
-  const float4 b = *reinterpret_cast<const float4*>(base + (((c + 1) ^ sw) << 4));
-  o[0] = a.x; o[1] = a.y; o[2] = a.z; o[3] = a.w; o[4] = b.x; o[5] = b.y; o[6] = b.z; o[7] = b.w;
+  const int c = (kappa0 & 31) >> 2, sw = row & 7, odd = (kappa0 >> 5) & 1;
+  const float4 a = *reinterpret_cast<const float4*>(base + (((c + odd) ^ sw) << 4));
+  const float4 b = *reinterpret_cast<const float4*>(base + (((c + 1 - odd) ^ sw) << 4));
+  const float4 lo = odd ? b : a, hi = odd ? a : b;
+  o[0] = lo.x; o[1] = lo.y; o[2] = lo.z; o[3] = lo.w; o[4] = hi.x; o[5] = hi.y; o[6] = hi.z; o[7] = hi.w;
 }
 __device__ __forceinline__ void ld_bf8(const unsigned char* tile, int box_bytes, int row, int c16,
                                        float (&o)[8]) {

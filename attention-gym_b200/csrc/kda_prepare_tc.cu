@@ -70,11 +70,15 @@ constexpr int AQ = 0, PK = 64, W = 128, U = 256;
 constexpr int NT = 512;
 
 __device__ __forceinline__ void ld_g8(const unsigned char* g, int row, int kappa0, float (&o)[8]) {
+  // The eight lanes of a quarter-warp hold kappa0 = 0, 8, .., 56 (+64): two 32-float boxes, the same
+  // four even chunks in each.  Lanes of the odd box fetch their second chunk first, so each 16-byte
+  // load touches eight different chunks (no bank conflict).
   const unsigned char* base = g + (kappa0 >> 5) * 8192 + row * 128;
-  const int c = (kappa0 & 31) >> 2, sw = row & 7;
-  const float4 a = *reinterpret_cast<const float4*>(base + ((c ^ sw) << 4));
-  const float4 b = *reinterpret_cast<const float4*>(base + (((c + 1) ^ sw) << 4));
-  o[0] = a.x; o[1] = a.y; o[2] = a.z; o[3] = a.w; o[4] = b.x; o[5] = b.y; o[6] = b.z; o[7] = b.w;
+  const int c = (kappa0 & 31) >> 2, sw = row & 7, odd = (kappa0 >> 5) & 1;
+  const float4 a = *reinterpret_cast<const float4*>(base + (((c + odd) ^ sw) << 4));
+  const float4 b = *reinterpret_cast<const float4*>(base + (((c + 1 - odd) ^ sw) << 4));
+  const float4 lo = odd ? b : a, hi = odd ? a : b;
+  o[0] = lo.x; o[1] = lo.y; o[2] = lo.z; o[3] = lo.w; o[4] = hi.x; o[5] = hi.y; o[6] = hi.z; o[7] = hi.w;
 }
 __device__ __forceinline__ void ld_bf8(const unsigned char* tile, int box_bytes, int row, int c16,
                                        float (&o)[8]) {
@@ -247,8 +251,11 @@ __global__ void __launch_bounds__(NT, 1) kda_prepare_tc_kernel(const __grid_cons
     st_bf8(sm + pl::KN + kn_off(b), 16 * (b + 1) * 128, i, c16, o);
     for (int rr = b + 1; rr < 4; ++rr) {
       const int slot = b == 0 ? rr - 1 : (b == 1 ? rr + 1 : 5);
-      const float4 t0 = *reinterpret_cast<const float4*>(tab + slot * 128 + c0);
-      const float4 t1 = *reinterpret_cast<const float4*>(tab + slot * 128 + c0 + 4);
+      // lanes 32 bytes apart: the upper four of a quarter-warp read their halves in the other order
+      const int odd = (c16 >> 2) & 1;
+      const float4 ta = *reinterpret_cast<const float4*>(tab + slot * 128 + c0 + 4 * odd);
+      const float4 tb = *reinterpret_cast<const float4*>(tab + slot * 128 + c0 + 4 - 4 * odd);
+      const float4 t0 = odd ? tb : ta, t1 = odd ? ta : tb;
       const float f[8] = {t0.x, t0.y, t0.z, t0.w, t1.x, t1.y, t1.z, t1.w};     // 2^{R_r - R_b} <= 1
 #pragma unroll
       for (int e = 0; e < 8; ++e) o[e] = kk[e] * (ei[e] * f[e]);

@@ -1,6 +1,6 @@
 """The operators run on the caller's stream without host synchronisation, read packed-sequence
 offsets on the device, and size their grids by the chunk capacity -- so a captured CUDA graph can be
-replayed on new data and on a different split of the same token budget into sequences (the
+replayed on new data and on a different split of the same number of tokens into sequences (the
 reference's fixed-capacity graph replay, attn_gym/linear/kda/chunk_scheduler.py:112-239)."""
 
 import pytest
@@ -32,7 +32,7 @@ def _step(bufs):
 
 def test_packed_forward_backward_graph_replays_on_other_sequences():
     first = _packed_case([200, 333, 64, 427], 2, seed=51)       # 1024 tokens, 4 sequences
-    second = _packed_case([5, 700, 130, 189], 2, seed=52)       # same budget, different split
+    second = _packed_case([5, 700, 130, 189], 2, seed=52)       # same token count, different split
     static = {n: t.cuda().clone() for n, t in first.items()}
     side = torch.cuda.Stream()
     side.wait_stream(torch.cuda.current_stream())
