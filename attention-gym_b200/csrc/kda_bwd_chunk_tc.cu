@@ -423,7 +423,29 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
       st_bf8(sm + bl::KN0 + t0 * 16, rows * 128, j, c16, kk);
     }
   };
-  build_row_tiles(0, 1536);
+  // Tiles 0..2 in one pass over the rows j < 48: k_j and G_j are read once for all the tiles that
+  // hold row j (tiles ri >= j / 16).  Threads 0..255 take a row of block 0 (three tiles), the others a
+  // row of block 1 and one of block 2 (two tiles + one): three tile rows per thread either way.
+  {
+    const int c16 = tid & 15;
+    auto fused_row = [&](int j) {
+      float kk[8], gj[8];
+      ld_bf8(sm + bl::K, 8192, j, c16, kk);
+      ld_g8(sG, j, 8 * c16, gj);
+#pragma unroll
+      for (int ri = 0; ri < 3; ++ri) {
+        if (ri >= (j >> 4)) {
+          float rr[8], o[8];
+          ld_g8(sG, 16 * ri, 8 * c16, rr);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) o[e] = kk[e] * fexp2(fminf(rr[e] - gj[e], 126.f));
+          st_bf8(sm + bl::KN0 + (ri == 0 ? 0 : (ri == 1 ? 4096 : 12288)), 2048 * (ri + 1), j, c16, o);
+        }
+      }
+    };
+    if (tid < 256) fused_row(tid >> 4);
+    else { fused_row(16 + ((tid - 256) >> 4)); fused_row(32 + ((tid - 256) >> 4)); }
+  }
   // sum_i k dks 2^{G_last - G_i} over this thread's rows: the last row of dG needs the block-wide sum
   {
     float a[16], kdk = 0.f;
@@ -545,28 +567,34 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
   }
   // meanwhile: column-type gated tiles.  Block cj holds rows 16 cj .. 63 of
   //   Qn[i][kappa] = q_i 2^{G_i - R'_cj},  Kp[i][kappa] = beta_i k_i 2^{G_i - R'_cj},  R'_cj = G[16 cj + 15]
-  auto build_col = [&](int cj, int local, int qoff, int koff) {
-    const int rows = 64 - 16 * cj;
-    const int r = local >> 4, c16 = local & 15, i = 16 * cj + r;
-    float qq[8], kk[8], gi[8], rr[8];
+  // Column blocks cjA and cjA + 1 in one pass: q_i, k_i, G_i are read once for both tiles (block
+  // cjA + 1 holds the rows i >= 16 (cjA + 1) only).
+  auto fused_col = [&](int i, int c16, int cjA, int q0, int k0, int q1, int k1) {
+    float qq[8], kk[8], gi[8];
     ld_bf8(sm + bl::Q, 8192, i, c16, qq);
     ld_bf8(sm + bl::K, 8192, i, c16, kk);
     ld_g8(sG, i, 8 * c16, gi);
-    ld_g8(sG, 16 * cj + 15, 8 * c16, rr);
     const float b = s_beta[i];
 #pragma unroll
-    for (int e = 0; e < 8; ++e) {
-      const float ex = fexp2(fminf(gi[e] - rr[e], 126.f));
-      qq[e] *= ex;
-      kk[e] *= ex * b;
+    for (int t = 0; t < 2; ++t) {
+      const int cj = cjA + t;
+      if (i >= 16 * cj) {
+        float rr[8], oq[8], ok[8];
+        ld_g8(sG, 16 * cj + 15, 8 * c16, rr);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const float ex = fexp2(fminf(gi[e] - rr[e], 126.f));
+          oq[e] = qq[e] * ex;
+          ok[e] = kk[e] * (ex * b);
+        }
+        st_bf8(sm + (t == 0 ? q0 : q1), (64 - 16 * cj) * 128, i - 16 * cj, c16, oq);
+        st_bf8(sm + (t == 0 ? k0 : k1), (64 - 16 * cj) * 128, i - 16 * cj, c16, ok);
+      }
     }
-    st_bf8(sm + qoff, rows * 128, r, c16, qq);
-    st_bf8(sm + koff, rows * 128, r, c16, kk);
   };
-  for (int task = tid; task < 1792; task += NT) {          // blocks 0 (64 rows) and 1 (48 rows)
-    if (task < 1024) build_col(0, task, bl::QN0, bl::KP0);
-    else build_col(1, task - 1024, bl::QN1, bl::KP1);
-  }
+#pragma unroll
+  for (int task = tid; task < 1024; task += NT)           // blocks 0 (64 rows) and 1 (48 rows)
+    fused_col(task >> 4, task & 15, 0, bl::QN0, bl::KP0, bl::QN1, bl::KP1);
   tc_mark(p, it, 9);
   if (!mbar_wait(&bar[4], ph)) *s_abort = 1;
   tc_fence_after();
@@ -630,10 +658,7 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
   tc_mark(p, it, 10);
   if (!mbar_wait(&bar[5], ph)) *s_abort = 1;   // row-type tiles are free again
   tc_fence_after();
-  for (int task = tid; task < 768; task += NT) {           // blocks 2 (32 rows) and 3 (16 rows)
-    if (task < 512) build_col(2, task, bl::QN2, bl::KP2);
-    else build_col(3, task - 512, bl::QN3, bl::KP3);
-  }
+  fused_col(32 + (tid >> 4), tid & 15, 2, bl::QN2, bl::KP2, bl::QN3, bl::KP3);   // blocks 2 and 3
   fence_async_smem();
   tc_fence_before();
   __syncthreads();
