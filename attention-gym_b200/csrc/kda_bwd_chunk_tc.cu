@@ -461,12 +461,17 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
 
   // ---- phase 2 epilogue: dv (staged) and its dbeta term; X tile (dkgb^T stays in tensor memory) ----
   {
-    float a[16], pb[16];
+    float a[16], pb[16], bt[16];
+#pragma unroll
+    for (int q4 = 0; q4 < 4; ++q4) {
+      const float4 b4 = *reinterpret_cast<const float4*>(s_beta + r0 + 4 * q4);
+      bt[4 * q4] = b4.x; bt[4 * q4 + 1] = b4.y; bt[4 * q4 + 2] = b4.z; bt[4 * q4 + 3] = b4.w;
+    }
     tmem_ld16(tl + tc::DVB + r0, a);      // this thread = value channel v = L
 #pragma unroll
     for (int ii = 0; ii < 16; ++ii) {
       const int s = r0 + ii;
-      st_bf(sm + bl::DVO, 8192, s, L, a[ii] * s_beta[s]);
+      st_bf(sm + bl::DVO, 8192, s, L, a[ii] * bt[ii]);
       pb[ii] = a[ii] * ld_bf(sm + bl::V, 8192, s, L);
     }
     {   // dbeta term 0: one slot per (channel quadrant, row), summed in a fixed order at the end
@@ -480,7 +485,7 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
 #pragma unroll
       for (int jj = 0; jj < 16; ++jj) {
         const int s = r0 + jj;
-        y[jj] = (t > s && t < valid) ? a[jj] * s_beta[s] : 0.f;
+        y[jj] = (t > s && t < valid) ? a[jj] * bt[jj] : 0.f;
       }
 #pragma unroll
       for (int qd = 0; qd < 2; ++qd) {
@@ -698,8 +703,10 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
       const int rb = r0 + 8 * grp;
       unsigned char* rowB = sm + constB + rb * 128;
       unsigned char* rowG = sm + constG + rb * 128;
-      float a[8], a2[8], e[8], f[8], kr[8], bt[8], dkr[8], dgr[8];
+      float a[8], a2[8], e[8], f[8], kr[8], dkr[8], dgr[8];
       int oB[8], oG[8];
+      const float4 b0 = *reinterpret_cast<const float4*>(s_beta + rb), b1 = *reinterpret_cast<const float4*>(s_beta + rb + 4);
+      const float bt[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
 #pragma unroll
       for (int ii = 0; ii < 8; ++ii) {
         oB[ii] = ii * 128 + ((cB ^ ii) << 4);
@@ -708,7 +715,6 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
         e[ii] = fexp2(g - gfirst);
         f[ii] = fexp2(rlast - g);
         kr[ii] = __bfloat162float(*reinterpret_cast<const bf16*>(rowB + bl::K + oB[ii]));
-        bt[ii] = s_beta[rb + ii];
       }
       tmem_ld8(tl + tc::DQ + rb, a);
       tmem_ld8(tl + tc::DVB + rb, a2);
