@@ -334,7 +334,12 @@ __global__ void __launch_bounds__(NT, 1) kda_prepare_tc_kernel(const __grid_cons
   // ---- phase 3a: this warp reads columns i = 16 wq .. 16 wq + 15 of both accumulators; lanes 0..15
   //      of a quadrant hold the rows j = 16 quad + lane (M = 64 layout)
   {
-    float a[16], pk[16];
+    float a[16], pk[16], bt[16];
+#pragma unroll
+    for (int q4 = 0; q4 < 4; ++q4) {
+      const float4 b4 = *reinterpret_cast<const float4*>(s_beta + 16 * wq + 4 * q4);
+      bt[4 * q4] = b4.x; bt[4 * q4 + 1] = b4.y; bt[4 * q4 + 2] = b4.z; bt[4 * q4 + 3] = b4.w;
+    }
     tmem_ld16(tl + pt::AQ + 16 * wq, a);
     tmem_ld16(tl + pt::PK + 16 * wq, pk);
     if (lid < 16) {
@@ -344,7 +349,7 @@ __global__ void __launch_bounds__(NT, 1) kda_prepare_tc_kernel(const __grid_cons
         const int i = 16 * wq + ii;
         const float x = (j <= i && i < valid) ? a[ii] * p.scale : 0.f;
         *reinterpret_cast<bf16*>(sm + pl::AQK + sw128(i, j)) = __float2bfloat16(x);
-        Lf[i * pl::LP + j] = (j < i) ? pk[ii] * s_beta[i] : 0.f;
+        Lf[i * pl::LP + j] = (j < i) ? pk[ii] * bt[ii] : 0.f;
       }
     }
   }
@@ -376,21 +381,24 @@ __global__ void __launch_bounds__(NT, 1) kda_prepare_tc_kernel(const __grid_cons
   }
   __syncthreads();
   pr_mark(p, it, 6);
-  // A[r][c] = -A[r][r] * sum_{c <= m < r} L[r][m] A[m][c], one block diagonal at a time; the inner
-  // loops are unrolled so that all shared-memory loads of a product are in flight together
-  // Each thread owns a 2 x 2 tile of a 16 x 16 result block: 16-byte loads along k for the row
-  // operand, 8-byte loads for the column operand (the plain one-output-per-thread form is bound by
-  // shared-memory load issue).
+  // A[r][c] = -A[r][r] * sum_{c <= m < r} L[r][m] A[m][c], one block diagonal at a time.
+  // A pair of adjacent lanes owns a 2 x 2 tile of a 16 x 16 result block and splits the inner
+  // dimension between its lanes in interleaved groups of four (16-byte loads along k for the row
+  // operand, 8-byte loads for the column operand; the two lanes' column rows sit 16 banks apart);
+  // one shuffle per accumulator joins the halves and each lane then stores one row of the tile.
   auto round = [&](auto dist_tag) {
     constexpr int DIST = decltype(dist_tag)::value;
     constexpr int pairs = 4 - DIST;
-    if (tid < pairs * 64) {
-      const int c = tid >> 6, r = c + DIST, i = 2 * ((tid >> 3) & 7), j = 2 * (tid & 7);
+    const int ks = tid & 1, rest = tid >> 1;
+    const bool act = tid < pairs * 128;                           // whole warps
+    const int c = rest >> 6, r = c + DIST, i = 2 * ((rest >> 3) & 7), j = 2 * (rest & 7);
+    if (act) {
       const float* A0 = Lf + (16 * r + i) * pl::LP + 16 * c;      // L[r][c .. r-1], rows i, i + 1
       const float* B_ = Af + (16 * c) * pl::LP + 16 * c + j;      // A[c .. r-1][c], columns j, j + 1
       float s00 = 0.f, s01 = 0.f, s10 = 0.f, s11 = 0.f;
 #pragma unroll
-      for (int k = 0; k < 16 * DIST; k += 4) {
+      for (int m = 0; m < 2 * DIST; ++m) {
+        const int k = 4 * (ks + 2 * m);
         const float4 a0 = *reinterpret_cast<const float4*>(A0 + k);
         const float4 a1 = *reinterpret_cast<const float4*>(A0 + pl::LP + k);
         const float av0[4] = {a0.x, a0.y, a0.z, a0.w}, av1[4] = {a1.x, a1.y, a1.z, a1.w};
@@ -401,17 +409,19 @@ __global__ void __launch_bounds__(NT, 1) kda_prepare_tc_kernel(const __grid_cons
           s10 = fmaf(av1[kk], bv.x, s10); s11 = fmaf(av1[kk], bv.y, s11);
         }
       }
-      *reinterpret_cast<float2*>(s_tmp + (c << 8) + i * 16 + j) = make_float2(s00, s01);
-      *reinterpret_cast<float2*>(s_tmp + (c << 8) + (i + 1) * 16 + j) = make_float2(s10, s11);
+      s00 += __shfl_xor_sync(0xffffffffu, s00, 1); s01 += __shfl_xor_sync(0xffffffffu, s01, 1);
+      s10 += __shfl_xor_sync(0xffffffffu, s10, 1); s11 += __shfl_xor_sync(0xffffffffu, s11, 1);
+      *reinterpret_cast<float2*>(s_tmp + (c << 8) + (i + ks) * 16 + j) =
+          ks ? make_float2(s10, s11) : make_float2(s00, s01);
     }
     __syncthreads();
-    if (tid < pairs * 64) {
-      const int c = tid >> 6, r = c + DIST, i = 2 * ((tid >> 3) & 7), j = 2 * (tid & 7);
+    if (act) {
       const float* A0 = Af + (16 * r + i) * pl::LP + 16 * r;      // A[r][r], rows i, i + 1
       const float* B_ = s_tmp + (c << 8) + j;
       float s00 = 0.f, s01 = 0.f, s10 = 0.f, s11 = 0.f;
 #pragma unroll
-      for (int k = 0; k < 16; k += 4) {
+      for (int m = 0; m < 2; ++m) {
+        const int k = 4 * (ks + 2 * m);
         const float4 a0 = *reinterpret_cast<const float4*>(A0 + k);
         const float4 a1 = *reinterpret_cast<const float4*>(A0 + pl::LP + k);
         const float av0[4] = {a0.x, a0.y, a0.z, a0.w}, av1[4] = {a1.x, a1.y, a1.z, a1.w};
@@ -422,9 +432,10 @@ __global__ void __launch_bounds__(NT, 1) kda_prepare_tc_kernel(const __grid_cons
           s10 = fmaf(av1[kk], bv.x, s10); s11 = fmaf(av1[kk], bv.y, s11);
         }
       }
-      float* dst = Af + (16 * r + i) * pl::LP + 16 * c + j;
-      *reinterpret_cast<float2*>(dst) = make_float2(-s00, -s01);
-      *reinterpret_cast<float2*>(dst + pl::LP) = make_float2(-s10, -s11);
+      s00 += __shfl_xor_sync(0xffffffffu, s00, 1); s01 += __shfl_xor_sync(0xffffffffu, s01, 1);
+      s10 += __shfl_xor_sync(0xffffffffu, s10, 1); s11 += __shfl_xor_sync(0xffffffffu, s11, 1);
+      float* dst = Af + (16 * r + i + ks) * pl::LP + 16 * c + j;
+      *reinterpret_cast<float2*>(dst) = ks ? make_float2(-s10, -s11) : make_float2(-s00, -s01);
     }
     __syncthreads();
   };
