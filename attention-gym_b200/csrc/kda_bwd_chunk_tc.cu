@@ -406,21 +406,20 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
   // overlay dO / v_new (dead) and are built while the phase 1 products run; the last one reaches
   // into the dv2 tile and waits for them.
   auto build_row_tiles = [&](int begin, int end) {
+    // (only the last tile, ri = 3, is built here: tasks 1536 .. 2559; its reference row depends on
+    // the channel piece only, which is the same for a thread's tasks)
+    float rr[8];
+    ld_g8(sG, 48, 8 * (tid & 15), rr);
+#pragma unroll
     for (int task = begin + tid; task < end; task += NT) {
-      int ri, t0;
-      if (task < 256) { ri = 0; t0 = 0; }
-      else if (task < 768) { ri = 1; t0 = 256; }
-      else if (task < 1536) { ri = 2; t0 = 768; }
-      else { ri = 3; t0 = 1536; }
-      const int rows = 16 * (ri + 1), local = task - t0;
+      const int local = task - 1536;
       const int j = local >> 4, c16 = local & 15;
-      float kk[8], gj[8], rr[8];
+      float kk[8], gj[8];
       ld_bf8(sm + bl::K, 8192, j, c16, kk);
       ld_g8(sG, j, 8 * c16, gj);
-      ld_g8(sG, 16 * ri, 8 * c16, rr);
 #pragma unroll
       for (int e = 0; e < 8; ++e) kk[e] *= fexp2(fminf(rr[e] - gj[e], 126.f));
-      st_bf8(sm + bl::KN0 + t0 * 16, rows * 128, j, c16, kk);
+      st_bf8(sm + bl::KN0 + 1536 * 16, 64 * 128, j, c16, kk);
     }
   };
   // Tiles 0..2 in one pass over the rows j < 48: k_j and G_j are read once for all the tiles that
@@ -574,7 +573,8 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
   //   Qn[i][kappa] = q_i 2^{G_i - R'_cj},  Kp[i][kappa] = beta_i k_i 2^{G_i - R'_cj},  R'_cj = G[16 cj + 15]
   // Column blocks cjA and cjA + 1 in one pass: q_i, k_i, G_i are read once for both tiles (block
   // cjA + 1 holds the rows i >= 16 (cjA + 1) only).
-  auto fused_col = [&](int i, int c16, int cjA, int q0, int k0, int q1, int k1) {
+  auto fused_col = [&](int i, int c16, int cjA, int q0, int k0, int q1, int k1, const float (&ref0)[8],
+                       const float (&ref1)[8]) {
     float qq[8], kk[8], gi[8];
     ld_bf8(sm + bl::Q, 8192, i, c16, qq);
     ld_bf8(sm + bl::K, 8192, i, c16, kk);
@@ -584,11 +584,10 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
     for (int t = 0; t < 2; ++t) {
       const int cj = cjA + t;
       if (i >= 16 * cj) {
-        float rr[8], oq[8], ok[8];
-        ld_g8(sG, 16 * cj + 15, 8 * c16, rr);
+        float oq[8], ok[8];
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
-          const float ex = fexp2(fminf(gi[e] - rr[e], 126.f));
+          const float ex = fexp2(fminf(gi[e] - (t == 0 ? ref0[e] : ref1[e]), 126.f));
           oq[e] = qq[e] * ex;
           ok[e] = kk[e] * (ex * b);
         }
@@ -597,9 +596,14 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
       }
     }
   };
+  {   // the reference rows R'_cj depend on the channel piece only, which is the same for a thread's tasks
+    float ref0[8], ref1[8];
+    ld_g8(sG, 15, 8 * (tid & 15), ref0);
+    ld_g8(sG, 31, 8 * (tid & 15), ref1);
 #pragma unroll
-  for (int task = tid; task < 1024; task += NT)           // blocks 0 (64 rows) and 1 (48 rows)
-    fused_col(task >> 4, task & 15, 0, bl::QN0, bl::KP0, bl::QN1, bl::KP1);
+    for (int task = tid; task < 1024; task += NT)         // blocks 0 (64 rows) and 1 (48 rows)
+      fused_col(task >> 4, task & 15, 0, bl::QN0, bl::KP0, bl::QN1, bl::KP1, ref0, ref1);
+  }
   tc_mark(p, it, 9);
   if (!mbar_wait(&bar[4], ph)) *s_abort = 1;
   tc_fence_after();
@@ -663,7 +667,12 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
   tc_mark(p, it, 10);
   if (!mbar_wait(&bar[5], ph)) *s_abort = 1;   // row-type tiles are free again
   tc_fence_after();
-  fused_col(32 + (tid >> 4), tid & 15, 2, bl::QN2, bl::KP2, bl::QN3, bl::KP3);   // blocks 2 and 3
+  {
+    float ref0[8], ref1[8];
+    ld_g8(sG, 47, 8 * (tid & 15), ref0);
+    ld_g8(sG, 63, 8 * (tid & 15), ref1);
+    fused_col(32 + (tid >> 4), tid & 15, 2, bl::QN2, bl::KP2, bl::QN3, bl::KP3, ref0, ref1);   // blocks 2 and 3
+  }
   fence_async_smem();
   tc_fence_before();
   __syncthreads();
