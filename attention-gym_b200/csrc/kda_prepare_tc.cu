@@ -283,14 +283,15 @@ __global__ void __launch_bounds__(NT, 1) kda_prepare_tc_kernel(const __grid_cons
   }
   // ---- phase 1b, while the products run: the WY operands beta k 2^G, beta v and the results kg, qg,
   //      each in place or into its staging tile -----------------------------------------------------------
+  float gl[8];                       // last gate row: depends on the channel piece only
+  ld_g8(sG, valid - 1, 8 * (tid & 15), gl);
   for (int task = tid; task < 1024; task += NT) {
     const int i = task >> 4, c16 = task & 15, c0 = 8 * c16;
-    float qq[8], kk[8], vv[8], g[8], gl[8], o[8];
+    float qq[8], kk[8], vv[8], g[8], o[8];
     ld_bf8(sm + pl::Q, 8192, i, c16, qq);
     ld_bf8(sm + pl::K, 8192, i, c16, kk);
     ld_bf8(sm + pl::V, 8192, i, c16, vv);
     ld_g8(sG, i, c0, g);
-    ld_g8(sG, valid - 1, c0, gl);
     const float bt = s_beta[i];
 #pragma unroll
     for (int e = 0; e < 8; ++e) {
