@@ -229,9 +229,13 @@ __global__ void __launch_bounds__(NT, 1) kda_prepare_tc_kernel(const __grid_cons
   if (*s_abort) return 2;
 
   // ---- phase 1a: the operands of the pairwise products; one (row, 8 channels) piece per task ---------
-  for (int task = tid; task < 1024; task += NT) {
+  float gkeep[2][8];                 // the gate rows of this thread's two tasks, reused by phase 1b
+#pragma unroll
+  for (int n = 0; n < 2; ++n) {
+    const int task = tid + n * NT;
     const int i = task >> 4, c16 = task & 15, b = i >> 4, c0 = 8 * c16;
-    float qq[8], kk[8], g[8], r[8], ei[8], o[8];
+    float qq[8], kk[8], r[8], ei[8], o[8];
+    float (&g)[8] = gkeep[n];
     ld_bf8(sm + pl::Q, 8192, i, c16, qq);
     ld_bf8(sm + pl::K, 8192, i, c16, kk);
     ld_g8(sG, i, c0, g);
@@ -285,13 +289,15 @@ __global__ void __launch_bounds__(NT, 1) kda_prepare_tc_kernel(const __grid_cons
   //      each in place or into its staging tile -----------------------------------------------------------
   float gl[8];                       // last gate row: depends on the channel piece only
   ld_g8(sG, valid - 1, 8 * (tid & 15), gl);
-  for (int task = tid; task < 1024; task += NT) {
-    const int i = task >> 4, c16 = task & 15, c0 = 8 * c16;
-    float qq[8], kk[8], vv[8], g[8], o[8];
+#pragma unroll
+  for (int n = 0; n < 2; ++n) {
+    const int task = tid + n * NT;
+    const int i = task >> 4, c16 = task & 15;
+    float qq[8], kk[8], vv[8], o[8];
+    const float (&g)[8] = gkeep[n];
     ld_bf8(sm + pl::Q, 8192, i, c16, qq);
     ld_bf8(sm + pl::K, 8192, i, c16, kk);
     ld_bf8(sm + pl::V, 8192, i, c16, vv);
-    ld_g8(sG, i, c0, g);
     const float bt = s_beta[i];
 #pragma unroll
     for (int e = 0; e < 8; ++e) {
