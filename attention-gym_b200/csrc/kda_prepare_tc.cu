@@ -86,6 +86,13 @@ __device__ __forceinline__ void ld_bf8(const unsigned char* tile, int box_bytes,
   const float2 a = unpack_bf16(u.x), b = unpack_bf16(u.y), c = unpack_bf16(u.z), d = unpack_bf16(u.w);
   o[0] = a.x; o[1] = a.y; o[2] = b.x; o[3] = b.y; o[4] = c.x; o[5] = c.y; o[6] = d.x; o[7] = d.y;
 }
+__device__ __forceinline__ uint4 ld_raw8(const unsigned char* tile, int box_bytes, int row, int c16) {
+  return *reinterpret_cast<const uint4*>(tile + (c16 >> 3) * box_bytes + sw128_chunk(row, c16 & 7));
+}
+__device__ __forceinline__ void unpack8(const uint4& u, float (&o)[8]) {
+  const float2 a = unpack_bf16(u.x), b = unpack_bf16(u.y), c = unpack_bf16(u.z), d = unpack_bf16(u.w);
+  o[0] = a.x; o[1] = a.y; o[2] = b.x; o[3] = b.y; o[4] = c.x; o[5] = c.y; o[6] = d.x; o[7] = d.y;
+}
 __device__ __forceinline__ void st_bf8(unsigned char* tile, int box_bytes, int row, int c16,
                                        const float (&x)[8]) {
   uint4 u;
@@ -230,14 +237,17 @@ __global__ void __launch_bounds__(NT, 1) kda_prepare_tc_kernel(const __grid_cons
 
   // ---- phase 1a: the operands of the pairwise products; one (row, 8 channels) piece per task ---------
   float gkeep[2][8];                 // the gate rows of this thread's two tasks, reused by phase 1b
+  uint4 qkeep[2], kkeep[2];          // and their q, k pieces as raw bf16 vectors
 #pragma unroll
   for (int n = 0; n < 2; ++n) {
     const int task = tid + n * NT;
     const int i = task >> 4, c16 = task & 15, b = i >> 4, c0 = 8 * c16;
     float qq[8], kk[8], r[8], ei[8], o[8];
     float (&g)[8] = gkeep[n];
-    ld_bf8(sm + pl::Q, 8192, i, c16, qq);
-    ld_bf8(sm + pl::K, 8192, i, c16, kk);
+    qkeep[n] = ld_raw8(sm + pl::Q, 8192, i, c16);
+    kkeep[n] = ld_raw8(sm + pl::K, 8192, i, c16);
+    unpack8(qkeep[n], qq);
+    unpack8(kkeep[n], kk);
     ld_g8(sG, i, c0, g);
     ld_g8(sG, 16 * b, c0, r);
 #pragma unroll
@@ -295,8 +305,8 @@ __global__ void __launch_bounds__(NT, 1) kda_prepare_tc_kernel(const __grid_cons
     const int i = task >> 4, c16 = task & 15;
     float qq[8], kk[8], vv[8], o[8];
     const float (&g)[8] = gkeep[n];
-    ld_bf8(sm + pl::Q, 8192, i, c16, qq);
-    ld_bf8(sm + pl::K, 8192, i, c16, kk);
+    unpack8(qkeep[n], qq);
+    unpack8(kkeep[n], kk);
     ld_bf8(sm + pl::V, 8192, i, c16, vv);
     const float bt = s_beta[i];
 #pragma unroll
