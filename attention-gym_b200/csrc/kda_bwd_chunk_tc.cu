@@ -101,6 +101,13 @@ __device__ __forceinline__ void ld_bf8(const unsigned char* tile, int box_bytes,
   const float2 a = unpack_bf16(u.x), b = unpack_bf16(u.y), c = unpack_bf16(u.z), d = unpack_bf16(u.w);
   o[0] = a.x; o[1] = a.y; o[2] = b.x; o[3] = b.y; o[4] = c.x; o[5] = c.y; o[6] = d.x; o[7] = d.y;
 }
+__device__ __forceinline__ uint4 ld_raw8(const unsigned char* tile, int box_bytes, int row, int c16) {
+  return *reinterpret_cast<const uint4*>(tile + (c16 >> 3) * box_bytes + sw128_chunk(row, c16 & 7));
+}
+__device__ __forceinline__ void unpack8(const uint4& u, float (&o)[8]) {
+  const float2 a = unpack_bf16(u.x), b = unpack_bf16(u.y), c = unpack_bf16(u.z), d = unpack_bf16(u.w);
+  o[0] = a.x; o[1] = a.y; o[2] = b.x; o[3] = b.y; o[4] = c.x; o[5] = c.y; o[6] = d.x; o[7] = d.y;
+}
 __device__ __forceinline__ void st_bf8(unsigned char* tile, int box_bytes, int row, int c16,
                                        const float (&x)[8]) {
   uint4 u;
@@ -333,6 +340,11 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
   tc_mark(p, it, 3);      // every thread is done with the raw h / dh tiles
   if (*s_abort) return 3;
 
+  // This thread's two (row, 8-channel) pieces -- rows tid / 16 and tid / 16 + 32, channels 8 (tid % 16) --
+  // are the same in every pass that builds gated k tiles: their k (raw bf16) and gate values are read
+  // once and stay in registers.
+  float gkeep[2][8];
+  uint4 kkeep[2];
   // ---- phase 1 epilogue: operand tiles for the next products; dq^T and dks^T stay in tensor memory
   {
     float a[16];
@@ -345,13 +357,14 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
     }
     // k 2^G as a K-major tile [s][kappa]
 #pragma unroll
-    for (int task = tid; task < 1024; task += NT) {
-      const int i = task >> 4, c16 = task & 15;
-      float kk[8], gg[8];
-      ld_bf8(sm + bl::K, 8192, i, c16, kk);
-      ld_g8(sG, i, 8 * c16, gg);
+    for (int n = 0; n < 2; ++n) {
+      const int i = (tid >> 4) + 32 * n, c16 = tid & 15;
+      float kk[8];
+      kkeep[n] = ld_raw8(sm + bl::K, 8192, i, c16);
+      unpack8(kkeep[n], kk);
+      ld_g8(sG, i, 8 * c16, gkeep[n]);
 #pragma unroll
-      for (int e = 0; e < 8; ++e) kk[e] *= fexp2(gg[e]);
+      for (int e = 0; e < 8; ++e) kk[e] *= fexp2(gkeep[n][e]);
       st_bf8(sm + bl::KGM, 8192, i, c16, kk);
     }
     // dAqk (M = 64 accumulator: row r lives on lane 32 (r / 16) + r % 16)
@@ -411,14 +424,12 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
     float rr[8];
     ld_g8(sG, 48, 8 * (tid & 15), rr);
 #pragma unroll
-    for (int task = begin + tid; task < end; task += NT) {
-      const int local = task - 1536;
-      const int j = local >> 4, c16 = local & 15;
-      float kk[8], gj[8];
-      ld_bf8(sm + bl::K, 8192, j, c16, kk);
-      ld_g8(sG, j, 8 * c16, gj);
+    for (int n = 0; n < 2; ++n) {
+      const int j = (tid >> 4) + 32 * n, c16 = tid & 15;
+      float kk[8];
+      unpack8(kkeep[n], kk);
 #pragma unroll
-      for (int e = 0; e < 8; ++e) kk[e] *= fexp2(fminf(rr[e] - gj[e], 126.f));
+      for (int e = 0; e < 8; ++e) kk[e] *= fexp2(fminf(rr[e] - gkeep[n][e], 126.f));
       st_bf8(sm + bl::KN0 + 1536 * 16, 64 * 128, j, c16, kk);
     }
   };
@@ -574,11 +585,10 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
   // Column blocks cjA and cjA + 1 in one pass: q_i, k_i, G_i are read once for both tiles (block
   // cjA + 1 holds the rows i >= 16 (cjA + 1) only).
   auto fused_col = [&](int i, int c16, int cjA, int q0, int k0, int q1, int k1, const float (&ref0)[8],
-                       const float (&ref1)[8]) {
-    float qq[8], kk[8], gi[8];
+                       const float (&ref1)[8], const uint4& kraw, const float (&gi)[8]) {
+    float qq[8], kk[8];
     ld_bf8(sm + bl::Q, 8192, i, c16, qq);
-    ld_bf8(sm + bl::K, 8192, i, c16, kk);
-    ld_g8(sG, i, 8 * c16, gi);
+    unpack8(kraw, kk);
     const float b = s_beta[i];
 #pragma unroll
     for (int t = 0; t < 2; ++t) {
@@ -601,8 +611,9 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
     ld_g8(sG, 15, 8 * (tid & 15), ref0);
     ld_g8(sG, 31, 8 * (tid & 15), ref1);
 #pragma unroll
-    for (int task = tid; task < 1024; task += NT)         // blocks 0 (64 rows) and 1 (48 rows)
-      fused_col(task >> 4, task & 15, 0, bl::QN0, bl::KP0, bl::QN1, bl::KP1, ref0, ref1);
+    for (int n = 0; n < 2; ++n)                           // blocks 0 (64 rows) and 1 (48 rows)
+      fused_col((tid >> 4) + 32 * n, tid & 15, 0, bl::QN0, bl::KP0, bl::QN1, bl::KP1, ref0, ref1, kkeep[n],
+                gkeep[n]);
   }
   tc_mark(p, it, 9);
   if (!mbar_wait(&bar[4], ph)) *s_abort = 1;
@@ -671,7 +682,8 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
     float ref0[8], ref1[8];
     ld_g8(sG, 47, 8 * (tid & 15), ref0);
     ld_g8(sG, 63, 8 * (tid & 15), ref1);
-    fused_col(32 + (tid >> 4), tid & 15, 2, bl::QN2, bl::KP2, bl::QN3, bl::KP3, ref0, ref1);   // blocks 2 and 3
+    fused_col(32 + (tid >> 4), tid & 15, 2, bl::QN2, bl::KP2, bl::QN3, bl::KP3, ref0, ref1, kkeep[1],
+              gkeep[1]);                                   // blocks 2 and 3
   }
   fence_async_smem();
   tc_fence_before();
