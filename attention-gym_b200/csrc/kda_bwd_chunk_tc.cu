@@ -438,10 +438,9 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
   // row of block 1 and one of block 2 (two tiles + one): three tile rows per thread either way.
   {
     const int c16 = tid & 15;
-    auto fused_row = [&](int j) {
-      float kk[8], gj[8];
-      ld_bf8(sm + bl::K, 8192, j, c16, kk);
-      ld_g8(sG, j, 8 * c16, gj);
+    auto fused_row = [&](int j, const uint4& kraw, const float (&gj)[8]) {
+      float kk[8];
+      unpack8(kraw, kk);
 #pragma unroll
       for (int ri = 0; ri < 3; ++ri) {
         if (ri >= (j >> 4)) {
@@ -453,8 +452,14 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
         }
       }
     };
-    if (tid < 256) fused_row(tid >> 4);
-    else { fused_row(16 + ((tid - 256) >> 4)); fused_row(32 + ((tid - 256) >> 4)); }
+    fused_row(tid >> 4, kkeep[0], gkeep[0]);           // rows 0..31: the first kept piece
+    if (tid >= 256) {                                  // rows 32..47: not one of this thread's kept rows
+      const int j = 16 + (tid >> 4);
+      float g2[8];
+      const uint4 k2 = ld_raw8(sm + bl::K, 8192, j, c16);
+      ld_g8(sG, j, 8 * c16, g2);
+      fused_row(j, k2, g2);
+    }
   }
   // sum_i k dks 2^{G_last - G_i} over this thread's rows: the last row of dG needs the block-wide sum
   {
