@@ -165,6 +165,14 @@ __global__ void __launch_bounds__(NT, 1) kda_prepare_tc_kernel(const __grid_cons
     }
   };
 
+  // The 16 x 16 blocks above the diagonal of A are zero.  No work item writes them (the solve fills the
+  // diagonal and lower blocks only) and the fp32 matrix has a region of its own, so once is enough.
+  for (int idx = tid; idx < 6 * 256; idx += NT) {
+    const int blk = idx >> 8, i = (idx >> 4) & 15, j = idx & 15;
+    const int br = blk >= 5 ? 2 : (blk >= 3 ? 1 : 0);          // (0,1) (0,2) (0,3) (1,2) (1,3) (2,3)
+    const int bc = br == 0 ? blk + 1 : (br == 1 ? blk - 1 : 3);
+    Af[(16 * br + i) * pl::LP + 16 * bc + j] = 0.f;
+  }
   uint32_t ph = 0;
   int rc = 0, it = 0;
   bool pre = false;              // this item's loads were issued by the previous item
@@ -369,13 +377,6 @@ __global__ void __launch_bounds__(NT, 1) kda_prepare_tc_kernel(const __grid_cons
         Lf[i * pl::LP + j] = (j < i) ? pk[ii] * bt[ii] : 0.f;
       }
     }
-  }
-  // the 16 x 16 blocks above the diagonal of A are zero (every other entry is written below)
-  for (int idx = tid; idx < 6 * 256; idx += NT) {
-    const int blk = idx >> 8, i = (idx >> 4) & 15, j = idx & 15;
-    const int br = blk >= 5 ? 2 : (blk >= 3 ? 1 : 0);          // (0,1) (0,2) (0,3) (1,2) (1,3) (2,3)
-    const int bc = br == 0 ? blk + 1 : (br == 1 ? blk - 1 : 3);
-    Af[(16 * br + i) * pl::LP + 16 * bc + j] = 0.f;
   }
   __syncthreads();
   pr_mark(p, it, 5);
