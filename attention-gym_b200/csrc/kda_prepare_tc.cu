@@ -374,7 +374,7 @@ __global__ void __launch_bounds__(NT, 1) kda_prepare_tc_kernel(const __grid_cons
         const int i = 16 * wq + ii;
         const float x = (j <= i && i < valid) ? a[ii] * p.scale : 0.f;
         *reinterpret_cast<bf16*>(sm + pl::AQK + sw128(i, j)) = __float2bfloat16(x);
-        Lf[i * pl::LP + j] = (j < i) ? pk[ii] * bt[ii] : 0.f;
+        if (quad <= wq) Lf[i * pl::LP + j] = (j < i) ? pk[ii] * bt[ii] : 0.f;    // blocks above the diagonal are never read
       }
     }
   }
@@ -463,9 +463,14 @@ __global__ void __launch_bounds__(NT, 1) kda_prepare_tc_kernel(const __grid_cons
   pr_mark(p, it, 7);
   // A as a bf16 operand tile [i][j] (K-major, one 128-byte-swizzled box): also the stored tape
   for (int idx = tid; idx < 64 * 8; idx += NT) {
-    const int r = idx >> 3, c = idx & 7;
+    const int r = idx >> 3, c = idx & 7, odd = (c >> 2) & 1;
+    // lanes 32 bytes apart: the upper four of a quarter-warp read their halves in the other order
+    const float4 fa = *reinterpret_cast<const float4*>(Af + r * pl::LP + 8 * c + 4 * odd);
+    const float4 fb = *reinterpret_cast<const float4*>(Af + r * pl::LP + 8 * c + 4 - 4 * odd);
+    const float4 lo = odd ? fb : fa, hi = odd ? fa : fb;
+    const float f8[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
     uint4 v;
-    pack8v(Af + r * pl::LP + 8 * c, v);
+    pack8v(f8, v);
     *reinterpret_cast<uint4*>(sm + pl::AT + sw128_chunk(r, c)) = v;
   }
   fence_async_smem();
