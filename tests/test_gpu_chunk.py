@@ -176,3 +176,17 @@ def test_rejections():
                            c["v"].repeat(2, 1, 1, 1), c["cum_gate"].repeat(2, 1, 1, 1),
                            c["beta"].repeat(2, 1, 1),
                            cu_seqlens=torch.tensor([0, 64], dtype=torch.int32, device="cuda"))
+
+
+def test_many_short_sequences():
+    """300 packed sequences of 1..80 tokens (some empty): more offsets than the kernels keep in
+    shared memory, so the work-item search reads them from global memory."""
+    gen = torch.Generator().manual_seed(11)
+    lengths = torch.randint(0, 81, (300,), generator=gen).tolist()
+    lengths[7] = 0
+    inp = _case(1, sum(lengths), 1, seed=12, lengths=lengths)
+    got = _run_fused(inp)
+    ref_o, ref_s = orc.chunk_kda_ref(inp["q"].float(), inp["k"].float(), inp["v"].float(), inp["cum_gate"],
+                                     inp["beta"], inp["h0"], cu_seqlens=inp["cu_seqlens"])
+    assert_normalised(_active(inp, got["o"]).float(), _active(inp, ref_o), TOL, "output")
+    assert_normalised(got["state"], ref_s, TOL, "final states")
