@@ -150,15 +150,17 @@ def test_rejects_grad_and_bad_shapes():
                                c["gate_log2"].double(), c["beta"].double())
 
 
-@pytest.mark.parametrize("dtype,tol", [(torch.bfloat16, 2e-2), (torch.float16, 4e-3), (torch.float32, 2e-3)])
-def test_decode_step_fused_preprocessing(dtype, tol):
+@pytest.mark.parametrize("dtype,tol,w", [(torch.bfloat16, 2e-2, 4), (torch.float16, 4e-3, 4),
+                                         (torch.float32, 2e-3, 4), (torch.bfloat16, 2e-2, 2),
+                                         (torch.bfloat16, 2e-2, 3), (torch.bfloat16, 2e-2, 5)])
+def test_decode_step_fused_preprocessing(dtype, tol, w):
     """decode_step = conv decode + SiLU + l2norm(q, k) + bounded per-token gate + paged state update,
     against the composition of the CPU oracle's pieces; three steps on the same pools, with padding
     rows.  16-bit activations take the vector kernel, fp32 the scalar one; fp32 state."""
     from oracle.kda_oracle import (bounded_gate_cumsum_ref, causal_conv1d_ref, l2norm_ref,
                                    recurrent_kda_ref)
 
-    n, h, w, slots = 20, 4, 4, 24
+    n, h, slots = 20, 4, 24           # filter widths 2..4 take the vector kernel, wider ones the scalar one
     c = 3 * h * 128
     gen = torch.Generator().manual_seed(77)
     weight = (0.5 * torch.randn(c, w, generator=gen)).to(dtype)
