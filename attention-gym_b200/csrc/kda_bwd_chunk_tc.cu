@@ -48,11 +48,13 @@ struct BwdTcParams {
 // Debugging aid: phase timestamps of the 20th work item of the first 64 CTAs (steady state) into
 // the buffer set with kda_debug_set_profile_buffer.
 __device__ __forceinline__ void tc_mark(const BwdTcParams& p, int it, int slot) {
+#ifdef KDA_PHASE_PROFILE
   if (p.prof && it == 20 && threadIdx.x == 0 && blockIdx.x < 64) {
     long long t;
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
     p.prof[blockIdx.x * 32 + slot] = t;
   }
+#endif
 }
 
 namespace bl {  // shared-memory layout (bytes)

@@ -12,14 +12,21 @@ static const char* kStageNames[kStageCount] = {
     "gate_fwd", "gate_bwd", "l2norm", "conv", "chunk_offsets", "state_affine",
     "epilogue"};
 
-struct Pair { cudaEvent_t a, b; };
+struct Pair { cudaEvent_t a, b; int device; };
+constexpr int kMaxDevices = 64;
 static bool g_enabled = false;
 static std::mutex g_mu;
 static std::vector<Pair> g_pairs[kStageCount];
-static std::vector<cudaEvent_t> g_free;
+static std::vector<cudaEvent_t> g_free[kMaxDevices];   // an event belongs to the device it was created on
 
-static cudaEvent_t get_event() {
-  if (!g_free.empty()) { cudaEvent_t e = g_free.back(); g_free.pop_back(); return e; }
+static int current_device() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) dev = 0;
+  return dev;
+}
+
+static cudaEvent_t get_event(int dev) {
+  if (!g_free[dev].empty()) { cudaEvent_t e = g_free[dev].back(); g_free[dev].pop_back(); return e; }
   cudaEvent_t e;
   cudaEventCreate(&e);
   return e;
@@ -28,7 +35,8 @@ static cudaEvent_t get_event() {
 void stage_begin(int stage, cudaStream_t s) {
   if (!g_enabled) return;
   std::lock_guard<std::mutex> lock(g_mu);
-  Pair p{get_event(), get_event()};
+  const int dev = current_device();
+  Pair p{get_event(dev), get_event(dev), dev};
   cudaEventRecord(p.a, s);
   g_pairs[stage].push_back(p);
 }
@@ -68,7 +76,10 @@ extern "C" int kda_stage_timing_read(int64_t* launches, float* total_ms, int res
       }
     }
     if (reset) {
-      for (auto& p : kda::g_pairs[st]) { kda::g_free.push_back(p.a); kda::g_free.push_back(p.b); }
+      for (auto& p : kda::g_pairs[st]) {
+        kda::g_free[p.device].push_back(p.a);
+        kda::g_free[p.device].push_back(p.b);
+      }
       kda::g_pairs[st].clear();
     }
   }

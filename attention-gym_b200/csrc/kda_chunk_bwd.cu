@@ -31,14 +31,17 @@ int launch_recompute(const void* q, const void* k, const void* v, const float* g
 
 using kda::bf16;
 
+// Development builds (-DKDA_PHASE_PROFILE) can hand the persistent kernels a device buffer of
+// 64 x 32 int64 that receives %globaltimer stamps of their phases; the shipped library has neither
+// the setter nor the stamps.
 static long long* g_prof_buffer = nullptr;
 namespace kda { long long* debug_profile_buffer() { return g_prof_buffer; } }
-// Debugging aid: device buffer of 64 x 32 int64 that receives per-phase timestamps of the first
-// 64 chunks of head 0 from the backward chunk kernel (NULL switches it off).
+#ifdef KDA_PHASE_PROFILE
 extern "C" int kda_debug_set_profile_buffer(void* buffer) {
   g_prof_buffer = reinterpret_cast<long long*>(buffer);
   return KDA_OK;
 }
+#endif
 
 extern "C" int64_t kda_chunk_bwd_workspace_bytes(int64_t tokens, int heads, int64_t num_chunks) {
   const int64_t nd = tokens * heads * 128;

@@ -24,6 +24,8 @@ struct ChunkParams {
   bf16* aqk; bf16* akk;                 // tape [N, H, 64]
   bf16* w; bf16* u; bf16* kg; bf16* qg;  // [N, H, 128]
   const float* h0; float* ht;
+  float* trans_out;                     // slice transition [nseq, H, 128, 128], or NULL
+  const int32_t* limit_in; int32_t* limit_out;   // per (sequence, head) chunk limits of the state walk, or NULL
   bf16* o; bf16* h_out; bf16* vnew_out;
   const int32_t* cu_seqlens; const int32_t* chunk_offsets;
   int nseq, H;
@@ -36,7 +38,8 @@ int launch_prepare_tc(const bf16* q, const bf16* k, const bf16* v, const float* 
                       bf16* aqk, bf16* akk, bf16* w, bf16* u, bf16* kg, bf16* qg, const int32_t* cu,
                       const int32_t* co, int nseq, int H, int64_t tokens, int chunks, cudaStream_t s);
 int launch_state_fwd_tc(const bf16* w, const bf16* u, const bf16* kg, const bf16* qg, const bf16* aqk,
-                        const float* g, const float* h0, float* ht, bf16* o, bf16* h_out,
+                        const float* g, const float* h0, float* ht, float* trans_out,
+                        const int32_t* limit_in, int32_t* limit_out, bf16* o, bf16* h_out,
                         bf16* vnew_out, const int32_t* cu, const int32_t* co, int nseq, int H,
                         int64_t tokens, int chunks, cudaStream_t s);
 
@@ -46,8 +49,8 @@ int launch_prepare(const ChunkParams& p, int chunks, cudaStream_t s) {
                            p.chunk_offsets, p.nseq, p.H, p.tokens, chunks, s);
 }
 int launch_state_fwd(const ChunkParams& p, cudaStream_t s) {
-  return launch_state_fwd_tc(p.w, p.u, p.kg, p.qg, p.aqk, p.g, p.h0, p.ht, p.o, p.h_out, p.vnew_out,
-                             p.cu_seqlens, p.chunk_offsets, p.nseq, p.H, p.tokens, p.chunks, s);
+  return launch_state_fwd_tc(p.w, p.u, p.kg, p.qg, p.aqk, p.g, p.h0, p.ht, p.trans_out, p.limit_in,
+                             p.limit_out, p.o, p.h_out, p.vnew_out, p.cu_seqlens, p.chunk_offsets, p.nseq, p.H, p.tokens, p.chunks, s);
 }
 
 // Backward's recompute leg: w, u, kg, qg (and a scratch copy of the tape), then the chunk-entry states
@@ -86,7 +89,7 @@ static int chunk_fwd_impl(bool keep, const void* q, const void* k, const void* v
     return KDA_ERR_ARG;
   if (key_dim != 128 || value_dim != 128) return KDA_ERR_UNSUPPORTED;
   if (nseq < 1 || heads < 1 || tokens < 1 || num_chunks < 0) return KDA_ERR_ARG;
-  if ((int64_t)nseq * heads * 2 > 0x7fffffffLL) return KDA_ERR_UNSUPPORTED;
+  if ((int64_t)nseq * heads * 8 > 0x7fffffffLL) return KDA_ERR_UNSUPPORTED;
   if (workspace_bytes < (keep ? kda_chunk_bwd_workspace_bytes(tokens, heads, num_chunks)
                               : kda_chunk_fwd_workspace_bytes(tokens, heads)))
     return KDA_ERR_ARG;
@@ -172,10 +175,10 @@ extern "C" int kda_chunk_fwd_state(const float* cum_gate, const float* initial_s
                                    float* final_state, void* out, const void* aqk,
                                    const int32_t* cu_seqlens, const int32_t* chunk_offsets, int nseq,
                                    int64_t tokens, int heads, void* workspace, int use_u,
-                                   void* stream) {
+                                   const int32_t* chunk_limit, void* stream) {
   if (!cum_gate || !aqk || !cu_seqlens || !chunk_offsets || !workspace) return KDA_ERR_ARG;
   if (nseq < 1 || heads < 1 || tokens < 1) return KDA_ERR_ARG;
-  if ((int64_t)nseq * heads * 2 > 0x7fffffffLL) return KDA_ERR_UNSUPPORTED;
+  if ((int64_t)nseq * heads * 8 > 0x7fffffffLL) return KDA_ERR_UNSUPPORTED;
   kda::ChunkParams p{};
   const int64_t nd = tokens * heads * 128;
   bf16* ws = reinterpret_cast<bf16*>(workspace);
@@ -183,6 +186,33 @@ extern "C" int kda_chunk_fwd_state(const float* cum_gate, const float* initial_s
   p.aqk = (bf16*)aqk;
   p.w = ws; p.u = use_u ? ws + nd : nullptr; p.kg = ws + 2 * nd; p.qg = ws + 3 * nd;
   p.h0 = initial_state; p.ht = final_state; p.o = (bf16*)out;
+  p.limit_in = chunk_limit;
+  p.cu_seqlens = cu_seqlens; p.chunk_offsets = chunk_offsets; p.nseq = nseq; p.H = heads;
+  p.tokens = tokens;
+  return kda::launch_state_fwd(p, (cudaStream_t)stream);
+}
+
+// One launch for what a context-parallel rank needs before the boundary-state chain can pass through
+// it: b = the state leaving the slice for a zero entering state, and M = the dense slice transition,
+// so that the leaving state for any entering state is M h_in + b.  Half of the CTAs walk the chains
+// with u from a zero state, the other half with u = 0 from an identity state.
+extern "C" int kda_chunk_slice_map(const float* cum_gate, float* b_out, float* transition_out,
+                                   void* out, int32_t* chunk_limit_out, const void* aqk,
+                                   const int32_t* cu_seqlens,
+                                   const int32_t* chunk_offsets, int nseq, int64_t tokens, int heads,
+                                   void* workspace, void* stream) {
+  if (!cum_gate || !b_out || !transition_out || !aqk || !cu_seqlens || !chunk_offsets || !workspace)
+    return KDA_ERR_ARG;
+  if (nseq < 1 || heads < 1 || tokens < 1) return KDA_ERR_ARG;
+  if ((int64_t)nseq * heads * 8 > 0x7fffffffLL) return KDA_ERR_UNSUPPORTED;
+  kda::ChunkParams p{};
+  const int64_t nd = tokens * heads * 128;
+  bf16* ws = reinterpret_cast<bf16*>(workspace);
+  p.g = cum_gate;
+  p.aqk = (bf16*)aqk;
+  p.w = ws; p.u = ws + nd; p.kg = ws + 2 * nd; p.qg = ws + 3 * nd;
+  p.ht = b_out; p.trans_out = transition_out;
+  p.o = (bf16*)out; p.limit_out = chunk_limit_out;
   p.cu_seqlens = cu_seqlens; p.chunk_offsets = chunk_offsets; p.nseq = nseq; p.H = heads;
   p.tokens = tokens;
   return kda::launch_state_fwd(p, (cudaStream_t)stream);
@@ -194,8 +224,10 @@ extern "C" int kda_chunk_fwd_state(const float* cum_gate, const float* initial_s
 // Some hosts of this library cannot call cudaMalloc: a serving engine that has handed every free
 // byte of the device to its own paged pool, or a plugin running under a runtime that forbids
 // allocation once the model is loaded.  For them the w/u/kg/qg scratch of the forward lives in the
-// file-scope device array below instead of a caller workspace.  Every GPU that loads the library
-// holds the array (KDA_NOALLOC_SCRATCH_BYTES) until the process exits.
+// file-scope device array below instead of a caller workspace.  CUDA loads device code lazily, so
+// a GPU starts to hold the array (KDA_NOALLOC_SCRATCH_BYTES, until the process exits) when the first
+// call on it looks the array's address up, not when the library is opened: that first call belongs
+// in the host's start-up phase, before its own pool claims the rest of the device.
 // ------------------------------------------------------------------------------------------------
 namespace kda {
 static __device__ __align__(256) unsigned char g_noalloc_scratch[KDA_NOALLOC_SCRATCH_BYTES];
@@ -218,8 +250,10 @@ extern "C" int kda_chunk_fwd_noalloc(const void* q, const void* k, const void* v
   // once per device, with that device current.
   void* scratch = kda::g_noalloc_ptr[dev];
   if (!scratch) {
-    if (cudaGetSymbolAddress(&scratch, kda::g_noalloc_scratch) != cudaSuccess || !scratch)
+    if (cudaGetSymbolAddress(&scratch, kda::g_noalloc_scratch) != cudaSuccess || !scratch) {
+      cudaGetLastError();   // leave no stale error behind for the next entry point's launch check
       return KDA_ERR_LAUNCH;
+    }
     kda::g_noalloc_ptr[dev] = scratch;
   }
   // Nothing in the scratch has to start at zero: every row a kernel reads was written earlier in

@@ -46,11 +46,13 @@ struct PrepParams {
 };
 
 __device__ __forceinline__ void pr_mark(const PrepParams& p, int it, int slot) {
+#ifdef KDA_PHASE_PROFILE
   if (p.prof && it == 20 && threadIdx.x == 0 && blockIdx.x < 64) {
     long long t;
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
     p.prof[blockIdx.x * 32 + slot] = t;
   }
+#endif
 }
 
 namespace pl {  // shared-memory layout (bytes)

@@ -219,11 +219,13 @@ struct DecodeMaps { CUtensorMap src, dst; };   // [state rows, 128] fp32, box 32
 long long* debug_profile_buffer();
 // Debugging aid: timestamps of the 20th item of the first 64 CTAs (one thread per role).
 __device__ __forceinline__ void dec_mark(long long* prof, int i, int slot) {
+#ifdef KDA_PHASE_PROFILE
   if (prof && (i & 7) == 4 && blockIdx.x < 8 && slot < 4) {     // items 4, 12, 20, ... of the first 8 CTAs
     long long t;
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
     prof[blockIdx.x * 32 + (i >> 3) * 4 + slot] = t;
   }
+#endif
 }
 
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {

@@ -2,10 +2,12 @@
 //
 //   v_new = u - w h ;  o = qg h + Aqk v_new ;  h <- diag(2^{G_last}) h + kg^T v_new
 //
-// One CTA (256 threads) walks the chunks of one (sequence, head).  The fp32 state h [128 x 128]
-// lives in tensor memory for the whole walk (128 lanes x 128 columns) and never goes to HBM in
-// the forward pass; two more 128-column accumulators alternate as D1 = [w h ; qg h + Aqk v_new].
-// Warp w works on tensor-memory lanes 32 (w % 4) .. +31 and on the 64-column half w / 4.
+// NS = 1, 2 or 4 CTAs (256 threads each) walk the chunks of one (sequence, head); each owns
+// N = 128 / NS value columns of the state (every product below is separable along v), so a few long
+// chains still fill the SMs.  The fp32 state slice h [128 x N] lives in tensor memory for the whole
+// walk (128 lanes x N columns) and never goes to HBM in the forward pass; two more accumulators
+// alternate as D1 = [w h ; qg h + Aqk v_new].  Warp w works on tensor-memory lanes 32 (w % 4) .. +31
+// and on the half w / 4 of the slice's columns.
 // Per chunk:
 //   a. every thread reads its half row of h, writes it as bf16 into the swizzled MN-major B tile,
 //      multiplies by the chunk decay and stores it back to tensor memory;
@@ -28,7 +30,9 @@ constexpr int D = 128;
 struct StateTcParams {
   CUtensorMap tm_w, tm_qg, tm_kg, tm_u, tm_aqk;
   CUtensorMap tm_hout, tm_vnew, tm_o;      // result tiles leave shared memory with TMA stores
-  const float* g; const float* h0; float* ht;
+  const float* g; const float* h0; float* ht; float* trans_out;
+  const int32_t* limit_in;   // per (sequence, head): walk only this many leading chunks (NULL = all)
+  int32_t* limit_out;        // per (sequence, head): chunks after which the transition is exactly zero
   bf16* o; bf16* h_out; bf16* vnew_out;
   const int32_t* cu_seqlens; const int32_t* chunk_offsets;
   int* error;
@@ -40,11 +44,13 @@ struct StateTcParams {
 long long* debug_profile_buffer();
 
 __device__ __forceinline__ void st_mark(long long* prof, int c, int slot) {
+#ifdef KDA_PHASE_PROFILE
   if (prof && c == 10 && threadIdx.x == 0 && blockIdx.x < 64) {
     long long t;
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
     prof[blockIdx.x * 32 + 20 + slot] = t;
   }
+#endif
 }
 
 constexpr int kStageBytes = 32768 + 16384 + 16384 + 16384;   // A1, KG, U, A2
@@ -64,7 +70,40 @@ __device__ __forceinline__ void pack8(const float* x, uint4& o) {
 
 constexpr int kStateThreads = 256;
 
+// Value split of a chain: 128 / NS state columns per CTA.  Chosen from the number of chains against
+// the number of SMs (the reference tiles the same dimension: fwd/triton/chunk_delta_h.py:166 BV = 64,
+// bwd/cute/chunk_delta_h_bwd_v1_dispatch.py:53-55 BV = 16 / 32 by tile count); 0 = automatic.
+static int g_value_split = 0;
+static int pick_value_split(int64_t chains) {
+  if (g_value_split == 1 || g_value_split == 2 || g_value_split == 4) return g_value_split;
+  int dev = 0, sms = 148;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (chains * 4 <= sms) return 4;
+  if (chains * 2 <= sms) return 2;
+  return 1;
+}
+
+// Byte offset of the 16-byte piece holding columns c .. c + 7 of row r in a tile made of 64-column
+// boxes `box_bytes` apart.
+__device__ __forceinline__ int tile_off(int r, int c, int box_bytes) {
+  return (c >> 6) * box_bytes + sw128_chunk(r, (c & 63) >> 3);
+}
+
+// NS = number of CTAs that share one (sequence, head) chain; each owns N = 128 / NS value columns of
+// the state and of every [.., v] product (all of them are separable along v).  The operand tiles
+// w, qg, kg, Aqk are the same for the NS CTAs of a chain (the second to read them hits L2).
+// CTAs with blockIdx.x >= NS * nseq * H (present when trans_out != NULL) walk the same chains with
+// u = 0 from an identity state and write the slice transition instead of outputs.  Such a walk stops
+// as soon as the running transition is exactly zero in fp32 (every later one is then zero too) and
+// reports how many chunks that took (limit_out): past them an entering state cannot change any
+// output or state bit that fp32 can hold, so the corrective pass with the true entering state
+// (limit_in) only needs those leading chunks.  This is measured on the data, never assumed.
+template <int NS>
 __global__ void __launch_bounds__(kStateThreads) kda_state_fwd_tc_kernel(const __grid_constant__ StateTcParams p) {
+  constexpr int N = D / NS;            // state columns of this CTA
+  constexpr int NC = N / 2;            // columns per thread (two warps share a lane quadrant)
+  constexpr int NB = (N + 63) / 64;    // 64-column boxes of a slice-shaped tile
+  constexpr bool kTileStore = N >= 64; // results leave by TMA tile stores (whole boxes) or directly
   extern __shared__ unsigned char smem_dyn[];
   // 1024-byte alignment by offset, so the compiler still knows this is shared memory
   unsigned char* smem = smem_dyn + ((1024u - (saddr(smem_dyn) & 1023u)) & 1023u);
@@ -75,20 +114,33 @@ __global__ void __launch_bounds__(kStateThreads) kda_state_fwd_tc_kernel(const _
   volatile int* s_abort = reinterpret_cast<volatile int*>(bar_full + 5);
 
   const int tid = threadIdx.x, warp = tid >> 5, lid = tid & 31;
-  const int quad = warp & 3, half = warp >> 2;     // TMEM lane quadrant; 64-column half of the tiles
+  const int quad = warp & 3, sub = warp >> 2;      // TMEM lane quadrant; which half of the slice columns
   const int row = 32 * quad + lid;                 // TMEM lane = state row kappa / D1 row
   const int H = p.H;
-  const int head = blockIdx.x % H, seq = blockIdx.x / H;
+  const int chains = p.nseq * H;
+  int item = blockIdx.x / NS;
+  const int slice = blockIdx.x % NS;
+  const bool trans = item >= chains;               // transition CTA: identity state, u = 0, no outputs
+  if (trans) item -= chains;
+  const int head = item % H, seq = item / H;
+  const int v0 = slice * N;                        // first value column of the slice
+  const int col0 = sub * NC;                       // this thread's first column inside the slice
+  const int ucol0 = N < 64 ? (v0 & 63) : 0;        // where the slice starts inside the loaded u box
+  const bool use_u = p.use_u && !trans, use_o = p.use_o && !trans;
+  bf16* const h_out = trans ? nullptr : p.h_out;
+  bf16* const vnew_out = trans ? nullptr : p.vnew_out;
+  float* const ht = trans ? p.trans_out : p.ht;
   const int64_t bos = p.cu_seqlens[seq], eos = p.cu_seqlens[seq + 1];
   const int chunk0 = p.chunk_offsets[seq];
-  const int nchunks = p.chunk_offsets[seq + 1] - chunk0;
+  int nchunks = p.chunk_offsets[seq + 1] - chunk0;
+  if (p.limit_in && !trans) nchunks = min(nchunks, p.limit_in[item]);
   const int64_t sbase = ((int64_t)seq * H + head) * D * D;
 
   if (warp == 0) tmem_alloc(tmem_slot, 512);
   if (tid == 0) {
     mbar_init(&bar_full[0], 1); mbar_init(&bar_full[1], 1);
     mbar_init(bar_mma1, 1);
-    mbar_init(bar_mma2, p.use_o ? 2 : 1);          // one arrival per issuing thread
+    mbar_init(bar_mma2, use_o ? 2 : 1);            // one arrival per issuing thread
     mbar_init_fence();
     *s_abort = 0;
     tma_prefetch_desc(&p.tm_w); tma_prefetch_desc(&p.tm_qg); tma_prefetch_desc(&p.tm_kg);
@@ -105,73 +157,80 @@ __global__ void __launch_bounds__(kStateThreads) kda_state_fwd_tc_kernel(const _
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
   const uint32_t lane_off = (uint32_t)(32 * quad) << 16;
-  // state: columns 0..127; D1 = [w h ; qg h + Aqk v_new]: two buffers at columns 128 and 256, so the
+  // state: columns 0..N-1; D1 = [w h ; qg h + Aqk v_new]: two buffers at columns 128 and 256, so the
   // output rows of chunk c leave while the products of chunk c + 1 run
-  const uint32_t tDh = tmem + lane_off + 64 * half;
-  auto tD1 = [&](int c) { return tmem + 128 + 128 * (c & 1) + lane_off + 64 * half; };
+  const uint32_t tDh = tmem + lane_off + col0;
+  auto tD1 = [&](int c) { return tmem + 128 + 128 * (c & 1) + lane_off + col0; };
 
   auto chunk_valid = [&](int c) {
     int64_t rem = eos - (bos + (int64_t)c * 64);
     return rem >= 64 ? 64 : (int)rem;
   };
-  auto issue_stage = [&](int c) {   // thread 0 only
+  auto issue_stage = [&](int c) {   // one thread
     unsigned char* st = smem + (c & 1) * kStageBytes;
     uint64_t* bar = &bar_full[c & 1];
     const int y = (int)(bos + (int64_t)c * 64);
     const int x = head * D;
     uint32_t bytes = 2 * 8192 + 2 * 8192;                       // w, kg
-    if (p.use_u) bytes += 2 * 8192;
-    if (p.use_o) bytes += 2 * 8192 + 8192;                       // qg, Aqk
+    if (use_u) bytes += NB * 8192;
+    if (use_o) bytes += 2 * 8192 + 8192;                         // qg, Aqk
     mbar_expect_tx(bar, bytes);
     for (int b = 0; b < 2; ++b) {
       tma_load_2d(st + StateTcLayout::A1 + b * 16384, &p.tm_w, x + 64 * b, y, bar);
       tma_load_2d(st + StateTcLayout::KG + b * 8192, &p.tm_kg, x + 64 * b, y, bar);
-      if (p.use_u) tma_load_2d(st + StateTcLayout::U + b * 8192, &p.tm_u, x + 64 * b, y, bar);
-      if (p.use_o) tma_load_2d(st + StateTcLayout::A1 + b * 16384 + 8192, &p.tm_qg, x + 64 * b, y, bar);
+      if (use_o) tma_load_2d(st + StateTcLayout::A1 + b * 16384 + 8192, &p.tm_qg, x + 64 * b, y, bar);
     }
-    if (p.use_o) tma_load_2d(st + StateTcLayout::A2 + 8192, &p.tm_aqk, head * 64, y, bar);
+    if (use_u)
+      for (int b = 0; b < NB; ++b)     // the 64-column box(es) that hold the slice
+        tma_load_2d(st + StateTcLayout::U + b * 8192, &p.tm_u, x + 64 * ((v0 >> 6) + b), y, bar);
+    if (use_o) tma_load_2d(st + StateTcLayout::A2 + 8192, &p.tm_aqk, head * 64, y, bar);
   };
 
   if (tid == 64) {      // the TMA producer: lane 0 of a warp that is off the critical v_new path
     if (nchunks > 0) issue_stage(0);
     if (nchunks > 1) issue_stage(1);
   }
-  // initial state -> tensor memory (this thread owns 64 columns of state row `row`)
+  // initial state -> tensor memory (this thread owns NC columns of state row `row`)
   {
-    float x[32];
+    float x[16];
 #pragma unroll 1
-    for (int cb = 0; cb < 2; ++cb) {
+    for (int cb = 0; cb < NC / 16; ++cb) {
+      const int vcol = v0 + col0 + 16 * cb;
 #pragma unroll
-      for (int i = 0; i < 32; i += 4) {
+      for (int i = 0; i < 16; i += 4) {
         float4 v4 = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (p.h0)
-          v4 = *reinterpret_cast<const float4*>(p.h0 + sbase + (int64_t)row * D + 64 * half + 32 * cb + i);
+        if (trans) {
+          v4.x = row == vcol + i ? 1.f : 0.f; v4.y = row == vcol + i + 1 ? 1.f : 0.f;
+          v4.z = row == vcol + i + 2 ? 1.f : 0.f; v4.w = row == vcol + i + 3 ? 1.f : 0.f;
+        } else if (p.h0) {
+          v4 = *reinterpret_cast<const float4*>(p.h0 + sbase + (int64_t)row * D + vcol + i);
+        }
         x[i] = v4.x; x[i + 1] = v4.y; x[i + 2] = v4.z; x[i + 3] = v4.w;
       }
-      tmem_st32(tDh + 32 * cb, x);
+      tmem_st16(tDh + 16 * cb, x);
     }
     tmem_st_wait();
   }
-  const uint32_t idesc_kmn = instr_desc(128, 128, 0, 1);
-  const uint32_t idesc_mnmn = instr_desc(128, 128, 1, 1);
+  const uint32_t idesc_kmn = instr_desc(128, N, 0, 1);
+  const uint32_t idesc_mnmn = instr_desc(128, N, 1, 1);
   const uint32_t sH = saddr(smem + StateTcLayout::H), sVN = saddr(smem + StateTcLayout::VN);
   bool failed = false;
 
-  // Output rows of chunk c (threads of lane quadrants 2, 3 = D1 rows 64..127), 64 columns each:
+  // Output rows of chunk c (threads of lane quadrants 2, 3 = D1 rows 64..127), NC columns each:
   // into the staging tile (a full chunk, which then leaves with a TMA store) or straight to global
-  // memory (the last chunk of the sequence, which may be partial).
+  // memory (the last chunk of the sequence, which may be partial; every chunk of a narrow slice).
   auto store_o = [&](int c, bool staged) {
     const int64_t token0 = bos + (int64_t)c * 64;
     const bool live = row - 64 < chunk_valid(c);
-    bf16* orow = p.o + ((token0 + (live ? row - 64 : 0)) * H + head) * D + 64 * half;
-    unsigned char* obox = smem + StateTcLayout::OST + half * 8192;
-    float x[64];
-    tmem_ld64(tD1(c), x);
+    bf16* orow = p.o + ((token0 + (live ? row - 64 : 0)) * H + head) * D + v0 + col0;
+    float x[NC];
+    tmem_ld_n<NC>(tD1(c), x);
 #pragma unroll
-    for (int qd = 0; qd < 8; ++qd) {
+    for (int qd = 0; qd < NC / 8; ++qd) {
       uint4 v;
       pack8(x + 8 * qd, v);
-      if (staged) *reinterpret_cast<uint4*>(obox + sw128_chunk(row - 64, qd)) = v;
+      if (staged && kTileStore)
+        *reinterpret_cast<uint4*>(smem + StateTcLayout::OST + tile_off(row - 64, col0 + 8 * qd, 8192)) = v;
       else if (live) *reinterpret_cast<uint4*>(orow + 8 * qd) = v;
     }
   };
@@ -179,6 +238,7 @@ __global__ void __launch_bounds__(kStateThreads) kda_state_fwd_tc_kernel(const _
   float glast = 0.f;
   if (nchunks > 0)
     glast = p.g[((bos + chunk_valid(0) - 1) * H + head) * D + row];
+  int zero_from = nchunks;     // transition walk: first chunk that the (all-zero) running transition enters
 
   for (int c = 0; c < nchunks; ++c) {
     unsigned char* st = smem + (c & 1) * kStageBytes;
@@ -189,36 +249,51 @@ __global__ void __launch_bounds__(kStateThreads) kda_state_fwd_tc_kernel(const _
       glast = p.g[((token0 + 64 + chunk_valid(c + 1) - 1) * H + head) * D + row];
 
     st_mark(p.prof, c, 0);
-    // ---- a. h row -> bf16 B tile (MN-major: rows kappa, boxes = 64-wide v halves); decay in place
+    bool nonzero = false;
+    // ---- a. h row -> bf16 B tile (MN-major: rows kappa, 64-wide v boxes); decay in place
     {
-      float x[64];
-      unsigned char* box = smem + StateTcLayout::H + half * 16384;
-      tmem_ld64(tDh, x);
+      float x[NC];
+      tmem_ld_n<NC>(tDh, x);
+      if (trans) {
 #pragma unroll
-      for (int qd = 0; qd < 8; ++qd) {
-        uint4 v;
-        pack8(x + 8 * qd, v);
-        *reinterpret_cast<uint4*>(box + sw128_chunk(row, qd)) = v;
+        for (int i = 0; i < NC; ++i) nonzero |= x[i] != 0.f;
       }
 #pragma unroll
-      for (int i = 0; i < 64; ++i) x[i] *= dec;
-      tmem_st64(tDh, x);
+      for (int qd = 0; qd < NC / 8; ++qd) {
+        uint4 v;
+        pack8(x + 8 * qd, v);
+        *reinterpret_cast<uint4*>(smem + StateTcLayout::H + tile_off(row, col0 + 8 * qd, 16384)) = v;
+        if (!kTileStore && h_out)
+          *reinterpret_cast<uint4*>(h_out + (((int64_t)(chunk0 + c) * H + head) * D + row) * D + v0 + col0 +
+                                    8 * qd) = v;
+      }
+#pragma unroll
+      for (int i = 0; i < NC; ++i) x[i] *= dec;
+      tmem_st_n<NC>(tDh, x);
       tmem_st_wait();
     }
     st_mark(p.prof, c, 1);
     if (tid == 0) tma_store_wait_read();    // v_new / output staging of the previous chunk are free again
     fence_async_smem();
     tc_fence_before();
-    __syncthreads();
+    int any = 1;
+    if (trans) any = __syncthreads_or(nonzero); else __syncthreads();
     st_mark(p.prof, c, 2);
     if (*s_abort) { failed = true; break; }
+    if (!any) {
+      // the transition is exactly zero from here on; let the tile loads in flight land before leaving
+      zero_from = c;
+      if (!mbar_wait(&bar_full[c & 1], (c >> 1) & 1)) failed = true;
+      if (c + 1 < nchunks && !mbar_wait(&bar_full[(c + 1) & 1], ((c + 1) >> 1) & 1)) failed = true;
+      break;
+    }
 
     // ---- b. D1 = [w ; qg] h ;  the bf16 state tile also leaves as h[c] (kept for the backward pass)
     if (tid == 0) {
-      if (p.h_out) {
+      if (kTileStore && h_out) {
         const int yh = ((chunk0 + c) * H + head) * D;
-        tma_store_2d(&p.tm_hout, smem + StateTcLayout::H, 0, yh);
-        tma_store_2d(&p.tm_hout, smem + StateTcLayout::H + 16384, 64, yh);
+        for (int b = 0; b < NB; ++b)
+          tma_store_2d(&p.tm_hout, smem + StateTcLayout::H + b * 16384, v0 + 64 * b, yh);
         tma_store_commit();
       }
       st_mark(p.prof, c, 10);
@@ -241,16 +316,14 @@ __global__ void __launch_bounds__(kStateThreads) kda_state_fwd_tc_kernel(const _
       if (!mbar_wait(bar_mma1, c & 1)) *s_abort = 1;
       tc_fence_after();
       st_mark(p.prof, c, 4);
-      float x[64];
-      const unsigned char* ubox = st + StateTcLayout::U + half * 8192;
-      unsigned char* vbox = smem + StateTcLayout::VN + half * 8192;
-      tmem_ld64(tD1(c), x);
+      float x[NC];
+      tmem_ld_n<NC>(tD1(c), x);
 #pragma unroll
-      for (int qd = 0; qd < 8; ++qd) {
-        const int off = sw128_chunk(row, qd);
+      for (int qd = 0; qd < NC / 8; ++qd) {
+        const int col = col0 + 8 * qd;
         float y[8];
-        if (p.use_u) {
-          uint4 u4 = *reinterpret_cast<const uint4*>(ubox + off);
+        if (use_u) {
+          uint4 u4 = *reinterpret_cast<const uint4*>(st + StateTcLayout::U + tile_off(row, ucol0 + col, 8192));
           float2 a = unpack_bf16(u4.x), b = unpack_bf16(u4.y), cc = unpack_bf16(u4.z),
                  d = unpack_bf16(u4.w);
           y[0] = a.x; y[1] = a.y; y[2] = b.x; y[3] = b.y; y[4] = cc.x; y[5] = cc.y; y[6] = d.x; y[7] = d.y;
@@ -262,20 +335,21 @@ __global__ void __launch_bounds__(kStateThreads) kda_state_fwd_tc_kernel(const _
         for (int i = 0; i < 8; ++i) y[i] = row < valid ? y[i] - x[8 * qd + i] : 0.f;
         uint4 v;
         pack8(y, v);
-        *reinterpret_cast<uint4*>(vbox + off) = v;
-        if (p.vnew_out && valid < 64 && row < valid)     // a partial chunk cannot use the tile store
-          *reinterpret_cast<uint4*>(p.vnew_out + ((token0 + row) * H + head) * D + 64 * half + 8 * qd) = v;
+        *reinterpret_cast<uint4*>(smem + StateTcLayout::VN + tile_off(row, col, 8192)) = v;
+        // a partial chunk and a narrow slice cannot use the tile store
+        if (vnew_out && (!kTileStore || valid < 64) && row < valid)
+          *reinterpret_cast<uint4*>(vnew_out + ((token0 + row) * H + head) * D + v0 + col) = v;
       }
     } else {
       if (valid < 64) {
         // rows >= valid of the kg tile hold another sequence's tokens (or unwritten memory)
-        for (int idx = (quad - 2) * 32 + lid + 64 * half; idx < (64 - valid) * 16; idx += 128) {
+        for (int idx = (quad - 2) * 32 + lid + 64 * sub; idx < (64 - valid) * 16; idx += 128) {
           int r = valid + (idx >> 4), ch = idx & 15;
           *reinterpret_cast<uint4*>(st + StateTcLayout::KG + (ch >> 3) * 8192 + sw128_chunk(r, ch & 7)) =
               make_uint4(0, 0, 0, 0);
         }
       }
-      if (p.use_o && c > 0) store_o(c - 1, true);
+      if (use_o && c > 0) store_o(c - 1, true);
     }
     st_mark(p.prof, c, 5);
     if (tid == 0) tma_store_wait_read();    // the state tile is rewritten after the next barrier
@@ -288,16 +362,16 @@ __global__ void __launch_bounds__(kStateThreads) kda_state_fwd_tc_kernel(const _
     // ---- d. h += kg^T v_new (thread 0);  D1 += [0 ; Aqk] v_new (thread 32); v_new and the previous
     //         chunk's output rows leave
     if (tid == 0) {
-      const int x0 = head * D;
-      if (p.vnew_out && valid == 64) {
-        tma_store_2d(&p.tm_vnew, smem + StateTcLayout::VN, x0, (int)token0);
-        tma_store_2d(&p.tm_vnew, smem + StateTcLayout::VN + 8192, x0 + 64, (int)token0);
+      const int x0 = head * D + v0;
+      if (kTileStore) {
+        if (vnew_out && valid == 64)
+          for (int b = 0; b < NB; ++b)
+            tma_store_2d(&p.tm_vnew, smem + StateTcLayout::VN + b * 8192, x0 + 64 * b, (int)token0);
+        if (use_o && c > 0)
+          for (int b = 0; b < NB; ++b)
+            tma_store_2d(&p.tm_o, smem + StateTcLayout::OST + b * 8192, x0 + 64 * b, (int)token0 - 64);
+        tma_store_commit();
       }
-      if (p.use_o && c > 0) {
-        tma_store_2d(&p.tm_o, smem + StateTcLayout::OST, x0, (int)token0 - 64);
-        tma_store_2d(&p.tm_o, smem + StateTcLayout::OST + 8192, x0 + 64, (int)token0 - 64);
-      }
-      tma_store_commit();
       tc_fence_after();
       const uint32_t kg = saddr(st + StateTcLayout::KG);
 #pragma unroll
@@ -305,7 +379,7 @@ __global__ void __launch_bounds__(kStateThreads) kda_state_fwd_tc_kernel(const _
         umma(tmem, desc_mnmajor(kg, ks, 8192), desc_mnmajor(sVN, ks, 8192), idesc_mnmn, 1);
       umma_commit(bar_mma2);
       st_mark(p.prof, c, 7);
-    } else if (tid == 32 && p.use_o) {
+    } else if (tid == 32 && use_o) {
       tc_fence_after();
       const uint32_t a2 = saddr(st + StateTcLayout::A2);
 #pragma unroll
@@ -319,17 +393,18 @@ __global__ void __launch_bounds__(kStateThreads) kda_state_fwd_tc_kernel(const _
     if (tid == 64 && c + 2 < nchunks) issue_stage(c + 2);
     st_mark(p.prof, c, 9);
   }
-  if (!failed && p.use_o && nchunks > 0 && quad >= 2) store_o(nchunks - 1, false);
+  if (!failed && use_o && nchunks > 0 && quad >= 2) store_o(nchunks - 1, false);
   if (tid == 0) tma_store_wait_read();
+  if (!failed && trans && p.limit_out && tid == 0) atomicMax(p.limit_out + item, zero_from);
 
-  if (!failed && p.ht) {
-    float x[32];
+  if (!failed && ht) {
+    float x[16];
 #pragma unroll 1
-    for (int cb = 0; cb < 2; ++cb) {
-      tmem_ld32(tDh + 32 * cb, x);
+    for (int cb = 0; cb < NC / 16; ++cb) {
+      tmem_ld16(tDh + 16 * cb, x);
 #pragma unroll
-      for (int i = 0; i < 32; i += 4)
-        *reinterpret_cast<float4*>(p.ht + sbase + (int64_t)row * D + 64 * half + 32 * cb + i) =
+      for (int i = 0; i < 16; i += 4)
+        *reinterpret_cast<float4*>(ht + sbase + (int64_t)row * D + v0 + col0 + 16 * cb + i) =
             make_float4(x[i], x[i + 1], x[i + 2], x[i + 3]);
     }
   }
@@ -341,9 +416,23 @@ __global__ void __launch_bounds__(kStateThreads) kda_state_fwd_tc_kernel(const _
 
 static __device__ int g_state_tc_error = 0;
 
+template <int NS>
+static int launch_state_fwd_split(const StateTcParams& p, int64_t ctas, cudaStream_t s) {
+  const int smem = StateTcLayout::TOTAL + 1024;
+  if (cudaFuncSetAttribute(kda_state_fwd_tc_kernel<NS>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
+      cudaSuccess)
+    return KDA_ERR_LAUNCH;
+  StageScope timing(kStageStateFwd, s);
+  kda_state_fwd_tc_kernel<NS><<<(unsigned)(ctas * NS), kStateThreads, smem, s>>>(p);
+  return cudaGetLastError() == cudaSuccess ? KDA_OK : KDA_ERR_LAUNCH;
+}
+
 // ---- host side: tensor maps --------------------------------------------------------------------
+// trans_out != NULL adds a second set of CTAs that walk the same chains with u = 0 from an identity
+// state and write the dense slice transition [nseq, H, 128, 128] there, in the same launch.
 int launch_state_fwd_tc(const bf16* w, const bf16* u, const bf16* kg, const bf16* qg, const bf16* aqk,
-                        const float* g, const float* h0, float* ht, bf16* o, bf16* h_out,
+                        const float* g, const float* h0, float* ht, float* trans_out,
+                        const int32_t* limit_in, int32_t* limit_out, bf16* o, bf16* h_out,
                         bf16* vnew_out, const int32_t* cu, const int32_t* co, int nseq, int H,
                         int64_t tokens, int chunks, cudaStream_t s) {
   if (nseq == 0) return KDA_OK;
@@ -364,17 +453,17 @@ int launch_state_fwd_tc(const bf16* w, const bf16* u, const bf16* kg, const bf16
   if (!make_tensor_map(&p.tm_hout, h_out ? h_out : w, h_out ? (int64_t)chunks * H * D : tokens,
                        h_out ? D : cols, 128))
     return KDA_ERR_LAUNCH;
-  p.g = g; p.h0 = h0; p.ht = ht; p.o = o; p.h_out = h_out; p.vnew_out = vnew_out;
+  p.g = g; p.h0 = h0; p.ht = ht; p.trans_out = trans_out; p.limit_in = limit_in; p.limit_out = limit_out;
+  p.o = o; p.h_out = h_out; p.vnew_out = vnew_out;
   p.cu_seqlens = cu; p.chunk_offsets = co; p.error = error; p.nseq = nseq; p.H = H;
   p.use_u = u != nullptr; p.use_o = o != nullptr;
   p.prof = debug_profile_buffer();
-  const int smem = StateTcLayout::TOTAL + 1024;
-  if (cudaFuncSetAttribute(kda_state_fwd_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
-      cudaSuccess)
-    return KDA_ERR_LAUNCH;
-  StageScope timing(kStageStateFwd, s);
-  kda_state_fwd_tc_kernel<<<(unsigned)(nseq * H), kStateThreads, smem, s>>>(p);
-  return cudaGetLastError() == cudaSuccess ? KDA_OK : KDA_ERR_LAUNCH;
+  const int64_t ctas = (int64_t)nseq * H * (trans_out ? 2 : 1);
+  switch (pick_value_split(ctas)) {
+    case 4: return launch_state_fwd_split<4>(p, ctas, s);
+    case 2: return launch_state_fwd_split<2>(p, ctas, s);
+    default: return launch_state_fwd_split<1>(p, ctas, s);
+  }
 }
 
 
@@ -404,7 +493,13 @@ struct StateBwdLayout {
   static constexpr int TOTAL = BAR + 1024;
 };
 
+// NS CTAs share a chain, each owning N = 128 / NS value columns of dh, dO and dv2 (see the forward kernel).
+template <int NS>
 __global__ void __launch_bounds__(kStateThreads) kda_state_bwd_tc_kernel(const __grid_constant__ StateBwdTcParams p) {
+  constexpr int N = D / NS;
+  constexpr int NC = N / 2;
+  constexpr int NB = (N + 63) / 64;
+  constexpr bool kTileStore = N >= 64;
   extern __shared__ unsigned char smem_dyn[];
   unsigned char* smem = smem_dyn + ((1024u - (saddr(smem_dyn) & 1023u)) & 1023u);
   uint64_t* bar_full = reinterpret_cast<uint64_t*>(smem + StateBwdLayout::BAR);
@@ -414,10 +509,13 @@ __global__ void __launch_bounds__(kStateThreads) kda_state_bwd_tc_kernel(const _
   volatile int* s_abort = reinterpret_cast<volatile int*>(bar_full + 5);
 
   const int tid = threadIdx.x, warp = tid >> 5, lid = tid & 31;
-  const int quad = warp & 3, half = warp >> 2;     // TMEM lane quadrant; 64-column half of the tiles
+  const int quad = warp & 3, sub = warp >> 2;      // TMEM lane quadrant; which half of the slice columns
   const int row = 32 * quad + lid;                 // TMEM lane = state row kappa
   const int H = p.H;
-  const int head = blockIdx.x % H, seq = blockIdx.x / H;
+  const int item = blockIdx.x / NS, slice = blockIdx.x % NS;
+  const int head = item % H, seq = item / H;
+  const int v0 = slice * N, col0 = sub * NC;
+  const int dcol0 = N < 64 ? (v0 & 63) : 0;        // where the slice starts inside the loaded dO box
   const int64_t bos = p.cu_seqlens[seq], eos = p.cu_seqlens[seq + 1];
   const int chunk0 = p.chunk_offsets[seq];
   const int nchunks = p.chunk_offsets[seq + 1] - chunk0;
@@ -435,25 +533,26 @@ __global__ void __launch_bounds__(kStateThreads) kda_state_bwd_tc_kernel(const _
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
   const uint32_t lane_off = (uint32_t)(32 * quad) << 16;
-  const uint32_t tDh = tmem + lane_off + 64 * half, tDv = tmem + 128 + lane_off + 64 * half;
+  const uint32_t tDh = tmem + lane_off + col0, tDv = tmem + 128 + lane_off + col0;
 
   auto chunk_valid = [&](int c) {
     int64_t rem = eos - (bos + (int64_t)c * 64);
     return rem >= 64 ? 64 : (int)rem;
   };
-  auto issue_stage = [&](int it) {   // thread 0 only; iteration `it` handles chunk nchunks-1-it
+  auto issue_stage = [&](int it) {   // one thread; iteration `it` handles chunk nchunks-1-it
     const int c = nchunks - 1 - it;
     unsigned char* st = smem + (it & 1) * kBStageBytes;
     uint64_t* bar = &bar_full[it & 1];
     const int y = (int)(bos + (int64_t)c * 64);
     const int x = head * D;
-    mbar_expect_tx(bar, kBStageBytes);
+    mbar_expect_tx(bar, 3 * 16384 + NB * 8192 + 8192);
     for (int b = 0; b < 2; ++b) {
       tma_load_2d(st + StateBwdLayout::KG + b * 8192, &p.tm_kg, x + 64 * b, y, bar);
       tma_load_2d(st + StateBwdLayout::W + b * 8192, &p.tm_w, x + 64 * b, y, bar);
       tma_load_2d(st + StateBwdLayout::QG + b * 8192, &p.tm_qg, x + 64 * b, y, bar);
-      tma_load_2d(st + StateBwdLayout::DO + b * 8192, &p.tm_do, x + 64 * b, y, bar);
     }
+    for (int b = 0; b < NB; ++b)     // the 64-column box(es) of dO that hold the slice
+      tma_load_2d(st + StateBwdLayout::DO + b * 8192, &p.tm_do, x + 64 * ((v0 >> 6) + b), y, bar);
     tma_load_2d(st + StateBwdLayout::AQK, &p.tm_aqk, head * 64, y, bar);
   };
   if (tid == 64) {      // the TMA producer: lane 0 of a warp of its own
@@ -461,17 +560,17 @@ __global__ void __launch_bounds__(kStateThreads) kda_state_bwd_tc_kernel(const _
     if (nchunks > 1) issue_stage(1);
   }
   {
-    float x[32];
+    float x[16];
 #pragma unroll 1
-    for (int cb = 0; cb < 2; ++cb) {
+    for (int cb = 0; cb < NC / 16; ++cb) {
 #pragma unroll
-      for (int i = 0; i < 32; i += 4) {
+      for (int i = 0; i < 16; i += 4) {
         float4 v4 = make_float4(0.f, 0.f, 0.f, 0.f);
         if (p.dht)
-          v4 = *reinterpret_cast<const float4*>(p.dht + sbase + (int64_t)row * D + 64 * half + 32 * cb + i);
+          v4 = *reinterpret_cast<const float4*>(p.dht + sbase + (int64_t)row * D + v0 + col0 + 16 * cb + i);
         x[i] = v4.x; x[i + 1] = v4.y; x[i + 2] = v4.z; x[i + 3] = v4.w;
       }
-      tmem_st32(tDh + 32 * cb, x);
+      tmem_st16(tDh + 16 * cb, x);
     }
     tmem_st_wait();
   }
@@ -499,25 +598,28 @@ __global__ void __launch_bounds__(kStateThreads) kda_state_bwd_tc_kernel(const _
         const int off = (ch >> 3) * 8192 + sw128_chunk(r, ch & 7);
         *reinterpret_cast<uint4*>(st + StateBwdLayout::W + off) = make_uint4(0, 0, 0, 0);
         *reinterpret_cast<uint4*>(st + StateBwdLayout::QG + off) = make_uint4(0, 0, 0, 0);
-        *reinterpret_cast<uint4*>(st + StateBwdLayout::DO + off) = make_uint4(0, 0, 0, 0);
+        if (ch < 8 * NB)
+          *reinterpret_cast<uint4*>(st + StateBwdLayout::DO + off) = make_uint4(0, 0, 0, 0);
         if (ch < 8)
           *reinterpret_cast<uint4*>(st + StateBwdLayout::AQK + sw128_chunk(r, ch)) = make_uint4(0, 0, 0, 0);
       }
     }
     // ---- a. dh row -> bf16 B tile; decay in place ------------------------------------------------
     {
-      float x[64];
-      unsigned char* box = smem + StateBwdLayout::DH + half * 16384;
-      tmem_ld64(tDh, x);
+      float x[NC];
+      tmem_ld_n<NC>(tDh, x);
 #pragma unroll
-      for (int qd = 0; qd < 8; ++qd) {
+      for (int qd = 0; qd < NC / 8; ++qd) {
         uint4 v;
         pack8(x + 8 * qd, v);
-        *reinterpret_cast<uint4*>(box + sw128_chunk(row, qd)) = v;
+        *reinterpret_cast<uint4*>(smem + StateBwdLayout::DH + tile_off(row, col0 + 8 * qd, 16384)) = v;
+        if (!kTileStore)     // a narrow slice cannot use the tile store
+          *reinterpret_cast<uint4*>(p.dh_out + (((int64_t)(chunk0 + c) * H + head) * D + row) * D + v0 +
+                                    col0 + 8 * qd) = v;
       }
 #pragma unroll
-      for (int i = 0; i < 64; ++i) x[i] *= dec;
-      tmem_st64(tDh, x);
+      for (int i = 0; i < NC; ++i) x[i] *= dec;
+      tmem_st_n<NC>(tDh, x);
       tmem_st_wait();
     }
     if (tid == 0) tma_store_wait_read();    // the dv2 tile of the previous step is free again
@@ -527,46 +629,49 @@ __global__ void __launch_bounds__(kStateThreads) kda_state_bwd_tc_kernel(const _
     if (*s_abort) { failed = true; break; }
 
     // ---- b. dv2 = kg dh + Aqk^T dO ;  dh += qg^T dO ;  the bf16 dh tile leaves as dh[c] ------------------
+    // (the slice's dO columns start dcol0 columns into the loaded box: the operand descriptor starts there)
     if (tid == 0) {
-      const int yh = ((chunk0 + c) * H + head) * D;
-      tma_store_2d(&p.tm_dhout, smem + StateBwdLayout::DH, 0, yh);
-      tma_store_2d(&p.tm_dhout, smem + StateBwdLayout::DH + 16384, 64, yh);
-      tma_store_commit();
+      if (kTileStore) {
+        const int yh = ((chunk0 + c) * H + head) * D;
+        for (int b = 0; b < NB; ++b)
+          tma_store_2d(&p.tm_dhout, smem + StateBwdLayout::DH + b * 16384, v0 + 64 * b, yh);
+        tma_store_commit();
+      }
       tc_fence_after();
-      const uint32_t kg = saddr(st + StateBwdLayout::KG), dO = saddr(st + StateBwdLayout::DO),
+      const uint32_t kg = saddr(st + StateBwdLayout::KG), dO = saddr(st + StateBwdLayout::DO) + 2 * dcol0,
                      aqk = saddr(st + StateBwdLayout::AQK);
 #pragma unroll
       for (int ks = 0; ks < 8; ++ks)
         umma(tmem + 128, desc_kmajor(kg, ks, 8192), desc_mnmajor(sDH, ks, 16384),
-             instr_desc(64, 128, 0, 1), ks > 0);
+             instr_desc(64, N, 0, 1), ks > 0);
 #pragma unroll
       for (int ks = 0; ks < 4; ++ks)
-        umma(tmem + 128, desc_mnmajor(aqk, ks, 0), desc_mnmajor(dO, ks, 8192), instr_desc(64, 128, 1, 1), 1);
+        umma(tmem + 128, desc_mnmajor(aqk, ks, 0), desc_mnmajor(dO, ks, 8192), instr_desc(64, N, 1, 1), 1);
       umma_commit(bar_mma1);
     } else if (tid == 32) {
       tc_fence_after();
-      const uint32_t qg = saddr(st + StateBwdLayout::QG), dO = saddr(st + StateBwdLayout::DO);
+      const uint32_t qg = saddr(st + StateBwdLayout::QG), dO = saddr(st + StateBwdLayout::DO) + 2 * dcol0;
 #pragma unroll
       for (int ks = 0; ks < 4; ++ks)
-        umma(tmem, desc_mnmajor(qg, ks, 8192), desc_mnmajor(dO, ks, 8192), instr_desc(128, 128, 1, 1), 1);
+        umma(tmem, desc_mnmajor(qg, ks, 8192), desc_mnmajor(dO, ks, 8192), instr_desc(128, N, 1, 1), 1);
       umma_commit(bar_mma1);
     }
     if (!mbar_wait(bar_mma1, it & 1)) *s_abort = 1;
     tc_fence_after();
     // ---- c. dv2 rows (M = 64 accumulator: row j on lane 32 (j / 16) + j % 16) -----------------------
     {
-      float x[64];
+      float x[NC];
       const int j = quad * 16 + lid;
-      unsigned char* box = smem + StateBwdLayout::DV2 + half * 8192;
-      tmem_ld64(tDv, x);
+      tmem_ld_n<NC>(tDv, x);
       if (lid < 16) {
 #pragma unroll
-        for (int qd = 0; qd < 8; ++qd) {
+        for (int qd = 0; qd < NC / 8; ++qd) {
+          const int col = col0 + 8 * qd;
           uint4 v = make_uint4(0, 0, 0, 0);
           if (j < valid) pack8(x + 8 * qd, v);
-          *reinterpret_cast<uint4*>(box + sw128_chunk(j, qd)) = v;
-          if (valid < 64 && j < valid)        // a partial chunk cannot use the tile store
-            *reinterpret_cast<uint4*>(p.dv2_out + ((token0 + j) * H + head) * D + 64 * half + 8 * qd) = v;
+          *reinterpret_cast<uint4*>(smem + StateBwdLayout::DV2 + tile_off(j, col, 8192)) = v;
+          if ((!kTileStore || valid < 64) && j < valid)   // a partial chunk / narrow slice cannot use the tile store
+            *reinterpret_cast<uint4*>(p.dv2_out + ((token0 + j) * H + head) * D + v0 + col) = v;
         }
       }
     }
@@ -578,16 +683,16 @@ __global__ void __launch_bounds__(kStateThreads) kda_state_bwd_tc_kernel(const _
 
     // ---- d. dh -= w^T dv2 ;  dv2 leaves -----------------------------------------------------------------
     if (tid == 0) {
-      if (valid == 64) {
-        tma_store_2d(&p.tm_dv2out, smem + StateBwdLayout::DV2, head * D, (int)token0);
-        tma_store_2d(&p.tm_dv2out, smem + StateBwdLayout::DV2 + 8192, head * D + 64, (int)token0);
+      if (kTileStore && valid == 64) {
+        for (int b = 0; b < NB; ++b)
+          tma_store_2d(&p.tm_dv2out, smem + StateBwdLayout::DV2 + b * 8192, head * D + v0 + 64 * b, (int)token0);
         tma_store_commit();
       }
       tc_fence_after();
       const uint32_t w = saddr(st + StateBwdLayout::W);
 #pragma unroll
       for (int ks = 0; ks < 4; ++ks)
-        umma(tmem, desc_mnmajor(w, ks, 8192), desc_mnmajor(sDV2, ks, 8192), instr_desc(128, 128, 1, 1, 1), 1);
+        umma(tmem, desc_mnmajor(w, ks, 8192), desc_mnmajor(sDV2, ks, 8192), instr_desc(128, N, 1, 1, 1), 1);
       umma_commit(bar_mma2);
     }
     if (!mbar_wait(bar_mma2, it & 1)) *s_abort = 1;
@@ -597,13 +702,13 @@ __global__ void __launch_bounds__(kStateThreads) kda_state_bwd_tc_kernel(const _
   if (tid == 0) tma_store_wait_read();
 
   if (!failed && p.dh0) {
-    float x[32];
+    float x[16];
 #pragma unroll 1
-    for (int cb = 0; cb < 2; ++cb) {
-      tmem_ld32(tDh + 32 * cb, x);
+    for (int cb = 0; cb < NC / 16; ++cb) {
+      tmem_ld16(tDh + 16 * cb, x);
 #pragma unroll
-      for (int i = 0; i < 32; i += 4)
-        *reinterpret_cast<float4*>(p.dh0 + sbase + (int64_t)row * D + 64 * half + 32 * cb + i) =
+      for (int i = 0; i < 16; i += 4)
+        *reinterpret_cast<float4*>(p.dh0 + sbase + (int64_t)row * D + v0 + col0 + 16 * cb + i) =
             make_float4(x[i], x[i + 1], x[i + 2], x[i + 3]);
     }
   }
@@ -611,6 +716,17 @@ __global__ void __launch_bounds__(kStateThreads) kda_state_bwd_tc_kernel(const _
   tc_fence_before();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tmem, 256);
+}
+
+template <int NS>
+static int launch_state_bwd_split(const StateBwdTcParams& p, int64_t chains, cudaStream_t s) {
+  const int smem = StateBwdLayout::TOTAL + 1024;
+  if (cudaFuncSetAttribute(kda_state_bwd_tc_kernel<NS>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
+      cudaSuccess)
+    return KDA_ERR_LAUNCH;
+  StageScope timing(kStageStateBwd, s);
+  kda_state_bwd_tc_kernel<NS><<<(unsigned)(chains * NS), kStateThreads, smem, s>>>(p);
+  return cudaGetLastError() == cudaSuccess ? KDA_OK : KDA_ERR_LAUNCH;
 }
 
 int launch_state_bwd_tc(const bf16* w, const bf16* kg, const bf16* qg, const bf16* aqk, const bf16* dout,
@@ -631,13 +747,12 @@ int launch_state_bwd_tc(const bf16* w, const bf16* kg, const bf16* qg, const bf1
   p.error = nullptr;
   if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p.error), g_state_tc_error) != cudaSuccess)
     return KDA_ERR_LAUNCH;
-  const int smem = StateBwdLayout::TOTAL + 1024;
-  if (cudaFuncSetAttribute(kda_state_bwd_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
-      cudaSuccess)
-    return KDA_ERR_LAUNCH;
-  StageScope timing(kStageStateBwd, s);
-  kda_state_bwd_tc_kernel<<<(unsigned)(nseq * H), kStateThreads, smem, s>>>(p);
-  return cudaGetLastError() == cudaSuccess ? KDA_OK : KDA_ERR_LAUNCH;
+  const int64_t chains = (int64_t)nseq * H;
+  switch (pick_value_split(chains)) {
+    case 4: return launch_state_bwd_split<4>(p, chains, s);
+    case 2: return launch_state_bwd_split<2>(p, chains, s);
+    default: return launch_state_bwd_split<1>(p, chains, s);
+  }
 }
 
 }  // namespace kda
@@ -651,4 +766,12 @@ extern "C" int kda_device_error_word(void) {
   if (cudaMemcpyFromSymbol(&v, kda::g_state_tc_error, sizeof(int)) != cudaSuccess) return -1;
   cudaMemcpyToSymbol(kda::g_state_tc_error, &zero, sizeof(int));
   return v | (kda::bwd_chunk_tc_error_word() << 8) | (kda::prepare_tc_error_word() << 16);
+}
+
+// Forces the value split of the state recurrences (1, 2 or 4 CTAs per chain; 0 = choose from the
+// number of chains and SMs).  Every split gives the same bits; tests and tuning use this.
+extern "C" int kda_set_state_value_split(int split) {
+  if (split != 0 && split != 1 && split != 2 && split != 4) return KDA_ERR_ARG;
+  kda::g_value_split = split;
+  return KDA_OK;
 }

@@ -27,7 +27,6 @@ launch_count = 0
 _SIGNATURES = {
     "kda_b200_version": (c_int, []),
     "kda_device_error_word": (c_int, []),
-    "kda_debug_set_profile_buffer": (c_int, [c_void_p]),
     "kda_stage_count": (c_int, []),
     "kda_stage_name": (ctypes.c_char_p, [c_int]),
     "kda_stage_timing_enable": (c_int, [c_int]),
@@ -64,7 +63,9 @@ _SIGNATURES = {
     "kda_chunk_fwd_prepare": (c_int, [c_void_p] * 9 + [c_int, c_int64, c_int, c_int, c_void_p,
                                       c_int64, c_void_p]),
     "kda_chunk_fwd_state": (c_int, [c_void_p] * 7 + [c_int, c_int64, c_int, c_void_p, c_int,
-                                    c_void_p]),
+                                    c_void_p, c_void_p]),
+    "kda_chunk_slice_map": (c_int, [c_void_p] * 8 + [c_int, c_int64, c_int, c_void_p, c_void_p]),
+    "kda_set_state_value_split": (c_int, [c_int]),
     "kda_state_affine": (c_int, [c_void_p] * 4 + [c_int, c_int, c_int, c_void_p]),
     "kda_conv1d_fwd": (c_int, [c_void_p] * 4 + [c_int, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                c_int, c_void_p]),

@@ -6,10 +6,11 @@ eager fp32 PyTorch.  Neither ever falls back to the other.
 
 Differences from the reference, all widenings:
   * ``cu_seqlens`` may be int64 as well as int32;
-  * fp32 q/k/v given to ``chunk_kda(impl="fused")`` without autograd are evaluated by the exact
-    fp32 token scan instead of being rounded to bf16, for any K <= 256;
-  * ``chunk_kda(impl="fused")`` accepts only K = V = 128 on the bf16 chunked path, like the
-    reference's fused path.
+  * ``chunk_kda(impl="fused")`` runs the bf16 chunked kernels for K = V = 128 exactly as the
+    reference's fused path does (fp32 q/k/v are rounded to bf16, with or without autograd); fp32
+    inference inputs of any other head size up to 256, which the reference's fused path rejects,
+    are served by the exact fp32 token scan, and ``exact_fp32=True`` asks for that scan at
+    K = V = 128 too.  The scan is serial in T: meant for short sequences and accuracy checks.
 """
 
 from __future__ import annotations
@@ -45,7 +46,7 @@ def _per_token_gate(cumulative_gate, cu_seqlens):
 
 def chunk_kda(q, k, v, cumulative_gate, beta, initial_state=None, *, cu_seqlens=None,
               output_final_state=False, fastmath=False, autotune=True, impl=Impl.FUSED,
-              recompute=False):
+              recompute=False, exact_fp32=False):
     """Chunk-parallel KDA.
 
     q, k, cumulative_gate: ``[B, T, H, K]``; v: ``[B, T, H, V]``; beta: ``[B, T, H]``;
@@ -56,7 +57,9 @@ def chunk_kda(q, k, v, cumulative_gate, beta, initial_state=None, *, cu_seqlens=
     final state or None)``.  ``fastmath`` and ``autotune`` are accepted for signature
     compatibility; there is a single kernel configuration.  ``recompute`` (not in the reference,
     which always behaves as ``True``) makes the backward pass rebuild the forward intermediates
-    instead of keeping about 1.6 KiB per token and head between the two passes.
+    instead of keeping about 1.6 KiB per token and head between the two passes.  ``exact_fp32``
+    (not in the reference; inference only, fp32 inputs) evaluates the recurrence token by token in
+    fp32 instead of rounding the operands to bf16.
     """
     selected = resolve_impl(impl)
     if selected is Impl.REFERENCE and fastmath:
@@ -69,7 +72,11 @@ def chunk_kda(q, k, v, cumulative_gate, beta, initial_state=None, *, cu_seqlens=
                              output_final_state)
     tensors = (q, k, v, cumulative_gate, beta) + (() if initial_state is None else (initial_state,))
     needs_grad = torch.is_grad_enabled() and any(t.requires_grad for t in tensors)
-    if q.dtype == torch.float32 and q.is_cuda and not needs_grad and q.shape[-1] <= 256:
+    off_chunk_shape = q.shape[-1] != 128 or v.shape[-1] != 128
+    if exact_fp32 and (needs_grad or q.dtype != torch.float32):
+        raise ValueError("exact_fp32 needs float32 q, k, v and no autograd")
+    if (q.dtype == torch.float32 and q.is_cuda and not needs_grad and q.shape[-1] <= 256
+            and (exact_fp32 or off_chunk_shape)):
         # fp32-accurate path: the token scan on the per-token gate
         gate = _per_token_gate(cumulative_gate, cu_seqlens)
         return _fused_recurrent_forward(q, k, v, gate, beta, initial_state, cu_seqlens=cu_seqlens,

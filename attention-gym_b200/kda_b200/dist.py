@@ -8,11 +8,14 @@
   state [H, K, V] travels, along a point-to-point prefix chain (NCCL send/recv over NVLink):
 
       1. every rank, in parallel: the chunk-parallel part of its slice (pairwise products, solve,
-         w, u, kg, qg); middle ranks also run the recurrence from a zero state (-> b_r) and from an
-         identity state with u = 0 (-> M_r);
-      2. chain: recv h_in from rank r-1, h_out = M_r h_in + b_r, send to rank r+1 (the first rank
-         sends its true leaving state, the last rank only receives);
-      3. every rank, in parallel: the recurrence with the true h_in -> outputs.
+         w, u, kg, qg), then one launch that walks the slice from a zero state (-> b_r and the
+         outputs for a zero entering state) and, on other CTAs, from an identity state with u = 0
+         (-> M_r, and the number of chunks after which the running transition is exactly zero);
+         the first rank runs the plain recurrence with the true initial state instead;
+      2. chain: recv h_in from rank r-1, h_out = M_r h_in + b_r, send to rank r+1;
+      3. every rank, in parallel: the recurrence with the true h_in over the leading chunks that h_in
+         can still reach (all of them if the gates never forget completely), overwriting those
+         rows of the step-1 outputs.
 
 The backward pass runs the mirror-image chain (``cp_chunk_backward``): the gradient entering a
 slice from the right, ``dh_out``, maps affinely to the one leaving it on the left,
@@ -77,30 +80,53 @@ class CudaSlice:
                    _cabi.ptr(self.cu), _cabi.ptr(self.offsets), batch, batch * tokens, heads,
                    capacity, _cabi.ptr(self.ws), nbytes, _cabi.stream())
 
-    def _state(self, h_in, want_out, use_u):
+    def _state(self, h_in, out, use_u, want_final=True, limit=None):
         c = self._cabi
         batch, tokens, heads = self.shape
-        out = torch.empty_like(self.like_v) if want_out else None
-        final = torch.empty(batch, heads, 128, 128, dtype=torch.float32, device=self.gate.device)
+        final = (torch.empty(batch, heads, 128, 128, dtype=torch.float32, device=self.gate.device)
+                 if want_final else None)
         h_in = None if h_in is None else h_in.float().contiguous()
         c.call("kda_chunk_fwd_state", 1, c.ptr(self.gate), c.ptr(h_in), c.ptr(final), c.ptr(out),
                c.ptr(self.aqk), c.ptr(self.cu), c.ptr(self.offsets), batch, batch * tokens, heads,
-               c.ptr(self.ws), int(use_u), c.stream())
+               c.ptr(self.ws), int(use_u), c.ptr(limit), c.stream())
         return out, final
 
     def run(self, h_in):
         """(outputs, leaving state) for the entering state ``h_in`` (None = zeros)."""
-        return self._state(h_in, True, True)
+        return self._state(h_in, torch.empty_like(self.like_v), True)
 
     def zero_state_result(self):
         """b: the leaving state for a zero entering state."""
-        return self._state(None, False, True)[1]
+        return self._state(None, None, True)[1]
 
     def transition(self):
         """M [B, H, K, K]: the leaving state of the homogeneous recurrence started at identity."""
         batch, _, heads = self.shape
         eye = torch.eye(128, device=self.gate.device).expand(batch, heads, 128, 128).contiguous()
-        return self._state(eye, False, False)[1]
+        return self._state(eye, None, False)[1]
+
+    def slice_map(self, with_output=True):
+        """One launch for everything that does not depend on the entering state: (outputs for a zero
+        entering state or None, b, M, chunk limit).  Half of the CTAs walk the chains from a zero
+        state, the other half with u = 0 from an identity state; the latter stop once the running
+        transition is exactly zero and report after how many chunks that happened (int32 [B, H])."""
+        c = self._cabi
+        batch, tokens, heads = self.shape
+        dev = self.gate.device
+        b = torch.empty(batch, heads, 128, 128, dtype=torch.float32, device=dev)
+        trans = torch.empty_like(b)
+        out = torch.empty_like(self.like_v) if with_output else None
+        limit = torch.zeros(batch, heads, dtype=torch.int32, device=dev)
+        c.call("kda_chunk_slice_map", 1, c.ptr(self.gate), c.ptr(b), c.ptr(trans), c.ptr(out),
+               c.ptr(limit), c.ptr(self.aqk), c.ptr(self.cu), c.ptr(self.offsets), batch,
+               batch * tokens, heads, c.ptr(self.ws), c.stream())
+        return out, b, trans, limit
+
+    def correct(self, out, h_in, limit):
+        """Rewrite in ``out`` (outputs for a zero entering state) the leading chunks that the true
+        entering state ``h_in`` can still reach: the first ``limit`` chunks of every chain."""
+        self._state(h_in, out, True, want_final=False, limit=limit)
+        return out
 
     def affine(self, trans, h_in, b):
         c = self._cabi
@@ -111,12 +137,16 @@ class CudaSlice:
         return out
 
 
+class ChainTimeout(RuntimeError):
+    """A boundary state did not arrive from the neighbouring rank within the host deadline."""
+
+
 def _cp_forward(q, k, v, cumulative_gate, beta, initial_state=None, *, group=None,
-                     slice_factory: Callable = CudaSlice, rank: Optional[int] = None,
-                     world: Optional[int] = None, send: Optional[Callable] = None,
-                     recv: Optional[Callable] = None):
-    """cp_chunk_forward that also returns the entering state and the slice transition (middle ranks)."""
-    rank, world, send, recv = _resolve_p2p(group, rank, world, send, recv)
+                slice_factory: Callable = CudaSlice, rank: Optional[int] = None,
+                world: Optional[int] = None, send: Optional[Callable] = None,
+                recv: Optional[Callable] = None, timeout: Optional[float] = None):
+    """cp_chunk_forward that also returns the entering state and the slice transition."""
+    rank, world, send, recv = _resolve_p2p(group, rank, world, send, recv, timeout)
     last = rank + 1 == world
     if not last and q.shape[1] % 64:
         raise ValueError("every slice but the last must hold whole 64-token chunks")
@@ -126,48 +156,77 @@ def _cp_forward(q, k, v, cumulative_gate, beta, initial_state=None, *, group=Non
         if not last:
             send(h_out, 1)
         return out, h_out, initial_state, None
-    b = trans = None
-    if not last:                                                   # still step 1
-        b, trans = part.zero_state_result(), part.transition()
+    out, b, trans, limit = part.slice_map()                        # still step 1
     h_in = torch.empty(q.shape[0], q.shape[2], q.shape[3], v.shape[-1], dtype=torch.float32,
                        device=q.device)
     recv(h_in, rank - 1)                                           # step 2
+    h_out = part.affine(trans, h_in, b)
     if not last:
-        send(part.affine(trans, h_in, b), rank + 1)
-    out, h_out = part.run(h_in)                                    # step 3
+        send(h_out, rank + 1)
+    out = part.correct(out, h_in, limit)                           # step 3
     return out, h_out, h_in, trans
 
 
-def _resolve_p2p(group, rank, world, send, recv):
+def _resolve_p2p(group, rank, world, send, recv, timeout=None):
+    """Rank and size inside ``group`` plus send / recv callables that take group-local peer ranks.
+    ``timeout`` (seconds) puts a host deadline on every receive: ChainTimeout instead of a rank that
+    blocks forever on a neighbour that died."""
     if rank is None:
         import torch.distributed as dist
 
         rank, world = dist.get_rank(group), dist.get_world_size(group)
     if send is None:
+        import datetime
+        import time
+
         import torch.distributed as dist
 
+        def peer(r):      # torch's point-to-point calls take global ranks even with group=
+            return r if group is None else dist.get_global_rank(group, r)
+
         def send(t, dst):
-            dist.send(t, dst, group=group)
+            dist.send(t, peer(dst), group=group)
 
         def recv(t, src):
-            dist.recv(t, src, group=group)
+            if timeout is None:
+                dist.recv(t, peer(src), group=group)
+                return
+            work = dist.irecv(t, peer(src), group=group)
+            failure = f"no boundary state from rank {src} within {timeout} s"
+            if dist.get_backend(group) == "gloo":
+                # gloo completes a receive only inside wait(); its timed wait closes the pair when
+                # it runs out, so the group is good for nothing but tear-down afterwards
+                try:
+                    work.wait(timeout=datetime.timedelta(seconds=timeout))
+                except RuntimeError as exc:
+                    raise ChainTimeout(failure) from exc
+                return
+            deadline = time.monotonic() + timeout      # NCCL: completion is a CUDA event query
+            while not work.is_completed():
+                if time.monotonic() > deadline:
+                    raise ChainTimeout(failure)
+                time.sleep(0.0005)
+            work.wait()
     return rank, world, send, recv
 
 
 def cp_chunk_forward(q, k, v, cumulative_gate, beta, initial_state=None, *, group=None,
                      slice_factory: Callable = CudaSlice, rank: Optional[int] = None,
                      world: Optional[int] = None, send: Optional[Callable] = None,
-                     recv: Optional[Callable] = None):
+                     recv: Optional[Callable] = None, timeout: Optional[float] = None):
     """Context-parallel chunked forward of this rank's slice ``[1, T_local, H, 128]``.
 
     ``T_local`` must be a multiple of 64 on every rank but the last, so that slices hold whole
     chunks and the chunk-local cumulative gate needs no exchange.  ``initial_state`` is used on rank
     0 only.  Returns (local output, state leaving this slice); on the last rank the second result is
     the final state of the whole sequence.  Only boundary states are communicated:
-    ``send(tensor, dst)`` / ``recv(tensor, src)`` default to torch.distributed point-to-point calls.
+    ``send(tensor, dst)`` / ``recv(tensor, src)`` default to torch.distributed point-to-point calls
+    inside ``group`` (peer ranks are group-local).  ``timeout`` (seconds) bounds the host's wait for
+    the entering state; when it runs out the call raises ``ChainTimeout``.
     """
     return _cp_forward(q, k, v, cumulative_gate, beta, initial_state, group=group,
-                       slice_factory=slice_factory, rank=rank, world=world, send=send, recv=recv)[:2]
+                       slice_factory=slice_factory, rank=rank, world=world, send=send, recv=recv,
+                       timeout=timeout)[:2]
 
 
 def cuda_slice_grads(q, k, v, cumulative_gate, beta, h_in, d_out, dh_out):
@@ -255,4 +314,4 @@ def cp_chunk_kda(q, k, v, cumulative_gate, beta, initial_state=None, *, group=No
 
 
 __all__ = ["shard_ranges", "cp_chunk_forward", "cp_chunk_backward", "cp_chunk_kda",
-           "cuda_slice_grads", "CudaSlice"]
+           "cuda_slice_grads", "CudaSlice", "ChainTimeout"]

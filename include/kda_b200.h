@@ -39,17 +39,15 @@ extern "C" {
 /* Library identification: returns 100 * major + minor. */
 int kda_b200_version(void);
 
+/* 1 if a tensor-memory kernel abandoned a bounded barrier wait since the last call (clears the
+ * flag); synchronises the device.  For tests and debugging; no reference counterpart. */
+int kda_device_error_word(void);
+
 /* Optional per-kernel timing with CUDA events recorded on the launching stream (off by default).
  * kda_stage_timing_read synchronises the recorded events and fills launches[] / total_ms[] (arrays of
  * kda_stage_count() entries, indexed like kda_stage_name); reset != 0 clears the records.
  * No reference counterpart: the reference times stages with torch.profiler ranges
  * (attn_gym/linear/kda/utils.py:269-273). */
-/* 1 if a tensor-memory kernel abandoned a bounded barrier wait since the last call (clears the
- * flag); synchronises the device.  For tests and debugging; no reference counterpart. */
-int kda_device_error_word(void);
-/* Debugging aid: a device buffer of 64 x 32 int64 that receives per-phase %globaltimer stamps from
- * the backward chunk kernels (first 64 chunks of head 0); NULL switches it off. */
-int kda_debug_set_profile_buffer(void* buffer);
 int kda_stage_count(void);
 const char* kda_stage_name(int stage);
 int kda_stage_timing_enable(int on);
@@ -138,16 +136,21 @@ int kda_chunk_fwd(const void* q, const void* k, const void* v, const float* cum_
                   int nseq, int64_t tokens, int heads, int key_dim, int value_dim, int num_chunks,
                   void* workspace, int64_t workspace_bytes, void* stream);
 
-/* kda_chunk_fwd for callers that cannot allocate device memory (an inference server whose memory
- * pool already owns the whole GPU, a plugin that may not call cudaMalloc after start-up).  Same
- * arguments and results as kda_chunk_fwd without the workspace: the scratch is a static device
- * array of KDA_NOALLOC_SCRATCH_BYTES that every GPU loading the library keeps until exit.
+/* kda_chunk_fwd for callers that cannot allocate device memory while they run (an inference
+ * server whose memory pool already owns the whole GPU, a plugin that may not call cudaMalloc after
+ * start-up).  Same arguments and results as kda_chunk_fwd without the workspace: the scratch is a
+ * static device array of KDA_NOALLOC_SCRATCH_BYTES inside the library.
  * Limit: tokens * heads <= KDA_NOALLOC_SCRATCH_BYTES / 1024 (e.g. 1024 tokens x 32 heads), otherwise
  * KDA_ERR_SCRATCH.  The entry point calls no cudaMalloc / cudaFree or other allocating routine.
- * The first call on a device looks the array's device address up (cudaGetSymbolAddress with that
- * device current); make that first call before starting any stream capture.  All calls share the
- * array and it keeps the previous call's contents (nothing in it needs clearing); two calls whose
- * kernels overlap on the GPU -- different streams, different host threads -- race on it.
+ * First call on a device: CUDA loads device code lazily, so this call is what makes the device
+ * load the module that holds the array (the device keeps those bytes from then until the process
+ * exits) and looks the array's device address up (cudaGetSymbolAddress with that device current).
+ * Make it once per device during start-up -- before the host's own pool takes the remaining
+ * memory (afterwards the load fails and the call returns KDA_ERR_LAUNCH) and before any stream
+ * capture.  Later calls on that device touch no memory management at all.
+ * All calls share the array and it keeps the previous call's contents (nothing in it needs
+ * clearing); two calls whose kernels overlap on the GPU -- different streams, different host
+ * threads -- race on it.
  * It has no counterpart in the reference, whose operators allocate their intermediates with
  * torch. */
 #define KDA_NOALLOC_SCRATCH_BYTES (32 * 1024 * 1024)
@@ -199,7 +202,9 @@ int kda_chunk_bwd_saved(const void* q, const void* k, const void* v, const float
  * initial_state, final_state is the dense slice transition M [nseq, H, 128, 128] such that the state
  * leaving the slice is M h_in + b (context parallelism).  The reference fuses neither split nor
  * transition (kda/ops.py:78-89 `kda_delta_h` is its closest stage operator; docs/linear.md:220-222
- * leaves context parallelism to the caller). */
+ * leaves context parallelism to the caller).  chunk_limit (int32 [nseq, H] or NULL) cuts every walk
+ * short after that many chunks: only their rows of `out` are written, and final_state, if given,
+ * is the state after them. */
 int kda_chunk_fwd_prepare(const void* q, const void* k, const void* v, const float* cum_gate,
                           const float* beta, void* aqk, void* akk, const int32_t* cu_seqlens,
                           const int32_t* chunk_offsets, int nseq, int64_t tokens, int heads,
@@ -207,7 +212,30 @@ int kda_chunk_fwd_prepare(const void* q, const void* k, const void* v, const flo
 int kda_chunk_fwd_state(const float* cum_gate, const float* initial_state, float* final_state,
                         void* out, const void* aqk, const int32_t* cu_seqlens,
                         const int32_t* chunk_offsets, int nseq, int64_t tokens, int heads,
-                        void* workspace, int use_u, void* stream);
+                        void* workspace, int use_u, const int32_t* chunk_limit, void* stream);
+
+/* What a rank of the context-parallel chain computes while it waits for its entering state, in one
+ * launch over the workspace that kda_chunk_fwd_prepare filled: b_out = the state leaving the slice
+ * for a zero entering state and transition_out = the dense slice transition M, both
+ * [nseq, H, 128, 128] fp32 (then h_out = M h_in + b_out, kda_state_affine); optionally `out`, the
+ * outputs for a zero entering state, and chunk_limit_out (int32 [nseq, H], zero-initialised by the
+ * caller): the number of leading chunks after which the running transition is exactly zero in fp32.
+ * Past those chunks no entering state can change a bit of `out`, so the corrective pass
+ * (kda_chunk_fwd_state with the true entering state and chunk_limit = chunk_limit_out) only redoes
+ * the leading chunks; with gates that never forget completely the limit is the chunk count and the
+ * pass is a full one.  No reference counterpart (docs/linear.md:220-222 leaves context parallelism
+ * to the caller). */
+int kda_chunk_slice_map(const float* cum_gate, float* b_out, float* transition_out, void* out,
+                        int32_t* chunk_limit_out, const void* aqk, const int32_t* cu_seqlens,
+                        const int32_t* chunk_offsets, int nseq, int64_t tokens, int heads,
+                        void* workspace, void* stream);
+
+/* The serial state recurrences (forward and backward) run 1, 2 or 4 CTAs per (sequence, head),
+ * each owning 128 / split value columns of the state, so that a few long chains still fill the
+ * GPU; split = 0 (the default) chooses from the number of chains and SMs, as the reference picks
+ * its value tile (fwd/triton/chunk_delta_h.py:166, bwd/cute/chunk_delta_h_bwd_v1_dispatch.py:53-55).
+ * Every split gives the same bits.  Process-wide; for tests and tuning. */
+int kda_set_state_value_split(int split);
 
 /* h_out = transition * h_in + b for `count` independent [key_dim x value_dim] fp32 states
  * (transition: [count, key_dim, key_dim]); key_dim and value_dim multiples of 64.  Applies the

@@ -100,7 +100,14 @@ def recurrent_kda_ref(
 # --------------------------------------------------------------------------------------
 # chunked form  (reference: attn_gym/linear/kda/naive.py:99-241)
 # --------------------------------------------------------------------------------------
-def _chunk_intra(qc, kc, vc, gc, bc, sc):
+def _round_through(x, dtype):
+    """Round ``x`` to ``dtype`` and back; the gradient passes straight through the rounding."""
+    if dtype is None:
+        return x
+    return x + (x.detach().to(dtype).to(x.dtype) - x.detach())
+
+
+def _chunk_intra(qc, kc, vc, gc, bc, sc, store_dtype=None):
     """Intra-chunk quantities for a batch of chunks ``[..., C, D]`` (naive.py:111-131).
 
     Returns (Aqk, A, w, u, kg, qg, d_last) with
@@ -119,19 +126,25 @@ def _chunk_intra(qc, kc, vc, gc, bc, sc):
     a = torch.linalg.solve_triangular(eye + lower, eye.expand_as(lower).clone(), upper=False)
     aqk = (pq * sc).tril()
     gam = torch.exp2(gc)
-    w = a @ (kc * bc[..., None] * gam)
-    u = a @ (vc * bc[..., None])
+    a = _round_through(a, store_dtype)
+    w = a @ _round_through(kc * bc[..., None] * gam, store_dtype)
+    u = a @ _round_through(vc * bc[..., None], store_dtype)
     d_last = gc[..., -1, :]
     kg = kc * torch.exp2(d_last[..., None, :] - gc)
     qg = qc * gam * sc
     return aqk, a, w, u, kg, qg, d_last
 
 
-def _chunk_sequence(q, k, v, g, beta, state, sc, chunk, trace=None):
+def _chunk_sequence(q, k, v, g, beta, state, sc, chunk, trace=None, store_dtype=None):
     """One sequence ``[T, H, D]`` -> (o [T,H,V], final state [H,K,V]).
 
     Pads the tail chunk the way naive.py:196-201 does (zero q/k/v/beta, the last
     cumulative gate row repeated) so the padded rows neither write nor decay.
+
+    ``store_dtype`` (e.g. bfloat16) turns this into the *low-precision reference* of the
+    reference's stage tests (test/test_kda_kernels.py:722-756 ``_fwd_h_ref``, :141-156): the
+    intermediates a kernel pipeline stores in 16 bits -- Aqk, A, w, u, kg, qg, v_new and the
+    state as a matrix-product operand -- are rounded to that type, the fp32 state itself is not.
     """
     t, h, kd = q.shape
     vd = v.shape[-1]
@@ -152,20 +165,24 @@ def _chunk_sequence(q, k, v, g, beta, state, sc, chunk, trace=None):
     intra = []
     for c0 in range(0, n, group):
         sl = slice(c0, min(n, c0 + group))
-        intra.append(_chunk_intra(qc[:, sl], kc[:, sl], vc[:, sl], gc[:, sl], bc[:, sl], sc))
+        intra.append(_chunk_intra(qc[:, sl], kc[:, sl], vc[:, sl], gc[:, sl], bc[:, sl], sc,
+                                  store_dtype))
     aqk, a, w, u, kg, qg, d_last = (torch.cat([x[i] for x in intra], 1) for i in range(7))
+    if store_dtype is not None:
+        aqk, w, u, kg, qg = (_round_through(x, store_dtype) for x in (aqk, w, u, kg, qg))
     if trace is not None:
         trace.setdefault("intra", []).append(
             {"aqk": aqk, "akk": a, "w": w, "u": u, "kg": kg, "qg": qg})
     for c in range(n):
-        v_new = u[:, c] - w[:, c] @ state
+        operand = _round_through(state, store_dtype)
+        v_new = _round_through(u[:, c] - w[:, c] @ operand, store_dtype)
         if trace is not None:
             if state.requires_grad:
                 state.retain_grad()
                 v_new.retain_grad()
             trace.setdefault("h", []).append(state)
             trace.setdefault("v_new", []).append(v_new)
-        outs.append(qg[:, c] @ state + aqk[:, c] @ v_new)
+        outs.append(qg[:, c] @ operand + aqk[:, c] @ v_new)
         state = state * torch.exp2(d_last[:, c])[..., None] + kg[:, c].transpose(-1, -2) @ v_new
     o = torch.stack(outs, 1).reshape(h, n * chunk, vd).permute(1, 0, 2)[:t]
     return o, state
@@ -182,6 +199,7 @@ def chunk_kda_ref(
     scale: Optional[float] = None,
     chunk_size: int = CHUNK,
     trace: Optional[dict] = None,
+    store_dtype: Optional[torch.dtype] = None,
 ) -> Tuple[torch.Tensor, torch.Tensor]:
     """Chunk-parallel KDA from the chunk-local cumulative log2 gate; differentiable.
 
@@ -215,7 +233,7 @@ def chunk_kda_ref(
             continue
         o, s1 = _chunk_sequence(
             qf[row, bos:eos], kf[row, bos:eos], vf[row, bos:eos], gf[row, bos:eos],
-            bf[row, bos:eos], s0, sc, chunk_size, trace,
+            bf[row, bos:eos], s0, sc, chunk_size, trace, store_dtype,
         )
         rows[row].append(o)
         cursor[row] = eos
@@ -229,7 +247,8 @@ def chunk_kda_ref(
 
 
 def chunk_kda_grads_ref(q, k, v, cumulative_gate, beta, d_output, initial_state=None,
-                        d_final_state=None, cu_seqlens=None, dtype=torch.float64):
+                        d_final_state=None, cu_seqlens=None, dtype=torch.float64, trace=None,
+                        store_dtype=None):
     """Gradients of :func:`chunk_kda_ref` by autograd in ``dtype``.
 
     Returns dict(o, state, dq, dk, dv, dg, dbeta, dh0).  ``dg`` is the gradient with
@@ -238,7 +257,8 @@ def chunk_kda_grads_ref(q, k, v, cumulative_gate, beta, d_output, initial_state=
     """
     leaves = [x.detach().to(dtype).requires_grad_(True) for x in (q, k, v, cumulative_gate, beta)]
     h0 = None if initial_state is None else initial_state.detach().to(dtype).requires_grad_(True)
-    o, st = chunk_kda_ref(*leaves, initial_state=h0, cu_seqlens=cu_seqlens)
+    o, st = chunk_kda_ref(*leaves, initial_state=h0, cu_seqlens=cu_seqlens, trace=trace,
+                          store_dtype=store_dtype)
     loss = (o * d_output.to(dtype)).sum()
     if d_final_state is not None:
         loss = loss + (st * d_final_state.to(dtype)).sum()

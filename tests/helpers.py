@@ -36,3 +36,17 @@ def bf16_round(inp):
     for key in ("q", "k", "v"):
         out[key] = inp[key].bfloat16().float()
     return out
+
+
+def assert_budget(actual, golden, low_precision, name, dtype=torch.bfloat16):
+    """The reference's data-derived error budget (test/test_kda_kernels.py:141-156,
+    attn_gym/testing/kda.py:48-64): the kernel may be off the fp64 result by at most twice what an
+    independent low-precision evaluation of the same mathematics is off, plus a rounding band of
+    two ulps of ``dtype`` at the largest magnitude."""
+    g = golden.detach().double().cpu()
+    band = torch.finfo(dtype).eps * float(g.abs().max())
+    a_err = float((actual.detach().double().cpu() - g).abs().max())
+    r_err = float((low_precision.detach().double().cpu() - g).abs().max())
+    budget = 2.0 * r_err + 2.0 * band
+    assert a_err <= budget, (f"{name}: kernel error {a_err:.3e} exceeds budget {budget:.3e} "
+                             f"(low-precision reference error {r_err:.3e}, band {band:.3e})")

@@ -53,6 +53,13 @@ class OracleSlice:
             per_token[:, c0 + 1:c0 + 64] = gate[:, c0 + 1:c0 + 64] - gate[:, c0:min(t, c0 + 64) - 1]
         return orc.slice_transition_ref(k[0], per_token[0], beta[0])[None].float()
 
+    def slice_map(self):
+        out, b = self.run(None)
+        return out, b, self.transition(), None
+
+    def correct(self, out, h_in, limit):
+        return self.run(h_in)[0]
+
     def affine(self, trans, h_in, b):
         return trans @ h_in + b
 
@@ -155,3 +162,86 @@ def test_context_parallel_backward_chain_gloo(world):
         mp.spawn(_cp_bwd_worker, args=(world, port, ret), nprocs=world, join=True)
         for rank in range(world):
             assert ret[rank] < 2e-5, f"rank {rank}: gradient error {ret[rank]}"
+
+
+def _subgroup_worker(rank, world, port, ret):
+    """World of 4 = two independent context-parallel groups of 2 (ranks {0, 1} and {2, 3})."""
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "attention-gym_b200"))
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from kda_b200.dist import cp_chunk_forward
+        from oracle import kda_oracle as orc
+
+        torch.set_num_threads(1)
+        groups = [dist.new_group([0, 1]), dist.new_group([2, 3])]
+        mine = rank // 2
+        local = rank % 2
+        total = 64 * 2 * 2 + 17
+        inp = orc.make_inputs(1, total, 2, 16, 24, seed=40 + mine, with_state=True)   # other data per group
+        sl = slice(0, 128) if local == 0 else slice(128, total)
+        out, h_out = cp_chunk_forward(inp["q"][:, sl], inp["k"][:, sl], inp["v"][:, sl],
+                                      inp["cum_gate"][:, sl], inp["beta"][:, sl], inp["h0"],
+                                      group=groups[mine], slice_factory=OracleSlice, timeout=60.0)
+        ref_o, ref_s = orc.chunk_kda_ref(inp["q"].double(), inp["k"].double(), inp["v"].double(),
+                                         inp["cum_gate"].double(), inp["beta"].double(),
+                                         inp["h0"].double())
+        err_o = float((out.double() - ref_o[:, sl]).abs().max())
+        err_s = float((h_out.double() - ref_s).abs().max()) if local == 1 else 0.0
+        ret[rank] = (err_o, err_s)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_context_parallel_chain_inside_subgroups_gloo():
+    """Two context-parallel groups inside one world of four: boundary states must go to the
+    neighbour inside the group (group-local ranks are translated to global ones)."""
+    port = 29800 + (os.getpid() % 200)
+    with mp.Manager() as manager:
+        ret = manager.dict()
+        mp.spawn(_subgroup_worker, args=(4, port, ret), nprocs=4, join=True)
+        for rank in range(4):
+            err_o, err_s = ret[rank]
+            assert err_o < 1e-5 and err_s < 1e-5, f"rank {rank}: {err_o} {err_s}"
+
+
+def _timeout_worker(rank, world, port, ret):
+    """Rank 0 never sends its boundary state: rank 1 must give up with ChainTimeout instead of
+    blocking forever."""
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "attention-gym_b200"))
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    import time
+
+    from kda_b200.dist import ChainTimeout, cp_chunk_forward
+    from oracle import kda_oracle as orc
+
+    torch.set_num_threads(1)
+    inp = orc.make_inputs(1, 192, 1, 16, 24, seed=50)
+    if rank == 0:
+        time.sleep(4.0)                                      # a rank that hangs before its send
+        ret[0] = "idle"
+    else:
+        sl = slice(128, 192)
+        t0 = time.monotonic()
+        try:
+            cp_chunk_forward(inp["q"][:, sl], inp["k"][:, sl], inp["v"][:, sl],
+                             inp["cum_gate"][:, sl], inp["beta"][:, sl], None,
+                             slice_factory=OracleSlice, timeout=1.0)
+            ret[1] = "no timeout"
+        except ChainTimeout as exc:
+            ret[1] = (time.monotonic() - t0, str(exc))
+    os._exit(0)      # the timed-out gloo pair is closed: no collective tear-down
+
+
+def test_chain_receive_has_a_host_deadline_gloo():
+    port = 29850 + (os.getpid() % 100)
+    with mp.Manager() as manager:
+        ret = manager.dict()
+        mp.spawn(_timeout_worker, args=(2, port, ret), nprocs=2, join=True)
+        assert ret[0] == "idle"
+        waited, message = ret[1]
+        assert 0.9 <= waited < 3.5, waited
+        assert "no boundary state from rank 0" in message

@@ -116,6 +116,34 @@ def test_kept_intermediates_equal_recompute(case):
         assert torch.equal(kept[name], again[name]), name
 
 
+@pytest.mark.parametrize("case", [CASES[1], CASES[4]], ids=["dense", "packed"])
+@pytest.mark.parametrize("recompute", [False, True], ids=["kept", "recompute"])
+def test_value_split_of_the_state_recurrence_gives_the_same_bits(case, recompute):
+    """The serial state kernels run 1, 2 or 4 CTAs per (sequence, head), each owning a slice of the
+    value columns (the reference tiles the same dimension: fwd/triton/chunk_delta_h.py:166,
+    bwd/cute/chunk_delta_h_bwd_v1_dispatch.py:53-55).  The products are separable along v, so
+    outputs, states and all gradients are bitwise the same for every split."""
+    from kda_b200 import _cabi
+
+    inp = _case(**case)
+    gen = torch.Generator().manual_seed(98)
+    do = torch.randn(inp["v"].shape, generator=gen)
+    dst = torch.randn(inp["h0"].shape, generator=gen)
+    lib = _cabi.lib()
+    runs = {}
+    try:
+        for split in (1, 2, 4):
+            assert lib.kda_set_state_value_split(split) == 0
+            runs[split] = _run_fused(inp, do, dst, grad=True, recompute=recompute)
+    finally:
+        lib.kda_set_state_value_split(0)
+    assert lib.kda_set_state_value_split(3) == -1
+    for split in (2, 4):
+        for name in runs[1]:
+            assert torch.equal(runs[1][name], runs[split][name]), f"split {split}: {name}"
+    assert lib.kda_device_error_word() == 0
+
+
 def test_dense_batch_equals_packed():
     """A dense batch and its explicit equal-length packing give bitwise-equal results
     (reference: test/test_kda_cute_forward.py:368-410)."""
@@ -158,6 +186,32 @@ def test_nan_poisoned_suffix_is_ignored():
     res = _run_fused(bad)
     assert torch.equal(clean["o"][:, :120], res["o"][:, :120])
     assert torch.equal(clean["state"], res["state"])
+
+
+def test_nan_poisoned_suffix_is_ignored_in_backward():
+    """The same for the backward pass: NaN in every input row and in the output cotangent past
+    cu_seqlens[-1] changes no gradient of the active prefix and no state gradient, bit for bit
+    (reference: test/test_kda_ragged_bwd_wy.py:168-186, test_kda_ragged_public_backward.py:125-139).
+    Both the kept-intermediates and the recompute backward are checked."""
+    inp = _case(1, 200, 2, seed=10, lengths=[70, 0, 50])
+    gen = torch.Generator().manual_seed(3)
+    do = torch.randn(inp["v"].shape, generator=gen).bfloat16().float()
+    dst = 0.1 * torch.randn(3, 2, 128, 128, generator=gen)
+    bad = dict(inp)
+    for n in ("q", "k", "v", "cum_gate", "beta"):
+        x = inp[n].clone()
+        x[:, 120:] = float("nan")
+        bad[n] = x
+    do_bad = do.clone()
+    do_bad[:, 120:] = float("nan")
+    for recompute in (False, True):
+        clean = _run_fused(inp, do, dst, grad=True, recompute=recompute)
+        res = _run_fused(bad, do_bad, dst, grad=True, recompute=recompute)
+        for name in ("o", "dq", "dk", "dv", "dg", "dbeta"):
+            assert torch.isfinite(res[name][:, :120].float()).all(), name
+            assert torch.equal(clean[name][:, :120], res[name][:, :120]), name
+        assert torch.equal(clean["state"], res["state"])
+        assert torch.equal(clean["dh0"], res["dh0"])
 
 
 def test_rejections():

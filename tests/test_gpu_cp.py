@@ -1,7 +1,8 @@
 """Context-parallel forward on the CUDA kernels: the ranks of the boundary-state chain are run one
 after another in this process (mailbox send/recv), which exercises kda_chunk_fwd_prepare,
-kda_chunk_fwd_state (zero state, identity/transition, true state) and kda_state_affine.  The
-result must equal the single-GPU chunked forward of the whole sequence."""
+kda_chunk_slice_map (zero-state walk + transition walk with its measured early exit),
+kda_chunk_fwd_state (true state, chunk-limited) and kda_state_affine.  The result must equal the
+single-GPU chunked forward of the whole sequence."""
 
 import pytest
 import torch
@@ -14,11 +15,15 @@ from helpers import assert_normalised
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("world", [2, 4])
-def test_cp_matches_single_gpu(world):
-    per = 128
+@pytest.mark.parametrize("gate_scale", [1.0, 0.02], ids=["forgetful-gates", "mild-gates"])
+@pytest.mark.parametrize("world,per", [(2, 128), (4, 128), (2, 1024)])
+def test_cp_matches_single_gpu(world, per, gate_scale):
+    """With the benchmark's gates (logsigmoid of N(0, 1), about 2^-74 per chunk) a slice forgets its
+    entering state within a few chunks and the corrective pass is cut short; with gates scaled by
+    0.02 the transition stays dense and every chunk is redone.  Both must match the single pass."""
     total = per * world + 50
     inp = orc.make_inputs(1, total, 2, 128, 128, seed=31, with_state=True)
+    inp["cum_gate"] = inp["cum_gate"] * gate_scale
     c = {k: (v.cuda() if torch.is_tensor(v) else v) for k, v in inp.items()}
     q, k, v = (c[n].bfloat16() for n in ("q", "k", "v"))
     full_o, full_s = kda_b200.chunk_kda(q, k, v, c["cum_gate"], c["beta"], c["h0"],
@@ -58,6 +63,44 @@ def test_transition_matches_oracle():
     ref = orc.slice_transition_ref(inp["k"][0].bfloat16().float(), inp["gate_log2"][0],
                                    inp["beta"][0])
     assert_normalised(m[0], ref, 2e-2, "slice transition")
+
+
+def test_slice_map_in_one_launch_equals_the_two_passes():
+    """kda_chunk_slice_map gives b (zero entering state) and the transition M in one launch; both are
+    bitwise what the two separate state passes give.  Mild gates, so that M is far from zero."""
+    inp = orc.make_inputs(1, 192, 2, 128, 128, seed=34)
+    c = {k: (v.cuda() if torch.is_tensor(v) else v) for k, v in inp.items()}
+    cum = 0.02 * c["cum_gate"]
+    part = CudaSlice(c["q"].bfloat16(), c["k"].bfloat16(), c["v"].bfloat16(), cum, c["beta"])
+    out, b, m, limit = part.slice_map()
+    assert torch.equal(b, part.zero_state_result())
+    assert torch.equal(m, part.transition())
+    assert torch.equal(out, part.run(None)[0])
+    assert float(m.abs().max()) > 1e-2
+    assert limit.tolist() == [[3, 3]], "a dense transition must not cut the corrective pass"
+    ref = orc.slice_transition_ref(inp["k"][0].bfloat16().float(), 0.02 * inp["gate_log2"][0],
+                                   inp["beta"][0])
+    assert_normalised(m[0], ref, 2e-2, "slice transition (mild gates)")
+
+
+def test_forgetful_gates_cut_the_corrective_pass_short():
+    """Benchmark gates over 32 chunks: the transition walk reports that the slice forgets its entering
+    state after a few chunks; M is then exactly zero, and the chunk-limited corrective pass gives what
+    the full pass with the true entering state gives."""
+    inp = orc.make_inputs(1, 2048, 2, 128, 128, seed=35, with_state=True)
+    c = {k: (v.cuda() if torch.is_tensor(v) else v) for k, v in inp.items()}
+    part = CudaSlice(c["q"].bfloat16(), c["k"].bfloat16(), c["v"].bfloat16(), c["cum_gate"], c["beta"])
+    h_in = 50.0 * c["h0"]
+    out, b, m, limit = part.slice_map()
+    assert int(limit.max()) < 32 and int(limit.min()) >= 1, limit.tolist()
+    assert float(m.abs().max()) == 0.0
+    full_o, full_s = part.run(h_in)
+    fixed = part.correct(out.clone(), h_in, limit)
+    assert_normalised(fixed.float(), full_o.float(), 1e-4, "chunk-limited corrective pass vs full pass")
+    assert not torch.equal(out, full_o), "the entering state must matter in the leading chunks"
+    assert_normalised(part.affine(m, h_in, b), full_s, 1e-6, "M h_in + b vs the full pass")
+    from kda_b200 import _cabi
+    assert _cabi.lib().kda_device_error_word() == 0
 
 
 @pytest.mark.parametrize("world", [2, 3])

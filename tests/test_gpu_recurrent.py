@@ -66,6 +66,29 @@ def test_config0_fp32(golden):
     assert rel <= 2e-3, f"max relative error {rel:.3e}"
 
 
+def test_fp32_inputs_follow_the_reference_unless_exact_fp32_is_asked_for():
+    """fp32 q, k, v at K = V = 128: the default rounds them to bf16 and runs the chunked kernels, with
+    or without autograd, as the reference's fused path does (impl/fused.py:169-171);
+    exact_fp32=True runs the fp32 token scan instead."""
+    inp = orc.make_inputs(1, 130, 2, 128, 128, seed=13, with_state=True)
+    c = {k: (v.cuda() if torch.is_tensor(v) else v) for k, v in inp.items()}
+    args = (c["q"], c["k"], c["v"], c["cum_gate"], c["beta"], c["h0"])
+    with torch.no_grad():
+        o32, s32 = kda_b200.chunk_kda(*args, output_final_state=True)
+        ob, sb = kda_b200.chunk_kda(c["q"].bfloat16(), c["k"].bfloat16(), c["v"].bfloat16(),
+                                    *args[3:], output_final_state=True)
+        oe, se = kda_b200.chunk_kda(*args, output_final_state=True, exact_fp32=True)
+    assert o32.dtype == torch.float32 and torch.equal(o32, ob.float()) and torch.equal(s32, sb)
+    leaves = [t.clone().requires_grad_() for t in args]
+    og, sg = kda_b200.chunk_kda(*leaves, output_final_state=True)
+    assert torch.equal(og, o32) and torch.equal(sg, s32), "train and eval numerics differ"
+    ro, rs = orc.chunk_kda_ref(inp["q"], inp["k"], inp["v"], inp["cum_gate"], inp["beta"], inp["h0"])
+    assert_normalised(oe, ro, 1e-5, "exact fp32 output")
+    assert_normalised(se, rs, 1e-5, "exact fp32 state")
+    with pytest.raises(ValueError):
+        kda_b200.chunk_kda(*leaves, exact_fp32=True)
+
+
 def test_decode_paged_pool():
     n, h, kd, vd, slots = 6, 2, 128, 128, 9
     inp = orc.make_inputs(n, 1, h, kd, vd, seed=9)
@@ -89,6 +112,40 @@ def test_decode_paged_pool():
         assert_normalised(pool_gpu[slot], rs[0], 1e-4, f"paged state {i}")
     untouched = [s for s in range(slots) if s not in (3, 5, 8, 1)]
     assert torch.equal(pool_gpu[untouched].cpu(), pool[untouched])
+
+
+@pytest.mark.parametrize("pad,n", [(2 * 128 * 128, 5), (64, 150), (2, 5)],
+                         ids=["stride-2HKV", "stride+64", "stride+2"])
+def test_decode_strided_paged_pool(pad, n):
+    """A paged pool whose slots are contiguous inside but further apart than H*K*V elements (a view
+    into a larger cache, as serving engines hand over; reference: test/test_kda_recurrent.py:56-71,
+    207-290).  A slot stride that is a multiple of 128 takes the tensor-map decode kernel, the other
+    two the token scan (with 300 (sequence, head) pairs its float4 form, with 10 its scalar form);
+    the gaps between slots must stay untouched."""
+    h, slots = 2, n + 2
+    hkv = h * 128 * 128
+    inp = orc.make_inputs(n, 1, h, 128, 128, seed=31)
+    gen = torch.Generator().manual_seed(6)
+    backing = 0.02 * torch.randn(slots, hkv + pad, generator=gen)
+    backing_gpu = backing.cuda()
+    pool_gpu = backing_gpu[:, :hkv].view(slots, h, 128, 128)
+    assert pool_gpu.stride(0) == hkv + pad and not pool_gpu.is_contiguous()
+    pool = backing[:, :hkv].reshape(slots, h, 128, 128)
+    idx = (torch.randperm(slots - 1, generator=gen)[:n] + 1).to(torch.int32)
+    idx[1], idx[4] = 0, -3                                   # padding rows
+    q, k, v, g = (inp[x].bfloat16() for x in ("q", "k", "v", "gate_log2"))
+    beta = inp["beta"].bfloat16()
+    o, _ = kda_b200.recurrent_kda(q.cuda(), k.cuda(), v.cuda(), g.cuda(), beta.cuda(), pool_gpu,
+                                  state_indices=idx.cuda())
+    assert o[(idx <= 0).cuda()].abs().max() == 0
+    live = idx[idx > 0].long()
+    ro, rs = orc.recurrent_kda_ref(q[idx > 0].float(), k[idx > 0].float(), v[idx > 0].float(),
+                                   g[idx > 0].float(), beta[idx > 0].float(), pool[live])
+    assert_normalised(o[(idx > 0).cuda()].float(), ro, 2e-2, "strided pool outputs")
+    assert_normalised(pool_gpu[live.cuda()], rs, 1e-4, "strided pool states")
+    untouched = [s for s in range(slots) if s not in set(live.tolist())]
+    assert torch.equal(pool_gpu[untouched].cpu(), pool[untouched])
+    assert torch.equal(backing_gpu[:, hkv:].cpu(), backing[:, hkv:]), "the gaps between slots were written"
 
 
 def test_decode_ring_many_items():
