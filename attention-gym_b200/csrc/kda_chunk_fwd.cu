@@ -219,6 +219,207 @@ extern "C" int kda_chunk_slice_map(const float* cum_gate, float* b_out, float* t
 }
 
 // ------------------------------------------------------------------------------------------------
+// Dense batches: `batch` rows of `tokens_per_row` tokens each.
+//
+// The offsets are built on the device from the two sizes.  When the batch has fewer (row, head)
+// chains than half the SMs and the rows are long, every row is cut into segments of whole chunks
+// that are walked in parallel, exactly as the ranks of a context-parallel chain would:
+//   pass A  every segment from a zero state (outputs, b = its leaving state), and on further CTAs the
+//           segment transition M together with the number of chunks after which it is exactly zero;
+//   chain   h_in(s + 1) = M_s h_in(s) + b_s along each row (fp32, tiny);
+//   pass B  every segment again with its true entering state, over the leading chunks that state
+//           can still reach (all of them when the gates never forget completely).
+// With gates that forget within a few chunks the serial walk shrinks by the number of segments;
+// with gates that never forget it costs about what the unsegmented walk costs.  The results agree
+// with the unsegmented walk to fp32 resolution of the state, not bit for bit.
+// ------------------------------------------------------------------------------------------------
+namespace kda {
+
+int launch_state_affine(const float* M, const float* hin, const float* b, float* hout, int groups,
+                        int group, int64_t in_stride, int64_t out_stride, int K, int V, cudaStream_t s);
+
+static int g_row_segments = 0;   // 0 = choose; otherwise the forced number of segments per row (tests, tuning)
+
+struct DensePlan {
+  int segs;         // segments per row (1 = plain walk)
+  int seg_chunks;   // chunks per segment (the last one of a row may be shorter)
+  int row_chunks;
+  int64_t count;    // batch * segs
+};
+
+static DensePlan plan_dense(int batch, int64_t tokens_per_row, int heads) {
+  DensePlan pl;
+  pl.row_chunks = (int)((tokens_per_row + kChunk - 1) / kChunk);
+  int segs = 1;
+  if (g_row_segments > 0) {
+    segs = g_row_segments;
+  } else {
+    int dev = 0, sms = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int64_t chains = (int64_t)batch * heads;
+    if (chains * 2 <= sms) segs = (int)(sms / chains < 8 ? sms / chains : 8);
+    if (segs > pl.row_chunks / 64) segs = pl.row_chunks / 64;     // at least 64 chunks per segment
+  }
+  if (segs > pl.row_chunks) segs = pl.row_chunks;
+  if (segs < 1) segs = 1;
+  pl.seg_chunks = (pl.row_chunks + segs - 1) / segs;
+  pl.segs = (pl.row_chunks + pl.seg_chunks - 1) / pl.seg_chunks;
+  pl.count = (int64_t)batch * pl.segs;
+  return pl;
+}
+
+// sequence i = (row i / segs, segment i % segs)
+__global__ void dense_offsets_kernel(int32_t* cu, int32_t* co, int count, int segs, int tokens_per_row,
+                                     int row_chunks, int seg_chunks) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i > count) return;
+  const int row = i / segs, s = i % segs;
+  const int chunks = min(s * seg_chunks, row_chunks);
+  cu[i] = row * tokens_per_row + min(chunks * kChunk, tokens_per_row);
+  co[i] = row * row_chunks + chunks;
+}
+
+static int64_t align256(int64_t x) { return (x + 255) & ~(int64_t)255; }
+
+struct DenseScratch {   // byte offsets from the start of the scratch region
+  int64_t cu, co, limit, b, trans, hin, total;
+};
+static DenseScratch dense_scratch(int64_t count, int heads) {
+  DenseScratch d;
+  int64_t at = 0;
+  d.cu = at; at = align256(at + (count + 1) * 4);
+  d.co = at; at = align256(at + (count + 1) * 4);
+  d.limit = at; at = align256(at + count * heads * 4);
+  const int64_t states = count * heads * (int64_t)D * D * 4;
+  d.b = at; at += states;
+  d.trans = at; at += states;
+  d.hin = at; at += states;
+  d.total = at;
+  return d;
+}
+
+}  // namespace kda
+
+extern "C" int kda_set_row_segments(int segments) {
+  if (segments < 0 || segments > 64) return KDA_ERR_ARG;
+  kda::g_row_segments = segments;
+  return KDA_OK;
+}
+
+extern "C" int64_t kda_chunk_fwd_dense_workspace_bytes(int batch, int64_t tokens_per_row, int heads,
+                                                       int keep) {
+  if (batch < 1 || tokens_per_row < 1 || heads < 1) return 0;
+  const int64_t total = (int64_t)batch * tokens_per_row;
+  const kda::DensePlan pl = kda::plan_dense(batch, tokens_per_row, heads);
+  const int64_t base = keep ? kda_chunk_bwd_workspace_bytes(total, heads, (int64_t)batch * pl.row_chunks)
+                            : kda_chunk_fwd_workspace_bytes(total, heads);
+  // the plan may change with kda_set_row_segments between this call and the launch: size for the
+  // largest scratch either can ask for (segments only matter through count = batch * segs)
+  const int64_t worst = (int64_t)batch * (pl.segs > 8 ? pl.segs : 8);
+  return kda::align256(base) + kda::dense_scratch(worst, heads).total;
+}
+
+static int chunk_fwd_dense_impl(bool keep, const void* q, const void* k, const void* v,
+                                const float* cum_gate, const float* beta, const float* initial_state,
+                                float* final_state, void* out, void* aqk, void* akk, int batch,
+                                int64_t tokens_per_row, int heads, int key_dim, int value_dim,
+                                void* workspace, int64_t workspace_bytes, void* stream) {
+  if (!q || !k || !v || !cum_gate || !beta || !out || !aqk || !akk || !workspace) return KDA_ERR_ARG;
+  if (key_dim != 128 || value_dim != 128) return KDA_ERR_UNSUPPORTED;
+  if (batch < 1 || heads < 1 || tokens_per_row < 1) return KDA_ERR_ARG;
+  const int64_t total = (int64_t)batch * tokens_per_row;
+  if (total > 0x7fffffffLL) return KDA_ERR_UNSUPPORTED;
+  const kda::DensePlan pl = kda::plan_dense(batch, tokens_per_row, heads);
+  if (pl.count * heads * 8 > 0x7fffffffLL) return KDA_ERR_UNSUPPORTED;
+  const int chunks = batch * pl.row_chunks;
+  const int64_t base = kda::align256(keep ? kda_chunk_bwd_workspace_bytes(total, heads, chunks)
+                                          : kda_chunk_fwd_workspace_bytes(total, heads));
+  const kda::DenseScratch sc = kda::dense_scratch(pl.count, heads);
+  if (workspace_bytes < base + sc.total || ((uintptr_t)workspace & 15) != 0) return KDA_ERR_ARG;
+  unsigned char* scratch = reinterpret_cast<unsigned char*>(workspace) + base;
+  int32_t* cu = reinterpret_cast<int32_t*>(scratch + sc.cu);
+  int32_t* co = reinterpret_cast<int32_t*>(scratch + sc.co);
+  cudaStream_t s = (cudaStream_t)stream;
+  const int count = (int)pl.count;
+  kda::dense_offsets_kernel<<<(count + 256) / 256, 256, 0, s>>>(cu, co, count, pl.segs, (int)tokens_per_row,
+                                                              pl.row_chunks, pl.seg_chunks);
+  if (cudaGetLastError() != cudaSuccess) return KDA_ERR_LAUNCH;
+
+  kda::ChunkParams p{};
+  const int64_t nd = total * heads * 128;
+  bf16* ws = reinterpret_cast<bf16*>(workspace);
+  p.q = (const bf16*)q; p.k = (const bf16*)k; p.v = (const bf16*)v; p.g = cum_gate; p.beta = beta;
+  p.aqk = (bf16*)aqk; p.akk = (bf16*)akk;
+  p.w = ws; p.u = ws + nd; p.kg = ws + 2 * nd; p.qg = ws + 3 * nd;
+  p.o = (bf16*)out;
+  p.vnew_out = keep ? ws + 4 * nd : nullptr;
+  p.h_out = keep ? ws + 6 * nd : nullptr;
+  p.chunks = chunks;
+  p.cu_seqlens = cu; p.chunk_offsets = co; p.nseq = count; p.H = heads;
+  p.scale = 0.08838834764831845f;
+  p.tokens = total;
+  int rc = kda::launch_prepare(p, chunks, s);
+  if (rc) return rc;
+  if (pl.segs == 1) {
+    p.h0 = initial_state; p.ht = final_state;
+    return kda::launch_state_fwd(p, s);
+  }
+  // ---- pass A: zero-state walk of every segment + transitions with their measured reach
+  float* b = reinterpret_cast<float*>(scratch + sc.b);
+  float* trans = reinterpret_cast<float*>(scratch + sc.trans);
+  float* hin = reinterpret_cast<float*>(scratch + sc.hin);
+  int32_t* limit = reinterpret_cast<int32_t*>(scratch + sc.limit);
+  if (cudaMemsetAsync(limit, 0, (size_t)count * heads * 4, s) != cudaSuccess) return KDA_ERR_LAUNCH;
+  p.h0 = nullptr; p.ht = b; p.trans_out = trans; p.limit_out = limit;
+  rc = kda::launch_state_fwd(p, s);
+  if (rc) return rc;
+  // ---- chain along each row: h_in(0) = the row's initial state, h_in(s + 1) = M_s h_in(s) + b_s
+  const size_t row_bytes = (size_t)heads * 128 * 128 * 4;
+  cudaError_t e = initial_state
+      ? cudaMemcpy2DAsync(hin, row_bytes * pl.segs, initial_state, row_bytes, row_bytes, batch,
+                          cudaMemcpyDeviceToDevice, s)
+      : cudaMemset2DAsync(hin, row_bytes * pl.segs, 0, row_bytes, batch, s);
+  if (e != cudaSuccess) return KDA_ERR_LAUNCH;
+  const int64_t per_seg = (int64_t)heads * 128 * 128;
+  for (int sg = 0; sg + 1 < pl.segs; ++sg) {
+    rc = kda::launch_state_affine(trans + sg * per_seg, hin + sg * per_seg, b + sg * per_seg,
+                                  hin + (sg + 1) * per_seg, batch, heads, (int64_t)pl.segs * heads,
+                                  (int64_t)pl.segs * heads, 128, 128, s);
+    if (rc) return rc;
+  }
+  if (final_state) {
+    const int last = pl.segs - 1;
+    rc = kda::launch_state_affine(trans + last * per_seg, hin + last * per_seg, b + last * per_seg,
+                                  final_state, batch, heads, (int64_t)pl.segs * heads, heads, 128, 128, s);
+    if (rc) return rc;
+  }
+  // ---- pass B: the leading chunks of every segment with its true entering state
+  p.h0 = hin; p.ht = nullptr; p.trans_out = nullptr; p.limit_out = nullptr; p.limit_in = limit;
+  return kda::launch_state_fwd(p, s);
+}
+
+extern "C" int kda_chunk_fwd_dense(const void* q, const void* k, const void* v, const float* cum_gate,
+                                   const float* beta, const float* initial_state, float* final_state,
+                                   void* out, void* aqk, void* akk, int batch, int64_t tokens_per_row,
+                                   int heads, int key_dim, int value_dim, void* workspace,
+                                   int64_t workspace_bytes, void* stream) {
+  return chunk_fwd_dense_impl(false, q, k, v, cum_gate, beta, initial_state, final_state, out, aqk, akk,
+                              batch, tokens_per_row, heads, key_dim, value_dim, workspace,
+                              workspace_bytes, stream);
+}
+
+extern "C" int kda_chunk_fwd_dense_save(const void* q, const void* k, const void* v,
+                                        const float* cum_gate, const float* beta,
+                                        const float* initial_state, float* final_state, void* out,
+                                        void* aqk, void* akk, int batch, int64_t tokens_per_row,
+                                        int heads, int key_dim, int value_dim, void* saved,
+                                        int64_t saved_bytes, void* stream) {
+  return chunk_fwd_dense_impl(true, q, k, v, cum_gate, beta, initial_state, final_state, out, aqk, akk,
+                              batch, tokens_per_row, heads, key_dim, value_dim, saved, saved_bytes,
+                              stream);
+}
+
+// ------------------------------------------------------------------------------------------------
 // Chunked forward for callers that must not allocate.
 //
 // Some hosts of this library cannot call cudaMalloc: a serving engine that has handed every free

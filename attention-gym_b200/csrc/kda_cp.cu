@@ -13,13 +13,18 @@ namespace kda {
 __global__ void __launch_bounds__(256) state_affine_kernel(const float* __restrict__ M,
                                                            const float* __restrict__ hin,
                                                            const float* __restrict__ b,
-                                                           float* __restrict__ hout, int K, int V) {
+                                                           float* __restrict__ hout, int K, int V,
+                                                           int group, int64_t in_stride,
+                                                           int64_t out_stride) {
   __shared__ float sA[16][64 + 4];
   __shared__ float sB[16][64 + 4];
-  const int n = blockIdx.z, r0 = blockIdx.y * 64, c0 = blockIdx.x * 64;
+  const int r0 = blockIdx.y * 64, c0 = blockIdx.x * 64;
   const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
-  const float* Mn = M + (int64_t)n * K * K;
-  const float* Hn = hin + (int64_t)n * K * V;
+  // matrix blockIdx.z = (g, i) with i < group: inputs at g * in_stride + i, output at g * out_stride + i
+  const int64_t n = (int64_t)(blockIdx.z / group) * in_stride + blockIdx.z % group;
+  const int64_t no = (int64_t)(blockIdx.z / group) * out_stride + blockIdx.z % group;
+  const float* Mn = M + n * K * K;
+  const float* Hn = hin + n * K * V;
   float acc[4][4];
 #pragma unroll
   for (int i = 0; i < 4; ++i)
@@ -49,11 +54,21 @@ __global__ void __launch_bounds__(256) state_affine_kernel(const float* __restri
   }
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    int64_t o = (int64_t)n * K * V + (int64_t)(r0 + ty * 4 + i) * V + c0 + tx * 4;
-    float4 bv = *reinterpret_cast<const float4*>(b + o);
-    *reinterpret_cast<float4*>(hout + o) =
+    const int64_t e = (int64_t)(r0 + ty * 4 + i) * V + c0 + tx * 4;
+    float4 bv = *reinterpret_cast<const float4*>(b + n * K * V + e);
+    *reinterpret_cast<float4*>(hout + no * K * V + e) =
         make_float4(acc[i][0] + bv.x, acc[i][1] + bv.y, acc[i][2] + bv.z, acc[i][3] + bv.w);
   }
+}
+
+// `groups` x `group` products; the matrices of group g start at index g * in_stride (inputs) and
+// g * out_stride (output).
+int launch_state_affine(const float* M, const float* hin, const float* b, float* hout, int groups,
+                        int group, int64_t in_stride, int64_t out_stride, int K, int V, cudaStream_t s) {
+  if (groups <= 0 || group <= 0) return KDA_OK;
+  dim3 grid(V / 64, K / 64, groups * group);
+  state_affine_kernel<<<grid, 256, 0, s>>>(M, hin, b, hout, K, V, group, in_stride, out_stride);
+  return cudaGetLastError() == cudaSuccess ? KDA_OK : KDA_ERR_LAUNCH;
 }
 
 }  // namespace kda
@@ -63,8 +78,6 @@ extern "C" int kda_state_affine(const float* transition, const float* h_in, cons
   if (!transition || !h_in || !b || !h_out || count < 0) return KDA_ERR_ARG;
   if (key_dim % 64 || value_dim % 64 || key_dim <= 0 || value_dim <= 0) return KDA_ERR_UNSUPPORTED;
   if (count == 0) return KDA_OK;
-  dim3 grid(value_dim / 64, key_dim / 64, count);
-  kda::state_affine_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(transition, h_in, b, h_out,
-                                                                  key_dim, value_dim);
-  return cudaGetLastError() == cudaSuccess ? KDA_OK : KDA_ERR_LAUNCH;
+  return kda::launch_state_affine(transition, h_in, b, h_out, 1, count, 0, 0, key_dim, value_dim,
+                                  (cudaStream_t)stream);
 }

@@ -55,6 +55,12 @@ _SIGNATURES = {
                                    c_void_p, c_int64, c_void_p]),
     "kda_chunk_fwd_noalloc": (c_int, [c_void_p] * 12 + [c_int, c_int64, c_int, c_int, c_int, c_int,
                                       c_void_p]),
+    "kda_chunk_fwd_dense_workspace_bytes": (c_int64, [c_int, c_int64, c_int, c_int]),
+    "kda_chunk_fwd_dense": (c_int, [c_void_p] * 10 + [c_int, c_int64, c_int, c_int, c_int, c_void_p,
+                                    c_int64, c_void_p]),
+    "kda_chunk_fwd_dense_save": (c_int, [c_void_p] * 10 + [c_int, c_int64, c_int, c_int, c_int,
+                                         c_void_p, c_int64, c_void_p]),
+    "kda_set_row_segments": (c_int, [c_int]),
     "kda_chunk_bwd_workspace_bytes": (c_int64, [c_int64, c_int, c_int64]),
     "kda_chunk_bwd": (c_int, [c_void_p] * 18 + [c_int, c_int64, c_int, c_int, c_int, c_int, c_void_p,
                               c_int64, c_void_p]),

@@ -108,6 +108,18 @@ def _dense_offsets(q):
     return steps * tokens, steps * per_row, batch * per_row
 
 
+def _fwd_workspace_bytes(batch, tokens, heads, packed_nseq, keep):
+    """Bytes of the forward workspace (keep: the buffer that is handed on to the backward pass);
+    shape-only, so the real and the fake implementations agree."""
+    lib = _cabi.lib()
+    if packed_nseq is None:
+        return int(lib.kda_chunk_fwd_dense_workspace_bytes(batch, tokens, heads, int(keep)))
+    if keep:
+        return int(lib.kda_chunk_bwd_workspace_bytes(tokens, heads,
+                                                     chunk_capacity(tokens, packed_nseq, _CHUNK)))
+    return int(lib.kda_chunk_fwd_workspace_bytes(tokens, heads))
+
+
 def _chunk_fwd_impl(q, k, v, gate, beta, initial_state, cu_seqlens, chunk_offsets, want_state,
                     keep=False):
     _require_cuda(q, "the fused KDA core")
@@ -118,8 +130,7 @@ def _chunk_fwd_impl(q, k, v, gate, beta, initial_state, cu_seqlens, chunk_offset
     batch, tokens, heads, _ = q.shape
     packed = cu_seqlens is not None
     if not packed:
-        cu_seqlens, chunk_offsets, capacity = _dense_offsets(q)
-        nseq = batch
+        nseq, capacity = batch, None
     else:
         if batch != 1:
             raise ValueError("packed cu_seqlens require batch size one")
@@ -136,16 +147,19 @@ def _chunk_fwd_impl(q, k, v, gate, beta, initial_state, cu_seqlens, chunk_offset
     akk = torch.empty_like(aqk)
     state = (torch.empty(nseq, heads, 128, 128, dtype=torch.float32, device=q.device)
              if want_state else None)
-    if keep:
-        ws_bytes = _cabi.lib().kda_chunk_bwd_workspace_bytes(total, heads, capacity)
-    else:
-        ws_bytes = _cabi.lib().kda_chunk_fwd_workspace_bytes(total, heads)
+    ws_bytes = _fwd_workspace_bytes(batch, tokens, heads, None if not packed else nseq, keep)
     workspace = torch.empty(ws_bytes, dtype=torch.uint8, device=q.device)
-    _cabi.call("kda_chunk_fwd_save" if keep else "kda_chunk_fwd", 3, _cabi.ptr(q), _cabi.ptr(k), _cabi.ptr(v), _cabi.ptr(gate),
-               _cabi.ptr(beta), _cabi.ptr(initial_state), _cabi.ptr(state), _cabi.ptr(out),
-               _cabi.ptr(aqk), _cabi.ptr(akk), _cabi.ptr(cu_seqlens), _cabi.ptr(chunk_offsets),
-               nseq, total, heads, 128, 128, capacity, _cabi.ptr(workspace), ws_bytes,
-               _cabi.stream())
+    head = (_cabi.ptr(q), _cabi.ptr(k), _cabi.ptr(v), _cabi.ptr(gate), _cabi.ptr(beta),
+            _cabi.ptr(initial_state), _cabi.ptr(state), _cabi.ptr(out), _cabi.ptr(aqk), _cabi.ptr(akk))
+    if packed:
+        _cabi.call("kda_chunk_fwd_save" if keep else "kda_chunk_fwd", 3, *head, _cabi.ptr(cu_seqlens),
+                   _cabi.ptr(chunk_offsets), nseq, total, heads, 128, 128, capacity,
+                   _cabi.ptr(workspace), ws_bytes, _cabi.stream())
+    else:
+        # dense rows: offsets are built on the device, long rows of small batches are walked in
+        # parallel segments
+        _cabi.call("kda_chunk_fwd_dense_save" if keep else "kda_chunk_fwd_dense", 3, *head, batch,
+                   tokens, heads, 128, 128, _cabi.ptr(workspace), ws_bytes, _cabi.stream())
     if keep:
         return out, state, aqk, akk, workspace
     return out, state, aqk, akk
@@ -303,10 +317,8 @@ def _(q, k, v, gate, beta, initial_state, cu_seqlens, chunk_offsets, want_state)
     nseq = q.shape[0] if cu_seqlens is None else cu_seqlens.shape[0] - 1
     state = (q.new_empty((nseq, q.shape[2], q.shape[3], v.shape[-1]), dtype=torch.float32)
              if want_state else q.new_empty((0,), dtype=torch.float32))
-    total, heads = q.shape[0] * q.shape[1], q.shape[2]
-    chunks = (q.shape[0] * ((q.shape[1] + _CHUNK - 1) // _CHUNK) if cu_seqlens is None
-              else chunk_capacity(q.shape[1], nseq, _CHUNK))
-    nbytes = (7 * total * heads * 128 + 2 * chunks * heads * 128 * 128) * 2 + 256
+    nbytes = _fwd_workspace_bytes(q.shape[0], q.shape[1], q.shape[2],
+                                  None if cu_seqlens is None else nseq, True)
     return (v.new_empty(v.shape), state, _tape(q), _tape(q),
             q.new_empty((nbytes,), dtype=torch.uint8))
 

@@ -8,13 +8,20 @@ chunk 64; q, k L2-normalised N(0,1), v ~ N(0,1), g = logsigmoid(N(0,1)), beta = 
 dO ~ N(0,1)).  Inputs (1.5 GiB) are far larger than L2, so no flush is needed between steps.
 
 Rank 0 prints one JSON line.  ``value`` is device-resident throughput (CUDA events, max over
-ranks); ``e2e`` is the same step with pinned HOST buffers, host<->device copies inside the timed
-region; ``roofline`` describes the kernel that takes the largest share of the step (timed live
-with CUDA events on the launching stream); ``cpu_baseline`` is the CPU oracle port timed on a
-bounded sample on this machine's cores.  Multi-GPU runs shard by (batch, head) with no collective:
-every rank runs the full per-GPU workload (weak scaling).
+ranks, per-kernel event recording switched off); ``e2e`` is the same step with pinned HOST buffers,
+host<->device copies inside the timed region; ``kernels`` / ``roofline`` come from a second pass of
+the same steps with the library's per-kernel CUDA events on the launching stream switched on
+(``roofline`` describes the kernel with the largest share); ``cpu_baseline`` is the CPU
+implementation of the path timed on a bounded sample on this machine's cores.  Multi-GPU runs shard
+by (batch, head) with no collective: every rank runs the full per-GPU workload (weak scaling).
+Two more sub-objects measure the splits of a fixed amount of work over the N GPUs:
+``strong`` = the single B=8 batch of the headline configuration cut by (batch, head) with
+``shard_ranges`` (no collective), ``cp`` = one sequence of 1,048,576 tokens, forward, cut into N
+contiguous slices whose boundary states travel along an NCCL point-to-point chain
+(``cp_chunk_forward``), with a self-check against a single-GPU run on rank 0.
 
-``--impl reference`` times the CPU port of the reference path (the oracle) instead.
+``--impl reference`` times the reference's own CPU code for the path when ``oracle/_ref`` holds it
+(see oracle/build_ref.py), else the CPU port (the oracle).
 """
 
 from __future__ import annotations
@@ -202,8 +209,7 @@ def run_ours(args):
             step_device(kda_b200, dev)
             torch.cuda.synchronize()
         barrier()
-        _cabi.stage_timing(True)
-        _cabi.read_stage_timing(reset=True)
+        _cabi.stage_timing(False)
         launches0 = _cabi.launch_count
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         barrier()
@@ -215,9 +221,15 @@ def run_ours(args):
         barrier()
         clocks.mark(t_begin, time.monotonic())
     ms = start.elapsed_time(stop)
+    launches = _cabi.launch_count - launches0
+    # per-kernel breakdown: the same steps once more with the library's event pairs switched on
+    _cabi.read_stage_timing(reset=True)
+    _cabi.stage_timing(True)
+    for _ in range(args.steps):
+        step_device(kda_b200, dev)
+    torch.cuda.synchronize()
     stages = _cabi.read_stage_timing(reset=True)
     _cabi.stage_timing(False)
-    launches = _cabi.launch_count - launches0
 
     decode = None if args.skip_decode else bench_decode(kda_b200, _cabi, device, load_peaks())
     preops = None if (args.skip_decode or rank != 0) else bench_preops(device, load_peaks(), batch, tokens)
@@ -282,6 +294,15 @@ def run_ours(args):
         t = torch.tensor([ms, ms_e2e], device=device, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms, ms_e2e = float(t[0]), float(t[1])
+    strong = cp = None
+    if not args.skip_splits:
+        del dev
+        if e2e_steps:
+            del dev_in, host_out
+        torch.cuda.empty_cache()
+        strong = bench_strong(kda_b200, device, rank, world, args.steps, args.warmup, barrier)
+        torch.cuda.empty_cache()
+        cp = bench_cp(kda_b200, _cabi, device, rank, world, barrier)
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -314,6 +335,9 @@ def run_ours(args):
                     "peak": peaks["hbm_gbs"], "peak_source": peaks["source"], "unit": "GB/s",
                     "frac": round(achieved / peaks["hbm_gbs"], 4),
                     "traffic": NCU_TRAFFIC[top] * units if top in NCU_TRAFFIC else None,
+                    "traffic_source": ("ncu dram__bytes_read.sum + dram__bytes_write.sum of one capture of "
+                                       "the B=2 case (profiles/), scaled by the units of this launch; "
+                                       "not measured in this run") if top in NCU_TRAFFIC else None,
                     "bytes_per_token_head": per_unit, "ms_per_launch": round(per_launch_ms, 4)}
     path = {"hbm_frac": round(value * H * PATH_BYTES_FWD_BWD / 1e9 / world / peaks["hbm_gbs"], 4),
             "tensor_frac": round(value * H * PATH_FLOP_FWD_BWD / 1e12 / world / peaks["bf16_tflops"], 4),
@@ -339,10 +363,147 @@ def run_ours(args):
         "decode": decode,
         "preops": preops,
         "other_configs": others,
+        "strong": strong,
+        "cp": cp,
     }
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+def _max_over_ranks(values, device, world):
+    if world == 1:
+        return [float(v) for v in values]
+    import torch.distributed as dist
+
+    t = torch.tensor(values, device=device, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return [float(v) for v in t]
+
+
+def _all_ranks(values, device, world):
+    """[world][len(values)] list: every rank's row."""
+    t = torch.tensor(values, device=device, dtype=torch.float64)
+    if world == 1:
+        return [t.tolist()]
+    import torch.distributed as dist
+
+    rows = [torch.empty_like(t) for _ in range(world)]
+    dist.all_gather(rows, t)
+    return [r.tolist() for r in rows]
+
+
+def bench_strong(kda_b200, device, rank, world, steps, warmup, barrier):
+    """Strong scaling of the headline step: ONE batch of B=8 rows (config 1) cut over the ranks by
+    (batch, head) with shard_ranges; no collective on the data path.  Row r of the batch comes from
+    seed 9000 + r whatever the number of ranks, so every N works on the same global batch."""
+    from kda_b200.dist import shard_ranges
+
+    rows, heads = shard_ranges(8, H, world, rank)
+    parts = [_device_inputs(1, 4096, device, 9000 + r) for r in range(8)[rows]]
+    dev = {n: torch.cat([p[n] for p in parts], 0)[:, :, heads].contiguous() for n in parts[0]}
+    del parts
+    for _ in range(max(warmup, 3)):
+        step_device(kda_b200, dev)
+    barrier()
+    a, z = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(steps):
+        step_device(kda_b200, dev)
+    z.record()
+    barrier()
+    (ms,) = _max_over_ranks([a.elapsed_time(z)], device, world)
+    shape = dev["q"].shape
+    return {"workload": f"config1, one batch B=8 T=4096 H={H} fwd+bwd cut by (batch, head) over {world} "
+                        f"GPU(s): B={shape[0]} H={shape[2]} per GPU, no collective",
+            "scaling": "strong", "ms_per_step": round(ms / steps, 4),
+            "tokens_per_s": round(8 * 4096 * steps / (ms * 1e-3), 1)}
+
+
+def bench_cp(kda_b200, _cabi, device, rank, world, barrier, tokens=1 << 20, iters=3):
+    """Context parallelism (config 4): one sequence of `tokens` tokens, forward, in `world` contiguous
+    slices; only the fp32 boundary state [H, 128, 128] crosses GPUs, along an NCCL point-to-point
+    chain.  With one GPU this is the plain forward.  Includes a self-check: two reduced sequences
+    (65,536 tokens; the benchmark's forgetful gates, and gates scaled by 0.02 so that the slice
+    transitions stay dense) go through the same chain and the last rank's outputs and the final
+    state are compared on rank 0 with its own single-GPU pass over the whole sequence."""
+    from kda_b200.dist import cp_chunk_forward
+
+    per = tokens // world
+    if per % CHUNK:
+        raise SystemExit("slices must hold whole chunks")
+
+    def forward(d):
+        with torch.no_grad():
+            if world == 1:
+                return kda_b200.chunk_kda(d["q"], d["k"], d["v"], d["g"], d["beta"], output_final_state=True)
+            return cp_chunk_forward(d["q"], d["k"], d["v"], d["g"], d["beta"], None, timeout=120.0)
+
+    d = _device_inputs(1, per, device, 9100 + rank, with_do=False)
+    for _ in range(2):
+        forward(d)
+    barrier()
+    a, z = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(iters):
+        forward(d)
+    z.record()
+    barrier()
+    (ms,) = _max_over_ranks([a.elapsed_time(z)], device, world)
+    _cabi.read_stage_timing(reset=True)
+    _cabi.stage_timing(True)
+    forward(d)
+    torch.cuda.synchronize()
+    st = _cabi.read_stage_timing(reset=True)
+    _cabi.stage_timing(False)
+    per_rank = _all_ranks([st.get("prepare", (0, 0.0))[1], st.get("state_fwd", (0, 0.0))[1],
+                           st.get("state_fwd", (0, 0.0))[0]], device, world)
+    del d
+    torch.cuda.empty_cache()
+
+    # ---- self-check on reduced sequences
+    check = {}
+    small = 65536 // world
+    for name, scale in (("forgetful_gates", 1.0), ("mild_gates", 0.02)):
+        mine = _device_inputs(1, small, device, 9200 + rank, with_do=False)
+        mine["g"] = mine["g"] * scale
+        o, s = forward(mine)
+        if world == 1:
+            check[name] = "single GPU: nothing to compare"
+            continue
+        import torch.distributed as dist
+
+        if rank == world - 1:
+            dist.send(o.contiguous(), 0)
+            dist.send(s.contiguous(), 0)
+        if rank == 0:
+            o_last, s_last = torch.empty_like(o), torch.empty_like(s)
+            dist.recv(o_last, world - 1)
+            dist.recv(s_last, world - 1)
+            parts = [_device_inputs(1, small, device, 9200 + r, with_do=False) for r in range(world)]
+            whole = {n: torch.cat([p[n] for p in parts], 1) for n in parts[0]}
+            whole["g"] = whole["g"] * scale
+            with torch.no_grad():
+                ro, rs = kda_b200.chunk_kda(whole["q"], whole["k"], whole["v"], whole["g"], whole["beta"],
+                                            output_final_state=True)
+            ro = ro[:, -small:].float()
+            check[name] = {
+                "output_last_slice": float((o_last.float() - ro).abs().max() / ro.abs().max()),
+                "final_state": float((s_last - rs).abs().max() / rs.abs().max())}
+            del parts, whole
+        del mine
+        torch.cuda.empty_cache()
+    if rank == 0 and world > 1:
+        check["tolerance"] = 2e-2
+        check["ok"] = all(v <= 2e-2 for c in check.values() if isinstance(c, dict) for v in c.values())
+    return {"workload": f"config4: one sequence of {tokens} tokens, H{H}, forward with final state, "
+                        f"{world} contiguous slice(s); boundary states over an NCCL point-to-point chain",
+            "scaling": "strong", "ms_per_step": round(ms / iters, 3),
+            "tokens_per_s": round(tokens * iters / (ms * 1e-3), 1),
+            "per_rank_ms": {"prepare": [round(r[0], 3) for r in per_rank],
+                            "state_fwd": [round(r[1], 3) for r in per_rank],
+                            "state_fwd_launches": [int(r[2]) for r in per_rank]},
+            "check": check}
 
 
 def bench_decode(kda_b200, _cabi, device, peaks, nseq=256, steps=200):
@@ -579,26 +740,43 @@ def bench_preops(device, peaks, batch=8, tokens=4096, iters=20):
     return out
 
 
+CPU_SAMPLE = "chunk_kda fwd+bwd, B=1 T=1024 H=32 K=V=128, fp32, eager PyTorch on the host cores"
+
+
 def cpu_sample_step(threads):
-    """One bounded CPU sample: the oracle port, fwd+bwd, B=1 T=1024 H=32 K=V=128 fp32."""
+    """One bounded CPU sample of the path: B=1 T=1024 H=32 K=V=128 fp32 forward + backward, by the
+    reference's own ``chunk_kda(impl="reference")`` when oracle/_ref holds it, else by the oracle
+    port.  Returns (tokens, seconds, kind)."""
+    from oracle import build_ref
     from oracle import kda_oracle as orc
 
     torch.set_num_threads(threads)
     inp = orc.make_inputs(1, 1024, H, D, D, seed=7)
     gen = torch.Generator().manual_seed(3)
     do = torch.randn(inp["v"].shape, generator=gen)
+    reference_chunk_kda = build_ref.load_reference_chunk_kda()
     t0 = time.perf_counter()
-    orc.chunk_kda_grads_ref(inp["q"], inp["k"], inp["v"], inp["cum_gate"], inp["beta"], do,
-                            dtype=torch.float32)
-    return 1024, time.perf_counter() - t0
+    if reference_chunk_kda is not None:
+        leaves = [inp[n].clone().requires_grad_() for n in ("q", "k", "v", "cum_gate", "beta")]
+        o, _ = reference_chunk_kda(*leaves, impl="reference")
+        torch.autograd.grad(o, leaves, do)
+        kind = "reference"
+    else:
+        orc.chunk_kda_grads_ref(inp["q"], inp["k"], inp["v"], inp["cum_gate"], inp["beta"], do,
+                                dtype=torch.float32)
+        kind = "port"
+    return 1024, time.perf_counter() - t0, kind
 
 
 def cpu_baseline(bounded=True):
+    """One warm-up, then the best of three samples."""
     threads = os.cpu_count() or 1
-    tokens, secs = cpu_sample_step(threads)
-    return {"value": round(tokens / secs, 2), "unit": "tokens/s", "cores": threads, "kind": "port",
-            "sample": "oracle port (eager PyTorch fp32) chunk fwd+bwd, B=1 T=1024 H=32 K=V=128, "
-                      "1 run"}
+    cpu_sample_step(threads)
+    best = min((cpu_sample_step(threads) for _ in range(3)), key=lambda r: r[1])
+    tokens, secs, kind = best
+    return {"value": round(tokens / secs, 2), "unit": "tokens/s", "cores": threads, "kind": kind,
+            "sample": CPU_SAMPLE + ("" if kind == "reference" else " (oracle port)")
+                      + "; 1 warm-up, best of 3"}
 
 
 def run_reference(args):
@@ -606,14 +784,17 @@ def run_reference(args):
     if rank != 0:
         return
     threads = os.cpu_count() or 1
-    for _ in range(args.warmup):
+    kind = "port"
+    for _ in range(max(args.warmup, 1)):
         cpu_sample_step(threads)
     total_tokens, total_s = 0, 0.0
     for _ in range(args.steps):
-        n, s = cpu_sample_step(threads)
+        n, s, kind = cpu_sample_step(threads)
         total_tokens += n
         total_s += s
     value = total_tokens / total_s
+    what = ("the reference's chunk_kda(impl=\"reference\") from oracle/_ref" if kind == "reference"
+            else "oracle port")
     line = {
         "impl": "reference", "metric": METRIC, "value": round(value, 2), "unit": "tokens/s",
         "n_gpus": int(os.environ.get("WORLD_SIZE", "1")), "steps": args.steps,
@@ -623,7 +804,7 @@ def run_reference(args):
         "config": {"workload": "config1 shape, bounded CPU sample per step: chunk_kda fwd+bwd "
                                f"B=1 T=1024 H={H} K=V={D} chunk={CHUNK} (fp32, host cores)"},
         "cpu_baseline": {"value": round(value, 2), "unit": "tokens/s", "cores": threads,
-                         "kind": "port", "sample": "oracle port, B=1 T=1024 H=32 per step"},
+                         "kind": kind, "sample": f"{what}, B=1 T=1024 H=32 per step"},
         "e2e": {"value": round(value, 2), "unit": "tokens/s", "h2d_bytes_per_step": 0,
                 "d2h_bytes_per_step": 0},
     }
@@ -640,6 +821,8 @@ def main():
     ap.add_argument("--skip-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--skip-e2e", action="store_true", help="skip the host-buffer leg")
     ap.add_argument("--skip-decode", action="store_true", help="skip the decode-step measurement")
+    ap.add_argument("--skip-splits", action="store_true",
+                    help="skip the strong-scaling and context-parallel legs")
     ap.add_argument("--other-configs", action="store_true",
                     help="also time the packed (config 2) and 1M-token (config 4) workloads")
     ap.add_argument("--preops-only", action="store_true",

@@ -136,6 +136,32 @@ int kda_chunk_fwd(const void* q, const void* k, const void* v, const float* cum_
                   int nseq, int64_t tokens, int heads, int key_dim, int value_dim, int num_chunks,
                   void* workspace, int64_t workspace_bytes, void* stream);
 
+/* kda_chunk_fwd / kda_chunk_fwd_save for a dense batch of `batch` rows with `tokens_per_row` tokens each
+ * (q, k, v, out [batch * tokens_per_row, H, 128]; states [batch, H, 128, 128]): the offsets are built
+ * on the device.  A batch with fewer (row, head) chains than half the SMs and rows of at least 128
+ * chunks is cut into segments of whole chunks that are walked in parallel and stitched by the affine
+ * boundary-state map (the scheme of kda_chunk_slice_map inside one GPU): a pass from zero states, the
+ * chain h_in(s+1) = M_s h_in(s) + b_s, and a corrective pass over the leading chunks that the true
+ * entering state can still reach (measured: the chunks until the running transition is exactly
+ * zero in fp32; all of them when the gates never forget).  Results equal the unsegmented walk to
+ * fp32 resolution of the state.  workspace: kda_chunk_fwd_dense_workspace_bytes(.., keep) bytes with
+ * keep = 1 for the _save form, whose buffer kda_chunk_bwd_saved accepts as `saved`.
+ * kda_set_row_segments forces the number of segments per row (0 = choose; for tests and tuning).
+ * Replaces attn_gym::kda_chunk_fwd / _with_state (kda/ops.py:18-29); the reference lowers dense
+ * batches to the packed form too (kda/impl/fused.py:175-182) and walks every row serially. */
+int64_t kda_chunk_fwd_dense_workspace_bytes(int batch, int64_t tokens_per_row, int heads, int keep);
+int kda_chunk_fwd_dense(const void* q, const void* k, const void* v, const float* cum_gate,
+                        const float* beta, const float* initial_state, float* final_state, void* out,
+                        void* aqk, void* akk, int batch, int64_t tokens_per_row, int heads,
+                        int key_dim, int value_dim, void* workspace, int64_t workspace_bytes,
+                        void* stream);
+int kda_chunk_fwd_dense_save(const void* q, const void* k, const void* v, const float* cum_gate,
+                             const float* beta, const float* initial_state, float* final_state,
+                             void* out, void* aqk, void* akk, int batch, int64_t tokens_per_row,
+                             int heads, int key_dim, int value_dim, void* saved, int64_t saved_bytes,
+                             void* stream);
+int kda_set_row_segments(int segments);
+
 /* kda_chunk_fwd for callers that cannot allocate device memory while they run (an inference
  * server whose memory pool already owns the whole GPU, a plugin that may not call cudaMalloc after
  * start-up).  Same arguments and results as kda_chunk_fwd without the workspace: the scratch is a

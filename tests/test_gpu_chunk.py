@@ -144,6 +144,44 @@ def test_value_split_of_the_state_recurrence_gives_the_same_bits(case, recompute
     assert lib.kda_device_error_word() == 0
 
 
+@pytest.mark.parametrize("gate_scale", [1.0, 0.02], ids=["forgetful-gates", "mild-gates"])
+@pytest.mark.parametrize("segments", [2, 3, 5])
+def test_rows_walked_in_parallel_segments_match_the_serial_walk(segments, gate_scale):
+    """Long rows of a small dense batch are cut into segments that are walked in parallel and
+    stitched by the affine boundary-state map (kda_chunk_fwd_dense).  Forced here on a short case:
+    outputs, final states and -- through the kept h[c] / v_new -- all gradients must agree with the
+    serial walk to the resolution of the fp32 state, for gates that forget within a few chunks (the
+    corrective pass is cut short) and for gates that never do (it redoes every chunk)."""
+    from kda_b200 import _cabi
+
+    inp = _case(2, 64 * 23 + 17, 2, seed=21)          # 24 chunks per row, partial tail
+    inp["cum_gate"] = inp["cum_gate"] * gate_scale
+    inp["h0"] = 20.0 * inp["h0"]
+    gen = torch.Generator().manual_seed(97)
+    do = torch.randn(inp["v"].shape, generator=gen)
+    dst = torch.randn(inp["h0"].shape, generator=gen)
+    lib = _cabi.lib()
+    serial = _run_fused(inp, do, dst, grad=True)
+    try:
+        assert lib.kda_set_row_segments(segments) == 0
+        split = _run_fused(inp, do, dst, grad=True)
+        plain = _run_fused(inp)                         # the forward-only entry point as well
+    finally:
+        lib.kda_set_row_segments(0)
+    # gates that forget: the corrective pass restores the serial walk's bits almost everywhere;
+    # gates that do not: the boundary states come from M h_in + b, whose bf16 product roundings differ
+    # from the serial walk's, so the two agree like two bf16 evaluations do
+    tol = 1e-4 if gate_scale == 1.0 else 1e-2
+    for name in serial:
+        assert_normalised(split[name].float(), serial[name].float(), tol, f"{segments} segments: {name}")
+    assert torch.equal(plain["o"], split["o"]) and torch.equal(plain["state"], split["state"])
+    ref = orc.chunk_kda_grads_ref(inp["q"].float(), inp["k"].float(), inp["v"].float(), inp["cum_gate"],
+                                  inp["beta"], do.bfloat16().float(), inp["h0"], dst, dtype=torch.float32)
+    for name in serial:
+        assert_normalised(split[name].float(), ref[name], TOL, f"{segments} segments: {name} vs oracle")
+    assert lib.kda_device_error_word() == 0
+
+
 def test_dense_batch_equals_packed():
     """A dense batch and its explicit equal-length packing give bitwise-equal results
     (reference: test/test_kda_cute_forward.py:368-410)."""
