@@ -57,84 +57,143 @@ def shard_ranges(batch: int, heads: int, world: int, rank: int) -> Tuple[slice, 
     raise ValueError(f"cannot tile batch={batch} x heads={heads} over {world} ranks")
 
 
-class CudaSlice:
-    """One rank's slice on the CUDA kernels: ``prepare`` once, then any number of state passes."""
+def _auto_segments(batch, tokens, heads, device):
+    """Segments per row for the walks of a slice: as many as fill the SMs, at least 64 chunks each."""
+    sms = torch.cuda.get_device_properties(device).multi_processor_count
+    chains = batch * heads
+    segs = min(8, sms // chains) if chains * 2 <= sms else 1
+    return max(1, min(segs, ((tokens + 63) // 64) // 64))
 
-    def __init__(self, q, k, v, gate, beta):
+
+class CudaSlice:
+    """One rank's slice on the CUDA kernels: ``prepare`` once, then any number of state passes.
+
+    The rows of the slice are cut into ``segments`` runs of whole chunks (default: as many as fill
+    the GPU) that the state kernels walk in parallel; the affine maps of the segments are composed
+    into the map of the slice, and the entering state of every segment follows from the slice's
+    entering state by the same maps.  One segment per row is the plain serial walk."""
+
+    def __init__(self, q, k, v, gate, beta, segments=None):
         from . import _cabi
-        from .ops import _dense_offsets
 
         self._cabi = _cabi
         batch, tokens, heads, _ = q.shape
+        dev = q.device
         self.shape = (batch, tokens, heads)
         q, k, v = (t.to(torch.bfloat16).contiguous() for t in (q, k, v))
         self.gate, beta = gate.float().contiguous(), beta.float().contiguous()
-        self.cu, self.offsets, capacity = _dense_offsets(q)
+        row_chunks = (tokens + 63) // 64
+        segs = segments or _auto_segments(batch, tokens, heads, dev)
+        seg_chunks = -(-row_chunks // max(1, min(segs, row_chunks)))
+        self.segs = -(-row_chunks // seg_chunks)
+        self.nseq = batch * self.segs
+        idx = torch.arange(self.nseq + 1, dtype=torch.int32, device=dev)
+        row, sg = idx // self.segs, idx % self.segs
+        chunks = torch.clamp(sg * seg_chunks, max=row_chunks)
+        self.cu = (row * tokens + torch.clamp(chunks * 64, max=tokens)).to(torch.int32)
+        self.offsets = (row * row_chunks + chunks).to(torch.int32)
+        capacity = batch * row_chunks
         self.like_v = v
-        self.aqk = torch.empty(batch, tokens, heads, 64, dtype=q.dtype, device=q.device)
+        self.aqk = torch.empty(batch, tokens, heads, 64, dtype=q.dtype, device=dev)
         akk = torch.empty_like(self.aqk)
         nbytes = _cabi.lib().kda_chunk_fwd_workspace_bytes(batch * tokens, heads)
-        self.ws = torch.empty(nbytes, dtype=torch.uint8, device=q.device)
+        self.ws = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+        self._maps = None
         _cabi.call("kda_chunk_fwd_prepare", 2, _cabi.ptr(q), _cabi.ptr(k), _cabi.ptr(v),
                    _cabi.ptr(self.gate), _cabi.ptr(beta), _cabi.ptr(self.aqk), _cabi.ptr(akk),
-                   _cabi.ptr(self.cu), _cabi.ptr(self.offsets), batch, batch * tokens, heads,
+                   _cabi.ptr(self.cu), _cabi.ptr(self.offsets), self.nseq, batch * tokens, heads,
                    capacity, _cabi.ptr(self.ws), nbytes, _cabi.stream())
 
+    # ---- single launches over the segments (states are [batch * segments, H, 128, 128]) ----------
     def _state(self, h_in, out, use_u, want_final=True, limit=None):
         c = self._cabi
         batch, tokens, heads = self.shape
-        final = (torch.empty(batch, heads, 128, 128, dtype=torch.float32, device=self.gate.device)
+        final = (torch.empty(self.nseq, heads, 128, 128, dtype=torch.float32, device=self.gate.device)
                  if want_final else None)
         h_in = None if h_in is None else h_in.float().contiguous()
         c.call("kda_chunk_fwd_state", 1, c.ptr(self.gate), c.ptr(h_in), c.ptr(final), c.ptr(out),
-               c.ptr(self.aqk), c.ptr(self.cu), c.ptr(self.offsets), batch, batch * tokens, heads,
+               c.ptr(self.aqk), c.ptr(self.cu), c.ptr(self.offsets), self.nseq, batch * tokens, heads,
                c.ptr(self.ws), int(use_u), c.ptr(limit), c.stream())
         return out, final
 
-    def run(self, h_in):
-        """(outputs, leaving state) for the entering state ``h_in`` (None = zeros)."""
-        return self._state(h_in, torch.empty_like(self.like_v), True)
-
-    def zero_state_result(self):
-        """b: the leaving state for a zero entering state."""
-        return self._state(None, None, True)[1]
-
-    def transition(self):
-        """M [B, H, K, K]: the leaving state of the homogeneous recurrence started at identity."""
-        batch, _, heads = self.shape
-        eye = torch.eye(128, device=self.gate.device).expand(batch, heads, 128, 128).contiguous()
-        return self._state(eye, None, False)[1]
-
-    def slice_map(self, with_output=True):
-        """One launch for everything that does not depend on the entering state: (outputs for a zero
-        entering state or None, b, M, chunk limit).  Half of the CTAs walk the chains from a zero
-        state, the other half with u = 0 from an identity state; the latter stop once the running
-        transition is exactly zero and report after how many chunks that happened (int32 [B, H])."""
+    def _segment_maps(self, with_output):
         c = self._cabi
         batch, tokens, heads = self.shape
         dev = self.gate.device
-        b = torch.empty(batch, heads, 128, 128, dtype=torch.float32, device=dev)
+        b = torch.empty(self.nseq, heads, 128, 128, dtype=torch.float32, device=dev)
         trans = torch.empty_like(b)
         out = torch.empty_like(self.like_v) if with_output else None
-        limit = torch.zeros(batch, heads, dtype=torch.int32, device=dev)
+        limit = torch.zeros(self.nseq, heads, dtype=torch.int32, device=dev)
         c.call("kda_chunk_slice_map", 1, c.ptr(self.gate), c.ptr(b), c.ptr(trans), c.ptr(out),
-               c.ptr(limit), c.ptr(self.aqk), c.ptr(self.cu), c.ptr(self.offsets), batch,
+               c.ptr(limit), c.ptr(self.aqk), c.ptr(self.cu), c.ptr(self.offsets), self.nseq,
                batch * tokens, heads, c.ptr(self.ws), c.stream())
         return out, b, trans, limit
 
-    def correct(self, out, h_in, limit):
-        """Rewrite in ``out`` (outputs for a zero entering state) the leading chunks that the true
-        entering state ``h_in`` can still reach: the first ``limit`` chunks of every chain."""
-        self._state(h_in, out, True, want_final=False, limit=limit)
-        return out
+    def _by_segment(self, t):
+        batch, _, heads = self.shape
+        return t.view(batch, self.segs, heads, 128, 128)
 
     def affine(self, trans, h_in, b):
+        """trans @ h_in + b for stacks of [.., 128, 128] fp32 matrices."""
         c = self._cabi
         out = torch.empty_like(b)
-        c.call("kda_state_affine", 1, c.ptr(trans.contiguous()), c.ptr(h_in.contiguous()),
-               c.ptr(b.contiguous()), c.ptr(out), b.shape[0] * b.shape[1], b.shape[2], b.shape[3],
-               c.stream())
+        trans, h_in, b = trans.contiguous(), h_in.contiguous(), b.contiguous()
+        c.call("kda_state_affine", 1, c.ptr(trans), c.ptr(h_in), c.ptr(b), c.ptr(out),
+               b.numel() // (128 * 128), 128, 128, c.stream())
         return out
+
+    # ---- the slice as a whole (states are [batch, H, 128, 128]) ----------------------------------
+    def slice_map(self, with_output=True):
+        """Everything that does not depend on the entering state, in one launch plus a few tiny
+        compositions: (outputs for zero entering states or None, b, M, chunk limits) with
+        ``leaving state = M @ entering state + b`` for the slice.  Half of the CTAs walk the segments
+        from zero states, the other half with u = 0 from identity states; the latter stop once the
+        running transition is exactly zero and report after how many chunks (int32 per segment and
+        head): only those leading chunks of a segment can still feel its entering state."""
+        out, b, trans, limit = self._segment_maps(with_output)
+        self._maps = (b, trans)
+        bs, ms = self._by_segment(b), self._by_segment(trans)
+        b_all, m_all = bs[:, 0], ms[:, 0]
+        zero = torch.zeros_like(b_all) if self.segs > 1 else None
+        for sg in range(1, self.segs):
+            b_all = self.affine(ms[:, sg], b_all, bs[:, sg])
+            m_all = self.affine(ms[:, sg], m_all, zero)
+        return out, b_all.contiguous(), m_all.contiguous(), limit
+
+    def correct(self, out, h_in, limit):
+        """Rewrite in ``out`` (outputs for zero entering states) the chunks that the true entering
+        state ``h_in`` of the slice can still reach: the first ``limit`` chunks of every segment,
+        each walked from its own entering state (the slice's, pushed through the segment maps)."""
+        b, trans = self._maps
+        bs, ms = self._by_segment(b), self._by_segment(trans)
+        batch, _, heads = self.shape
+        h_seg = torch.empty(batch, self.segs, heads, 128, 128, dtype=torch.float32, device=out.device)
+        h_seg[:, 0] = 0.0 if h_in is None else h_in
+        for sg in range(1, self.segs):
+            h_seg[:, sg] = self.affine(ms[:, sg - 1], h_seg[:, sg - 1], bs[:, sg - 1])
+        self._state(h_seg.view(self.nseq, heads, 128, 128), out, True, want_final=False, limit=limit)
+        return out
+
+    def run(self, h_in):
+        """(outputs, leaving state) for the entering state ``h_in`` (None = zeros)."""
+        if self.segs == 1:
+            return self._state(h_in, torch.empty_like(self.like_v), True)
+        out, b, trans, limit = self.slice_map()
+        h_out = b if h_in is None else self.affine(trans, h_in.float(), b)
+        return self.correct(out, h_in, limit), h_out
+
+    def zero_state_result(self):
+        """b: the leaving state for a zero entering state (serial walk; one segment only)."""
+        assert self.segs == 1
+        return self._state(None, None, True)[1]
+
+    def transition(self):
+        """M [B, H, K, K]: the leaving state of the homogeneous recurrence started at identity
+        (serial walk; one segment only)."""
+        assert self.segs == 1
+        batch, _, heads = self.shape
+        eye = torch.eye(128, device=self.gate.device).expand(batch, heads, 128, 128).contiguous()
+        return self._state(eye, None, False)[1]
 
 
 class ChainTimeout(RuntimeError):

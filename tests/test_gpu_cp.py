@@ -58,7 +58,7 @@ def test_transition_matches_oracle():
     inp = orc.make_inputs(1, 128, 2, 128, 128, seed=32)
     c = {k: (v.cuda() if torch.is_tensor(v) else v) for k, v in inp.items()}
     part = CudaSlice(c["q"].bfloat16(), c["k"].bfloat16(), c["v"].bfloat16(), c["cum_gate"],
-                     c["beta"])
+                     c["beta"], segments=1)
     m = part.transition()
     ref = orc.slice_transition_ref(inp["k"][0].bfloat16().float(), inp["gate_log2"][0],
                                    inp["beta"][0])
@@ -71,7 +71,7 @@ def test_slice_map_in_one_launch_equals_the_two_passes():
     inp = orc.make_inputs(1, 192, 2, 128, 128, seed=34)
     c = {k: (v.cuda() if torch.is_tensor(v) else v) for k, v in inp.items()}
     cum = 0.02 * c["cum_gate"]
-    part = CudaSlice(c["q"].bfloat16(), c["k"].bfloat16(), c["v"].bfloat16(), cum, c["beta"])
+    part = CudaSlice(c["q"].bfloat16(), c["k"].bfloat16(), c["v"].bfloat16(), cum, c["beta"], segments=1)
     out, b, m, limit = part.slice_map()
     assert torch.equal(b, part.zero_state_result())
     assert torch.equal(m, part.transition())
@@ -89,7 +89,8 @@ def test_forgetful_gates_cut_the_corrective_pass_short():
     the full pass with the true entering state gives."""
     inp = orc.make_inputs(1, 2048, 2, 128, 128, seed=35, with_state=True)
     c = {k: (v.cuda() if torch.is_tensor(v) else v) for k, v in inp.items()}
-    part = CudaSlice(c["q"].bfloat16(), c["k"].bfloat16(), c["v"].bfloat16(), c["cum_gate"], c["beta"])
+    part = CudaSlice(c["q"].bfloat16(), c["k"].bfloat16(), c["v"].bfloat16(), c["cum_gate"], c["beta"],
+                     segments=1)
     h_in = 50.0 * c["h0"]
     out, b, m, limit = part.slice_map()
     assert int(limit.max()) < 32 and int(limit.min()) >= 1, limit.tolist()
@@ -101,6 +102,32 @@ def test_forgetful_gates_cut_the_corrective_pass_short():
     assert_normalised(part.affine(m, h_in, b), full_s, 1e-6, "M h_in + b vs the full pass")
     from kda_b200 import _cabi
     assert _cabi.lib().kda_device_error_word() == 0
+
+
+@pytest.mark.parametrize("gate_scale", [1.0, 0.02], ids=["forgetful-gates", "mild-gates"])
+@pytest.mark.parametrize("segments", [2, 3])
+def test_a_slice_walked_in_segments_has_the_same_affine_map(segments, gate_scale):
+    """A slice cut into segments that are walked in parallel: the composed (b, M), the outputs and the
+    leaving state for a given entering state agree with the serial walk of the slice."""
+    inp = orc.make_inputs(1, 64 * 12 + 30, 2, 128, 128, seed=36, with_state=True)
+    c = {k: (v.cuda() if torch.is_tensor(v) else v) for k, v in inp.items()}
+    cum = gate_scale * c["cum_gate"]
+    args = (c["q"].bfloat16(), c["k"].bfloat16(), c["v"].bfloat16(), cum, c["beta"])
+    h_in = 30.0 * c["h0"]
+    serial, split = CudaSlice(*args, segments=1), CudaSlice(*args, segments=segments)
+    assert split.segs == segments and split.nseq == segments
+    so, sb, sm, _ = serial.slice_map()
+    po, pb, pm, limit = split.slice_map()
+    tol = 1e-4 if gate_scale == 1.0 else 1e-2
+    assert_normalised(pb, sb, tol, "composed b")
+    if gate_scale != 1.0:
+        assert_normalised(pm, sm, tol, "composed M")
+    else:
+        assert float(pm.abs().max()) == 0.0 and float(sm.abs().max()) == 0.0
+    ref_o, ref_s = serial.run(h_in)
+    got_o, got_s = split.run(h_in)
+    assert_normalised(got_o.float(), ref_o.float(), tol, "outputs of the segmented walk")
+    assert_normalised(got_s, ref_s, tol, "leaving state of the segmented walk")
 
 
 @pytest.mark.parametrize("world", [2, 3])
