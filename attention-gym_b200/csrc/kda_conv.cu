@@ -785,11 +785,15 @@ __global__ void __launch_bounds__(128) conv_bwd_dx_edge_kernel(const ConvParams 
   if (c0 >= p.C) return;
   int64_t t0, t1;
   conv_run_of(p, blockIdx.x, t0, t1);
-  if (p.cu_seqlens) t1 = min(t1, (int64_t)p.cu_seqlens[p.nseq]);
   {
+    // the same test, on the same unclamped run, that made the one-pass kernel take or leave this
+    // run; clamping to the packed end first would make a run that ends in the unused tail of a
+    // fixed-capacity buffer look "simple" here although the one-pass kernel left it
     int seq_; int64_t bos_, eos_;
     if (t0 >= t1 || conv_run_simple(p, t0, t1, seq_, bos_, eos_)) return;
   }
+  if (p.cu_seqlens) t1 = min(t1, (int64_t)p.cu_seqlens[p.nseq]);
+  if (t0 >= t1) return;
   const T* x = reinterpret_cast<const T*>(p.x);
   const T* w = reinterpret_cast<const T*>(p.w);
   const T* dy = reinterpret_cast<const T*>(p.dy);

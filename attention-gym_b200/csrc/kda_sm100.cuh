@@ -43,10 +43,10 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(saddr(bar)), "r"(bytes)
                : "memory");
 }
-// Returns false if the phase did not complete within the spin limit.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+// Returns false if the phase did not complete within `limit` polls.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int limit = kSpinLimit) {
   uint32_t ok = 0;
-  for (int spin = 0; spin < kSpinLimit; ++spin) {
+  for (int spin = 0; spin < limit; ++spin) {
     asm volatile(
         "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}\n"

@@ -757,6 +757,30 @@ int launch_state_bwd_tc(const bf16* w, const bf16* kg, const bf16* qg, const bf1
 
 }  // namespace kda
 
+// Self-test of the bounded waits: one warp waits, with a small poll limit, on a barrier that nothing
+// ever arrives on.  The wait must run out, raise the error word (code 2) and let the kernel return
+// normally, leaving the context usable.  Nothing faults, traps or spins without bound.
+namespace kda {
+__global__ void bounded_wait_selftest_kernel(int* error, int limit) {
+  __shared__ uint64_t bar;
+  if (threadIdx.x == 0) {
+    sm100::mbar_init(&bar, 1);
+    sm100::mbar_init_fence();
+  }
+  __syncthreads();
+  if (threadIdx.x == 0 && !sm100::mbar_wait(&bar, 0, limit)) atomicExch(error, 2);
+}
+}  // namespace kda
+
+extern "C" int kda_selftest_bounded_wait(int poll_limit, void* stream) {
+  if (poll_limit < 1 || poll_limit > (1 << 20)) return KDA_ERR_ARG;
+  int* error = nullptr;
+  if (cudaGetSymbolAddress(reinterpret_cast<void**>(&error), kda::g_state_tc_error) != cudaSuccess)
+    return KDA_ERR_LAUNCH;
+  kda::bounded_wait_selftest_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(error, poll_limit);
+  return cudaGetLastError() == cudaSuccess ? KDA_OK : KDA_ERR_LAUNCH;
+}
+
 // 1 if a tensor-memory kernel gave up on a barrier wait since the last call (clears the flag).
 // Synchronises the device; meant for tests and debugging.
 namespace kda { int bwd_chunk_tc_error_word(); int prepare_tc_error_word(); }

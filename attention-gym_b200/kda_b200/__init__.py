@@ -10,12 +10,13 @@ from .chunk_schedule import (RaggedChunkMetadata, chunk_capacity,
                              prepare_ragged_chunk_metadata)
 from .masking import active_token_mask, mask_inactive_token_gradients, mask_inactive_tokens
 from .decode import decode_step
+from .layer import KDAAttention, KDAAttentionOutput
 from .preops import (bounded_gate_cumsum, causal_conv1d, causal_conv1d_decode, gated_output_norm,
                      l2norm)
 from .types import Impl
 
 __all__ = [
-    "Impl", "RaggedChunkMetadata", "active_token_mask", "bounded_gate_cumsum", "causal_conv1d",
+    "Impl", "KDAAttention", "KDAAttentionOutput", "RaggedChunkMetadata", "active_token_mask", "bounded_gate_cumsum", "causal_conv1d",
     "causal_conv1d_decode", "chunk_capacity", "chunk_kda", "decode_step", "gated_output_norm",
     "l2norm",
     "mask_inactive_token_gradients", "mask_inactive_tokens", "prepare_ragged_chunk_metadata",

@@ -27,6 +27,7 @@ launch_count = 0
 _SIGNATURES = {
     "kda_b200_version": (c_int, []),
     "kda_device_error_word": (c_int, []),
+    "kda_selftest_bounded_wait": (c_int, [c_int, c_void_p]),
     "kda_stage_count": (c_int, []),
     "kda_stage_name": (ctypes.c_char_p, [c_int]),
     "kda_stage_timing_enable": (c_int, [c_int]),

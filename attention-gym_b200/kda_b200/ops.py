@@ -44,13 +44,15 @@ _define("kda_chunk_bwd_with_state_grad", _BWD.format(state="Tensor initial_state
         + " -> (Tensor, Tensor, Tensor, Tensor, Tensor, Tensor)")
 # Training pair that keeps the forward intermediates instead of rebuilding them in the backward
 # pass (no reference counterpart: the reference always recomputes, bwd/cute/chunk_kda_bwd.py:54-85).
+# The backward operator also uses the buffer as its workspace (dv2 and dh[c] are written into it),
+# hence the mutation annotation.
 _define("kda_chunk_fwd_saved",
         "(Tensor q, Tensor k, Tensor v, Tensor cumulative_gate, Tensor beta, Tensor? initial_state, "
         "Tensor? cu_seqlens, Tensor? chunk_offsets, bool want_state) "
         "-> (Tensor, Tensor, Tensor, Tensor, Tensor)")
 _define("kda_chunk_bwd_saved",
         "(Tensor q, Tensor k, Tensor v, Tensor cumulative_gate, Tensor beta, Tensor Aqk, Tensor Akk, "
-        "Tensor saved, Tensor? cu_seqlens, Tensor? chunk_offsets, Tensor? d_output, "
+        "Tensor(a!) saved, Tensor? cu_seqlens, Tensor? chunk_offsets, Tensor? d_output, "
         "Tensor? d_final_state, Tensor? initial_state, bool want_state_grad) "
         "-> (Tensor, Tensor, Tensor, Tensor, Tensor, Tensor)")
 _define("kda_recurrent_fwd", _REC + " -> (Tensor, Tensor)")

@@ -39,9 +39,15 @@ extern "C" {
 /* Library identification: returns 100 * major + minor. */
 int kda_b200_version(void);
 
-/* 1 if a tensor-memory kernel abandoned a bounded barrier wait since the last call (clears the
- * flag); synchronises the device.  For tests and debugging; no reference counterpart. */
+/* Non-zero if a tensor-memory kernel abandoned a bounded barrier wait since the last call (clears
+ * the flag); synchronises the device.  Every wait in those kernels polls a bounded number of times;
+ * one that runs out makes the CTA record a code here and leave, so a lost arrival shows up as an
+ * error word, never as a hang.  kda_selftest_bounded_wait exercises exactly that path on purpose:
+ * a one-warp kernel waits `poll_limit` polls on a barrier nothing arrives on, then returns with
+ * code 2 in the error word; the context stays usable.  For tests and debugging; no reference
+ * counterpart. */
 int kda_device_error_word(void);
+int kda_selftest_bounded_wait(int poll_limit, void* stream);
 
 /* Optional per-kernel timing with CUDA events recorded on the launching stream (off by default).
  * kda_stage_timing_read synchronises the recorded events and fills launches[] / total_ms[] (arrays of

@@ -282,3 +282,24 @@ def test_many_short_sequences():
                                      inp["beta"], inp["h0"], cu_seqlens=inp["cu_seqlens"])
     assert_normalised(_active(inp, got["o"]).float(), _active(inp, ref_o), TOL, "output")
     assert_normalised(got["state"], ref_s, TOL, "final states")
+
+
+def test_a_bounded_wait_that_runs_out_reports_and_returns():
+    """Every barrier wait of the tensor-memory kernels is bounded.  The library's self-test makes one
+    run out on purpose (a barrier nothing arrives on, a few thousand polls): the kernel returns, the
+    error word carries the code, it is cleared by reading, and the next normal call works."""
+    from kda_b200 import _cabi
+
+    lib = _cabi.lib()
+    assert lib.kda_device_error_word() == 0
+    assert lib.kda_selftest_bounded_wait(4096, _cabi.stream()) == 0
+    torch.cuda.synchronize()
+    assert lib.kda_device_error_word() == 2
+    assert lib.kda_device_error_word() == 0
+    inp = _case(1, 130, 1, seed=14)
+    res = _run_fused(inp)
+    ref_o, _ = orc.chunk_kda_ref(inp["q"].float(), inp["k"].float(), inp["v"].float(), inp["cum_gate"],
+                                 inp["beta"], inp["h0"])
+    assert_normalised(res["o"].float(), ref_o, TOL, "output after the self-test")
+    assert lib.kda_device_error_word() == 0
+    assert lib.kda_selftest_bounded_wait(0, _cabi.stream()) == -1

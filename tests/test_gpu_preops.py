@@ -137,6 +137,31 @@ def test_conv_packed_and_decode():
     assert torch.equal(pool_gpu[[0, 3, 4]].cpu(), pool[[0, 3, 4]])
 
 
+@pytest.mark.parametrize("offsets,capacity", [([0, 70, 150, 150], 192), ([0, 70, 150], 150),
+                                              ([0, 5, 64, 64, 130, 321], 400), ([0, 128], 130)])
+def test_conv_packed_backward_in_a_fixed_capacity_buffer(offsets, capacity):
+    """bf16, width 4: input and weight gradients of packed sequences whose last 64-token run reaches
+    into the unused tail of the buffer (the one-pass kernel leaves such a run to the edge kernels),
+    against autograd through the CPU oracle; the tail of dx stays zero."""
+    gen = torch.Generator().manual_seed(4)
+    channels, active = 64, offsets[-1]
+    x = torch.randn(1, capacity, channels, generator=gen).bfloat16()
+    w = (0.5 * torch.randn(channels, 4, generator=gen)).bfloat16()
+    dy = torch.randn(1, capacity, channels, generator=gen).bfloat16()
+    dy[:, active:] = 0
+    cu = torch.tensor(offsets, dtype=torch.int32)
+    xr, wr = x.float().requires_grad_(), w.float().requires_grad_()
+    ref, _ = orc.causal_conv1d_ref(xr, wr, "silu", cu, None)
+    want = torch.autograd.grad(ref, (xr, wr), dy.float())
+    xg, wg = x.cuda().requires_grad_(), w.cuda().requires_grad_()
+    y = kda_b200.causal_conv1d(xg, wg, activation="silu", cu_seqlens=cu.cuda())
+    torch.testing.assert_close(y[:, :active].float().cpu(), ref[:, :active].detach(), atol=2e-2, rtol=2e-2)
+    got = torch.autograd.grad(y, (xg, wg), dy.cuda())
+    torch.testing.assert_close(got[0][:, :active].float().cpu(), want[0][:, :active], atol=3e-2, rtol=3e-2)
+    assert got[0][:, active:].abs().max() == 0 if active < capacity else True
+    torch.testing.assert_close(got[1].float().cpu(), want[1], atol=2e-1, rtol=3e-2)
+
+
 @pytest.mark.parametrize("dtype,dim,rows,tol", [
     (torch.bfloat16, 128, (3, 37, 4), 2e-2), (torch.float16, 64, (1, 130, 2), 4e-3),
     (torch.bfloat16, 256, (2, 19, 1), 2e-2), (torch.float32, 128, (2, 33, 4), 2e-5),
