@@ -38,6 +38,8 @@ struct BwdTcParams {
   CUtensorMap tm_dq, tm_dk, tm_dv, tm_dg;
   const float* beta;
   bf16* dq; bf16* dk; bf16* dv; float* dg; float* db;
+  // NORM kernels: q and k are the unnormalised rows, rstd_* their reciprocal norms [tokens, H]
+  const bf16* q; const bf16* k; const float* rstd_q; const float* rstd_k;
   const int32_t* cu_seqlens; const int32_t* chunk_offsets;
   int* error;
   int nseq, H, total;          // total = chunk capacity x heads work items
@@ -60,6 +62,7 @@ __device__ __forceinline__ void tc_mark(const BwdTcParams& p, int it, int slot) 
 namespace bl {  // shared-memory layout (bytes)
 constexpr int HH = 0, DHH = 32768, DO = 65536, VN = 81920, DV2 = 98304, V = 114688, K = 131072,
               Q = 147456, AK = 163840, G = 172032, MISC = 204800, TOTAL = 212992;
+constexpr int NORMX = TOTAL, TOTAL_NORM = TOTAL + 4096;      // row norms and row dots of the NORM kernels
 // overlays (valid once their host tiles are dead)
 constexpr int DWT = HH, KGM = HH + 16384;                       // after phase 0
 constexpr int X = DHH, Y = DHH + 8192, DA = DHH + 16384, DL = DHH + 24576;
@@ -156,8 +159,31 @@ __device__ __forceinline__ float warp_transpose_reduce16(float (&pb)[16], int li
   return pb[0] + __shfl_xor_sync(0xffffffffu, pb[0], 1);
 }
 
+// Sum pb[0..7] over the 32 lanes: afterwards lanes 4e .. 4e+3 all hold the total of entry e.
+__device__ __forceinline__ float warp_transpose_reduce8(float (&pb)[8], int lid) {
+#pragma unroll
+  for (int off = 16, n = 8; off >= 4; off >>= 1, n >>= 1) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (j < n / 2) {
+        const bool up = (lid & off) != 0;
+        const float send = up ? pb[j] : pb[j + n / 2];
+        const float keep = up ? pb[j + n / 2] : pb[j];
+        pb[j] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+      }
+    }
+  }
+  float v = pb[0] + __shfl_xor_sync(0xffffffffu, pb[0], 2);
+  return v + __shfl_xor_sync(0xffffffffu, v, 1);
+}
+
 constexpr int NT = 512;
 
+// NORM: the forward pass normalised q and k inside its first kernel; this kernel receives the
+// unnormalised rows with their reciprocal norms, normalises the q and k tiles as they land (to the
+// same bf16 values), and turns dq, dk into gradients of the unnormalised rows before they leave:
+// dx = rstd (dy - y <dy, y>)  (reference stage: bwd/triton/l2norm_bwd.py:37).
+template <bool NORM>
 __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_constant__ BwdTcParams p) {
   extern __shared__ unsigned char smem_dyn[];
   // 1024-byte alignment by offset, so the compiler still knows this is shared memory
@@ -169,6 +195,8 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
   float* s_db = s_beta + 64;                                              // [2 terms][4 quadrants][64]
   float* s_hd = s_db + 512;                                               // [4][128]
   float* s_kdk = s_hd + 512;                                              // [4][128]
+  float* s_rs = reinterpret_cast<float*>(sm + bl::NORMX);                 // [2 = q, k][64] reciprocal norms
+  float* s_dot = s_rs + 128;                                              // [2][64 rows][4 quadrants] <dy, y>
 
   const int tid = threadIdx.x, warp = tid >> 5, lid = tid & 31;
   const int quad = warp & 3, rq = warp >> 2;
@@ -223,6 +251,7 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
   bool pre = false;             // part 0 of this item's loads was issued by the previous item
   ChunkWork cw_next{};
   float beta_next = 0.f;
+  float rs_next = 0.f;          // NORM: threads 64..191 carry one reciprocal norm each (q rows, then k rows)
   for (int w = blockIdx.x; w < p.total; w += gridDim.x) {
   tc_mark(p, it, 15);
   const int chunk = w / H, head = w - chunk * H;
@@ -232,6 +261,13 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
   const int ty = (int)cw.token0, tx = head * 128;
   if (tid < 64)
     s_beta[tid] = pre ? beta_next : (tid < valid ? p.beta[(cw.token0 + tid) * H + head] : 0.f);
+  if constexpr (NORM) {
+    if (tid >= 64 && tid < 192) {
+      const int row = (tid - 64) & 63;
+      const float* rs = tid < 128 ? p.rstd_q : p.rstd_k;
+      s_rs[tid - 64] = pre ? rs_next : (row < valid ? rs[(cw.token0 + row) * H + head] : 0.f);
+    }
+  }
   __syncthreads();     // the previous item's staging tiles have been read; beta is in place
   tc_mark(p, it, 16);
   if (tid == 0) {
@@ -331,10 +367,34 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
       next_ok = cw_next.valid > 0;
       if (tid < 64)
         beta_next = (next_ok && tid < cw_next.valid) ? p.beta[(cw_next.token0 + tid) * H + head_n] : 0.f;
+      if constexpr (NORM) {
+        if (tid >= 64 && tid < 192) {
+          const int row = (tid - 64) & 63;
+          const float* rs = tid < 128 ? p.rstd_q : p.rstd_k;
+          rs_next = (next_ok && row < cw_next.valid) ? rs[(cw_next.token0 + row) * H + head_n] : 0.f;
+        }
+      }
     }
   }
   tc_mark(p, it, 2);
   if (!mbar_wait(&bar[7], ph)) *s_abort = 1;       // k, q, A, G, v have landed
+  if constexpr (NORM) {
+    // q and k rows to unit norm, rounded to bf16 as the forward pass rounded them: every later read
+    // of these tiles (by threads only) comes after the barrier below
+#pragma unroll
+    for (int n = 0; n < 2; ++n) {
+      const int i = (tid >> 4) + 32 * n, c16 = tid & 15;
+      float x[8];
+      ld_bf8(sm + bl::Q, 8192, i, c16, x);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) x[e] *= s_rs[i];
+      st_bf8(sm + bl::Q, 8192, i, c16, x);
+      ld_bf8(sm + bl::K, 8192, i, c16, x);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) x[e] *= s_rs[64 + i];
+      st_bf8(sm + bl::K, 8192, i, c16, x);
+    }
+  }
   const float glast = ld_g(sG, valid - 1, L);
   if (!mbar_wait(&bar[1], ph)) *s_abort = 1;
   tc_fence_after();
@@ -707,6 +767,21 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
   tc_mark(p, it, 12);
   // every tile but k, q, G is dead from here on: the next item's tiles start arriving
   if (tid == 0 && next_ok) issue_loads(0, chunk_n, head_n, cw_next.token0);
+  // NORM: the unnormalised q, k pieces this thread turns into y again once the epilogue below is
+  // through; fetched now so that their latency hides behind the epilogue instead of ending the item
+  uint4 raw_q[2], raw_k[2];
+  if constexpr (NORM) {
+#pragma unroll
+    for (int n = 0; n < 2; ++n) {
+      const int i = (tid >> 4) + 32 * n;
+      raw_q[n] = raw_k[n] = make_uint4(0, 0, 0, 0);
+      if (i < valid) {
+        const int64_t at = ((cw.token0 + i) * H + head) * 128 + 8 * (tid & 15);
+        raw_q[n] = *reinterpret_cast<const uint4*>(p.q + at);
+        raw_k[n] = *reinterpret_cast<const uint4*>(p.k + at);
+      }
+    }
+  }
 
   // ---- final epilogue: six accumulators, 8 rows at a time; thread = channel L, rows r0 .. r0 + 15 ------
   //   DQ: dq_inter^T   DVB: dq_intra^T   DKS: dks^T   DKG: dkgb^T   X: X1^T   DW: dk2^T
@@ -732,6 +807,7 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
       unsigned char* rowB = sm + constB + rb * 128;
       unsigned char* rowG = sm + constG + rb * 128;
       float a[8], a2[8], e[8], f[8], kr[8], dkr[8], dgr[8];
+      float ydq[8], ydk[8];       // NORM: y dy per row, summed over the channels below
       int oB[8], oG[8];
       const float4 b0 = *reinterpret_cast<const float4*>(s_beta + rb), b1 = *reinterpret_cast<const float4*>(s_beta + rb + 4);
       const float bt[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
@@ -751,6 +827,7 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
         const float dqv = e[ii] * fmaf(a[ii], sE0, a2[ii]);
         bf16* cell = reinterpret_cast<bf16*>(rowB + bl::Q + oB[ii]);
         dgr[ii] = __bfloat162float(*cell) * dqv;
+        if constexpr (NORM) ydq[ii] = dgr[ii];
         *cell = __float2bfloat16(dqv);
       }
       tmem_ld8(tl + tc::DKS + rb, a);
@@ -776,9 +853,17 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
       for (int ii = 0; ii < 8; ++ii) {
         const float x = a[ii] * f[ii];
         *reinterpret_cast<bf16*>(rowB + bl::K + oB[ii]) = __float2bfloat16(dkr[ii] + x);
+        if constexpr (NORM) ydk[ii] = kr[ii] * (dkr[ii] + x);
         float dgv = fmaf(-kr[ii], x, dgr[ii]) * kLn2;
         if (rb + ii == valid - 1) dgv += hdv;
         *reinterpret_cast<float*>(rowG + bl::G + oG[ii]) = dgv;
+      }
+      if constexpr (NORM) {      // one slot per (row, channel quadrant), summed in a fixed order later
+        const float tq = warp_transpose_reduce8(ydq, lid), tk = warp_transpose_reduce8(ydk, lid);
+        if ((lid & 3) == 0) {
+          s_dot[(rb + (lid >> 2)) * 4 + quad] = tq;
+          s_dot[256 + (rb + (lid >> 2)) * 4 + quad] = tk;
+        }
       }
     }
     {
@@ -787,6 +872,32 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
     }
   }
   tc_mark(p, it, 13);
+  if constexpr (NORM) {
+    // dq, dk (staged, bf16) -> gradients of the unnormalised rows, one (row, 8 channels) piece per task;
+    // y is rebuilt from the unnormalised row exactly as it was when the tile landed
+    __syncthreads();
+#pragma unroll
+    for (int n = 0; n < 2; ++n) {
+      const int i = (tid >> 4) + 32 * n, c16 = tid & 15;
+#pragma unroll
+      for (int t = 0; t < 2; ++t) {
+        const float4 d4 = *reinterpret_cast<const float4*>(s_dot + 256 * t + 4 * i);
+        const float dot = (d4.x + d4.y) + (d4.z + d4.w), rs = s_rs[64 * t + i];
+        uint4 raw = t == 0 ? raw_q[n] : raw_k[n];
+        float y[8], d[8];
+        unpack8(raw, y);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) y[e] *= rs;
+        pack8v(y, raw);
+        unpack8(raw, y);
+        unsigned char* tile = sm + (t == 0 ? bl::Q : bl::K);
+        ld_bf8(tile, 8192, i, c16, d);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) d[e] = rs * (d[e] - y[e] * dot);
+        st_bf8(tile, 8192, i, c16, d);
+      }
+    }
+  }
   fence_async_smem();
   __syncthreads();
   if (valid == 64) {
@@ -840,11 +951,14 @@ static __device__ int g_bwd_tc_error = 0;
 int launch_bwd_chunk_tc(const bf16* q, const bf16* k, const bf16* v, const float* g, const float* beta,
                         const bf16* akk, const bf16* h, const bf16* dh, const bf16* vnew,
                         const bf16* dv2, const bf16* dout, bf16* dq, bf16* dk, bf16* dv, float* dg,
-                        float* db, const int32_t* cu, const int32_t* co, int nseq, int H,
-                        int64_t tokens, int chunks, long long* prof, cudaStream_t s) {
+                        float* db, const float* rstd_q, const float* rstd_k, const int32_t* cu,
+                        const int32_t* co, int nseq, int H, int64_t tokens, int chunks, long long* prof,
+                        cudaStream_t s) {
   if (chunks == 0) return KDA_OK;
+  if ((rstd_q == nullptr) != (rstd_k == nullptr)) return KDA_ERR_ARG;
   BwdTcParams p;
   p.prof = prof;
+  p.q = q; p.k = k; p.rstd_q = rstd_q; p.rstd_k = rstd_k;
   const int64_t cols = (int64_t)H * 128, hrows = (int64_t)chunks * H * 128;
   bool ok = make_tensor_map(&p.tm_h, h, hrows, 128, 128) && make_tensor_map(&p.tm_dh, dh, hrows, 128, 128) &&
             make_tensor_map(&p.tm_do, dout, tokens, cols, 64) && make_tensor_map(&p.tm_vn, vnew, tokens, cols, 64) &&
@@ -865,12 +979,12 @@ int launch_bwd_chunk_tc(const bf16* q, const bf16* k, const bf16* v, const float
     return KDA_ERR_LAUNCH;
   if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p.error), g_bwd_tc_error) != cudaSuccess)
     return KDA_ERR_LAUNCH;
-  const int smem = bl::TOTAL + 1024;
-  if (cudaFuncSetAttribute(kda_bwd_chunk_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
-      cudaSuccess)
+  const int smem = (rstd_q ? bl::TOTAL_NORM : bl::TOTAL) + 1024;
+  auto kernel = rstd_q ? kda_bwd_chunk_tc_kernel<true> : kda_bwd_chunk_tc_kernel<false>;
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
     return KDA_ERR_LAUNCH;
   StageScope timing(kStageBwdChunk, s);
-  kda_bwd_chunk_tc_kernel<<<(unsigned)(p.total < sms ? p.total : sms), NT, smem, s>>>(p);
+  kernel<<<(unsigned)(p.total < sms ? p.total : sms), NT, smem, s>>>(p);
   return cudaGetLastError() == cudaSuccess ? KDA_OK : KDA_ERR_LAUNCH;
 }
 

@@ -20,8 +20,9 @@ int launch_state_bwd_tc(const bf16* w, const bf16* kg, const bf16* qg, const bf1
 int launch_bwd_chunk_tc(const bf16* q, const bf16* k, const bf16* v, const float* g, const float* beta,
                         const bf16* akk, const bf16* h, const bf16* dh, const bf16* vnew,
                         const bf16* dv2, const bf16* dout, bf16* dq, bf16* dk, bf16* dv, float* dg,
-                        float* db, const int32_t* cu, const int32_t* co, int nseq, int H,
-                        int64_t tokens, int chunks, long long* prof, cudaStream_t s);
+                        float* db, const float* rstd_q, const float* rstd_k, const int32_t* cu,
+                        const int32_t* co, int nseq, int H, int64_t tokens, int chunks, long long* prof,
+                        cudaStream_t s);
 int launch_recompute(const void* q, const void* k, const void* v, const float* g, const float* beta,
                      const void* aqk, const void* akk, const float* h0, void* w, void* u, void* kg,
                      void* qg, void* h_out, void* vnew_out, const int32_t* cu, const int32_t* co,
@@ -50,7 +51,7 @@ extern "C" int64_t kda_chunk_bwd_workspace_bytes(int64_t tokens, int heads, int6
   return (6 * nd + 2 * hs + nd) * 2 + 256;
 }
 
-static int chunk_bwd_impl(bool saved, const void* q, const void* k, const void* v, const float* cum_gate,
+static int chunk_bwd_impl(bool saved, const float* rstd_q, const float* rstd_k, const void* q, const void* k, const void* v, const float* cum_gate,
                           const float* beta, const void* aqk, const void* akk,
                           const float* initial_state, const void* d_out,
                           const float* d_final_state, void* dq, void* dk, void* dv, float* dg,
@@ -86,8 +87,8 @@ static int chunk_bwd_impl(bool saved, const void* q, const void* k, const void* 
   if (rc) return rc;
   return kda::launch_bwd_chunk_tc(qb, kb, vb, cum_gate, beta, (const bf16*)akk, hbuf, dhbuf, vnew, dv2,
                                   (const bf16*)d_out, (bf16*)dq, (bf16*)dk, (bf16*)dv, dg, dbeta,
-                                  cu_seqlens, chunk_offsets, nseq, heads, tokens, num_chunks,
-                                  g_prof_buffer, s);
+                                  rstd_q, rstd_k, cu_seqlens, chunk_offsets, nseq, heads, tokens,
+                                  num_chunks, g_prof_buffer, s);
 }
 
 #define KDA_BWD_ARGS                                                                              \
@@ -101,9 +102,17 @@ static int chunk_bwd_impl(bool saved, const void* q, const void* k, const void* 
       d_initial_state, cu_seqlens, chunk_offsets, nseq, tokens, heads, key_dim, value_dim, num_chunks
 
 extern "C" int kda_chunk_bwd(KDA_BWD_ARGS, void* workspace, int64_t workspace_bytes, void* stream) {
-  return chunk_bwd_impl(false, KDA_BWD_PASS, workspace, workspace_bytes, stream);
+  return chunk_bwd_impl(false, nullptr, nullptr, KDA_BWD_PASS, workspace, workspace_bytes, stream);
 }
 
 extern "C" int kda_chunk_bwd_saved(KDA_BWD_ARGS, void* saved, int64_t saved_bytes, void* stream) {
-  return chunk_bwd_impl(true, KDA_BWD_PASS, saved, saved_bytes, stream);
+  return chunk_bwd_impl(true, nullptr, nullptr, KDA_BWD_PASS, saved, saved_bytes, stream);
+}
+
+// Backward of kda_chunk_fwd_qknorm(keep = 1): q and k are the unnormalised rows, rstd_q / rstd_k the
+// reciprocal norms the forward pass wrote; dq and dk come back as gradients of the unnormalised rows.
+extern "C" int kda_chunk_bwd_qknorm_saved(KDA_BWD_ARGS, const float* rstd_q, const float* rstd_k,
+                                          void* saved, int64_t saved_bytes, void* stream) {
+  if (!rstd_q || !rstd_k) return KDA_ERR_ARG;
+  return chunk_bwd_impl(true, rstd_q, rstd_k, KDA_BWD_PASS, saved, saved_bytes, stream);
 }

@@ -23,6 +23,7 @@ struct ChunkParams {
   const bf16* q; const bf16* k; const bf16* v; const float* g; const float* beta;
   bf16* aqk; bf16* akk;                 // tape [N, H, 64]
   bf16* w; bf16* u; bf16* kg; bf16* qg;  // [N, H, 128]
+  float* rstd_q; float* rstd_k; float eps;   // q / k arrive unnormalised when these are set
   const float* h0; float* ht;
   float* trans_out;                     // slice transition [nseq, H, 128, 128], or NULL
   const int32_t* limit_in; int32_t* limit_out;   // per (sequence, head) chunk limits of the state walk, or NULL
@@ -35,8 +36,9 @@ struct ChunkParams {
 };
 
 int launch_prepare_tc(const bf16* q, const bf16* k, const bf16* v, const float* g, const float* beta,
-                      bf16* aqk, bf16* akk, bf16* w, bf16* u, bf16* kg, bf16* qg, const int32_t* cu,
-                      const int32_t* co, int nseq, int H, int64_t tokens, int chunks, cudaStream_t s);
+                      bf16* aqk, bf16* akk, bf16* w, bf16* u, bf16* kg, bf16* qg, float* rstd_q,
+                      float* rstd_k, float eps, const int32_t* cu, const int32_t* co, int nseq, int H,
+                      int64_t tokens, int chunks, cudaStream_t s);
 int launch_state_fwd_tc(const bf16* w, const bf16* u, const bf16* kg, const bf16* qg, const bf16* aqk,
                         const float* g, const float* h0, float* ht, float* trans_out,
                         const int32_t* limit_in, int32_t* limit_out, bf16* o, bf16* h_out,
@@ -45,8 +47,8 @@ int launch_state_fwd_tc(const bf16* w, const bf16* u, const bf16* kg, const bf16
 
 // forward: the whole chunk-parallel part (tape, w, u, kg, qg) in one tcgen05 kernel
 int launch_prepare(const ChunkParams& p, int chunks, cudaStream_t s) {
-  return launch_prepare_tc(p.q, p.k, p.v, p.g, p.beta, p.aqk, p.akk, p.w, p.u, p.kg, p.qg, p.cu_seqlens,
-                           p.chunk_offsets, p.nseq, p.H, p.tokens, chunks, s);
+  return launch_prepare_tc(p.q, p.k, p.v, p.g, p.beta, p.aqk, p.akk, p.w, p.u, p.kg, p.qg, p.rstd_q,
+                           p.rstd_k, p.eps, p.cu_seqlens, p.chunk_offsets, p.nseq, p.H, p.tokens, chunks, s);
 }
 int launch_state_fwd(const ChunkParams& p, cudaStream_t s) {
   return launch_state_fwd_tc(p.w, p.u, p.kg, p.qg, p.aqk, p.g, p.h0, p.ht, p.trans_out, p.limit_in,
@@ -78,7 +80,7 @@ int launch_recompute(const void* q, const void* k, const void* v, const float* g
 
 using kda::bf16;
 
-static int chunk_fwd_impl(bool keep, const void* q, const void* k, const void* v, const float* cum_gate,
+static int chunk_fwd_impl(bool keep, float* rstd_q, float* rstd_k, float eps, const void* q, const void* k, const void* v, const float* cum_gate,
                              const float* beta, const float* initial_state, float* final_state,
                              void* out, void* aqk, void* akk, const int32_t* cu_seqlens,
                              const int32_t* chunk_offsets, int nseq, int64_t tokens, int heads,
@@ -100,6 +102,7 @@ static int chunk_fwd_impl(bool keep, const void* q, const void* k, const void* v
   p.q = (const bf16*)q; p.k = (const bf16*)k; p.v = (const bf16*)v; p.g = cum_gate; p.beta = beta;
   p.aqk = (bf16*)aqk; p.akk = (bf16*)akk;
   p.w = ws; p.u = ws + nd; p.kg = ws + 2 * nd; p.qg = ws + 3 * nd;
+  p.rstd_q = rstd_q; p.rstd_k = rstd_k; p.eps = eps;
   p.h0 = initial_state; p.ht = final_state; p.o = (bf16*)out;
   // keep: the workspace has the backward layout (w, u, kg, qg, v_new, dv2, h, dh) and the state
   // walk also leaves v_new and the chunk-entry states there
@@ -121,9 +124,25 @@ extern "C" int kda_chunk_fwd(const void* q, const void* k, const void* v, const 
                              const int32_t* chunk_offsets, int nseq, int64_t tokens, int heads,
                              int key_dim, int value_dim, int num_chunks, void* workspace,
                              int64_t workspace_bytes, void* stream) {
-  return chunk_fwd_impl(false, q, k, v, cum_gate, beta, initial_state, final_state, out, aqk, akk,
-                        cu_seqlens, chunk_offsets, nseq, tokens, heads, key_dim, value_dim,
+  return chunk_fwd_impl(false, nullptr, nullptr, 0.f, q, k, v, cum_gate, beta, initial_state, final_state,
+                        out, aqk, akk, cu_seqlens, chunk_offsets, nseq, tokens, heads, key_dim, value_dim,
                         num_chunks, workspace, workspace_bytes, stream);
+}
+
+// kda_chunk_fwd / kda_chunk_fwd_save (keep != 0) for unnormalised q and k: every q and k row is scaled
+// to unit L2 norm, x * rsqrt(sum x^2 + eps), inside the first kernel, and the reciprocal norms go to
+// rstd_q / rstd_k (fp32 [tokens, heads]) for kda_chunk_bwd_qknorm_saved.
+extern "C" int kda_chunk_fwd_qknorm(const void* q, const void* k, const void* v, const float* cum_gate,
+                                    const float* beta, const float* initial_state, float* final_state,
+                                    void* out, void* aqk, void* akk, float* rstd_q, float* rstd_k,
+                                    float eps, const int32_t* cu_seqlens, const int32_t* chunk_offsets,
+                                    int nseq, int64_t tokens, int heads, int key_dim, int value_dim,
+                                    int num_chunks, void* workspace, int64_t workspace_bytes, int keep,
+                                    void* stream) {
+  if (!rstd_q || !rstd_k || !(eps >= 0.f)) return KDA_ERR_ARG;
+  return chunk_fwd_impl(keep != 0, rstd_q, rstd_k, eps, q, k, v, cum_gate, beta, initial_state,
+                        final_state, out, aqk, akk, cu_seqlens, chunk_offsets, nseq, tokens, heads,
+                        key_dim, value_dim, num_chunks, workspace, workspace_bytes, stream);
 }
 
 extern "C" int kda_chunk_fwd_save(const void* q, const void* k, const void* v, const float* cum_gate,
@@ -132,8 +151,8 @@ extern "C" int kda_chunk_fwd_save(const void* q, const void* k, const void* v, c
                                   const int32_t* chunk_offsets, int nseq, int64_t tokens, int heads,
                                   int key_dim, int value_dim, int num_chunks, void* saved,
                                   int64_t saved_bytes, void* stream) {
-  return chunk_fwd_impl(true, q, k, v, cum_gate, beta, initial_state, final_state, out, aqk, akk,
-                        cu_seqlens, chunk_offsets, nseq, tokens, heads, key_dim, value_dim,
+  return chunk_fwd_impl(true, nullptr, nullptr, 0.f, q, k, v, cum_gate, beta, initial_state, final_state,
+                        out, aqk, akk, cu_seqlens, chunk_offsets, nseq, tokens, heads, key_dim, value_dim,
                         num_chunks, saved, saved_bytes, stream);
 }
 

@@ -38,6 +38,8 @@ struct PrepParams {
   CUtensorMap tm_qg, tm_kg, tm_w, tm_u, tm_aqk, tm_akk;     // results
   const float* beta;
   bf16* qg; bf16* kg; bf16* w; bf16* u; bf16* aqk; bf16* akk;
+  float* rstd_q; float* rstd_k;    // NORM kernels: 1 / sqrt(sum x^2 + eps) of every q and k row, [tokens, H]
+  float eps;
   const int32_t* cu_seqlens; const int32_t* chunk_offsets;
   int* error;
   int nseq, H, total;          // total = chunk capacity x heads work items
@@ -109,6 +111,12 @@ __device__ __forceinline__ void pack8v(const float* x, uint4& o) {
 // byte offset of Kn_r inside the KN region: the tiles have 16, 32, 48, 64 rows of 256 bytes
 __device__ __forceinline__ int kn_off(int r) { return 4096 * (r * (r + 1) / 2); }
 
+// NORM: q and k arrive unnormalised; every row is scaled to unit L2 norm (and rounded to bf16, as a
+// separate l2norm launch would leave it) while its pieces pass through the registers of phase 1a,
+// and the two reciprocal norms are kept for the backward pass
+// (reference stages: fwd/triton/l2norm_fwd.py:22, applied right before the core in
+// examples/kda_training.py:412-421).
+template <bool NORM>
 __global__ void __launch_bounds__(NT, 1) kda_prepare_tc_kernel(const __grid_constant__ PrepParams p) {
   extern __shared__ unsigned char smem_dyn[];
   // 1024-byte alignment by offset, so the compiler still knows this is shared memory
@@ -258,6 +266,29 @@ __global__ void __launch_bounds__(NT, 1) kda_prepare_tc_kernel(const __grid_cons
     kkeep[n] = ld_raw8(sm + pl::K, 8192, i, c16);
     unpack8(qkeep[n], qq);
     unpack8(kkeep[n], kk);
+    if constexpr (NORM) {
+      // the 16 lanes of a half-warp hold one row: sum of squares in the order of the stand-alone
+      // kernel (eight fused multiply-adds per lane, then a butterfly over the lanes)
+      float sq = 0.f, sk = 0.f;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) { sq = fmaf(qq[e], qq[e], sq); sk = fmaf(kk[e], kk[e], sk); }
+#pragma unroll
+      for (int d = 8; d > 0; d >>= 1) {
+        sq += __shfl_xor_sync(0xffffffffu, sq, d);
+        sk += __shfl_xor_sync(0xffffffffu, sk, d);
+      }
+      const float rq = rsqrtf(sq + p.eps), rk = rsqrtf(sk + p.eps);
+      if (c16 == 0 && i < valid) {
+        p.rstd_q[(cw.token0 + i) * H + head] = rq;
+        p.rstd_k[(cw.token0 + i) * H + head] = rk;
+      }
+#pragma unroll
+      for (int e = 0; e < 8; ++e) { qq[e] *= rq; kk[e] *= rk; }
+      pack8v(qq, qkeep[n]);        // the bf16 rows are what every later step works with
+      pack8v(kk, kkeep[n]);
+      unpack8(qkeep[n], qq);
+      unpack8(kkeep[n], kk);
+    }
     ld_g8(sG, i, c0, g);
     ld_g8(sG, 16 * b, c0, r);
 #pragma unroll
@@ -581,8 +612,9 @@ static __device__ int g_prepare_error = 0;
 long long* debug_profile_buffer();
 
 int launch_prepare_tc(const bf16* q, const bf16* k, const bf16* v, const float* g, const float* beta,
-                      bf16* aqk, bf16* akk, bf16* w, bf16* u, bf16* kg, bf16* qg, const int32_t* cu,
-                      const int32_t* co, int nseq, int H, int64_t tokens, int chunks, cudaStream_t s) {
+                      bf16* aqk, bf16* akk, bf16* w, bf16* u, bf16* kg, bf16* qg, float* rstd_q,
+                      float* rstd_k, float eps, const int32_t* cu, const int32_t* co, int nseq, int H,
+                      int64_t tokens, int chunks, cudaStream_t s) {
   if (chunks == 0) return KDA_OK;
   PrepParams p;
   const int64_t cols = (int64_t)H * 128, acols = (int64_t)H * 64;
@@ -593,6 +625,8 @@ int launch_prepare_tc(const bf16* q, const bf16* k, const bf16* v, const float* 
             make_tensor_map(&p.tm_aqk, aqk, tokens, acols, 64) && make_tensor_map(&p.tm_akk, akk, tokens, acols, 64);
   if (!ok) return KDA_ERR_LAUNCH;
   p.beta = beta; p.qg = qg; p.kg = kg; p.w = w; p.u = u; p.aqk = aqk; p.akk = akk;
+  p.rstd_q = rstd_q; p.rstd_k = rstd_k; p.eps = eps;
+  if ((rstd_q == nullptr) != (rstd_k == nullptr)) return KDA_ERR_ARG;
   p.cu_seqlens = cu; p.chunk_offsets = co; p.nseq = nseq; p.H = H;
   p.total = chunks * H;
   p.scale = 0.08838834764831845f;  // 128^-0.5
@@ -603,11 +637,11 @@ int launch_prepare_tc(const bf16* q, const bf16* k, const bf16* v, const float* 
       cudaGetSymbolAddress(reinterpret_cast<void**>(&p.error), g_prepare_error) != cudaSuccess)
     return KDA_ERR_LAUNCH;
   const int smem = pl::TOTAL + 1024;
-  if (cudaFuncSetAttribute(kda_prepare_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
-      cudaSuccess)
+  auto kernel = rstd_q ? kda_prepare_tc_kernel<true> : kda_prepare_tc_kernel<false>;
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
     return KDA_ERR_LAUNCH;
   StageScope timing(kStagePrepare, s);
-  kda_prepare_tc_kernel<<<(unsigned)(p.total < sms ? p.total : sms), NT, smem, s>>>(p);
+  kernel<<<(unsigned)(p.total < sms ? p.total : sms), NT, smem, s>>>(p);
   return cudaGetLastError() == cudaSuccess ? KDA_OK : KDA_ERR_LAUNCH;
 }
 

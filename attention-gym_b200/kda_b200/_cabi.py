@@ -54,6 +54,10 @@ _SIGNATURES = {
                               c_int64, c_void_p]),
     "kda_chunk_fwd_save": (c_int, [c_void_p] * 12 + [c_int, c_int64, c_int, c_int, c_int, c_int,
                                    c_void_p, c_int64, c_void_p]),
+    "kda_chunk_fwd_qknorm": (c_int, [c_void_p] * 12 + [c_float, c_void_p, c_void_p, c_int, c_int64, c_int,
+                                     c_int, c_int, c_int, c_void_p, c_int64, c_int, c_void_p]),
+    "kda_chunk_bwd_qknorm_saved": (c_int, [c_void_p] * 18 + [c_int, c_int64, c_int, c_int, c_int, c_int,
+                                           c_void_p, c_void_p, c_void_p, c_int64, c_void_p]),
     "kda_chunk_fwd_noalloc": (c_int, [c_void_p] * 12 + [c_int, c_int64, c_int, c_int, c_int, c_int,
                                       c_void_p]),
     "kda_chunk_fwd_dense_workspace_bytes": (c_int64, [c_int, c_int64, c_int, c_int]),

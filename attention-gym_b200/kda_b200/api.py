@@ -46,7 +46,7 @@ def _per_token_gate(cumulative_gate, cu_seqlens):
 
 def chunk_kda(q, k, v, cumulative_gate, beta, initial_state=None, *, cu_seqlens=None,
               output_final_state=False, fastmath=False, autotune=True, impl=Impl.FUSED,
-              recompute=False, exact_fp32=False):
+              recompute=False, exact_fp32=False, normalize_qk=False, norm_eps=1e-6):
     """Chunk-parallel KDA.
 
     q, k, cumulative_gate: ``[B, T, H, K]``; v: ``[B, T, H, V]``; beta: ``[B, T, H]``;
@@ -59,7 +59,11 @@ def chunk_kda(q, k, v, cumulative_gate, beta, initial_state=None, *, cu_seqlens=
     which always behaves as ``True``) makes the backward pass rebuild the forward intermediates
     instead of keeping about 1.6 KiB per token and head between the two passes.  ``exact_fp32``
     (not in the reference; inference only, fp32 inputs) evaluates the recurrence token by token in
-    fp32 instead of rounding the operands to bf16.
+    fp32 instead of rounding the operands to bf16.  ``normalize_qk`` (not in the reference, whose
+    callers run ``l2norm`` on q and k as separate launches right before this op) takes unnormalised
+    q and k and applies ``x * rsqrt(sum(x^2) + norm_eps)`` per row inside the first kernel, and its
+    backward inside the last one: the same values as ``chunk_kda(l2norm(q), l2norm(k), ...)`` with
+    one full read and write of q and k saved in each direction.
     """
     selected = resolve_impl(impl)
     if selected is Impl.REFERENCE and fastmath:
@@ -68,6 +72,10 @@ def chunk_kda(q, k, v, cumulative_gate, beta, initial_state=None, *, cu_seqlens=
                         op_name="chunk_kda", gate_name="cumulative_gate")
     cu_seqlens = _narrow_offsets(cu_seqlens)
     if selected is Impl.REFERENCE:
+        if normalize_qk:
+            qf, kf = q.float(), k.float()
+            q = (qf * torch.rsqrt((qf * qf).sum(-1, keepdim=True) + norm_eps)).to(q.dtype)
+            k = (kf * torch.rsqrt((kf * kf).sum(-1, keepdim=True) + norm_eps)).to(k.dtype)
         return reference_kda("chunk", q, k, v, cumulative_gate, beta, initial_state, cu_seqlens,
                              output_final_state)
     tensors = (q, k, v, cumulative_gate, beta) + (() if initial_state is None else (initial_state,))
@@ -75,6 +83,13 @@ def chunk_kda(q, k, v, cumulative_gate, beta, initial_state=None, *, cu_seqlens=
     off_chunk_shape = q.shape[-1] != 128 or v.shape[-1] != 128
     if exact_fp32 and (needs_grad or q.dtype != torch.float32):
         raise ValueError("exact_fp32 needs float32 q, k, v and no autograd")
+    if normalize_qk:
+        if exact_fp32:
+            raise ValueError("normalize_qk belongs to the chunked bf16 kernels, not to exact_fp32")
+        return _fused_chunk_forward(q, k, v, cumulative_gate, beta, initial_state,
+                                    cu_seqlens=cu_seqlens, output_final_state=output_final_state,
+                                    fastmath=fastmath, autotune=autotune, recompute=recompute,
+                                    normalize_qk=True, norm_eps=norm_eps)
     if (q.dtype == torch.float32 and q.is_cuda and not needs_grad and q.shape[-1] <= 256
             and (exact_fp32 or off_chunk_shape)):
         # fp32-accurate path: the token scan on the per-token gate

@@ -80,10 +80,38 @@ class _ChunkKDA(torch.autograd.Function):
         return dq, dk, dv, dg, db, dh0, None, None, None, None, None, None
 
 
+class _ChunkKDAQKNorm(torch.autograd.Function):
+    """chunk_kda on unnormalised q and k: the L2 normalisation and its backward run inside the first
+    forward kernel and the last backward kernel."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, gate, beta, initial_state, cu_seqlens, chunk_offsets,
+                output_final_state, eps):
+        keep = any(ctx.needs_input_grad[:6])
+        out, state, aqk, akk, saved, rstd_q, rstd_k = ops.chunk_fwd_qknorm_op(
+            q, k, v, gate, beta, initial_state, cu_seqlens, chunk_offsets, output_final_state, keep, eps)
+        ctx.save_for_backward(q, k, v, gate, beta, aqk, akk, initial_state, cu_seqlens, chunk_offsets,
+                              saved, rstd_q, rstd_k)
+        ctx.set_materialize_grads(False)
+        return (out, state) if output_final_state else out
+
+    @staticmethod
+    @torch.autograd.function.once_differentiable
+    def backward(ctx, d_output, d_final_state=None):
+        (q, k, v, gate, beta, aqk, akk, initial_state, cu_seqlens, chunk_offsets, saved, rstd_q,
+         rstd_k) = ctx.saved_tensors
+        dq, dk, dv, dg, db, dh0 = ops.chunk_bwd_qknorm_op(
+            q, k, v, gate, beta, aqk, akk, saved, rstd_q, rstd_k, cu_seqlens, chunk_offsets, d_output,
+            d_final_state, initial_state, initial_state is not None)
+        return dq, dk, dv, dg, db, (dh0 if initial_state is not None else None), None, None, None, None
+
+
 def chunk_forward(q, k, v, cumulative_gate, beta, initial_state=None, *, cu_seqlens=None,
                   metadata: RaggedChunkMetadata | None = None, output_final_state=False,
-                  fastmath=False, autotune=True, recompute=False):
-    """Normalise inputs and run the fused chunk operators (reference: impl/fused.py:147-216)."""
+                  fastmath=False, autotune=True, recompute=False, normalize_qk=False,
+                  norm_eps=1e-6):
+    """Normalise inputs and run the fused chunk operators (reference: impl/fused.py:147-216).
+    ``normalize_qk`` fuses ``l2norm(q)``, ``l2norm(k)`` (and their backward) into the core."""
     if metadata is not None:
         assert cu_seqlens is None
         metadata.validate_chunk_size(_CHUNK)
@@ -99,7 +127,13 @@ def chunk_forward(q, k, v, cumulative_gate, beta, initial_state=None, *, cu_seql
         initial_state = initial_state.float().contiguous()
     cu = None if metadata is None else metadata.cu_seqlens
     offsets = None if metadata is None else metadata.chunk_offsets
-    if output_final_state:
+    if normalize_qk:
+        if recompute:
+            raise ValueError("normalize_qk keeps the forward intermediates; recompute=True is not available")
+        res = _ChunkKDAQKNorm.apply(q, k, v, cumulative_gate, beta, initial_state, cu, offsets,
+                                    bool(output_final_state), float(norm_eps))
+        out, state = res if output_final_state else (res, None)
+    elif output_final_state:
         out, state = _ChunkKDA.apply(q, k, v, cumulative_gate, beta, initial_state, cu, offsets,
                                      True, fastmath, autotune, recompute)
     else:

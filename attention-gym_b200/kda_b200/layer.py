@@ -13,8 +13,10 @@ flow of ``forward`` (reference lines in brackets):
     o, g_b_proj(g_a_proj(hidden)) --gated_output_norm--> y --out_proj--> result    [:507-539]
 
 The projections are cuBLAS GEMMs (``F.linear``); everything between them is this package:
-one conv kernel, two l2norm launches, one gate kernel, the chunked core, and the output epilogue
-``rms_norm(o) * weight * sigmoid(gate logits)`` as ONE kernel where the reference runs three.
+one conv kernel, one gate kernel, the chunked core with the q / k L2 normalisation fused into its
+first forward and last backward kernel (``fuse_qk_norm=False`` runs the two l2norm launches of the
+reference instead), and the output epilogue ``rms_norm(o) * weight * sigmoid(gate logits)`` as ONE
+kernel where the reference runs three.
 Packed inputs share one chunk schedule between the gate and the core, as in the reference.
 ``backend="reference"`` evaluates the same layer in eager fp32 PyTorch (dense inputs only), for
 parity checks; there is no fallback from one backend to the other.
@@ -55,7 +57,7 @@ class KDAAttention(nn.Module):
                  short_conv_kernel_size: int = 4, lower_bound: float = -5.0,
                  backend: str = "fused", fastmath: bool = False, rms_norm_eps: float = 1e-5,
                  compute_dtype: Optional[torch.dtype] = None, device=None,
-                 mask_inactive_capacity: bool = False) -> None:
+                 mask_inactive_capacity: bool = False, fuse_qk_norm: bool = True) -> None:
         super().__init__()
         if hidden_size < 1 or num_heads < 1 or head_dim < 1:
             raise ValueError("hidden_size, num_heads, and head_dim must be positive")
@@ -73,6 +75,7 @@ class KDAAttention(nn.Module):
         self.chunk_size, self.lower_bound, self.backend = chunk_size, lower_bound, backend
         self.fastmath, self.rms_norm_eps = fastmath, rms_norm_eps
         self.mask_inactive_capacity = mask_inactive_capacity
+        self.fuse_qk_norm = fuse_qk_norm
         self.compute_dtype = ((torch.bfloat16 if backend == "fused" else torch.float32)
                               if compute_dtype is None else compute_dtype)
         if backend == "fused" and self.compute_dtype != torch.bfloat16:
@@ -170,7 +173,8 @@ class KDAAttention(nn.Module):
             out, final_state = self._reference_core(q, k, v, raw_gate, beta, initial_state,
                                                     return_final_state)
         else:
-            q, k = l2norm(q.contiguous()), l2norm(k.contiguous())
+            if not self.fuse_qk_norm:
+                q, k = l2norm(q.contiguous()), l2norm(k.contiguous())
             metadata = (None if cu_seqlens is None
                         else prepare_ragged_chunk_metadata(cu_seqlens, tokens, self.chunk_size))
             gate = _bounded_gate_cumsum(raw_gate, self.A_log, self.dt_bias, chunk_size=self.chunk_size,
@@ -178,7 +182,7 @@ class KDAAttention(nn.Module):
                                         metadata=metadata)
             out, final_state = _chunk_kda(q, k, v.contiguous(), gate, beta, initial_state,
                                           metadata=metadata, output_final_state=return_final_state,
-                                          fastmath=self.fastmath)
+                                          fastmath=self.fastmath, normalize_qk=self.fuse_qk_norm)
         out = mask_inactive_tokens(out, mask)
         logits = self._linear(self._linear(hidden, self.g_a_proj), self.g_b_proj).view_as(out)
         if self.backend == "fused":

@@ -55,6 +55,17 @@ _define("kda_chunk_bwd_saved",
         "Tensor(a!) saved, Tensor? cu_seqlens, Tensor? chunk_offsets, Tensor? d_output, "
         "Tensor? d_final_state, Tensor? initial_state, bool want_state_grad) "
         "-> (Tensor, Tensor, Tensor, Tensor, Tensor, Tensor)")
+# The chunked pair with the layer's q / k L2 normalisation fused in (no reference counterpart as one
+# operator: the reference runs l2norm as separate launches, fwd/triton/l2norm_fwd.py:84,143).
+_define("kda_chunk_fwd_qknorm",
+        "(Tensor q, Tensor k, Tensor v, Tensor cumulative_gate, Tensor beta, Tensor? initial_state, "
+        "Tensor? cu_seqlens, Tensor? chunk_offsets, bool want_state, bool keep, float eps) "
+        "-> (Tensor, Tensor, Tensor, Tensor, Tensor, Tensor, Tensor)")
+_define("kda_chunk_bwd_qknorm",
+        "(Tensor q, Tensor k, Tensor v, Tensor cumulative_gate, Tensor beta, Tensor Aqk, Tensor Akk, "
+        "Tensor(a!) saved, Tensor rstd_q, Tensor rstd_k, Tensor? cu_seqlens, Tensor? chunk_offsets, "
+        "Tensor? d_output, Tensor? d_final_state, Tensor? initial_state, bool want_state_grad) "
+        "-> (Tensor, Tensor, Tensor, Tensor, Tensor, Tensor)")
 _define("kda_recurrent_fwd", _REC + " -> (Tensor, Tensor)")
 _define("kda_recurrent_fwd_no_state", _REC + " -> Tensor")
 _define("kda_recurrent_fwd_paged",
@@ -192,7 +203,7 @@ def _chunk_fwd_ragged_with_state(q, k, v, gate, beta, initial_state, cu_seqlens,
 
 
 def _chunk_bwd_impl(q, k, v, gate, beta, aqk, akk, cu_seqlens, chunk_offsets, d_output,
-                    d_final_state, initial_state, want_state_grad, saved=None):
+                    d_final_state, initial_state, want_state_grad, saved=None, rstd=None):
     batch, tokens, heads, _ = q.shape
     if cu_seqlens is None:
         cu_seqlens, chunk_offsets, capacity = _dense_offsets(q)
@@ -225,12 +236,17 @@ def _chunk_bwd_impl(q, k, v, gate, beta, aqk, akk, cu_seqlens, chunk_offsets, d_
         workspace = saved
     else:
         workspace = torch.empty(ws_bytes, dtype=torch.uint8, device=q.device)
-    _cabi.call("kda_chunk_bwd_saved" if saved is not None else "kda_chunk_bwd", 5, _cabi.ptr(q), _cabi.ptr(k), _cabi.ptr(v), _cabi.ptr(gate),
-               _cabi.ptr(beta), _cabi.ptr(aqk), _cabi.ptr(akk), _cabi.ptr(initial_state),
-               _cabi.ptr(d_output), _cabi.ptr(d_final_state), _cabi.ptr(dq), _cabi.ptr(dk),
-               _cabi.ptr(dv), _cabi.ptr(dg), _cabi.ptr(db), _cabi.ptr(dh0), _cabi.ptr(cu_seqlens),
-               _cabi.ptr(chunk_offsets), nseq, total, heads, 128, 128, capacity,
-               _cabi.ptr(workspace), ws_bytes, _cabi.stream())
+    head = (_cabi.ptr(q), _cabi.ptr(k), _cabi.ptr(v), _cabi.ptr(gate),
+            _cabi.ptr(beta), _cabi.ptr(aqk), _cabi.ptr(akk), _cabi.ptr(initial_state),
+            _cabi.ptr(d_output), _cabi.ptr(d_final_state), _cabi.ptr(dq), _cabi.ptr(dk),
+            _cabi.ptr(dv), _cabi.ptr(dg), _cabi.ptr(db), _cabi.ptr(dh0), _cabi.ptr(cu_seqlens),
+            _cabi.ptr(chunk_offsets), nseq, total, heads, 128, 128, capacity)
+    if rstd is not None:
+        _cabi.call("kda_chunk_bwd_qknorm_saved", 2, *head, _cabi.ptr(rstd[0]), _cabi.ptr(rstd[1]),
+                   _cabi.ptr(workspace), ws_bytes, _cabi.stream())
+    else:
+        _cabi.call("kda_chunk_bwd_saved" if saved is not None else "kda_chunk_bwd", 5, *head,
+                   _cabi.ptr(workspace), ws_bytes, _cabi.stream())
     return dq, dk, dv, dg, db, dh0
 
 
@@ -266,6 +282,78 @@ def _chunk_bwd_saved(q, k, v, gate, beta, aqk, akk, saved, cu_seqlens, chunk_off
     if dh0 is None:
         dh0 = torch.empty(0, dtype=torch.float32, device=q.device)
     return dq, dk, dv, dg, db, dh0
+
+
+@torch.library.impl(_lib, "kda_chunk_fwd_qknorm", "CUDA")
+def _chunk_fwd_qknorm(q, k, v, gate, beta, initial_state, cu_seqlens, chunk_offsets, want_state, keep,
+                      eps):
+    _require_cuda(q, "the fused KDA core")
+    if q.shape[-1] != 128 or v.shape[-1] != 128:
+        raise ValueError("the fused KDA core requires K=V=128")
+    if q.dtype != torch.bfloat16 or k.dtype != torch.bfloat16 or v.dtype != torch.bfloat16:
+        raise TypeError("the fused KDA core takes bfloat16 q, k, v")
+    batch, tokens, heads, _ = q.shape
+    packed = cu_seqlens is not None
+    if not packed:
+        cu_seqlens, chunk_offsets, capacity = _dense_offsets(q)
+        nseq = batch
+    else:
+        if batch != 1:
+            raise ValueError("packed cu_seqlens require batch size one")
+        nseq = cu_seqlens.shape[0] - 1
+        capacity = chunk_capacity(tokens, nseq, _CHUNK)
+    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    gate, beta = gate.float().contiguous(), beta.float().contiguous()
+    if initial_state is not None:
+        initial_state = initial_state.float().contiguous()
+    total = batch * tokens
+    out = torch.zeros_like(v) if packed else torch.empty_like(v)
+    aqk = torch.empty(batch, tokens, heads, _CHUNK, dtype=q.dtype, device=q.device)
+    akk = torch.empty_like(aqk)
+    alloc = torch.zeros if packed else torch.empty
+    rstd_q = alloc(batch, tokens, heads, dtype=torch.float32, device=q.device)
+    rstd_k = alloc(batch, tokens, heads, dtype=torch.float32, device=q.device)
+    state = (torch.empty(nseq, heads, 128, 128, dtype=torch.float32, device=q.device)
+             if want_state else q.new_empty((0,), dtype=torch.float32))
+    ws_bytes = _fwd_workspace_bytes(1, total, heads, nseq, keep)
+    workspace = torch.empty(ws_bytes, dtype=torch.uint8, device=q.device)
+    _cabi.call("kda_chunk_fwd_qknorm", 3, _cabi.ptr(q), _cabi.ptr(k), _cabi.ptr(v), _cabi.ptr(gate),
+               _cabi.ptr(beta), _cabi.ptr(initial_state), _cabi.ptr(state) if want_state else None,
+               _cabi.ptr(out), _cabi.ptr(aqk), _cabi.ptr(akk), _cabi.ptr(rstd_q), _cabi.ptr(rstd_k),
+               float(eps), _cabi.ptr(cu_seqlens), _cabi.ptr(chunk_offsets), nseq, total, heads, 128, 128,
+               capacity, _cabi.ptr(workspace), ws_bytes, int(keep), _cabi.stream())
+    return out, state, aqk, akk, workspace, rstd_q, rstd_k
+
+
+@torch.library.impl(_lib, "kda_chunk_bwd_qknorm", "CUDA")
+def _chunk_bwd_qknorm(q, k, v, gate, beta, aqk, akk, saved, rstd_q, rstd_k, cu_seqlens, chunk_offsets,
+                      d_output, d_final_state, initial_state, want_state_grad):
+    dq, dk, dv, dg, db, dh0 = _chunk_bwd_impl(q, k, v, gate, beta, aqk, akk, cu_seqlens, chunk_offsets,
+                                              d_output, d_final_state, initial_state, want_state_grad,
+                                              saved=saved, rstd=(rstd_q.contiguous(), rstd_k.contiguous()))
+    if dh0 is None:
+        dh0 = torch.empty(0, dtype=torch.float32, device=q.device)
+    return dq, dk, dv, dg, db, dh0
+
+
+@torch.library.register_fake(f"{_NS}::kda_chunk_fwd_qknorm")
+def _(q, k, v, gate, beta, initial_state, cu_seqlens, chunk_offsets, want_state, keep, eps):
+    nseq = q.shape[0] if cu_seqlens is None else cu_seqlens.shape[0] - 1
+    state = (q.new_empty((nseq, q.shape[2], q.shape[3], v.shape[-1]), dtype=torch.float32)
+             if want_state else q.new_empty((0,), dtype=torch.float32))
+    nbytes = _fwd_workspace_bytes(1, q.shape[0] * q.shape[1], q.shape[2], nseq, keep)
+    rstd = q.new_empty(q.shape[:3], dtype=torch.float32)
+    return (v.new_empty(v.shape), state, _tape(q), _tape(q), q.new_empty((nbytes,), dtype=torch.uint8),
+            rstd, torch.empty_like(rstd))
+
+
+@torch.library.register_fake(f"{_NS}::kda_chunk_bwd_qknorm")
+def _(q, k, v, gate, beta, aqk, akk, saved, rstd_q, rstd_k, cu_seqlens, chunk_offsets, d_output,
+      d_final_state, initial_state, want_state_grad):
+    nseq = q.shape[0] if cu_seqlens is None else cu_seqlens.shape[0] - 1
+    dh0 = (q.new_empty((nseq, q.shape[2], q.shape[3], v.shape[-1]), dtype=torch.float32)
+           if want_state_grad else q.new_empty((0,), dtype=torch.float32))
+    return (*_bwd_fake(q, k, v, gate, beta), dh0)
 
 
 def _tape(q):
@@ -660,6 +748,8 @@ chunk_fwd_ragged_op = _ops.kda_chunk_fwd_ragged.default
 chunk_fwd_ragged_with_state_op = _ops.kda_chunk_fwd_ragged_with_state.default
 chunk_fwd_saved_op = _ops.kda_chunk_fwd_saved.default
 chunk_bwd_saved_op = _ops.kda_chunk_bwd_saved.default
+chunk_fwd_qknorm_op = _ops.kda_chunk_fwd_qknorm.default
+chunk_bwd_qknorm_op = _ops.kda_chunk_bwd_qknorm.default
 chunk_bwd_op = _ops.kda_chunk_bwd.default
 chunk_bwd_with_state_grad_op = _ops.kda_chunk_bwd_with_state_grad.default
 recurrent_fwd_op = _ops.kda_recurrent_fwd.default

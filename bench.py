@@ -233,6 +233,7 @@ def run_ours(args):
 
     decode = None if args.skip_decode else bench_decode(kda_b200, _cabi, device, load_peaks())
     preops = None if (args.skip_decode or rank != 0) else bench_preops(device, load_peaks(), batch, tokens)
+    norm_fusion = None if (args.skip_decode or rank != 0) else bench_layer_norm_fusion(kda_b200, device, batch, tokens)
     others = None
     if args.other_configs and rank == 0:
         del dev
@@ -362,6 +363,7 @@ def run_ours(args):
         "cpu_baseline": cpu,
         "decode": decode,
         "preops": preops,
+        "layer_qk_norm": norm_fusion,
         "other_configs": others,
         "strong": strong,
         "cp": cp,
@@ -504,6 +506,40 @@ def bench_cp(kda_b200, _cabi, device, rank, world, barrier, tokens=1 << 20, iter
                             "state_fwd": [round(r[1], 3) for r in per_rank],
                             "state_fwd_launches": [int(r[2]) for r in per_rank]},
             "check": check}
+
+
+def bench_layer_norm_fusion(kda_b200, device, batch=8, tokens=4096, iters=10):
+    """The q / k L2 normalisation of the layer at the headline shapes, fwd+bwd: as the two separate
+    l2norm launches of the reference before the core (and two more after it in backward), against
+    chunk_kda(normalize_qk=True), which normalises inside its first forward and last backward
+    kernel.  Same unnormalised q, k in both arms; CUDA events."""
+    d = _device_inputs(batch, tokens, device, 9300)
+    gen = torch.Generator(device=device).manual_seed(9301)
+    d["q"] = (d["q"].float() * (0.5 + 3 * torch.rand(batch, tokens, H, 1, generator=gen, device=device))).bfloat16()
+    d["k"] = (d["k"].float() * (0.5 + 3 * torch.rand(batch, tokens, H, 1, generator=gen, device=device))).bfloat16()
+
+    def step(fused):
+        q, k, v, g, beta = (d[n].detach().requires_grad_(True) for n in ("q", "k", "v", "g", "beta"))
+        if fused:
+            o, _ = kda_b200.chunk_kda(q, k, v, g, beta, normalize_qk=True)
+        else:
+            o, _ = kda_b200.chunk_kda(kda_b200.l2norm(q), kda_b200.l2norm(k), v, g, beta)
+        return torch.autograd.grad(o, (q, k, v, g, beta), d["do"])
+
+    out = {}
+    for name, fused in (("separate_l2norm_launches", False), ("normalisation_inside_the_core", True)):
+        for _ in range(3):
+            step(fused)
+        a, z = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        a.record()
+        for _ in range(iters):
+            step(fused)
+        z.record()
+        torch.cuda.synchronize()
+        out[name] = {"ms_per_step": round(a.elapsed_time(z) / iters, 4)}
+    out["workload"] = f"l2norm(q), l2norm(k) + chunk_kda fwd+bwd, B={batch} T={tokens} H={H}"
+    return out
 
 
 def bench_decode(kda_b200, _cabi, device, peaks, nseq=256, steps=200):

@@ -228,6 +228,30 @@ int kda_chunk_bwd_saved(const void* q, const void* k, const void* v, const float
                         int key_dim, int value_dim, int num_chunks, void* saved, int64_t saved_bytes,
                         void* stream);
 
+/* The chunked pair with the q / k L2 normalisation of the layer fused in (the reference runs it as
+ * separate launches right before and after the core: fwd/triton/l2norm_fwd.py:22,
+ * bwd/triton/l2norm_bwd.py:37, examples/kda_training.py:412-421).  q and k are the unnormalised rows.
+ * kda_chunk_fwd_qknorm normalises them inside its first kernel -- y = x * rsqrt(sum x^2 + eps), rounded
+ * to bf16 exactly as kda_l2norm_fwd would leave them, so the results are those of kda_l2norm_fwd
+ * followed by kda_chunk_fwd / kda_chunk_fwd_save (keep != 0) bit for bit -- and writes the reciprocal
+ * norms to rstd_q / rstd_k (fp32 [tokens, heads]).  kda_chunk_bwd_qknorm_saved is kda_chunk_bwd_saved
+ * for that forward: it returns dq and dk as gradients of the unnormalised rows,
+ * dx = rstd (dy - y <dy, y>).  One full read and write of q and k is saved in each direction. */
+int kda_chunk_fwd_qknorm(const void* q, const void* k, const void* v, const float* cum_gate,
+                         const float* beta, const float* initial_state, float* final_state, void* out,
+                         void* aqk, void* akk, float* rstd_q, float* rstd_k, float eps,
+                         const int32_t* cu_seqlens, const int32_t* chunk_offsets, int nseq,
+                         int64_t tokens, int heads, int key_dim, int value_dim, int num_chunks,
+                         void* workspace, int64_t workspace_bytes, int keep, void* stream);
+int kda_chunk_bwd_qknorm_saved(const void* q, const void* k, const void* v, const float* cum_gate,
+                               const float* beta, const void* aqk, const void* akk,
+                               const float* initial_state, const void* d_out,
+                               const float* d_final_state, void* dq, void* dk, void* dv, float* dg,
+                               float* dbeta, float* d_initial_state, const int32_t* cu_seqlens,
+                               const int32_t* chunk_offsets, int nseq, int64_t tokens, int heads,
+                               int key_dim, int value_dim, int num_chunks, const float* rstd_q,
+                               const float* rstd_k, void* saved, int64_t saved_bytes, void* stream);
+
 /* The two halves of kda_chunk_fwd: `prepare` = the chunk-parallel part (fills aqk, akk and the
  * workspace), `state` = the serial state recurrence over the workspace (writes out and final_state,
  * either may be NULL).  use_u == 0 runs the homogeneous recurrence: with identity matrices as

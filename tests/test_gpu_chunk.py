@@ -182,6 +182,63 @@ def test_rows_walked_in_parallel_segments_match_the_serial_walk(segments, gate_s
     assert lib.kda_device_error_word() == 0
 
 
+@pytest.mark.parametrize("case", [CASES[1], CASES[2], CASES[4]], ids=["dense", "dense-tail", "packed"])
+def test_qk_normalisation_fused_into_the_core(case):
+    """chunk_kda(..., normalize_qk=True) on unnormalised q and k: the forward results and every
+    gradient that does not pass through the normalisation are bitwise those of
+    chunk_kda(l2norm(q), l2norm(k), ...); dq and dk, which the fused backward derives from the
+    unrounded core gradients, agree closely; and everything matches the oracle composition
+    (reference stages: fwd/triton/l2norm_fwd.py:22, bwd/triton/l2norm_bwd.py:37)."""
+    inp = _case(**case)
+    gen = torch.Generator().manual_seed(96)
+    scale_q = 0.5 + 3.0 * torch.rand(inp["q"].shape[:3], generator=gen)
+    scale_k = 0.5 + 3.0 * torch.rand(inp["k"].shape[:3], generator=gen)
+    raw_q = (inp["q"].float() * scale_q[..., None]).bfloat16()
+    raw_k = (inp["k"].float() * scale_k[..., None]).bfloat16()
+    do = torch.randn(inp["v"].shape, generator=gen).bfloat16()
+    dst = 0.1 * torch.randn(inp["h0"].shape, generator=gen)
+    cu = None if inp["cu_seqlens"] is None else inp["cu_seqlens"].cuda()
+    if cu is not None:
+        do[:, int(inp["cu_seqlens"][-1]):] = 0
+
+    def run(fused):
+        q, k, v = (t.cuda().requires_grad_() for t in (raw_q, raw_k, inp["v"]))
+        g, beta, h0 = (inp[n].cuda().requires_grad_() for n in ("cum_gate", "beta", "h0"))
+        if fused:
+            o, st = kda_b200.chunk_kda(q, k, v, g, beta, h0, cu_seqlens=cu, output_final_state=True,
+                                       normalize_qk=True)
+        else:
+            o, st = kda_b200.chunk_kda(kda_b200.l2norm(q), kda_b200.l2norm(k), v, g, beta, h0,
+                                       cu_seqlens=cu, output_final_state=True)
+        grads = torch.autograd.grad((o, st), (q, k, v, g, beta, h0), (do.cuda(), dst.cuda()))
+        return dict(zip(("o", "state", "dq", "dk", "dv", "dg", "dbeta", "dh0"), (o, st) + grads))
+
+    one, two = run(True), run(False)
+    for name in ("o", "state", "dv", "dg", "dbeta", "dh0"):
+        assert torch.equal(_active(inp, one[name]) if one[name].ndim > 3 and name not in ("state", "dh0")
+                           else one[name],
+                           _active(inp, two[name]) if two[name].ndim > 3 and name not in ("state", "dh0")
+                           else two[name]), name
+    assert torch.equal(_active(inp, one["dbeta"]), _active(inp, two["dbeta"]))
+    for name in ("dq", "dk"):
+        assert_normalised(_active(inp, one[name]).float(), _active(inp, two[name]).float(), 1e-2, name)
+    # oracle: l2norm then the chunked recurrence, differentiated in fp32 on the CPU
+    leaves = [t.float().requires_grad_() for t in (raw_q, raw_k, inp["v"])]
+    leaves += [inp[n].clone().requires_grad_() for n in ("cum_gate", "beta", "h0")]
+    qn = leaves[0] * torch.rsqrt((leaves[0] ** 2).sum(-1, keepdim=True) + 1e-6)
+    kn = leaves[1] * torch.rsqrt((leaves[1] ** 2).sum(-1, keepdim=True) + 1e-6)
+    ro, rs = orc.chunk_kda_ref(qn, kn, leaves[2], leaves[3], leaves[4], leaves[5], inp["cu_seqlens"])
+    ref = torch.autograd.grad((ro, rs), leaves, (do.float(), dst))
+    for name, r in zip(("dq", "dk", "dv", "dg", "dbeta", "dh0"), ref):
+        a = one[name] if name == "dh0" else _active(inp, one[name])
+        b = r if name == "dh0" else _active(inp, r)
+        assert_normalised(a.float(), b, TOL, f"{name} vs oracle")
+    assert_normalised(_active(inp, one["o"]).float(), _active(inp, ro.detach()), TOL, "output vs oracle")
+    with pytest.raises(ValueError):
+        kda_b200.chunk_kda(raw_q.cuda(), raw_k.cuda(), inp["v"].cuda(), inp["cum_gate"].cuda(),
+                           inp["beta"].cuda(), cu_seqlens=cu, normalize_qk=True, recompute=True)
+
+
 def test_dense_batch_equals_packed():
     """A dense batch and its explicit equal-length packing give bitwise-equal results
     (reference: test/test_kda_cute_forward.py:368-410)."""

@@ -136,6 +136,24 @@ def test_fixed_capacity_buffer_with_poisoned_suffix():
         assert_normalised(a.float(), b.float(), 3e-2, f"gradient of {name}")
 
 
+def test_fused_qk_norm_equals_the_separate_l2norm_launches():
+    """The layer with the normalisation inside the core against the same layer running l2norm as
+    separate launches: same forward bits, gradients of the hidden states close."""
+    fused, _ = _models(64, 2, seed=74)
+    apart = KDAAttention(64, 2, 128, backend="fused", device="cuda", fuse_qk_norm=False)
+    apart.load_state_dict(fused.state_dict())
+    x = torch.randn(2, 200, 64, device="cuda")
+    cot = torch.randn(2, 200, 64, device="cuda")
+    res = []
+    for model in (fused, apart):
+        xin = x.clone().requires_grad_()
+        out = model(xin, return_final_state=True)
+        res.append((out, torch.autograd.grad(out.hidden_states, xin, cot)[0]))
+    assert torch.equal(res[0][0].hidden_states, res[1][0].hidden_states)
+    assert torch.equal(res[0][0].final_state, res[1][0].final_state)
+    assert_normalised(res[0][1], res[1][1], 2e-2, "hidden gradient")
+
+
 def test_constructor_and_forward_checks():
     with pytest.raises(ValueError):
         KDAAttention(32, 1, 64, backend="fused")

@@ -74,6 +74,26 @@ def test_chunk_backward_ops(packed):
     _check(ops.kda_chunk_bwd_saved.default, *args, aqk, akk, saved, cu, co, do, None, None, False)
 
 
+@pytest.mark.parametrize("packed", [False, True], ids=["dense", "packed"])
+def test_chunk_ops_with_fused_qk_normalisation(packed):
+    if packed:
+        c = _chunk_inputs(1, 300, 2, lengths=[65, 0, 100, 64])
+        meta = prepare_ragged_chunk_metadata(c["cu_seqlens"], 300, 64)
+        cu, co = meta.cu_seqlens, meta.chunk_offsets
+    else:
+        c = _chunk_inputs(2, 130, 2)
+        cu = co = None
+    args = (3 * c["q"], 2 * c["k"], c["v"], c["cum_gate"], c["beta"])
+    _check(ops.kda_chunk_fwd_qknorm.default, *args, c["h0"], cu, co, True, True, 1e-6)
+    _check(ops.kda_chunk_fwd_qknorm.default, *args, None, cu, co, False, False, 1e-6)
+    out, state, aqk, akk, saved, rq, rk = ops.kda_chunk_fwd_qknorm(*args, c["h0"], cu, co, True, True, 1e-6)
+    gen = torch.Generator(device="cuda").manual_seed(1)
+    do = torch.randn(out.shape, generator=gen, device="cuda").bfloat16()
+    dst = torch.randn(state.shape, generator=gen, device="cuda")
+    _check(ops.kda_chunk_bwd_qknorm.default, *args, aqk, akk, saved, rq, rk, cu, co, do, dst, c["h0"], True)
+    _check(ops.kda_chunk_bwd_qknorm.default, *args, aqk, akk, saved, rq, rk, cu, co, do, None, None, False)
+
+
 def test_saved_buffer_of_the_fake_matches_the_library():
     """The meta implementation of kda_chunk_fwd_saved sizes the kept-intermediates buffer with the
     library's own shape-only function, for dense and packed inputs."""
@@ -152,7 +172,8 @@ def test_every_operator_of_the_namespace_is_covered():
     covered = {
         "kda_chunk_fwd", "kda_chunk_fwd_with_state", "kda_chunk_fwd_ragged",
         "kda_chunk_fwd_ragged_with_state", "kda_chunk_fwd_saved", "kda_chunk_bwd",
-        "kda_chunk_bwd_with_state_grad", "kda_chunk_bwd_saved", "kda_recurrent_fwd",
+        "kda_chunk_bwd_with_state_grad", "kda_chunk_bwd_saved", "kda_chunk_fwd_qknorm",
+        "kda_chunk_bwd_qknorm", "kda_recurrent_fwd",
         "kda_recurrent_fwd_no_state", "kda_recurrent_fwd_paged", "kda_prepare_chunk_offsets",
         "kda_bounded_gate_fwd_dense", "kda_bounded_gate_fwd_ragged", "kda_bounded_gate_bwd",
         "kda_l2norm_fwd", "kda_l2norm_bwd", "kda_output_gate_fwd", "kda_output_gate_bwd",
