@@ -303,7 +303,7 @@ def run_ours(args):
         torch.cuda.empty_cache()
         strong = bench_strong(kda_b200, device, rank, world, args.steps, args.warmup, barrier)
         torch.cuda.empty_cache()
-        cp = bench_cp(kda_b200, _cabi, device, rank, world, barrier)
+        cp = bench_cp(kda_b200, _cabi, device, rank, world, barrier, tokens=args.cp_tokens)
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -861,6 +861,10 @@ def main():
                     help="skip the strong-scaling and context-parallel legs")
     ap.add_argument("--other-configs", action="store_true",
                     help="also time the packed (config 2) and 1M-token (config 4) workloads")
+    ap.add_argument("--cp-only", action="store_true",
+                    help="run only the long-sequence forward leg (for profiler captures)")
+    ap.add_argument("--cp-tokens", type=int, default=1 << 20,
+                    help="tokens of the long-sequence forward leg")
     ap.add_argument("--preops-only", action="store_true",
                     help="measure only the gate / l2norm / short-conv pre-ops (for profiler captures)")
     args = ap.parse_args()
@@ -869,6 +873,15 @@ def main():
         return
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback of the fused path)")
+    if args.cp_only:
+        import kda_b200
+        from kda_b200 import _cabi
+
+        torch.cuda.set_device(0)
+        dev0 = torch.device("cuda", 0)
+        print(json.dumps({"cp": bench_cp(kda_b200, _cabi, dev0, 0, 1, torch.cuda.synchronize,
+                                         tokens=args.cp_tokens)}), flush=True)
+        return
     if args.preops_only:
         import kda_b200  # noqa: F401  (registers the operators)
         torch.cuda.set_device(0)
