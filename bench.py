@@ -234,6 +234,7 @@ def run_ours(args):
     decode = None if args.skip_decode else bench_decode(kda_b200, _cabi, device, load_peaks())
     preops = None if (args.skip_decode or rank != 0) else bench_preops(device, load_peaks(), batch, tokens)
     norm_fusion = None if (args.skip_decode or rank != 0) else bench_layer_norm_fusion(kda_b200, device, batch, tokens)
+    layer = None if (args.skip_decode or rank != 0) else bench_layer(kda_b200, _cabi, device)
     others = None
     if args.other_configs and rank == 0:
         del dev
@@ -364,6 +365,7 @@ def run_ours(args):
         "decode": decode,
         "preops": preops,
         "layer_qk_norm": norm_fusion,
+        "layer": layer,
         "other_configs": others,
         "strong": strong,
         "cp": cp,
@@ -540,6 +542,42 @@ def bench_layer_norm_fusion(kda_b200, device, batch=8, tokens=4096, iters=10):
         out[name] = {"ms_per_step": round(a.elapsed_time(z) / iters, 4)}
     out["workload"] = f"l2norm(q), l2norm(k) + chunk_kda fwd+bwd, B={batch} T={tokens} H={H}"
     return out
+
+
+def bench_layer(kda_b200, _cabi, device, batch=2, tokens=4096, hidden=4096, iters=5):
+    """One KDAAttention layer (the reference example's module on these kernels), forward + backward
+    at H=32, head 128: ms per step and how it splits between this library's kernels (CUDA-event
+    pairs of the library) and everything else (the cuBLAS projections, casts, masks)."""
+    torch.manual_seed(11)
+    layer = kda_b200.KDAAttention(hidden, H, D, backend="fused", device=device)
+    x = torch.randn(batch, tokens, hidden, device=device, dtype=torch.bfloat16, requires_grad=True)
+    params = list(layer.parameters())
+
+    def step():
+        out = layer(x).hidden_states
+        return torch.autograd.grad(out, [x] + params, torch.ones_like(out))
+
+    for _ in range(2):
+        step()
+    torch.cuda.synchronize()
+    a, z = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(iters):
+        step()
+    z.record()
+    torch.cuda.synchronize()
+    ms = a.elapsed_time(z) / iters
+    _cabi.read_stage_timing(reset=True)
+    _cabi.stage_timing(True)
+    step()
+    torch.cuda.synchronize()
+    stages = _cabi.read_stage_timing(reset=True)
+    _cabi.stage_timing(False)
+    ours = sum(v[1] for v in stages.values())
+    return {"workload": f"KDAAttention fwd+bwd, B={batch} T={tokens} hidden={hidden} H={H} head={D}, bf16",
+            "ms_per_step": round(ms, 3), "tokens_per_s": round(batch * tokens / (ms * 1e-3), 1),
+            "ms_in_this_librarys_kernels": round(ours, 3),
+            "kernels_ms": {k: round(v[1], 3) for k, v in stages.items()}}
 
 
 def bench_decode(kda_b200, _cabi, device, peaks, nseq=256, steps=200):
