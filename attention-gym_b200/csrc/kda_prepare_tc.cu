@@ -125,9 +125,9 @@ __global__ void __launch_bounds__(NT, 1) kda_prepare_tc_kernel(const __grid_cons
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm + pl::MISC + 64);
   volatile int* s_abort = reinterpret_cast<volatile int*>(sm + pl::MISC + 72);
   float* s_beta = reinterpret_cast<float*>(sm + pl::MISC + 128);           // [64]
-  float* s_tmp = s_beta + 64;                                              // [3][256] inverse scratch
   float* Lf = reinterpret_cast<float*>(sm + pl::LF);
   float* Af = reinterpret_cast<float*>(sm + pl::AF);
+  float* Bf = reinterpret_cast<float*>(sm + pl::KN);     // A[r][r] L[r][m] blocks: the column-operand tiles are dead by then
   float* tab = reinterpret_cast<float*>(sm + pl::TAB);   // [14][128], see phase 1
   const unsigned char* sG = sm + pl::G;
 
@@ -432,7 +432,34 @@ __global__ void __launch_bounds__(NT, 1) kda_prepare_tc_kernel(const __grid_cons
   }
   __syncthreads();
   pr_mark(p, it, 6);
-  // A[r][c] = -A[r][r] * sum_{c <= m < r} L[r][m] A[m][c], one block diagonal at a time.
+  // B[r][m] = A[r][r] L[r][m] for the six blocks below the diagonal, all at once (they only need the
+  // diagonal blocks): with them every block of the inverse is ONE product,
+  //   A[r][c] = -sum_{c <= m < r} B[r][m] A[m][c],
+  // so the block diagonals at distance 1, 2, 3 cost one barrier each instead of two.
+  if (tid < 384) {
+    const int blk = tid >> 6, tile = tid & 63, i = 2 * (tile >> 3), j = 2 * (tile & 7);
+    const int r = blk < 3 ? blk + 1 : (blk < 5 ? blk - 1 : 3);     // (1,0) (2,0) (3,0) (2,1) (3,1) (3,2)
+    const int m = blk < 3 ? 0 : (blk < 5 ? 1 : 2);
+    const float* A0 = Af + (16 * r + i) * pl::LP + 16 * r;          // A[r][r], rows i, i + 1
+    const float* B_ = Lf + (16 * r) * pl::LP + 16 * m + j;          // L[r][m], columns j, j + 1
+    float s00 = 0.f, s01 = 0.f, s10 = 0.f, s11 = 0.f;
+#pragma unroll
+    for (int k = 0; k < 16; k += 4) {
+      const float4 a0 = *reinterpret_cast<const float4*>(A0 + k);
+      const float4 a1 = *reinterpret_cast<const float4*>(A0 + pl::LP + k);
+      const float av0[4] = {a0.x, a0.y, a0.z, a0.w}, av1[4] = {a1.x, a1.y, a1.z, a1.w};
+#pragma unroll
+      for (int kk = 0; kk < 4; ++kk) {
+        const float2 bv = *reinterpret_cast<const float2*>(B_ + (k + kk) * pl::LP);
+        s00 = fmaf(av0[kk], bv.x, s00); s01 = fmaf(av0[kk], bv.y, s01);
+        s10 = fmaf(av1[kk], bv.x, s10); s11 = fmaf(av1[kk], bv.y, s11);
+      }
+    }
+    float* dst = Bf + (16 * r + i) * pl::LP + 16 * m + j;
+    *reinterpret_cast<float2*>(dst) = make_float2(s00, s01);
+    *reinterpret_cast<float2*>(dst + pl::LP) = make_float2(s10, s11);
+  }
+  __syncthreads();
   // A pair of adjacent lanes owns a 2 x 2 tile of a 16 x 16 result block and splits the inner
   // dimension between its lanes in interleaved groups of four (16-byte loads along k for the row
   // operand, 8-byte loads for the column operand; the two lanes' column rows sit 16 banks apart);
@@ -444,7 +471,7 @@ __global__ void __launch_bounds__(NT, 1) kda_prepare_tc_kernel(const __grid_cons
     const bool act = tid < pairs * 128;                           // whole warps
     const int c = rest >> 6, r = c + DIST, i = 2 * ((rest >> 3) & 7), j = 2 * (rest & 7);
     if (act) {
-      const float* A0 = Lf + (16 * r + i) * pl::LP + 16 * c;      // L[r][c .. r-1], rows i, i + 1
+      const float* A0 = Bf + (16 * r + i) * pl::LP + 16 * c;      // B[r][c .. r-1], rows i, i + 1
       const float* B_ = Af + (16 * c) * pl::LP + 16 * c + j;      // A[c .. r-1][c], columns j, j + 1
       float s00 = 0.f, s01 = 0.f, s10 = 0.f, s11 = 0.f;
 #pragma unroll
@@ -456,29 +483,6 @@ __global__ void __launch_bounds__(NT, 1) kda_prepare_tc_kernel(const __grid_cons
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk) {
           const float2 bv = *reinterpret_cast<const float2*>(B_ + (k + kk) * pl::LP);
-          s00 = fmaf(av0[kk], bv.x, s00); s01 = fmaf(av0[kk], bv.y, s01);
-          s10 = fmaf(av1[kk], bv.x, s10); s11 = fmaf(av1[kk], bv.y, s11);
-        }
-      }
-      s00 += __shfl_xor_sync(0xffffffffu, s00, 1); s01 += __shfl_xor_sync(0xffffffffu, s01, 1);
-      s10 += __shfl_xor_sync(0xffffffffu, s10, 1); s11 += __shfl_xor_sync(0xffffffffu, s11, 1);
-      *reinterpret_cast<float2*>(s_tmp + (c << 8) + (i + ks) * 16 + j) =
-          ks ? make_float2(s10, s11) : make_float2(s00, s01);
-    }
-    __syncthreads();
-    if (act) {
-      const float* A0 = Af + (16 * r + i) * pl::LP + 16 * r;      // A[r][r], rows i, i + 1
-      const float* B_ = s_tmp + (c << 8) + j;
-      float s00 = 0.f, s01 = 0.f, s10 = 0.f, s11 = 0.f;
-#pragma unroll
-      for (int m = 0; m < 2; ++m) {
-        const int k = 4 * (ks + 2 * m);
-        const float4 a0 = *reinterpret_cast<const float4*>(A0 + k);
-        const float4 a1 = *reinterpret_cast<const float4*>(A0 + pl::LP + k);
-        const float av0[4] = {a0.x, a0.y, a0.z, a0.w}, av1[4] = {a1.x, a1.y, a1.z, a1.w};
-#pragma unroll
-        for (int kk = 0; kk < 4; ++kk) {
-          const float2 bv = *reinterpret_cast<const float2*>(B_ + (k + kk) * 16);
           s00 = fmaf(av0[kk], bv.x, s00); s01 = fmaf(av0[kk], bv.y, s01);
           s10 = fmaf(av1[kk], bv.x, s10); s11 = fmaf(av1[kk], bv.y, s11);
         }
