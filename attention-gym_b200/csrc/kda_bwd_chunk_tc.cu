@@ -62,7 +62,9 @@ __device__ __forceinline__ void tc_mark(const BwdTcParams& p, int it, int slot) 
 namespace bl {  // shared-memory layout (bytes)
 constexpr int HH = 0, DHH = 32768, DO = 65536, VN = 81920, DV2 = 98304, V = 114688, K = 131072,
               Q = 147456, AK = 163840, G = 172032, MISC = 204800, TOTAL = 212992;
-constexpr int NORMX = TOTAL, TOTAL_NORM = TOTAL + 4096;      // row norms and row dots of the NORM kernels
+constexpr int OFFS = TOTAL, kOffCache = 256;                 // cu_seqlens / chunk_offsets entries kept in shared memory
+constexpr int NORMX = OFFS + 2048, TOTAL_PLAIN = NORMX;      // row norms and row dots of the NORM kernels
+constexpr int TOTAL_NORM = NORMX + 4096;
 // overlays (valid once their host tiles are dead)
 constexpr int DWT = HH, KGM = HH + 16384;                       // after phase 0
 constexpr int X = DHH, Y = DHH + 8192, DA = DHH + 16384, DL = DHH + 24576;
@@ -204,6 +206,15 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
   const int r0 = 16 * rq;                        // first of the 16 chunk rows it handles
   const int H = p.H;
 
+  // Work items are located by a binary search over the sequence offsets: from shared memory when
+  // they fit (a chain of dependent global loads per item would sit on the critical path).
+  int32_t* s_cu = reinterpret_cast<int32_t*>(sm + bl::OFFS);
+  int32_t* s_co = s_cu + bl::kOffCache;
+  const bool cached = p.nseq + 1 <= bl::kOffCache;
+  if (cached)
+    for (int i = tid; i <= p.nseq; i += NT) { s_cu[i] = p.cu_seqlens[i]; s_co[i] = p.chunk_offsets[i]; }
+  const int32_t* cu_off = cached ? s_cu : p.cu_seqlens;
+  const int32_t* ch_off = cached ? s_co : p.chunk_offsets;
   if (warp == 0) tmem_alloc(tmem_slot, 512);
   if (tid == 0) {
     // arrival counts = number of threads that issue (and commit) products of that group
@@ -222,10 +233,10 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
   // Loads of one work item, in two parts so that the next item's tiles start arriving as soon as
   // their shared-memory regions die.  Part 0 (barrier 0): h, dh, dO, v_new, dv2, v, A -- dead once
   // the last products of the current item have completed.  Part 1 (barrier 7): k, q, G, whose
-  // tiles stage dk, dq, dG until the current item's stores have read them.  Thread 0 only.
-  auto issue_loads = [&](int part, int chunk, int head, int64_t token0) {
+  // tiles stage dk, dq, dG until the current item's stores have read them.  Part 0 is issued by thread 0.
+  auto issue_loads = [&](int chunk, int head, int64_t token0) {
     const int ty = (int)token0, tx = head * 128;
-    if (part == 0) {
+    {
       const int yh = (chunk * H + head) * 128;
       mbar_expect_tx(&bar[0], 2 * 32768 + 4 * 16384 + 8192);
       for (int b = 0; b < 2; ++b) {
@@ -237,12 +248,53 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
       }
       for (int b = 0; b < 2; ++b) tma_load_2d(sm + bl::V + b * 8192, &p.tm_v, tx + 64 * b, ty, &bar[0]);
       tma_load_2d(sm + bl::AK, &p.tm_a, head * 64, ty, &bar[0]);
-    } else {
-      mbar_expect_tx(&bar[7], 2 * 16384 + 32768);
-      for (int b = 0; b < 2; ++b) tma_load_2d(sm + bl::K + b * 8192, &p.tm_k, tx + 64 * b, ty, &bar[7]);
-      for (int b = 0; b < 4; ++b) tma_load_2d(sm + bl::G + b * 8192, &p.tm_g, tx + 32 * b, ty, &bar[7]);
-      for (int b = 0; b < 2; ++b) tma_load_2d(sm + bl::Q + b * 8192, &p.tm_q, tx + 64 * b, ty, &bar[7]);
     }
+  };
+  // Part 1 is issued by the first eight lanes of warp 4, one tile each (a single thread would spend
+  // about 50 ns per tile on the critical path of the item); lane 0 first waits until the previous
+  // item's dk, dq, dG stores -- its own -- have read the tiles that are about to be overwritten.
+  auto issue_part1 = [&](int head, int64_t token0) {      // whole warp 4
+    const int ty = (int)token0, tx = head * 128;
+    if (lid == 0) {
+      tma_store_wait_read();
+      mbar_expect_tx(&bar[7], 2 * 16384 + 32768);
+    }
+    __syncwarp();
+    if (lid < 2) tma_load_2d(sm + bl::K + lid * 8192, &p.tm_k, tx + 64 * lid, ty, &bar[7]);
+    else if (lid < 6) tma_load_2d(sm + bl::G + (lid - 2) * 8192, &p.tm_g, tx + 32 * (lid - 2), ty, &bar[7]);
+    else if (lid < 8) tma_load_2d(sm + bl::Q + (lid - 6) * 8192, &p.tm_q, tx + 64 * (lid - 6), ty, &bar[7]);
+  };
+
+  // Phase-0 products: one issuing thread per accumulator (lane 0 of warps 0..3).  A product's time is
+  // about its shared-memory operand bytes / 128 B per clock (4 KB + 2 KB for M = 128, N = 64, K = 16),
+  // and the issuing thread is held while the queue is full: issuing them from the end of the
+  // previous item was measured and gained 1 % (the stores and reloads compete for the same bandwidth).
+  auto issue_phase0 = [&]() {
+    tc_fence_after();
+    const uint32_t hh = saddr(sm + bl::HH), dhh = saddr(sm + bl::DHH), dO = saddr(sm + bl::DO),
+                   vn = saddr(sm + bl::VN), dv2 = saddr(sm + bl::DV2);
+    if (warp == 0) {
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks)
+        umma(tmem + tc::DW, desc_kmajor(hh, ks, 16384), desc_kmajor(dv2, ks, 8192),
+             instr_desc(128, 64, 0, 0, 1), ks > 0);
+    } else if (warp == 1) {
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks)
+        umma(tmem + tc::DAQK, desc_kmajor(dO, ks, 8192), desc_kmajor(vn, ks, 8192),
+             instr_desc(64, 64, 0, 0), ks > 0);
+    } else if (warp == 2) {
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks)
+        umma(tmem + tc::DQ, desc_kmajor(hh, ks, 16384), desc_kmajor(dO, ks, 8192),
+             instr_desc(128, 64, 0, 0), ks > 0);
+    } else {
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks)
+        umma(tmem + tc::DKS, desc_kmajor(dhh, ks, 16384), desc_kmajor(vn, ks, 8192),
+             instr_desc(128, 64, 0, 0), ks > 0);
+    }
+    umma_commit(&bar[1]);
   };
 
   // persistent walk over the (chunk, head) work items
@@ -255,7 +307,7 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
   for (int w = blockIdx.x; w < p.total; w += gridDim.x) {
   tc_mark(p, it, 15);
   const int chunk = w / H, head = w - chunk * H;
-  const ChunkWork cw = pre ? cw_next : locate_chunk(p.cu_seqlens, p.chunk_offsets, p.nseq, chunk);
+  const ChunkWork cw = pre ? cw_next : locate_chunk(cu_off, ch_off, p.nseq, chunk);
   if (cw.valid == 0) continue;              // capacity slot past the last active chunk
   const int valid = cw.valid;
   const int ty = (int)cw.token0, tx = head * 128;
@@ -270,13 +322,8 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
   }
   __syncthreads();     // the previous item's staging tiles have been read; beta is in place
   tc_mark(p, it, 16);
-  if (tid == 0) {
-    if (!pre) issue_loads(0, chunk, head, cw.token0);
-    if (valid < 64) {          // the fix-up of a partial chunk needs every tile before the first product
-      tma_store_wait_read();
-      issue_loads(1, chunk, head, cw.token0);
-    }
-  }
+  if (tid == 0 && !pre) issue_loads(chunk, head, cw.token0);
+  if (warp == 4 && valid < 64) issue_part1(head, cw.token0);   // the fix-up of a partial chunk needs every tile before the first product
   int chunk_n = 0, head_n = 0;
   bool next_ok = false;
   tc_mark(p, it, 17);
@@ -308,38 +355,9 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
   __syncthreads();
   if (*s_abort) return 2;
 
-  // ---- phase 0 UMMAs: one issuing thread per accumulator (lane 0 of warps 0..3) -------------------
-  if (lid == 0 && warp < 4) {
-    tc_fence_after();
-    const uint32_t hh = saddr(sm + bl::HH), dhh = saddr(sm + bl::DHH), dO = saddr(sm + bl::DO),
-                   vn = saddr(sm + bl::VN), dv2 = saddr(sm + bl::DV2);
-    if (warp == 0) {
-#pragma unroll
-      for (int ks = 0; ks < 8; ++ks)
-        umma(tmem + tc::DW, desc_kmajor(hh, ks, 16384), desc_kmajor(dv2, ks, 8192),
-             instr_desc(128, 64, 0, 0, 1), ks > 0);
-    } else if (warp == 1) {
-#pragma unroll
-      for (int ks = 0; ks < 8; ++ks)
-        umma(tmem + tc::DAQK, desc_kmajor(dO, ks, 8192), desc_kmajor(vn, ks, 8192),
-             instr_desc(64, 64, 0, 0), ks > 0);
-    } else if (warp == 2) {
-#pragma unroll
-      for (int ks = 0; ks < 8; ++ks)
-        umma(tmem + tc::DQ, desc_kmajor(hh, ks, 16384), desc_kmajor(dO, ks, 8192),
-             instr_desc(128, 64, 0, 0), ks > 0);
-    } else {
-#pragma unroll
-      for (int ks = 0; ks < 8; ++ks)
-        umma(tmem + tc::DKS, desc_kmajor(dhh, ks, 16384), desc_kmajor(vn, ks, 8192),
-             instr_desc(128, 64, 0, 0), ks > 0);
-    }
-    umma_commit(&bar[1]);
-    if (warp == 0 && valid == 64) {   // k, q, G: their tiles staged the previous item's dk, dq, dG
-      tma_store_wait_read();
-      issue_loads(1, chunk, head, cw.token0);
-    }
-  }
+  // ---- phase 0 UMMAs ---------------------------------------------------------------------------------
+  if (lid == 0 && warp < 4) issue_phase0();
+  if (warp == 4 && valid == 64) issue_part1(head, cw.token0);   // k, q, G: their tiles staged the previous item's dk, dq, dG
   // meanwhile: hd[kappa] = sum_v h dh over this thread's quarter of v
   {
     float s = 0.f;
@@ -363,7 +381,7 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
     if (wn < p.total) {
       chunk_n = wn / H;
       head_n = wn - chunk_n * H;
-      cw_next = locate_chunk(p.cu_seqlens, p.chunk_offsets, p.nseq, chunk_n);
+      cw_next = locate_chunk(cu_off, ch_off, p.nseq, chunk_n);
       next_ok = cw_next.valid > 0;
       if (tid < 64)
         beta_next = (next_ok && tid < cw_next.valid) ? p.beta[(cw_next.token0 + tid) * H + head_n] : 0.f;
@@ -766,7 +784,13 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
   tc_fence_after();
   tc_mark(p, it, 12);
   // every tile but k, q, G is dead from here on: the next item's tiles start arriving
-  if (tid == 0 && next_ok) issue_loads(0, chunk_n, head_n, cw_next.token0);
+  if (tid == 0 && next_ok) issue_loads(chunk_n, head_n, cw_next.token0);
+  if (warp == 5 && lid < 8 && next_ok) {      // and its k, q, G tiles are asked into L2 for the load that follows the stores
+    const int ty = (int)cw_next.token0, tx = head_n * 128;
+    if (lid < 2) tma_prefetch_2d(&p.tm_k, tx + 64 * lid, ty);
+    else if (lid < 6) tma_prefetch_2d(&p.tm_g, tx + 32 * (lid - 2), ty);
+    else tma_prefetch_2d(&p.tm_q, tx + 64 * (lid - 6), ty);
+  }
   // NORM: the unnormalised q, k pieces this thread turns into y again once the epilogue below is
   // through; fetched now so that their latency hides behind the epilogue instead of ending the item
   uint4 raw_q[2], raw_k[2];
@@ -901,7 +925,7 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
   fence_async_smem();
   __syncthreads();
   if (valid == 64) {
-    if (tid == 0) {
+    if (tid == 128) {      // the thread that reloads these tiles for the next item
       for (int b = 0; b < 2; ++b) {
         tma_store_2d(&p.tm_dq, sm + bl::Q + b * 8192, tx + 64 * b, ty);
         tma_store_2d(&p.tm_dk, sm + bl::K + b * 8192, tx + 64 * b, ty);
@@ -939,7 +963,7 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
   ph ^= 1;
   ++it;
   }  // work items
-  if (tid == 0) tma_store_wait_read();      // staged tiles must outlive the bulk stores' reads
+  if (tid == 0 || tid == 128) tma_store_wait_read();      // staged tiles must outlive the bulk stores' reads
   if (rc && tid == 0 && p.error) atomicExch(p.error, rc);
   tc_fence_before();
   __syncthreads();
@@ -979,7 +1003,7 @@ int launch_bwd_chunk_tc(const bf16* q, const bf16* k, const bf16* v, const float
     return KDA_ERR_LAUNCH;
   if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p.error), g_bwd_tc_error) != cudaSuccess)
     return KDA_ERR_LAUNCH;
-  const int smem = (rstd_q ? bl::TOTAL_NORM : bl::TOTAL) + 1024;
+  const int smem = (rstd_q ? bl::TOTAL_NORM : bl::TOTAL_PLAIN) + 1024;
   auto kernel = rstd_q ? kda_bwd_chunk_tc_kernel<true> : kda_bwd_chunk_tc_kernel<false>;
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
     return KDA_ERR_LAUNCH;
