@@ -382,49 +382,72 @@ __global__ void __launch_bounds__(256) l2norm_bwd_vec_kernel(const uint4* __rest
   }
 }
 
-// dA_log[h] = sum over partial rows and channels, d_dt_bias[h, c] = sum over partial rows (fixed order).
-// One block per head; when K divides 256 the 256 / K row groups of a block work side by side, each
-// thread keeping eight rows of loads in flight.
+// dA_log[h] = sum over partial rows and channels, d_dt_bias[h, c] = sum over partial rows; every sum
+// in a fixed order.  Blocks 0 .. ceil(HK / 32) - 1 own 32 channels of d_dt_bias each: eight row groups
+// side by side, sixteen rows of loads in flight per thread.  The H blocks after them own one head of
+// dA_log: the head's rows x K slice is walked by the whole block, sixteen loads in flight per thread.
 __global__ void __launch_bounds__(256) gate_bwd_reduce_kernel(const float* __restrict__ pa,
                                                               const float* __restrict__ pb, int64_t rows,
-                                                              int K, float* __restrict__ dA,
+                                                              int H, int K, float* __restrict__ dA,
                                                               float* __restrict__ dbias) {
-  __shared__ float s_a[256], s_b[256];
-  const int h = blockIdx.x, tid = threadIdx.x;
-  const int64_t HK = (int64_t)gridDim.x * K;
-  const bool split = K <= 256 && 256 % K == 0;
-  const int groups = split ? 256 / K : 1;
-  float total = 0.f;
-  for (int c0 = 0; c0 < K; c0 += 256) {
-    const int c = split ? tid % K : c0 + tid, g = split ? tid / K : 0;
-    float a = 0.f, b = 0.f;
-    if (c < K) {
-      const float* qa = pa + (int64_t)h * K + c;
-      const float* qb = pb + (int64_t)h * K + c;
-      int64_t r = g;
-      for (; r + 7 * groups < rows; r += 8 * groups) {
-        float va[8], vb[8];
+  __shared__ float s_part[256];
+  const int tid = threadIdx.x, lane = tid & 31, grp = tid >> 5;
+  const int64_t HK = (int64_t)H * K;
+  const int col_blocks = (int)((HK + 31) / 32);
+  if ((int)blockIdx.x < col_blocks) {
+    const int64_t ch = (int64_t)blockIdx.x * 32 + lane;
+    float b = 0.f;
+    if (ch < HK) {
+      const float* q = pb + ch;
+      int64_t r = grp;
+      for (; r + 15 * 8 < rows; r += 16 * 8) {
+        float v[16];
 #pragma unroll
-        for (int u = 0; u < 8; ++u) { va[u] = qa[(r + u * groups) * HK]; vb[u] = qb[(r + u * groups) * HK]; }
+        for (int u = 0; u < 16; ++u) v[u] = q[(r + 8 * u) * HK];
 #pragma unroll
-        for (int u = 0; u < 8; ++u) { a += va[u]; b += vb[u]; }
+        for (int u = 0; u < 16; ++u) b += v[u];
       }
-      for (; r < rows; r += groups) { a += qa[r * HK]; b += qb[r * HK]; }
+      for (; r < rows; r += 8) b += q[r * HK];
     }
-    s_a[tid] = a; s_b[tid] = b;
+    s_part[tid] = b;
     __syncthreads();
-    if (c < K && g == 0) {
-      float bs = 0.f;
-      for (int q = 0; q < groups; ++q) bs += s_b[q * K + (split ? c : tid)];
-      dbias[(int64_t)h * K + c] = bs;
+    if (grp == 0 && ch < HK) {
+      float t = 0.f;
+#pragma unroll
+      for (int g = 0; g < 8; ++g) t += s_part[32 * g + lane];
+      dbias[ch] = t;
     }
-    if (tid == 0) {
-      const int n = split ? 256 : min(256, K - c0);
-      for (int q = 0; q < n; ++q) total += s_a[q];
-    }
-    __syncthreads();
+    return;
   }
-  if (tid == 0) dA[h] = total;
+  const int h = (int)blockIdx.x - col_blocks;
+  const float* q = pa + (int64_t)h * K;
+  const int64_t n = rows * K;
+  float a = 0.f;
+  int64_t e = tid;
+  for (; e + 15 * 256 < n; e += 16 * 256) {
+    float v[16];
+#pragma unroll
+    for (int u = 0; u < 16; ++u) {
+      const int64_t i = e + 256 * u, r = i / K;
+      v[u] = q[r * HK + (i - r * K)];
+    }
+#pragma unroll
+    for (int u = 0; u < 16; ++u) a += v[u];
+  }
+  for (; e < n; e += 256) {
+    const int64_t r = e / K;
+    a += q[r * HK + (e - r * K)];
+  }
+  s_part[tid] = a;
+  __syncthreads();
+  if (tid < 32) {
+    float t = 0.f;
+#pragma unroll
+    for (int g = 0; g < 8; ++g) t += s_part[32 * g + tid];
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) t += __shfl_xor_sync(0xffffffffu, t, d);
+    if (tid == 0) dA[h] = t;
+  }
 }
 
 static int check_launch() { return cudaGetLastError() == cudaSuccess ? KDA_OK : KDA_ERR_LAUNCH; }
@@ -501,8 +524,9 @@ extern "C" int kda_gate_bwd_reduce(const float* dA_partial, const float* dbias_p
                                    int heads, int dim, float* dA_log, float* d_dt_bias, void* stream) {
   if (!dA_partial || !dbias_partial || !dA_log || !d_dt_bias || rows < 0 || heads < 1 || dim < 1)
     return KDA_ERR_ARG;
-  kda::gate_bwd_reduce_kernel<<<(unsigned)heads, 256, 0, (cudaStream_t)stream>>>(
-      dA_partial, dbias_partial, rows, dim, dA_log, d_dt_bias);
+  const unsigned blocks = (unsigned)(((int64_t)heads * dim + 31) / 32 + heads);
+  kda::gate_bwd_reduce_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(
+      dA_partial, dbias_partial, rows, heads, dim, dA_log, d_dt_bias);
   return kda::check_launch();
 }
 
