@@ -4,6 +4,9 @@
   (sequences are independent; the reference checks the same property at small sizes,
   test/test_kda_ragged_public_backward.py:142-191);
 * a prefix computed alone gives bitwise the same outputs (causality);
+* the output is linear in (v, initial state) for fixed q, k, gates and beta, and the backward pass
+  is the adjoint of that linear map: <dO, o> + <dS, S_T> = <dv, v> + <dh0, h0> over all 8 x 4096 x 32
+  (token, head) pairs at once;
 * 1024 decode steps end in the state the chunked core reaches on the same tokens;
 * the context-parallel boundary-state chain reproduces the single pass over 1 M tokens;
 
@@ -88,6 +91,50 @@ def test_config1_rows_are_independent_and_match_the_oracle():
     # causal: the first 512 tokens of row 3 against the fp32 recurrence, heads 5 and 6
     ro, _ = _oracle_slice(q[3, :512], k[3, :512], v[3, :512], g2[3, :512], beta[3, :512], None, (5, 7))
     assert_normalised(full[0][3, :512, 5:7].float(), ro[0], 2e-2, "config 1 output vs oracle")
+
+
+def test_config1_linear_in_values_and_backward_is_the_adjoint():
+    """B=8, T=4096, H=32: for fixed q, k, gates and beta the core is a linear map (v, h0) -> (o, S_T).
+    Checked over the whole batch: additivity of the forward pass, and the inner-product identity
+    <dO, o> + <dS, S_T> = <dv, v> + <dh0, h0> that ties the backward kernels (state-gradient walk and
+    chunk backward) to the forward ones.  Every product is rounded to bf16 once on the way, so the
+    two sides agree to about the bf16 spacing of the largest term, not bitwise."""
+    torch.cuda.empty_cache()
+    gen = _gen(131)
+    B, T = 8, 4096
+    q, k = _unit((B, T, H, D), gen), _unit((B, T, H, D), gen)
+    va = torch.randn(B, T, H, D, generator=gen, device="cuda").bfloat16()
+    vb = torch.randn(B, T, H, D, generator=gen, device="cuda").bfloat16()
+    g2 = _gate((B, T, H, D), gen)
+    cum = g2.view(B, T // 64, 64, H, D).cumsum(2).view(B, T, H, D)
+    beta = torch.sigmoid(torch.randn(B, T, H, generator=gen, device="cuda"))
+    ha = 0.05 * torch.randn(B, H, D, D, generator=gen, device="cuda")
+    hb = 0.05 * torch.randn(B, H, D, D, generator=gen, device="cuda")
+    do = torch.randn(B, T, H, D, generator=gen, device="cuda").bfloat16()
+    dst = 0.1 * torch.randn(B, H, D, D, generator=gen, device="cuda")
+
+    def fwd(v, h0):
+        with torch.no_grad():
+            return kda_b200.chunk_kda(q, k, v, cum, beta, h0, output_final_state=True)
+
+    oa, sa = fwd(va, ha)
+    ob, sb = fwd(vb, hb)
+    # the summed values are rounded to bf16 once more (2^-9 relative), well inside the tolerance
+    os_, ss = fwd((va.float() + vb.float()).bfloat16(), ha + hb)
+    assert_normalised(os_.float(), oa.float() + ob.float(), 1e-2, "o(v_a + v_b) against o(v_a) + o(v_b)")
+    assert_normalised(ss, sa + sb, 1e-2, "S_T(v_a + v_b) against S_T(v_a) + S_T(v_b)")
+    del oa, sa, ob, sb, os_, ss
+
+    ins = [t.detach().clone().requires_grad_(True) for t in (q, k, va, cum, beta, ha)]
+    o, st = kda_b200.chunk_kda(*ins, output_final_state=True)
+    grads = torch.autograd.grad((o, st), ins, (do, dst))
+    dv, dh0 = grads[2], grads[5]
+    lhs = (do.double() * o.double()).sum() + (dst.double() * st.double()).sum()
+    rhs = (dv.double() * va.double()).sum() + (dh0.double() * ha.double()).sum()
+    # scale of the sums: sqrt(number of terms) x typical term; bf16 rounding of o and dv gives a
+    # relative 2^-9 on each term with random sign
+    scale = ((do.double() * o.double()).abs().sum() + (dv.double() * va.double()).abs().sum()).item()
+    assert abs(lhs.item() - rhs.item()) <= 2e-4 * scale, (lhs.item(), rhs.item(), scale)
 
 
 def test_config2_packed_sequences_are_independent_and_match_the_oracle():
