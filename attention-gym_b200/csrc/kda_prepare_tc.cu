@@ -196,11 +196,10 @@ __global__ void __launch_bounds__(NT, 1) kda_prepare_tc_kernel(const __grid_cons
   const int ty = (int)cw.token0, tx = head * 128;
   if (tid < 64)
     s_beta[tid] = pre ? beta_next : (tid < valid ? p.beta[(cw.token0 + tid) * H + head] : 0.f);
-  if (tid == 0) {
-    tma_store_wait_read();                   // the previous item's staging tiles have been read
-    if (!pre) { issue_loads(0, head, cw.token0); issue_loads(1, head, cw.token0); issue_loads(2, head, cw.token0); }
-  }
-  __syncthreads();
+  // No CTA barrier here: everything written before the barrier that ends the table step (beta, the
+  // table over the A tile, tiles loaded for an item without prefetch) was last read before the
+  // previous item's final barrier, where thread 0 had also drained every store group but w, u.
+  if (tid == 0 && !pre) { issue_loads(0, head, cw.token0); issue_loads(1, head, cw.token0); issue_loads(2, head, cw.token0); }
   // the next item: located (and its beta fetched) while this item's tiles arrive
   int head_n = 0;
   bool next_ok = false;
@@ -249,6 +248,7 @@ __global__ void __launch_bounds__(NT, 1) kda_prepare_tc_kernel(const __grid_cons
     const int rr = bb == 0 ? k6 + 1 : (bb == 1 ? k6 - 1 : 3);
     tab[e] = fexp2(gate(16 * rr) - gate(16 * bb));
   }
+  if (tid == 0) tma_store_wait_read();       // the w, u staging tiles (over Kr / Kn) of the previous item have been read
   __syncthreads();
   pr_mark(p, it, 2);
   if (*s_abort) return 2;
@@ -573,6 +573,7 @@ __global__ void __launch_bounds__(NT, 1) kda_prepare_tc_kernel(const __grid_cons
   }
   fence_async_smem();
   tc_fence_before();
+  if (tid == 0) tma_store_wait_read();       // qg, kg, Aqk, A have left their tiles (issued long ago)
   __syncthreads();
   pr_mark(p, it, 10);
   if (*s_abort) return 4;
