@@ -301,6 +301,7 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
   uint32_t ph = 0;              // parity of this item's barrier phases
   int it = 0, rc = 0;
   bool pre = false;             // part 0 of this item's loads was issued by the previous item
+  bool prev_full = false;       // the previous item was a full chunk (its results left through bulk stores)
   ChunkWork cw_next{};
   float beta_next = 0.f;
   float rs_next = 0.f;          // NORM: threads 64..191 carry one reciprocal norm each (q rows, then k rows)
@@ -320,7 +321,11 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
       s_rs[tid - 64] = pre ? rs_next : (row < valid ? rs[(cw.token0 + row) * H + head] : 0.f);
     }
   }
-  __syncthreads();     // the previous item's staging tiles have been read; beta is in place
+  // Between two full chunks nothing that is written before the next barrier (beta, the row norms,
+  // hd) is still read by the previous item, whose accumulators were read before its last barrier
+  // and whose bulk stores are drained by the thread that reloads their tiles: no barrier.
+  const bool chained = valid == 64 && prev_full;
+  if (!chained) __syncthreads();     // the previous item's staging tiles have been read
   tc_mark(p, it, 16);
   if (tid == 0 && !pre) issue_loads(chunk, head, cw.token0);
   if (warp == 4 && valid < 64) issue_part1(head, cw.token0);   // the fix-up of a partial chunk needs every tile before the first product
@@ -352,8 +357,10 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
     }
     fence_async_smem();
   }
-  __syncthreads();
-  if (*s_abort) return 2;
+  if (!chained) {
+    __syncthreads();
+    if (*s_abort) return 2;
+  }
 
   // ---- phase 0 UMMAs ---------------------------------------------------------------------------------
   if (lid == 0 && warp < 4) issue_phase0();
@@ -923,6 +930,7 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
     }
   }
   fence_async_smem();
+  tc_fence_before();     // every accumulator has been read: the next item's first products may overwrite them
   __syncthreads();
   if (valid == 64) {
     if (tid == 128) {      // the thread that reloads these tiles for the next item
@@ -960,6 +968,7 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
   tc_mark(p, it, 18);
   if (rc) break;
   pre = next_ok;
+  prev_full = valid == 64;
   ph ^= 1;
   ++it;
   }  // work items
