@@ -197,8 +197,10 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
   float* s_db = s_beta + 64;                                              // [2 terms][4 quadrants][64]
   float* s_hd = s_db + 512;                                               // [4][128]
   float* s_kdk = s_hd + 512;                                              // [4][128]
-  float* s_rs = reinterpret_cast<float*>(sm + bl::NORMX);                 // [2 = q, k][64] reciprocal norms
-  float* s_dot = s_rs + 128;                                              // [2][64 rows][4 quadrants] <dy, y>
+  // reciprocal norms [2 = q, k][64], one copy per item parity: an item's copy is written while the
+  // item before it runs, so barriers lie between that write and its first read
+  float* s_rs2 = reinterpret_cast<float*>(sm + bl::NORMX);
+  float* s_dot = s_rs2 + 256;                                             // [2][64 rows][4 quadrants] <dy, y>
 
   const int tid = threadIdx.x, warp = tid >> 5, lid = tid & 31;
   const int quad = warp & 3, rq = warp >> 2;
@@ -304,7 +306,6 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
   bool prev_full = false;       // the previous item was a full chunk (its results left through bulk stores)
   ChunkWork cw_next{};
   float beta_next = 0.f;
-  float rs_next = 0.f;          // NORM: threads 64..191 carry one reciprocal norm each (q rows, then k rows)
   for (int w = blockIdx.x; w < p.total; w += gridDim.x) {
   tc_mark(p, it, 15);
   const int chunk = w / H, head = w - chunk * H;
@@ -314,17 +315,18 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
   const int ty = (int)cw.token0, tx = head * 128;
   if (tid < 64)
     s_beta[tid] = pre ? beta_next : (tid < valid ? p.beta[(cw.token0 + tid) * H + head] : 0.f);
+  float* s_rs = s_rs2 + 128 * (it & 1);
   if constexpr (NORM) {
-    if (tid >= 64 && tid < 192) {
+    if (!pre && tid >= 64 && tid < 192) {      // (with pre the item before this one wrote them)
       const int row = (tid - 64) & 63;
       const float* rs = tid < 128 ? p.rstd_q : p.rstd_k;
-      s_rs[tid - 64] = pre ? rs_next : (row < valid ? rs[(cw.token0 + row) * H + head] : 0.f);
+      s_rs[tid - 64] = row < valid ? rs[(cw.token0 + row) * H + head] : 0.f;
     }
   }
-  // Between two full chunks nothing that is written before the next barrier (beta, the row norms,
-  // hd) is still read by the previous item, whose accumulators were read before its last barrier
+  // Between two full chunks nothing that is written before the next barrier (beta, hd) is read
+  // before it or is still read by the previous item, whose accumulators were read before its last barrier
   // and whose bulk stores are drained by the thread that reloads their tiles: no barrier.
-  const bool chained = valid == 64 && prev_full;
+  const bool chained = valid == 64 && prev_full && pre;
   if (!chained) __syncthreads();     // the previous item's staging tiles have been read
   tc_mark(p, it, 16);
   if (tid == 0 && !pre) issue_loads(chunk, head, cw.token0);
@@ -396,7 +398,8 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
         if (tid >= 64 && tid < 192) {
           const int row = (tid - 64) & 63;
           const float* rs = tid < 128 ? p.rstd_q : p.rstd_k;
-          rs_next = (next_ok && row < cw_next.valid) ? rs[(cw_next.token0 + row) * H + head_n] : 0.f;
+          s_rs2[128 * ((it + 1) & 1) + tid - 64] =
+              (next_ok && row < cw_next.valid) ? rs[(cw_next.token0 + row) * H + head_n] : 0.f;
         }
       }
     }
