@@ -197,6 +197,7 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
   float* s_db = s_beta + 64;                                              // [2 terms][4 quadrants][64]
   float* s_hd = s_db + 512;                                               // [4][128]
   float* s_kdk = s_hd + 512;                                              // [4][128]
+  int* s_next = reinterpret_cast<int*>(s_kdk + 512);                      // next item: token0 (two words), valid
   // reciprocal norms [2 = q, k][64], one copy per item parity: an item's copy is written while the
   // item before it runs, so barriers lie between that write and its first read
   float* s_rs2 = reinterpret_cast<float*>(sm + bl::NORMX);
@@ -384,25 +385,16 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
     }
     s_hd[rq * 128 + L] = s;
   }
-  // the next work item: located (and its beta fetched) while the first products run
-  {
+  // the next work item is located by one thread of a warp that issues nothing while the first
+  // products run (the search is a chain of dependent loads: done by every thread it sat on the
+  // path of the issuing warps); everybody reads the result after the barrier below
+  if (tid == 160) {
     const int wn = w + (int)gridDim.x;
-    if (wn < p.total) {
-      chunk_n = wn / H;
-      head_n = wn - chunk_n * H;
-      cw_next = locate_chunk(cu_off, ch_off, p.nseq, chunk_n);
-      next_ok = cw_next.valid > 0;
-      if (tid < 64)
-        beta_next = (next_ok && tid < cw_next.valid) ? p.beta[(cw_next.token0 + tid) * H + head_n] : 0.f;
-      if constexpr (NORM) {
-        if (tid >= 64 && tid < 192) {
-          const int row = (tid - 64) & 63;
-          const float* rs = tid < 128 ? p.rstd_q : p.rstd_k;
-          s_rs2[128 * ((it + 1) & 1) + tid - 64] =
-              (next_ok && row < cw_next.valid) ? rs[(cw_next.token0 + row) * H + head_n] : 0.f;
-        }
-      }
-    }
+    ChunkWork nx{};
+    if (wn < p.total) nx = locate_chunk(cu_off, ch_off, p.nseq, wn / H);
+    s_next[0] = (int)(nx.token0 & 0xffffffffLL);
+    s_next[1] = (int)(nx.token0 >> 32);
+    s_next[2] = nx.valid;
   }
   tc_mark(p, it, 2);
   if (!mbar_wait(&bar[7], ph)) *s_abort = 1;       // k, q, A, G, v have landed
@@ -429,6 +421,24 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
   __syncthreads();
   tc_mark(p, it, 3);      // every thread is done with the raw h / dh tiles
   if (*s_abort) return 3;
+  {   // the next item, and what this thread carries over to it
+    const int wn = w + (int)gridDim.x;
+    chunk_n = wn / H;
+    head_n = wn - chunk_n * H;
+    cw_next.token0 = (int64_t)(((uint64_t)(uint32_t)s_next[1] << 32) | (uint32_t)s_next[0]);
+    cw_next.valid = s_next[2];
+    next_ok = cw_next.valid > 0;        // 0 also when there is no further item
+    if (tid < 64)
+      beta_next = (next_ok && tid < cw_next.valid) ? p.beta[(cw_next.token0 + tid) * H + head_n] : 0.f;
+    if constexpr (NORM) {
+      if (tid >= 64 && tid < 192) {
+        const int row = (tid - 64) & 63;
+        const float* rs = tid < 128 ? p.rstd_q : p.rstd_k;
+        s_rs2[128 * ((it + 1) & 1) + tid - 64] =
+            (next_ok && row < cw_next.valid) ? rs[(cw_next.token0 + row) * H + head_n] : 0.f;
+      }
+    }
+  }
 
   // This thread's two (row, 8-channel) pieces -- rows tid / 16 and tid / 16 + 32, channels 8 (tid % 16) --
   // are the same in every pass that builds gated k tiles: their k (raw bf16) and gate values are read
