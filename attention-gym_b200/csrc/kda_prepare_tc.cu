@@ -125,6 +125,7 @@ __global__ void __launch_bounds__(NT, 1) kda_prepare_tc_kernel(const __grid_cons
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm + pl::MISC + 64);
   volatile int* s_abort = reinterpret_cast<volatile int*>(sm + pl::MISC + 72);
   float* s_beta = reinterpret_cast<float*>(sm + pl::MISC + 128);           // [64]
+  int* s_next = reinterpret_cast<int*>(sm + pl::MISC + 96);                // next item: token0 (two words), valid
   float* Lf = reinterpret_cast<float*>(sm + pl::LF);
   float* Af = reinterpret_cast<float*>(sm + pl::AF);
   float* Bf = reinterpret_cast<float*>(sm + pl::KN);     // A[r][r] L[r][m] blocks: the column-operand tiles are dead by then
@@ -200,19 +201,17 @@ __global__ void __launch_bounds__(NT, 1) kda_prepare_tc_kernel(const __grid_cons
   // table over the A tile, tiles loaded for an item without prefetch) was last read before the
   // previous item's final barrier, where thread 0 had also drained every store group but w, u.
   if (tid == 0 && !pre) { issue_loads(0, head, cw.token0); issue_loads(1, head, cw.token0); issue_loads(2, head, cw.token0); }
-  // the next item: located (and its beta fetched) while this item's tiles arrive
+  // the next item is located by one thread while this item's tiles arrive (the search is a chain of
+  // dependent loads); everybody reads the result after the barrier that ends the table step
   int head_n = 0;
   bool next_ok = false;
-  {
+  if (tid == 160) {
     const int wn = wi + (int)gridDim.x;
-    if (wn < p.total) {
-      const int chunk_n = wn / H;
-      head_n = wn - chunk_n * H;
-      cw_next = locate_chunk(cu_off, ch_off, p.nseq, chunk_n);
-      next_ok = cw_next.valid > 0;
-      if (tid < 64)
-        beta_next = (next_ok && tid < cw_next.valid) ? p.beta[(cw_next.token0 + tid) * H + head_n] : 0.f;
-    }
+    ChunkWork nx{};
+    if (wn < p.total) nx = locate_chunk(cu_off, ch_off, p.nseq, wn / H);
+    s_next[0] = (int)(nx.token0 & 0xffffffffLL);
+    s_next[1] = (int)(nx.token0 >> 32);
+    s_next[2] = nx.valid;
   }
   auto body = [&]() -> int {
   pr_mark(p, it, 0);
@@ -252,6 +251,15 @@ __global__ void __launch_bounds__(NT, 1) kda_prepare_tc_kernel(const __grid_cons
   __syncthreads();
   pr_mark(p, it, 2);
   if (*s_abort) return 2;
+  {   // the next item, and the beta value this thread carries over to it
+    const int wn = wi + (int)gridDim.x;
+    head_n = wn - (wn / H) * H;
+    cw_next.token0 = (int64_t)(((uint64_t)(uint32_t)s_next[1] << 32) | (uint32_t)s_next[0]);
+    cw_next.valid = s_next[2];
+    next_ok = cw_next.valid > 0;        // 0 also when there is no further item
+    if (tid < 64)
+      beta_next = (next_ok && tid < cw_next.valid) ? p.beta[(cw_next.token0 + tid) * H + head_n] : 0.f;
+  }
 
   // ---- phase 1a: the operands of the pairwise products; one (row, 8 channels) piece per task ---------
   float gkeep[2][8];                 // the gate rows of this thread's two tasks, reused by phase 1b
