@@ -49,7 +49,10 @@ struct PrepParams {
 
 __device__ __forceinline__ void pr_mark(const PrepParams& p, int it, int slot) {
 #ifdef KDA_PHASE_PROFILE
-  if (p.prof && it == 20 && threadIdx.x == 0 && blockIdx.x < 64) {
+#ifndef KDA_PROFILE_THREAD
+#define KDA_PROFILE_THREAD 0
+#endif
+  if (p.prof && it == 20 && threadIdx.x == KDA_PROFILE_THREAD && blockIdx.x < 64) {
     long long t;
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
     p.prof[blockIdx.x * 32 + slot] = t;
@@ -58,17 +61,17 @@ __device__ __forceinline__ void pr_mark(const PrepParams& p, int it, int slot) {
 }
 
 namespace pl {  // shared-memory layout (bytes)
-constexpr int Q = 0, K = 16384, V = 32768, G = 49152, KR = 81920, KN = 98304, QR = 139264,
+constexpr int Q = 0, K = 16384, V = 32768, G = 49152, QKR = 81920, KN = 114688,
               KG = 155648, AT = 172032, AQK = 180224, LF = 188416, AF = 205824, MISC = 223232,
               OFFS = 228352, TOTAL = 230400;
 constexpr int kOffCache = 256;          // cu_seqlens / chunk_offsets entries kept in shared memory
 constexpr int TAB = AT;                 // phase 1 table (3 KiB) over the A / Aqk tiles, dead until phase 3
 constexpr int QG = Q;                   // qg is staged in place over q
-constexpr int W = KR, U = KR + 16384;   // result staging over Kr / Kn, dead after phase 2
+constexpr int W = QKR, U = QKR + 16384; // result staging over the Qr / Kr tile, dead after phase 2
 constexpr int LP = 68;                  // pitch of the fp32 matrices L and A
 }  // namespace pl
 namespace pt {  // tensor-memory columns
-constexpr int AQ = 0, PK = 64, W = 128, U = 256;
+constexpr int AQ = 0, W = 128, U = 256;   // AQ: 32 columns per row block, Aqk^T then P^T
 }
 
 constexpr int NT = 512;
@@ -148,7 +151,7 @@ __global__ void __launch_bounds__(NT, 1) kda_prepare_tc_kernel(const __grid_cons
   if (warp == 0) tmem_alloc(tmem_slot, 512);
   if (tid == 0) {
     mbar_init(&bar[0], 1);
-    mbar_init(&bar[1], 8);       // one arrival per issuing thread
+    mbar_init(&bar[1], 4);       // one arrival per issuing thread
     mbar_init(&bar[2], 2);
     mbar_init_fence();
     *s_abort = 0;
@@ -306,8 +309,10 @@ __global__ void __launch_bounds__(NT, 1) kda_prepare_tc_kernel(const __grid_cons
       qq[e] *= er;
       o[e] = kk[e] * er;
     }
-    st_bf8(sm + pl::QR, 8192, i, c16, qq);
-    st_bf8(sm + pl::KR, 8192, i, c16, o);
+    // one row-operand tile for both sides: rows 32 b .. 32 b + 15 hold Qr of block b, the next 16 Kr,
+    // so that one N = 32 product per row block and k step gives Aqk^T and P^T side by side
+    st_bf8(sm + pl::QKR, 16384, 32 * b + (i & 15), c16, qq);
+    st_bf8(sm + pl::QKR, 16384, 32 * b + 16 + (i & 15), c16, o);
     // column operands Kn_r[i] = k_i 2^{R_r - G_i} for the row blocks r >= b
 #pragma unroll
     for (int e = 0; e < 8; ++e) o[e] = kk[e] * ei[e];
@@ -333,15 +338,15 @@ __global__ void __launch_bounds__(NT, 1) kda_prepare_tc_kernel(const __grid_cons
   // ---- phase 2: pairwise products, one issuing thread per row block (lane 0 of warps 0..3) ---------
   //   Aqk^T[j][i in block r] = sum_kappa Kn_r[j] Qr[i],   P^T[j][i] = sum_kappa Kn_r[j] Kr[i]
   //   (M = 64 rows j of which the first 16 (r + 1) are meaningful; the rest are masked below)
-  if (lid == 0 && warp < 8) {          // warps 0..3: Aqk^T of row block r; warps 4..7: P^T
+  if (lid == 0 && warp < 4) {
     tc_fence_after();
-    const int r = warp & 3;
+    const int r = warp;
     const uint32_t kn = saddr(sm + pl::KN + kn_off(r)), box = 16 * (r + 1) * 128;
-    const uint32_t rows = saddr(sm + (warp < 4 ? pl::QR : pl::KR)) + 2048 * r;
-    const uint32_t acc = tmem + (warp < 4 ? pt::AQ : pt::PK) + 16 * r;
-    const uint32_t id = instr_desc(64, 16, 0, 0);
+    const uint32_t rows = saddr(sm + pl::QKR) + 4096 * r;
+    const uint32_t acc = tmem + pt::AQ + 32 * r;       // columns 32 r .. +15: Aqk^T, +16 .. +31: P^T
+    const uint32_t id = instr_desc(64, 32, 0, 0);
 #pragma unroll
-    for (int ks = 0; ks < 8; ++ks) umma(acc, desc_kmajor(kn, ks, box), desc_kmajor(rows, ks, 8192), id, ks > 0);
+    for (int ks = 0; ks < 8; ++ks) umma(acc, desc_kmajor(kn, ks, box), desc_kmajor(rows, ks, 16384), id, ks > 0);
     umma_commit(&bar[1]);
   }
   // ---- phase 1b, while the products run: the WY operands beta k 2^G, beta v and the results kg, qg,
@@ -372,7 +377,9 @@ __global__ void __launch_bounds__(NT, 1) kda_prepare_tc_kernel(const __grid_cons
     st_bf8(sm + pl::V, 8192, i, c16, vv);
   }
   fence_async_smem();
+  pr_mark(p, it, 12);
   __syncthreads();
+  pr_mark(p, it, 13);
   if (tid == 0) {
     // kg and qg leave; G is dead: the next item's gates start arriving
     if (valid == 64) {
@@ -406,8 +413,8 @@ __global__ void __launch_bounds__(NT, 1) kda_prepare_tc_kernel(const __grid_cons
       const float4 b4 = *reinterpret_cast<const float4*>(s_beta + 16 * wq + 4 * q4);
       bt[4 * q4] = b4.x; bt[4 * q4 + 1] = b4.y; bt[4 * q4 + 2] = b4.z; bt[4 * q4 + 3] = b4.w;
     }
-    tmem_ld16(tl + pt::AQ + 16 * wq, a);
-    tmem_ld16(tl + pt::PK + 16 * wq, pk);
+    tmem_ld16(tl + pt::AQ + 32 * wq, a);
+    tmem_ld16(tl + pt::AQ + 32 * wq + 16, pk);
     if (lid < 16) {
       const int j = 16 * quad + lid;
 #pragma unroll
