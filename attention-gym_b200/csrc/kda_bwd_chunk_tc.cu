@@ -60,7 +60,7 @@ __device__ __forceinline__ void tc_mark(const BwdTcParams& p, int it, int slot) 
 }
 
 namespace bl {  // shared-memory layout (bytes)
-constexpr int HH = 0, DHH = 32768, DO = 65536, VN = 81920, DV2 = 98304, V = 114688, K = 131072,
+constexpr int HH = 0, DHH = 32768, VN = 65536, DO = 81920, DV2 = 90112, V = 114688, K = 131072,
               Q = 147456, AK = 163840, G = 172032, MISC = 204800, TOTAL = 212992;
 constexpr int OFFS = TOTAL, kOffCache = 256;                 // cu_seqlens / chunk_offsets entries kept in shared memory
 constexpr int NORMX = OFFS + 2048, TOTAL_PLAIN = NORMX;      // row norms and row dots of the NORM kernels
@@ -68,15 +68,17 @@ constexpr int TOTAL_NORM = NORMX + 4096;
 // overlays (valid once their host tiles are dead)
 constexpr int DWT = HH, KGM = HH + 16384;                       // after phase 0
 constexpr int X = DHH, Y = DHH + 8192, DA = DHH + 16384, DL = DHH + 24576;
-constexpr int KN0 = DO;                                         // row-type tiles: 40960 bytes from DO
+// dO and dv2 are interleaved by 64-channel box (dO box b at DO + 16384 b, dv2 box b right behind it),
+// so that [dO; dv2] is one 128-row operand: h dO and h dv2 are one N = 128 product per k step.
+constexpr int KN0 = VN;                                         // row-type tiles: 40960 bytes from v_new (tiles 0..2 end where dv2 box 0 begins)
 constexpr int QN0 = HH, KP0 = HH + 16384;                       // column block 0 (64 rows)
-constexpr int QN1 = 106496, KP1 = 118784;                       // column block 1 (48 rows)
-constexpr int QN2 = DO, KP2 = DO + 8192;                        // column block 2 (32 rows), after R1
-constexpr int QN3 = DO + 16384, KP3 = DO + 20480;               // column block 3 (16 rows)
+constexpr int QN1 = 106496, KP1 = 118784;                       // column block 1 (48 rows): dv2 box 1 and v, dead by then
+constexpr int QN2 = 65536, KP2 = 65536 + 8192;                  // column block 2 (32 rows), after R1
+constexpr int QN3 = 65536 + 16384, KP3 = 65536 + 20480;         // column block 3 (16 rows)
 constexpr int DVO = HH;                                         // dv staging (phase 2, h tile is dead)
 }  // namespace bl
 namespace tc {  // tensor-memory columns
-constexpr int DQ = 0, DKS = 64, DW = 128, DVB = 192, DKG = 256, X = 320, Y = 384, DAQK = 448, DL = 448;
+constexpr int DQ = 0, DW = 64, DKS = 128, DVB = 192, DKG = 256, X = 320, Y = 384, DAQK = 448, DL = 448;   // DQ, DW adjacent: one N = 128 product
 }
 
 __device__ __forceinline__ float ld_bf(const unsigned char* tile, int box_bytes, int row, int col) {
@@ -221,7 +223,7 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
   if (warp == 0) tmem_alloc(tmem_slot, 512);
   if (tid == 0) {
     // arrival counts = number of threads that issue (and commit) products of that group
-    const int counts[8] = {1, 4, 3, 1, 1, 2, 4, 1};
+    const int counts[8] = {1, 3, 3, 1, 1, 2, 4, 1};
     for (int i = 0; i < 8; ++i) mbar_init(&bar[i], counts[i]);
     mbar_init_fence();
     *s_abort = 0;
@@ -244,8 +246,8 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
       mbar_expect_tx(&bar[0], 2 * 32768 + 4 * 16384 + 8192);
       for (int b = 0; b < 2; ++b) {
         tma_load_2d(sm + bl::HH + b * 16384, &p.tm_h, 64 * b, yh, &bar[0]);
-        tma_load_2d(sm + bl::DO + b * 8192, &p.tm_do, tx + 64 * b, ty, &bar[0]);
-        tma_load_2d(sm + bl::DV2 + b * 8192, &p.tm_dv2, tx + 64 * b, ty, &bar[0]);
+        tma_load_2d(sm + bl::DO + b * 16384, &p.tm_do, tx + 64 * b, ty, &bar[0]);
+        tma_load_2d(sm + bl::DV2 + b * 16384, &p.tm_dv2, tx + 64 * b, ty, &bar[0]);
         tma_load_2d(sm + bl::DHH + b * 16384, &p.tm_dh, 64 * b, yh, &bar[0]);
         tma_load_2d(sm + bl::VN + b * 8192, &p.tm_vn, tx + 64 * b, ty, &bar[0]);
       }
@@ -275,22 +277,17 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
   auto issue_phase0 = [&]() {
     tc_fence_after();
     const uint32_t hh = saddr(sm + bl::HH), dhh = saddr(sm + bl::DHH), dO = saddr(sm + bl::DO),
-                   vn = saddr(sm + bl::VN), dv2 = saddr(sm + bl::DV2);
-    if (warp == 0) {
+                   vn = saddr(sm + bl::VN);
+    if (warp == 0) {         // dq_inter^T and dw^T: h [dO; dv2], N = 128 (the sign of dw is applied where it is read)
 #pragma unroll
       for (int ks = 0; ks < 8; ++ks)
-        umma(tmem + tc::DW, desc_kmajor(hh, ks, 16384), desc_kmajor(dv2, ks, 8192),
-             instr_desc(128, 64, 0, 0, 1), ks > 0);
+        umma(tmem + tc::DQ, desc_kmajor(hh, ks, 16384), desc_kmajor(dO, ks, 16384),
+             instr_desc(128, 128, 0, 0), ks > 0);
     } else if (warp == 1) {
 #pragma unroll
       for (int ks = 0; ks < 8; ++ks)
-        umma(tmem + tc::DAQK, desc_kmajor(dO, ks, 8192), desc_kmajor(vn, ks, 8192),
+        umma(tmem + tc::DAQK, desc_kmajor(dO, ks, 16384), desc_kmajor(vn, ks, 8192),
              instr_desc(64, 64, 0, 0), ks > 0);
-    } else if (warp == 2) {
-#pragma unroll
-      for (int ks = 0; ks < 8; ++ks)
-        umma(tmem + tc::DQ, desc_kmajor(hh, ks, 16384), desc_kmajor(dO, ks, 8192),
-             instr_desc(128, 64, 0, 0), ks > 0);
     } else {
 #pragma unroll
       for (int ks = 0; ks < 8; ++ks)
@@ -345,11 +342,12 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
   // in every token tile and repeat the last gate row, so no later step needs a row guard.
   if (valid < 64) {
     const int tiles[6] = {bl::DO, bl::VN, bl::DV2, bl::V, bl::K, bl::Q};
+    const int boxes[6] = {16384, 8192, 16384, 8192, 8192, 8192};
     for (int idx = tid; idx < (64 - valid) * 16; idx += NT) {
       const int r = valid + (idx >> 4), ch = idx & 15;
 #pragma unroll
       for (int t = 0; t < 6; ++t)
-        *reinterpret_cast<uint4*>(sm + tiles[t] + (ch >> 3) * 8192 + sw128_chunk(r, ch & 7)) = make_uint4(0, 0, 0, 0);
+        *reinterpret_cast<uint4*>(sm + tiles[t] + (ch >> 3) * boxes[t] + sw128_chunk(r, ch & 7)) = make_uint4(0, 0, 0, 0);
       if (ch < 8) *reinterpret_cast<uint4*>(sm + bl::AK + sw128_chunk(r, ch)) = make_uint4(0, 0, 0, 0);
     }
     for (int idx = tid; idx < (64 - valid) * 32; idx += NT) {
@@ -366,7 +364,7 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
   }
 
   // ---- phase 0 UMMAs ---------------------------------------------------------------------------------
-  if (lid == 0 && warp < 4) issue_phase0();
+  if (lid == 0 && warp < 3) issue_phase0();
   if (warp == 4 && valid == 64) issue_part1(head, cw.token0);   // k, q, G: their tiles staged the previous item's dk, dq, dG
   // meanwhile: hd[kappa] = sum_v h dh over this thread's quarter of v (giving the quarter of the
   // issuing warps 0..3 to warps 4..7 as well was measured: slower, 1.383 against 1.364 ms)
@@ -449,7 +447,9 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
   // ---- phase 1 epilogue: operand tiles for the next products; dq^T and dks^T stay in tensor memory
   {
     float a[16];
-    tmem_ld16(tl + tc::DW + r0, a);      // dw^T (already negated)
+    tmem_ld16(tl + tc::DW + r0, a);      // h dv2: dw^T = -(h dv2)
+#pragma unroll
+    for (int jj = 0; jj < 16; ++jj) a[jj] = -a[jj];
 #pragma unroll
     for (int qd = 0; qd < 2; ++qd) {
       uint4 v;
@@ -496,7 +496,7 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
     if (warp == 0) {
 #pragma unroll
       for (int ks = 0; ks < 4; ++ks)
-        umma(tmem + tc::DVB, desc_mnmajor(dv2, ks, 8192), desc_mnmajor(ak, ks, 0),
+        umma(tmem + tc::DVB, desc_mnmajor(dv2, ks, 16384), desc_mnmajor(ak, ks, 0),
              instr_desc(128, 64, 1, 1), ks > 0);
     } else if (warp == 1) {
 #pragma unroll
@@ -506,7 +506,7 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
     } else {
 #pragma unroll
       for (int ks = 0; ks < 8; ++ks)
-        umma(tmem + tc::X, desc_kmajor(dv2, ks, 8192), desc_kmajor(v, ks, 8192),
+        umma(tmem + tc::X, desc_kmajor(dv2, ks, 16384), desc_kmajor(v, ks, 8192),
              instr_desc(64, 64, 0, 0), ks > 0);
 #pragma unroll
       for (int ks = 0; ks < 8; ++ks)
@@ -517,8 +517,8 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
   }
   // Row-type gated tiles  Kn_ri[j][kappa] = k_j 2^{R_ri - G_j},  j < 16 (ri + 1): the four tiles
   // (16, 32, 48, 64 rows) are one flat list of 2560 eight-channel tasks.  The first three tiles
-  // overlay dO / v_new (dead) and are built while the phase 1 products run; the last one reaches
-  // into the dv2 tile and waits for them.
+  // overlay v_new and box 0 of dO (dead) and are built while the phase 1 products run; the last one
+  // covers box 0 of dv2 and waits for them.
   auto build_row_tiles = [&](int begin, int end) {
     // (only the last tile, ri = 3, is built here: tasks 1536 .. 2559; its reference row depends on
     // the channel piece only, which is the same for a thread's tasks)

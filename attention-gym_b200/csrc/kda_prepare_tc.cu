@@ -561,7 +561,13 @@ __global__ void __launch_bounds__(NT, 1) kda_prepare_tc_kernel(const __grid_cons
   if (!mbar_wait(&bar[2], ph)) *s_abort = 1;
   tc_fence_after();
   pr_mark(p, it, 9);
-  if (tid == 0 && next_ok) issue_loads(2, head_n, cw_next.token0);      // the k and v tiles are dead
+  if (warp == 0 && lid < 4 && next_ok) {      // the k and v tiles are dead: one lane per 64-channel tile
+    // (a thread spends about 50 ns per bulk copy it issues, and this warp's share of the epilogue
+    // below is what the barrier after it waits for)
+    const int b = lid >> 1, tyn = (int)cw_next.token0, txn = head_n * 128 + 64 * b;
+    if (lid & 1) tma_load_2d(sm + pl::V + b * 8192, &p.tm_v, txn, tyn, &bar[0]);
+    else tma_load_2d(sm + pl::K + b * 8192, &p.tm_k, txn, tyn, &bar[0]);
+  }
 
   // ---- epilogue: rows i = 16 quad + lane (lanes 0..15), columns 32 wq .. 32 wq + 31 of w and u -----------
   {
