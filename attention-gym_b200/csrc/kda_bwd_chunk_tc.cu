@@ -239,6 +239,8 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
   // their shared-memory regions die.  Part 0 (barrier 0): h, dh, dO, v_new, dv2, v, A -- dead once
   // the last products of the current item have completed.  Part 1 (barrier 7): k, q, G, whose
   // tiles stage dk, dq, dG until the current item's stores have read them.  Part 0 is issued by thread 0.
+  // (Spreading part 0 over lane 0 of 13 warps and the stores and reloads of part 1 over three
+  // threads was measured: 1.361 against 1.345 ms.)
   auto issue_loads = [&](int chunk, int head, int64_t token0) {
     const int ty = (int)token0, tx = head * 128;
     {
