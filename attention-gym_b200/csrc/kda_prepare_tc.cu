@@ -336,6 +336,8 @@ __global__ void __launch_bounds__(NT, 1) kda_prepare_tc_kernel(const __grid_cons
   pr_mark(p, it, 3);
 
   // ---- phase 2: pairwise products, one issuing thread per row block (lane 0 of warps 0..3) ---------
+  //   (issuing the products of row blocks 0, 1 half way through phase 1a, behind one more barrier,
+  //   was measured: 0.887 against 0.850 ms)
   //   Aqk^T[j][i in block r] = sum_kappa Kn_r[j] Qr[i],   P^T[j][i] = sum_kappa Kn_r[j] Kr[i]
   //   (M = 64 rows j of which the first 16 (r + 1) are meaningful; the rest are masked below)
   if (lid == 0 && warp < 4) {
