@@ -223,7 +223,7 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
   if (warp == 0) tmem_alloc(tmem_slot, 512);
   if (tid == 0) {
     // arrival counts = number of threads that issue (and commit) products of that group
-    const int counts[8] = {1, 3, 3, 1, 1, 2, 4, 1};
+    const int counts[8] = {1, 3, 3, 1, 1, 2, 4, 3};
     for (int i = 0; i < 8; ++i) mbar_init(&bar[i], counts[i]);
     mbar_init_fence();
     *s_abort = 0;
@@ -239,8 +239,7 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
   // their shared-memory regions die.  Part 0 (barrier 0): h, dh, dO, v_new, dv2, v, A -- dead once
   // the last products of the current item have completed.  Part 1 (barrier 7): k, q, G, whose
   // tiles stage dk, dq, dG until the current item's stores have read them.  Part 0 is issued by thread 0.
-  // (Spreading part 0 over lane 0 of 13 warps and the stores and reloads of part 1 over three
-  // threads was measured: 1.361 against 1.345 ms.)
+  // (Part 0 spread over lane 0 of 13 warps, one tile each, was measured: 1.40 against 1.366 ms.)
   auto issue_loads = [&](int chunk, int head, int64_t token0) {
     const int ty = (int)token0, tx = head * 128;
     {
@@ -257,19 +256,23 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
       tma_load_2d(sm + bl::AK, &p.tm_a, head * 64, ty, &bar[0]);
     }
   };
-  // Part 1 is issued by the first eight lanes of warp 4, one tile each (a single thread would spend
-  // about 50 ns per tile on the critical path of the item); lane 0 first waits until the previous
-  // item's dk, dq, dG stores -- its own -- have read the tiles that are about to be overwritten.
-  auto issue_part1 = [&](int head, int64_t token0) {      // whole warp 4
+  // Part 1 is issued by lane 0 of warps 4, 5, 6 (q, k, G): each of them also issued the bulk stores
+  // out of the tiles it reloads (dq, dk, dG of the previous item), so each waits for its own stores
+  // only and the three drain, and reload, side by side (measured on one GPU against one thread doing
+  // all stores and eight lanes the loads: 1.351 against 1.366 ms).
+  auto reload_piece = [&](int which, int head, int64_t token0) {
     const int ty = (int)token0, tx = head * 128;
-    if (lid == 0) {
-      tma_store_wait_read();
-      mbar_expect_tx(&bar[7], 2 * 16384 + 32768);
+    tma_store_wait_read();
+    if (which == 0) {
+      mbar_expect_tx(&bar[7], 16384);
+      for (int b = 0; b < 2; ++b) tma_load_2d(sm + bl::Q + b * 8192, &p.tm_q, tx + 64 * b, ty, &bar[7]);
+    } else if (which == 1) {
+      mbar_expect_tx(&bar[7], 16384);
+      for (int b = 0; b < 2; ++b) tma_load_2d(sm + bl::K + b * 8192, &p.tm_k, tx + 64 * b, ty, &bar[7]);
+    } else {
+      mbar_expect_tx(&bar[7], 32768);
+      for (int b = 0; b < 4; ++b) tma_load_2d(sm + bl::G + b * 8192, &p.tm_g, tx + 32 * b, ty, &bar[7]);
     }
-    __syncwarp();
-    if (lid < 2) tma_load_2d(sm + bl::K + lid * 8192, &p.tm_k, tx + 64 * lid, ty, &bar[7]);
-    else if (lid < 6) tma_load_2d(sm + bl::G + (lid - 2) * 8192, &p.tm_g, tx + 32 * (lid - 2), ty, &bar[7]);
-    else if (lid < 8) tma_load_2d(sm + bl::Q + (lid - 6) * 8192, &p.tm_q, tx + 64 * (lid - 6), ty, &bar[7]);
   };
 
   // Phase-0 products: one issuing thread per accumulator (lane 0 of warps 0..3).  A product's time is
@@ -330,7 +333,7 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
   if (!chained) __syncthreads();     // the previous item's staging tiles have been read
   tc_mark(p, it, 16);
   if (tid == 0 && !pre) issue_loads(chunk, head, cw.token0);
-  if (warp == 4 && valid < 64) issue_part1(head, cw.token0);   // the fix-up of a partial chunk needs every tile before the first product
+  if (lid == 0 && warp >= 4 && warp < 7 && valid < 64) reload_piece(warp - 4, head, cw.token0);   // the fix-up of a partial chunk needs every tile before the first product
   int chunk_n = 0, head_n = 0;
   bool next_ok = false;
   tc_mark(p, it, 17);
@@ -367,7 +370,7 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
 
   // ---- phase 0 UMMAs ---------------------------------------------------------------------------------
   if (lid == 0 && warp < 3) issue_phase0();
-  if (warp == 4 && valid == 64) issue_part1(head, cw.token0);   // k, q, G: their tiles staged the previous item's dk, dq, dG
+  if (lid == 0 && warp >= 4 && warp < 7 && valid == 64) reload_piece(warp - 4, head, cw.token0);   // k, q, G: their tiles staged the previous item's dk, dq, dG
   // meanwhile: hd[kappa] = sum_v h dh over this thread's quarter of v (giving the quarter of the
   // issuing warps 0..3 to warps 4..7 as well was measured: slower, 1.383 against 1.364 ms)
   {
@@ -949,12 +952,10 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
   tc_fence_before();     // every accumulator has been read: the next item's first products may overwrite them
   __syncthreads();
   if (valid == 64) {
-    if (tid == 128) {      // the thread that reloads these tiles for the next item
-      for (int b = 0; b < 2; ++b) {
-        tma_store_2d(&p.tm_dq, sm + bl::Q + b * 8192, tx + 64 * b, ty);
-        tma_store_2d(&p.tm_dk, sm + bl::K + b * 8192, tx + 64 * b, ty);
-      }
-      for (int b = 0; b < 4; ++b) tma_store_2d(&p.tm_dg, sm + bl::G + b * 8192, tx + 32 * b, ty);
+    if (lid == 0 && warp >= 4 && warp < 7) {
+      if (warp == 4) { for (int b = 0; b < 2; ++b) tma_store_2d(&p.tm_dq, sm + bl::Q + b * 8192, tx + 64 * b, ty); }
+      else if (warp == 5) { for (int b = 0; b < 2; ++b) tma_store_2d(&p.tm_dk, sm + bl::K + b * 8192, tx + 64 * b, ty); }
+      else { for (int b = 0; b < 4; ++b) tma_store_2d(&p.tm_dg, sm + bl::G + b * 8192, tx + 32 * b, ty); }
       tma_store_commit();
     }
   } else {
@@ -988,7 +989,7 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
   ph ^= 1;
   ++it;
   }  // work items
-  if (tid == 0 || tid == 128) tma_store_wait_read();      // staged tiles must outlive the bulk stores' reads
+  if (lid == 0 && (warp == 0 || (warp >= 4 && warp < 7))) tma_store_wait_read();      // staged tiles must outlive the bulk stores' reads
   if (rc && tid == 0 && p.error) atomicExch(p.error, rc);
   tc_fence_before();
   __syncthreads();
