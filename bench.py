@@ -58,7 +58,7 @@ STAGE_BYTES = {
 }
 # DRAM bytes per (token, head) and launch that ncu measured (dram__bytes_read + dram__bytes_write on
 # the B=2 case, which grows in proportion to the units; see profiles/)
-NCU_TRAFFIC = {"bwd_chunk": 4367, "state_fwd": 2017, "state_bwd": 1788, "prepare": 2376}
+NCU_TRAFFIC = {"bwd_chunk": 4370, "state_fwd": 2018, "state_bwd": 1780, "prepare": 2383}
 # algorithmic FLOP per (token, head) of each kernel (dense 64-wide tiles, no causal discount;
 # P = 2*64*128 = 16384, S = 2*128*128 = 32768); they add up to PATH_FLOP_FWD_BWD
 STAGE_FLOP = {
