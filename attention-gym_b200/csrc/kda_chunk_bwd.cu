@@ -105,6 +105,30 @@ extern "C" int kda_chunk_bwd(KDA_BWD_ARGS, void* workspace, int64_t workspace_by
   return chunk_bwd_impl(false, nullptr, nullptr, KDA_BWD_PASS, workspace, workspace_bytes, stream);
 }
 
+// The state-gradient walk of kda_chunk_bwd_saved alone: d_initial_state for the cotangents
+// (d_out, d_final_state), from the tapes in `saved` (w, kg, qg; read only) -- the part of the backward
+// pass that a context-parallel slice needs before the state gradient of the next slice has arrived.
+extern "C" int kda_chunk_bwd_state_saved(const float* cum_gate, const void* aqk, const void* d_out,
+                                         const float* d_final_state, float* d_initial_state,
+                                         const int32_t* cu_seqlens, const int32_t* chunk_offsets,
+                                         int nseq, int64_t tokens, int heads, int key_dim,
+                                         int value_dim, int num_chunks, void* saved,
+                                         int64_t saved_bytes, void* stream) {
+  if (!cum_gate || !aqk || !d_out || !d_initial_state || !cu_seqlens || !chunk_offsets || !saved)
+    return KDA_ERR_ARG;
+  if (key_dim != 128 || value_dim != 128) return KDA_ERR_UNSUPPORTED;
+  if (nseq < 1 || heads < 1 || tokens < 1 || num_chunks < 0) return KDA_ERR_ARG;
+  if (saved_bytes < kda_chunk_bwd_workspace_bytes(tokens, heads, num_chunks)) return KDA_ERR_ARG;
+  if (((uintptr_t)saved & 15) != 0) return KDA_ERR_ARG;
+  const int64_t nd = tokens * heads * 128;
+  const int64_t hs = (int64_t)num_chunks * heads * 128 * 128;
+  bf16* b = reinterpret_cast<bf16*>(saved);
+  bf16 *w = b, *kg = b + 2 * nd, *qg = b + 3 * nd, *dv2 = b + 5 * nd, *dhbuf = b + 6 * nd + hs;
+  return kda::launch_state_bwd_tc(w, kg, qg, (const bf16*)aqk, (const bf16*)d_out, cum_gate,
+                                  d_final_state, d_initial_state, dhbuf, dv2, cu_seqlens,
+                                  chunk_offsets, nseq, heads, tokens, num_chunks, (cudaStream_t)stream);
+}
+
 extern "C" int kda_chunk_bwd_saved(KDA_BWD_ARGS, void* saved, int64_t saved_bytes, void* stream) {
   return chunk_bwd_impl(true, nullptr, nullptr, KDA_BWD_PASS, saved, saved_bytes, stream);
 }

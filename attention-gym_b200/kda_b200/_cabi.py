@@ -71,6 +71,8 @@ _SIGNATURES = {
                               c_int64, c_void_p]),
     "kda_chunk_bwd_saved": (c_int, [c_void_p] * 18 + [c_int, c_int64, c_int, c_int, c_int, c_int,
                                     c_void_p, c_int64, c_void_p]),
+    "kda_chunk_bwd_state_saved": (c_int, [c_void_p] * 7 + [c_int, c_int64, c_int, c_int, c_int, c_int,
+                                          c_void_p, c_int64, c_void_p]),
     "kda_chunk_fwd_prepare": (c_int, [c_void_p] * 9 + [c_int, c_int64, c_int, c_int, c_void_p,
                                       c_int64, c_void_p]),
     "kda_chunk_fwd_state": (c_int, [c_void_p] * 7 + [c_int, c_int64, c_int, c_void_p, c_int,

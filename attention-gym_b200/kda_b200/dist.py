@@ -20,9 +20,10 @@
 The backward pass runs the mirror-image chain (``cp_chunk_backward``): the gradient entering a
 slice from the right, ``dh_out``, maps affinely to the one leaving it on the left,
 ``dh_in = M_r^T dh_out + c_r`` with the same transition ``M_r``; ``c_r`` is the slice's own backward
-with ``dh_out = 0``.  So middle ranks compute ``c_r`` in parallel, the [H, K, V] gradient travels
+with ``dh_out = 0``.  So middle ranks compute ``c_r`` in parallel (one forward pass with kept
+intermediates, then the reverse state walk alone: ``CudaSliceTape``), the [H, K, V] gradient travels
 from the last rank to the first, and every rank then runs its local backward with the true
-``dh_out``.  ``cp_chunk_kda`` ties both chains into one differentiable call.
+``dh_out`` from the same intermediates.  ``cp_chunk_kda`` ties both chains into one differentiable call.
 
 The reference has no multi-GPU code on this path (docs/linear.md:220-222 leaves context
 parallelism to the caller); the per-slice math is the chunk recurrence of
@@ -302,6 +303,39 @@ def cuda_slice_grads(q, k, v, cumulative_gate, beta, h_in, d_out, dh_out):
         return torch.autograd.grad((out, h_out), leaves, (d_out, dh_out))
 
 
+class CudaSliceTape:
+    """One forward pass of a slice with its intermediates kept, for the two backward steps of a middle
+    rank: ``state_grad`` (the reverse state walk alone: the gradient of the entering state for a given
+    gradient of the leaving one) and ``grads`` (the whole backward pass).  Both read the same tapes;
+    neither repeats the forward pass."""
+
+    def __init__(self, q, k, v, cumulative_gate, beta, h_in):
+        from . import ops
+
+        batch, heads = q.shape[0], q.shape[2]
+        if h_in is None:
+            h_in = torch.zeros(batch, heads, q.shape[3], v.shape[3], dtype=torch.float32, device=q.device)
+        self.args = (q.to(torch.bfloat16).contiguous(), k.to(torch.bfloat16).contiguous(),
+                     v.to(torch.bfloat16).contiguous(), cumulative_gate.float().contiguous(),
+                     beta.float().contiguous())
+        self.h_in = h_in.float().contiguous()
+        self.dtypes = (q.dtype, k.dtype, v.dtype, cumulative_gate.dtype, beta.dtype)
+        _, _, self.aqk, self.akk, self.saved = ops.chunk_fwd_saved_op(*self.args, self.h_in, None, None, True)
+
+    def state_grad(self, d_out, dh_out):
+        from . import ops
+
+        return ops.chunk_bwd_state_saved_op(self.args[3], self.aqk, self.saved, None, None,
+                                            d_out.contiguous(), dh_out)
+
+    def grads(self, d_out, dh_out):
+        from . import ops
+
+        dq, dk, dv, dg, db, dh = ops.chunk_bwd_saved_op(*self.args, self.aqk, self.akk, self.saved, None,
+                                                        None, d_out.contiguous(), dh_out, self.h_in, True)
+        return tuple(t.to(dt) for t, dt in zip((dq, dk, dv, dg, db), self.dtypes)) + (dh,)
+
+
 def _transposed_affine(trans, dh_out, c):
     """M^T dh_out + c for M [B, H, K, K] and states [B, H, K, V] (fp32)."""
     return torch.baddbmm(c.flatten(0, 1), trans.flatten(0, 1).transpose(1, 2).float(),
@@ -332,13 +366,22 @@ def cp_chunk_backward(q, k, v, cumulative_gate, beta, h_in, trans, d_out, d_fina
             send(grads[5].contiguous(), rank - 1)
         return grads
     c = None
-    if rank > 0:      # middle rank, in parallel with the others: c = the backward with dh_out = 0
+    tape = None
+    if rank > 0:      # middle rank, in parallel with the others: c = the state gradient for dh_out = 0
         zero = torch.zeros(shape, dtype=torch.float32, device=q.device)
-        c = local_grads(q, k, v, cumulative_gate, beta, h_in, d_out, zero)[5]
+        if local_grads is cuda_slice_grads:
+            # one forward pass with kept intermediates serves both steps, and the first step is the
+            # reverse state walk alone (no dq, dk, dv, dG, dbeta are formed for the zero cotangent)
+            tape = CudaSliceTape(q, k, v, cumulative_gate, beta, h_in)
+            c = tape.state_grad(d_out, zero)
+        else:
+            c = local_grads(q, k, v, cumulative_gate, beta, h_in, d_out, zero)[5]
     dh_out = torch.empty(shape, dtype=torch.float32, device=q.device)
     recv(dh_out, rank + 1)
     if rank > 0:
         send(_transposed_affine(trans, dh_out, c.float()).contiguous(), rank - 1)
+    if tape is not None:
+        return tape.grads(d_out, dh_out)
     return local_grads(q, k, v, cumulative_gate, beta, h_in, d_out, dh_out)
 
 
@@ -373,4 +416,4 @@ def cp_chunk_kda(q, k, v, cumulative_gate, beta, initial_state=None, *, group=No
 
 
 __all__ = ["shard_ranges", "cp_chunk_forward", "cp_chunk_backward", "cp_chunk_kda",
-           "cuda_slice_grads", "CudaSlice", "ChainTimeout"]
+           "cuda_slice_grads", "CudaSlice", "CudaSliceTape", "ChainTimeout"]

@@ -55,6 +55,12 @@ _define("kda_chunk_bwd_saved",
         "Tensor(a!) saved, Tensor? cu_seqlens, Tensor? chunk_offsets, Tensor? d_output, "
         "Tensor? d_final_state, Tensor? initial_state, bool want_state_grad) "
         "-> (Tensor, Tensor, Tensor, Tensor, Tensor, Tensor)")
+# The reverse state-gradient walk of kda_chunk_bwd_saved alone (no reference counterpart: it serves the
+# context-parallel backward chain, which needs the gradient of a slice's entering state before the
+# state gradient of the next slice has arrived).
+_define("kda_chunk_bwd_state_saved",
+        "(Tensor cumulative_gate, Tensor Aqk, Tensor(a!) saved, Tensor? cu_seqlens, "
+        "Tensor? chunk_offsets, Tensor d_output, Tensor? d_final_state) -> Tensor")
 # The chunked pair with the layer's q / k L2 normalisation fused in (no reference counterpart as one
 # operator: the reference runs l2norm as separate launches, fwd/triton/l2norm_fwd.py:84,143).
 _define("kda_chunk_fwd_qknorm",
@@ -284,6 +290,34 @@ def _chunk_bwd_saved(q, k, v, gate, beta, aqk, akk, saved, cu_seqlens, chunk_off
     return dq, dk, dv, dg, db, dh0
 
 
+@torch.library.impl(_lib, "kda_chunk_bwd_state_saved", "CUDA")
+def _chunk_bwd_state_saved(gate, aqk, saved, cu_seqlens, chunk_offsets, d_output, d_final_state):
+    _require_cuda(d_output, "the fused KDA core")
+    batch, tokens, heads, dim = d_output.shape
+    if dim != 128 or gate.shape[-1] != 128:
+        raise ValueError("the fused KDA core requires K=V=128")
+    if cu_seqlens is None:
+        cu_seqlens, chunk_offsets, capacity = _dense_offsets(d_output)
+        nseq = batch
+    else:
+        nseq = cu_seqlens.shape[0] - 1
+        capacity = chunk_capacity(tokens, nseq, _CHUNK)
+    total = batch * tokens
+    ws_bytes = _cabi.lib().kda_chunk_bwd_workspace_bytes(total, heads, capacity)
+    if saved.numel() < ws_bytes or saved.dtype != torch.uint8 or not saved.is_cuda:
+        raise ValueError("`saved` is not the buffer kda_chunk_fwd_saved returned for these shapes")
+    gate = gate.float().contiguous()
+    d_output = d_output.to(torch.bfloat16).contiguous()
+    if d_final_state is not None:
+        d_final_state = d_final_state.float().contiguous()
+    dh0 = torch.empty(nseq, heads, 128, 128, dtype=torch.float32, device=d_output.device)
+    _cabi.call("kda_chunk_bwd_state_saved", 1, _cabi.ptr(gate), _cabi.ptr(aqk.contiguous()),
+               _cabi.ptr(d_output), _cabi.ptr(d_final_state), _cabi.ptr(dh0), _cabi.ptr(cu_seqlens),
+               _cabi.ptr(chunk_offsets), nseq, total, heads, 128, 128, capacity, _cabi.ptr(saved),
+               saved.numel(), _cabi.stream())
+    return dh0
+
+
 @torch.library.impl(_lib, "kda_chunk_fwd_qknorm", "CUDA")
 def _chunk_fwd_qknorm(q, k, v, gate, beta, initial_state, cu_seqlens, chunk_offsets, want_state, keep,
                       eps):
@@ -420,6 +454,12 @@ def _(q, k, v, gate, beta, aqk, akk, saved, cu_seqlens, chunk_offsets, d_output,
     dh0 = (q.new_empty((nseq, q.shape[2], q.shape[3], v.shape[-1]), dtype=torch.float32)
            if want_state_grad else q.new_empty((0,), dtype=torch.float32))
     return (*_bwd_fake(q, k, v, gate, beta), dh0)
+
+
+@torch.library.register_fake(f"{_NS}::kda_chunk_bwd_state_saved")
+def _(gate, aqk, saved, cu_seqlens, chunk_offsets, d_output, d_final_state):
+    nseq = d_output.shape[0] if cu_seqlens is None else cu_seqlens.shape[0] - 1
+    return d_output.new_empty((nseq, d_output.shape[2], 128, 128), dtype=torch.float32)
 
 
 # --------------------------------------------------------------------------------------------
@@ -748,6 +788,7 @@ chunk_fwd_ragged_op = _ops.kda_chunk_fwd_ragged.default
 chunk_fwd_ragged_with_state_op = _ops.kda_chunk_fwd_ragged_with_state.default
 chunk_fwd_saved_op = _ops.kda_chunk_fwd_saved.default
 chunk_bwd_saved_op = _ops.kda_chunk_bwd_saved.default
+chunk_bwd_state_saved_op = _ops.kda_chunk_bwd_state_saved.default
 chunk_fwd_qknorm_op = _ops.kda_chunk_fwd_qknorm.default
 chunk_bwd_qknorm_op = _ops.kda_chunk_bwd_qknorm.default
 chunk_bwd_op = _ops.kda_chunk_bwd.default

@@ -228,6 +228,19 @@ int kda_chunk_bwd_saved(const void* q, const void* k, const void* v, const float
                         int key_dim, int value_dim, int num_chunks, void* saved, int64_t saved_bytes,
                         void* stream);
 
+/* The reverse state-gradient walk of kda_chunk_bwd_saved alone: d_initial_state [nseq, H, 128, 128] for
+ * the cotangents (d_out, d_final_state), read from the tapes a kda_chunk_fwd_save call left in `saved`
+ * (which stay intact; the buffer's workspace part is overwritten, as by kda_chunk_bwd_saved).  It is
+ * what a slice of a context-parallel backward chain computes before the state gradient of the next
+ * slice has arrived (the chain's affine term, kda_b200/dist.py); no dq, dk, dv, dG, dbeta are formed.
+ * No reference counterpart: the reference has no context parallelism; the walk itself replaces
+ * BlackwellDeltaHBwdV1 (bwd/cute/chunk_delta_h_bwd_v1.py:694, loop :1147-1276). */
+int kda_chunk_bwd_state_saved(const float* cum_gate, const void* aqk, const void* d_out,
+                              const float* d_final_state, float* d_initial_state,
+                              const int32_t* cu_seqlens, const int32_t* chunk_offsets, int nseq,
+                              int64_t tokens, int heads, int key_dim, int value_dim, int num_chunks,
+                              void* saved, int64_t saved_bytes, void* stream);
+
 /* The chunked pair with the q / k L2 normalisation of the layer fused in (the reference runs it as
  * separate launches right before and after the core: fwd/triton/l2norm_fwd.py:22,
  * bwd/triton/l2norm_bwd.py:37, examples/kda_training.py:412-421).  q and k are the unnormalised rows.

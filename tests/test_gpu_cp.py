@@ -10,7 +10,7 @@ import torch
 import kda_b200
 from kda_b200.dist import CudaSlice, cp_chunk_forward
 from oracle import kda_oracle as orc
-from helpers import assert_normalised
+from helpers import assert_normalised, to_cuda
 
 pytestmark = pytest.mark.gpu
 
@@ -178,3 +178,25 @@ def test_cp_backward_matches_single_gpu(world):
         got = torch.cat([grads[r][i] for r in range(world)], 1)
         assert_normalised(got.float(), ref[i].float(), 2e-2, f"cp {name} vs single GPU")
     assert_normalised(grads[0][5], ref[5], 2e-2, "cp d_initial_state vs single GPU")
+
+
+def test_state_gradient_walk_alone_equals_the_full_backward():
+    """The reverse state walk on kept intermediates (what a middle rank of the backward chain runs
+    before the next slice's state gradient has arrived) returns the entering-state gradient of the
+    full backward pass bit for bit, leaves the intermediates intact, and the full backward pass on
+    the same buffer afterwards equals autograd on a fresh forward pass."""
+    from kda_b200.dist import CudaSliceTape, cuda_slice_grads
+
+    inp = to_cuda(orc.make_inputs(2, 200, 2, 128, 128, seed=31), torch.bfloat16)
+    gen = torch.Generator(device="cuda").manual_seed(5)
+    h_in = 0.1 * torch.randn(2, 2, 128, 128, generator=gen, device="cuda")
+    d_out = torch.randn(2, 200, 2, 128, generator=gen, device="cuda").bfloat16()
+    dh_out = 0.1 * torch.randn(2, 2, 128, 128, generator=gen, device="cuda")
+    args = (inp["q"], inp["k"], inp["v"], inp["cum_gate"], inp["beta"])
+    ref = cuda_slice_grads(*args, h_in, d_out, dh_out)
+    ref0 = cuda_slice_grads(*args, h_in, d_out, torch.zeros_like(dh_out))
+    tape = CudaSliceTape(*args, h_in)
+    assert torch.equal(tape.state_grad(d_out, torch.zeros_like(dh_out)), ref0[5])
+    assert torch.equal(tape.state_grad(d_out, dh_out), ref[5])
+    for name, a, b in zip(("dq", "dk", "dv", "dg", "dbeta", "dh_in"), tape.grads(d_out, dh_out), ref):
+        assert torch.equal(a, b), name

@@ -72,6 +72,8 @@ def test_chunk_backward_ops(packed):
            True)
     _check(ops.kda_chunk_bwd_saved.default, *args, aqk, akk, saved, cu, co, do, dst, c["h0"], True)
     _check(ops.kda_chunk_bwd_saved.default, *args, aqk, akk, saved, cu, co, do, None, None, False)
+    _check(ops.kda_chunk_bwd_state_saved.default, c["cum_gate"], aqk, saved, cu, co, do, dst)
+    _check(ops.kda_chunk_bwd_state_saved.default, c["cum_gate"], aqk, saved, cu, co, do, None)
 
 
 @pytest.mark.parametrize("packed", [False, True], ids=["dense", "packed"])
@@ -172,7 +174,8 @@ def test_every_operator_of_the_namespace_is_covered():
     covered = {
         "kda_chunk_fwd", "kda_chunk_fwd_with_state", "kda_chunk_fwd_ragged",
         "kda_chunk_fwd_ragged_with_state", "kda_chunk_fwd_saved", "kda_chunk_bwd",
-        "kda_chunk_bwd_with_state_grad", "kda_chunk_bwd_saved", "kda_chunk_fwd_qknorm",
+        "kda_chunk_bwd_with_state_grad", "kda_chunk_bwd_saved", "kda_chunk_bwd_state_saved",
+        "kda_chunk_fwd_qknorm",
         "kda_chunk_bwd_qknorm", "kda_recurrent_fwd",
         "kda_recurrent_fwd_no_state", "kda_recurrent_fwd_paged", "kda_prepare_chunk_offsets",
         "kda_bounded_gate_fwd_dense", "kda_bounded_gate_fwd_ragged", "kda_bounded_gate_bwd",
