@@ -341,6 +341,37 @@ def test_many_short_sequences():
     assert_normalised(got["state"], ref_s, TOL, "final states")
 
 
+@pytest.mark.parametrize("normalize", [False, True], ids=["plain", "qk-norm"])
+def test_repeated_runs_of_a_ragged_batch_give_the_same_bits(normalize):
+    """Full chunks, partial tail chunks and empty sequences mixed, with enough (chunk, head) items
+    for every persistent CTA to walk dozens of them: the two persistent kernels hand shared-memory
+    tiles from one item to the next without a CTA barrier between full chunks, so a missing ordering
+    would show up as run-to-run differences.  Twenty runs must agree bit for bit (outputs, final
+    states and all gradients), and the device error word must stay clear."""
+    from kda_b200 import _cabi
+
+    gen = torch.Generator().manual_seed(21)
+    picks = [1, 63, 64, 65, 127, 128, 200, 1000, 2048, 77, 0]
+    lengths = [picks[i] for i in torch.randint(0, len(picks), (24,), generator=gen).tolist()]
+    inp = orc.make_inputs(1, sum(lengths), 16, 128, 128, seed=22, lengths=lengths)
+    q, k, v = (inp[n].bfloat16().cuda() for n in ("q", "k", "v"))
+    gate, beta, cu = inp["cum_gate"].cuda(), inp["beta"].cuda(), inp["cu_seqlens"].cuda()
+    do = torch.randn(v.shape, generator=torch.Generator(device="cuda").manual_seed(3), device="cuda").bfloat16()
+
+    def run():
+        ins = [t.detach().clone().requires_grad_(True) for t in (q, k, v, gate, beta)]
+        o, st = kda_b200.chunk_kda(*ins, cu_seqlens=cu, output_final_state=True, normalize_qk=normalize)
+        return (o, st) + torch.autograd.grad(o, ins, do)
+
+    first = run()
+    assert all(torch.isfinite(t.float()).all() for t in first)
+    for _ in range(20):
+        for name, a, b in zip(("o", "state", "dq", "dk", "dv", "dg", "dbeta"), first, run()):
+            assert torch.equal(a, b), name
+    torch.cuda.synchronize()
+    assert _cabi.lib().kda_device_error_word() == 0
+
+
 def test_a_bounded_wait_that_runs_out_reports_and_returns():
     """Every barrier wait of the tensor-memory kernels is bounded.  The library's self-test makes one
     run out on purpose (a barrier nothing arrives on, a few thousand polls): the kernel returns, the
