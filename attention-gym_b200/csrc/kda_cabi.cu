@@ -2,6 +2,8 @@
 #include <mutex>
 #include <vector>
 
+#include <nvtx3/nvToolsExt.h>
+
 #include "../../include/kda_b200.h"
 #include "kda_timing.cuh"
 
@@ -11,6 +13,19 @@ static const char* kStageNames[kStageCount] = {
     "prepare", "state_fwd", "state_bwd", "bwd_chunk", "recurrent",
     "gate_fwd", "gate_bwd", "l2norm", "conv", "chunk_offsets", "state_affine",
     "epilogue"};
+
+// Every kernel launch of the library sits in an NVTX range (a few nanoseconds when no tool is
+// attached), named after the reference's profiler ranges for the stages the kernel fuses
+// (fwd/cute/chunk_kda_fwd.py:94-119, bwd/cute/chunk_kda_bwd.py:58-129, kda/utils.py:269), so a
+// timeline of this library reads like one of the reference.
+static const char* kStageTraceNames[kStageCount] = {
+    "kda/fused/chunk_kda_fwd_intra",                        // gating, pairwise products, solve, w / u
+    "kda/fused/inter_chunk_state+output_composition",
+    "kda/fused/backward_dav+delta_h",
+    "kda/fused/backward_wy_dqkg+intra",
+    "kda/fused/recurrent",
+    "kda/fused/gate_cumsum_fwd", "kda/fused/gate_cumsum_bwd", "kda/fused/l2norm", "kda/fused/short_conv",
+    "kda/fused/chunk_offsets", "kda/fused/state_affine", "kda/fused/output_gate_norm"};
 
 struct Pair { cudaEvent_t a, b; int device; };
 constexpr int kMaxDevices = 64;
@@ -33,6 +48,7 @@ static cudaEvent_t get_event(int dev) {
 }
 
 void stage_begin(int stage, cudaStream_t s) {
+  nvtxRangePushA(kStageTraceNames[stage]);
   if (!g_enabled) return;
   std::lock_guard<std::mutex> lock(g_mu);
   const int dev = current_device();
@@ -41,6 +57,7 @@ void stage_begin(int stage, cudaStream_t s) {
   g_pairs[stage].push_back(p);
 }
 void stage_end(int stage, cudaStream_t s) {
+  nvtxRangePop();
   if (!g_enabled) return;
   std::lock_guard<std::mutex> lock(g_mu);
   if (!g_pairs[stage].empty()) cudaEventRecord(g_pairs[stage].back().b, s);

@@ -7,6 +7,7 @@ is torch's current CUDA stream.
 
 from __future__ import annotations
 
+import contextlib
 import ctypes
 import os
 from ctypes import c_float, c_int, c_int64, c_void_p
@@ -131,10 +132,21 @@ def stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 
 
+def profiler_range(name: str):
+    """A named range in torch profiler traces, free when no profiler is active (the reference's
+    mechanism, attn_gym/linear/kda/utils.py:269-273)."""
+    if torch.autograd.profiler._is_profiler_enabled:
+        return torch.profiler.record_function(name)
+    return contextlib.nullcontext()
+
+
 def call(name: str, launches: int, *args):
-    """Invoke an entry point that returns a status code; raise on failure."""
+    """Invoke an entry point that returns a status code; raise on failure.  Under an active torch
+    profiler the call is a range named after the entry point; inside it, every kernel launch is an
+    NVTX range named after the reference stages it fuses (kda_cabi.cu)."""
     global launch_count
-    rc = getattr(lib(), name)(*args)
+    with profiler_range("kda_b200/" + name):
+        rc = getattr(lib(), name)(*args)
     if rc != 0:
         raise RuntimeError(f"{name} failed: {_ERRORS.get(rc, rc)}")
     launch_count += launches

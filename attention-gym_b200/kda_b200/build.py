@@ -72,7 +72,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
             sys.stderr.write(out.decode())
         if proc.returncode:
             raise RuntimeError(f"nvcc failed on {src}")
-    subprocess.check_call([_nvcc(), "-shared", "-o", LIB_PATH, *objs, "-lcudart"])
+    subprocess.check_call([_nvcc(), "-shared", "-o", LIB_PATH, *objs, "-lcudart", "-ldl"])
     return LIB_PATH
 
 

@@ -110,3 +110,18 @@ def test_masks():
     z.sum().backward()
     assert x.grad[:, :4].min() == 1 and x.grad[:, 4:].abs().max() == 0
     assert kda_b200.mask_inactive_tokens(x, None) is x
+
+
+def test_profiler_range_is_free_without_a_profiler_and_named_under_one():
+    """The reference's tracing mechanism (kda/utils.py:269-273): a null context when no torch
+    profiler is active, a record_function range when one is."""
+    import contextlib
+
+    import torch
+    from kda_b200 import _cabi
+
+    assert isinstance(_cabi.profiler_range("kda_b200/x"), contextlib.nullcontext)
+    with torch.profiler.profile(activities=[torch.profiler.ProfilerActivity.CPU]) as prof:
+        with _cabi.profiler_range("kda_b200/some_entry"):
+            torch.ones(4).sum()
+    assert any(e.name == "kda_b200/some_entry" for e in prof.events())

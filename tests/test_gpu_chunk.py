@@ -372,6 +372,24 @@ def test_repeated_runs_of_a_ragged_batch_give_the_same_bits(normalize):
     assert _cabi.lib().kda_device_error_word() == 0
 
 
+def test_library_calls_show_up_as_named_ranges_in_a_profiler_trace():
+    """Under a torch profiler every C-ABI call of a forward + backward step is a named range
+    (reference: profiler_range around each stage, fwd/cute/chunk_kda_fwd.py:94-119); without a
+    profiler nothing is recorded (and nothing is paid)."""
+    inp = _case(2, 256, 2, seed=2)
+    do = torch.randn(inp["v"].shape, generator=torch.Generator().manual_seed(1))
+    _run_fused(inp, do, grad=True)
+    with torch.profiler.profile(activities=[torch.profiler.ProfilerActivity.CPU,
+                                            torch.profiler.ProfilerActivity.CUDA]) as prof:
+        _run_fused(inp, do, grad=True)
+        torch.cuda.synchronize()
+    names = {e.name for e in prof.events()}
+    assert any(n.startswith("kda_b200/kda_chunk_fwd") for n in names), sorted(names)[:40]
+    assert "kda_b200/kda_chunk_bwd_saved" in names
+    kernels = " ".join(sorted(names))
+    assert "kda_prepare_tc_kernel" in kernels and "kda_bwd_chunk_tc_kernel" in kernels
+
+
 def test_a_bounded_wait_that_runs_out_reports_and_returns():
     """Every barrier wait of the tensor-memory kernels is bounded.  The library's self-test makes one
     run out on purpose (a barrier nothing arrives on, a few thousand polls): the kernel returns, the
