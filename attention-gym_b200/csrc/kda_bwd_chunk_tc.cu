@@ -787,6 +787,15 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
     }
   }
   tc_mark(p, it, 10);
+  // the next item's k, q, G tiles are asked into L2 for the reload that follows this item's stores (without
+  // the request the kernel takes 7 % longer; asked for here, two phases before the end, rather than with
+  // the other tiles' loads: 1 % faster; earlier still: slower)
+  if (warp == 5 && lid < 8 && next_ok) {
+    const int ty = (int)cw_next.token0, tx = head_n * 128;
+    if (lid < 2) tma_prefetch_2d(&p.tm_k, tx + 64 * lid, ty);
+    else if (lid < 6) tma_prefetch_2d(&p.tm_g, tx + 32 * (lid - 2), ty);
+    else tma_prefetch_2d(&p.tm_q, tx + 64 * (lid - 6), ty);
+  }
   if (!mbar_wait(&bar[5], ph)) *s_abort = 1;   // row-type tiles are free again
   tc_fence_after();
   {
@@ -811,12 +820,6 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
   tc_mark(p, it, 12);
   // every tile but k, q, G is dead from here on: the next item's tiles start arriving
   if (tid == 0 && next_ok) issue_loads(chunk_n, head_n, cw_next.token0);
-  if (warp == 5 && lid < 8 && next_ok) {      // and its k, q, G tiles are asked into L2 for the load that follows the stores
-    const int ty = (int)cw_next.token0, tx = head_n * 128;
-    if (lid < 2) tma_prefetch_2d(&p.tm_k, tx + 64 * lid, ty);
-    else if (lid < 6) tma_prefetch_2d(&p.tm_g, tx + 32 * (lid - 2), ty);
-    else tma_prefetch_2d(&p.tm_q, tx + 64 * (lid - 6), ty);
-  }
   // NORM: the unnormalised q, k pieces this thread turns into y again once the epilogue below is
   // through; fetched now so that their latency hides behind the epilogue instead of ending the item
   uint4 raw_q[2], raw_k[2];
