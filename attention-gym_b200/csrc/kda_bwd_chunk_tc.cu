@@ -43,6 +43,7 @@ struct BwdTcParams {
   const int32_t* cu_seqlens; const int32_t* chunk_offsets;
   int* error;
   int nseq, H, total;          // total = chunk capacity x heads work items
+  int64_t tokens;              // rows of the packed buffers
   float scale;
   long long* prof;
 };
@@ -314,6 +315,10 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
   const int chunk = w / H, head = w - chunk * H;
   const ChunkWork cw = pre ? cw_next : locate_chunk(cu_off, ch_off, p.nseq, chunk);
   if (cw.valid == 0) continue;              // capacity slot past the last active chunk
+  if (!pre && !chunk_in_range(cw, p.tokens)) {     // (with pre the previous item checked it)
+    if (tid == 0 && p.error) atomicExch(p.error, kOffsetsOutOfRange);
+    continue;
+  }
   const int valid = cw.valid;
   const int ty = (int)cw.token0, tx = head * 128;
   if (tid < 64)
@@ -396,6 +401,7 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
     const int wn = w + (int)gridDim.x;
     ChunkWork nx{};
     if (wn < p.total) nx = locate_chunk(cu_off, ch_off, p.nseq, wn / H);
+    if (!chunk_in_range(nx, p.tokens)) nx.valid = 0;     // not prefetched; the item itself reports and skips
     s_next[0] = (int)(nx.token0 & 0xffffffffLL);
     s_next[1] = (int)(nx.token0 >> 32);
     s_next[2] = nx.valid;
@@ -1025,6 +1031,7 @@ int launch_bwd_chunk_tc(const bf16* q, const bf16* k, const bf16* v, const float
   p.beta = beta; p.dq = dq; p.dk = dk; p.dv = dv; p.dg = dg; p.db = db;
   p.cu_seqlens = cu; p.chunk_offsets = co; p.nseq = nseq; p.H = H;
   p.total = chunks * H;
+  p.tokens = tokens;
   p.scale = 0.08838834764831845f;
   int dev = 0, sms = 0;
   if (cudaGetDevice(&dev) != cudaSuccess ||

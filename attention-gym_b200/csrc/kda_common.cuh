@@ -75,7 +75,15 @@ struct ChunkWork {
   int local_chunk;
   int64_t token0;  // first token of the chunk in the packed buffer
   int valid;       // rows of the chunk that hold tokens (1..64); 0 = inactive capacity slot
+  int64_t seq_end; // end of the chunk's sequence in the packed buffer
 };
+
+// Device-side check of the offsets a chunk was located with: the chunks of a sequence that does not
+// lie inside the packed buffer (inconsistent cu_seqlens / chunk_offsets) are skipped by the kernels and
+// reported through their error word (code kOffsetsOutOfRange) instead of being read or written.  The
+// reference asserts its offsets on the device in its scheduler kernel (kda/chunk_scheduler.py:278-293); the
+// host-side validation cannot see the values without a device synchronisation.
+constexpr int kOffsetsOutOfRange = 9;
 
 __device__ __forceinline__ ChunkWork locate_chunk(const int32_t* __restrict__ cu_seqlens,
                                                   const int32_t* __restrict__ chunk_offsets,
@@ -85,6 +93,7 @@ __device__ __forceinline__ ChunkWork locate_chunk(const int32_t* __restrict__ cu
   w.seq = 0;
   w.local_chunk = 0;
   w.token0 = 0;
+  w.seq_end = 0;
   if (global_chunk >= chunk_offsets[nseq]) return w;
   // upper_bound(chunk_offsets, global_chunk) - 1; repeated offsets (empty sequences) are skipped
   int lo = 0, hi = nseq;  // answer in [0, nseq)
@@ -98,7 +107,12 @@ __device__ __forceinline__ ChunkWork locate_chunk(const int32_t* __restrict__ cu
   w.token0 = bos + (int64_t)w.local_chunk * kChunk;
   int64_t rem = eos - w.token0;
   w.valid = rem >= kChunk ? kChunk : (rem > 0 ? (int)rem : 0);
+  w.seq_end = eos;
   return w;
+}
+
+__device__ __forceinline__ bool chunk_in_range(const ChunkWork& w, int64_t tokens) {
+  return w.token0 >= 0 && w.seq_end <= tokens && w.token0 + w.valid <= w.seq_end;
 }
 
 // ------------------------------------------------------------------------------------------

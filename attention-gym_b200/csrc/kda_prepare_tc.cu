@@ -43,6 +43,7 @@ struct PrepParams {
   const int32_t* cu_seqlens; const int32_t* chunk_offsets;
   int* error;
   int nseq, H, total;          // total = chunk capacity x heads work items
+  int64_t tokens;              // rows of the packed buffers
   float scale;
   long long* prof;             // debugging aid: phase timestamps of the 20th item of the first 64 CTAs
 };
@@ -196,6 +197,10 @@ __global__ void __launch_bounds__(NT, 1) kda_prepare_tc_kernel(const __grid_cons
   const int chunk = wi / H, head = wi - chunk * H;
   const ChunkWork cw = pre ? cw_next : locate_chunk(cu_off, ch_off, p.nseq, chunk);
   if (cw.valid == 0) continue;               // capacity slot past the last active chunk
+  if (!pre && !chunk_in_range(cw, p.tokens)) {     // (with pre the previous item checked it)
+    if (tid == 0 && p.error) atomicExch(p.error, kOffsetsOutOfRange);
+    continue;
+  }
   const int valid = cw.valid;
   const int ty = (int)cw.token0, tx = head * 128;
   if (tid < 64)
@@ -212,6 +217,9 @@ __global__ void __launch_bounds__(NT, 1) kda_prepare_tc_kernel(const __grid_cons
     const int wn = wi + (int)gridDim.x;
     ChunkWork nx{};
     if (wn < p.total) nx = locate_chunk(cu_off, ch_off, p.nseq, wn / H);
+    if (!chunk_in_range(nx, p.tokens)) {     // not prefetched; the item itself reports and skips
+      nx.valid = 0;
+    }
     s_next[0] = (int)(nx.token0 & 0xffffffffLL);
     s_next[1] = (int)(nx.token0 >> 32);
     s_next[2] = nx.valid;
@@ -657,6 +665,7 @@ int launch_prepare_tc(const bf16* q, const bf16* k, const bf16* v, const float* 
   if ((rstd_q == nullptr) != (rstd_k == nullptr)) return KDA_ERR_ARG;
   p.cu_seqlens = cu; p.chunk_offsets = co; p.nseq = nseq; p.H = H;
   p.total = chunks * H;
+  p.tokens = tokens;
   p.scale = 0.08838834764831845f;  // 128^-0.5
   p.prof = debug_profile_buffer();
   int dev = 0, sms = 0;

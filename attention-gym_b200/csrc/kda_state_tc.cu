@@ -37,6 +37,7 @@ struct StateTcParams {
   const int32_t* cu_seqlens; const int32_t* chunk_offsets;
   int* error;
   int nseq, H;
+  int64_t tokens;            // rows of the packed buffers
   int use_u, use_o;
   long long* prof;      // debugging aid: phase timestamps of chunk 10 of the first 64 CTAs (rows 32..63)
 };
@@ -133,6 +134,11 @@ __global__ void __launch_bounds__(kStateThreads) kda_state_fwd_tc_kernel(const _
   const int64_t bos = p.cu_seqlens[seq], eos = p.cu_seqlens[seq + 1];
   const int chunk0 = p.chunk_offsets[seq];
   int nchunks = p.chunk_offsets[seq + 1] - chunk0;
+  if (bos < 0 || eos < bos || eos > p.tokens || chunk0 < 0 || (int64_t)nchunks * 64 < eos - bos) {
+    // offsets that do not describe a run inside the packed buffer: the sequence is treated as empty
+    if (tid == 0 && p.error) atomicExch(p.error, kOffsetsOutOfRange);
+    nchunks = 0;
+  }
   if (p.limit_in && !trans) nchunks = min(nchunks, p.limit_in[item]);
   const int64_t sbase = ((int64_t)seq * H + head) * D * D;
 
@@ -455,7 +461,7 @@ int launch_state_fwd_tc(const bf16* w, const bf16* u, const bf16* kg, const bf16
     return KDA_ERR_LAUNCH;
   p.g = g; p.h0 = h0; p.ht = ht; p.trans_out = trans_out; p.limit_in = limit_in; p.limit_out = limit_out;
   p.o = o; p.h_out = h_out; p.vnew_out = vnew_out;
-  p.cu_seqlens = cu; p.chunk_offsets = co; p.error = error; p.nseq = nseq; p.H = H;
+  p.cu_seqlens = cu; p.chunk_offsets = co; p.error = error; p.nseq = nseq; p.H = H; p.tokens = tokens;
   p.use_u = u != nullptr; p.use_o = o != nullptr;
   p.prof = debug_profile_buffer();
   const int64_t ctas = (int64_t)nseq * H * (trans_out ? 2 : 1);
@@ -482,6 +488,7 @@ struct StateBwdTcParams {
   const int32_t* cu_seqlens; const int32_t* chunk_offsets;
   int* error;
   int nseq, H;
+  int64_t tokens;            // rows of the packed buffers
 };
 
 constexpr int kBStageBytes = 4 * 16384 + 8192;   // KG, W, QG, DO, AQK
@@ -518,7 +525,11 @@ __global__ void __launch_bounds__(kStateThreads) kda_state_bwd_tc_kernel(const _
   const int dcol0 = N < 64 ? (v0 & 63) : 0;        // where the slice starts inside the loaded dO box
   const int64_t bos = p.cu_seqlens[seq], eos = p.cu_seqlens[seq + 1];
   const int chunk0 = p.chunk_offsets[seq];
-  const int nchunks = p.chunk_offsets[seq + 1] - chunk0;
+  int nchunks = p.chunk_offsets[seq + 1] - chunk0;
+  if (bos < 0 || eos < bos || eos > p.tokens || chunk0 < 0 || (int64_t)nchunks * 64 < eos - bos) {
+    if (tid == 0 && p.error) atomicExch(p.error, kOffsetsOutOfRange);     // treated as an empty sequence
+    nchunks = 0;
+  }
   const int64_t sbase = ((int64_t)seq * H + head) * D * D;
 
   if (warp == 0) tmem_alloc(tmem_slot, 256);
@@ -743,7 +754,7 @@ int launch_state_bwd_tc(const bf16* w, const bf16* kg, const bf16* qg, const bf1
       !make_tensor_map(&p.tm_dv2out, dv2_out, tokens, cols, 64))
     return KDA_ERR_LAUNCH;
   p.g = g; p.dht = dht; p.dh0 = dh0; p.dh_out = dh_out; p.dv2_out = dv2_out;
-  p.cu_seqlens = cu; p.chunk_offsets = co; p.nseq = nseq; p.H = H;
+  p.cu_seqlens = cu; p.chunk_offsets = co; p.nseq = nseq; p.H = H; p.tokens = tokens;
   p.error = nullptr;
   if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p.error), g_state_tc_error) != cudaSuccess)
     return KDA_ERR_LAUNCH;

@@ -39,10 +39,15 @@ extern "C" {
 /* Library identification: returns 100 * major + minor. */
 int kda_b200_version(void);
 
-/* Non-zero if a tensor-memory kernel abandoned a bounded barrier wait since the last call (clears
- * the flag); synchronises the device.  Every wait in those kernels polls a bounded number of times;
- * one that runs out makes the CTA record a code here and leave, so a lost arrival shows up as an
- * error word, never as a hang.  kda_selftest_bounded_wait exercises exactly that path on purpose:
+/* Non-zero if a tensor-memory kernel abandoned a bounded barrier wait or met offsets that leave the
+ * packed buffer since the last call (clears the flag); synchronises the device.  Byte 0: the state
+ * walks, byte 1: the chunk backward kernel, byte 2: the prepare kernel.  Every wait in those kernels
+ * polls a bounded number of times; one that runs out makes the CTA record a code here and leave, so
+ * a lost arrival shows up as an error word, never as a hang.  Code 9: cu_seqlens / chunk_offsets
+ * describe a sequence that does not lie inside the `tokens` rows of the buffers; its chunks were
+ * skipped (the sequence is treated as empty) instead of being read or written -- the device-side
+ * counterpart of the reference's offset assertion (kda/chunk_scheduler.py:278-293), which the host
+ * cannot check without a synchronisation.  kda_selftest_bounded_wait exercises exactly that path on purpose:
  * a one-warp kernel waits `poll_limit` polls on a barrier nothing arrives on, then returns with
  * code 2 in the error word; the context stays usable.  For tests and debugging; no reference
  * counterpart. */

@@ -390,6 +390,43 @@ def test_library_calls_show_up_as_named_ranges_in_a_profiler_trace():
     assert "kda_prepare_tc_kernel" in kernels and "kda_bwd_chunk_tc_kernel" in kernels
 
 
+def test_offsets_that_leave_the_buffer_are_skipped_and_reported():
+    """cu_seqlens whose last sequence ends beyond the packed buffer (a value the host-side validation
+    cannot see without a device synchronisation): every kernel of the chunked pair treats the chunks
+    that do not lie inside the buffer as absent and raises its part of the device error word, the
+    tensors stay finite, and the next, well-formed call is unaffected (reference: the device-side
+    offset assertion of its scheduler, kda/chunk_scheduler.py:278-293)."""
+    from kda_b200 import _cabi, ops
+
+    inp = _case(1, 256, 2, seed=41)
+    q, k, v = (inp[n].cuda() for n in ("q", "k", "v"))
+    gate, beta = inp["cum_gate"].cuda(), inp["beta"].cuda()
+    h0 = torch.zeros(2, 2, 128, 128, device="cuda")
+    cu = torch.tensor([0, 100, 320], dtype=torch.int32, device="cuda")      # the buffer holds 256 tokens
+    co = torch.tensor([0, 2, 6], dtype=torch.int32, device="cuda")
+    torch.cuda.synchronize()
+    assert _cabi.lib().kda_device_error_word() == 0
+    out, state, aqk, akk, saved = ops.chunk_fwd_saved_op(q, k, v, gate, beta, h0, cu, co, True)
+    torch.cuda.synchronize()
+    word = _cabi.lib().kda_device_error_word()
+    assert word & 0xff == 9 and (word >> 16) & 0xff == 9, hex(word)      # state walk, prepare kernel
+    assert torch.isfinite(out.float()).all() and torch.isfinite(state).all()
+    do = torch.ones_like(out)
+    grads = ops.chunk_bwd_saved_op(q, k, v, gate, beta, aqk, akk, saved, cu, co, do, None, h0, True)
+    torch.cuda.synchronize()
+    word = _cabi.lib().kda_device_error_word()
+    assert word & 0xff == 9 and (word >> 8) & 0xff == 9, hex(word)       # state-gradient walk, chunk backward
+    assert all(torch.isfinite(g.float()).all() for g in grads)
+    # a well-formed call afterwards: clean error word, results as ever
+    good = _case(1, 300, 2, seed=5, lengths=[65, 63, 0, 30, 128])
+    got = _run_fused(good)
+    torch.cuda.synchronize()
+    assert _cabi.lib().kda_device_error_word() == 0
+    ref_o, _ = orc.chunk_kda_ref(good["q"].float(), good["k"].float(), good["v"].float(), good["cum_gate"],
+                                 good["beta"], good["h0"], cu_seqlens=good["cu_seqlens"])
+    assert_normalised(_active(good, got["o"]).float(), _active(good, ref_o), TOL, "output after the reported call")
+
+
 def test_a_bounded_wait_that_runs_out_reports_and_returns():
     """Every barrier wait of the tensor-memory kernels is bounded.  The library's self-test makes one
     run out on purpose (a barrier nothing arrives on, a few thousand polls): the kernel returns, the
