@@ -71,7 +71,10 @@ struct GateParams {
   const int32_t* cu_seqlens; const int32_t* chunk_offsets; int nseq;
   int batch, T, H, K, chunk;
   float lower_bound;
+  int* error;                 // device error word of the gate kernels
 };
+
+static __device__ int g_gate_error = 0;
 
 __device__ __forceinline__ bool gate_locate(const GateParams& p, int gc, int64_t& token0,
                                             int& valid) {
@@ -86,6 +89,11 @@ __device__ __forceinline__ bool gate_locate(const GateParams& p, int gc, int64_t
     token0 = bos + (int64_t)(gc - p.chunk_offsets[lo]) * p.chunk;
     int64_t rem = eos - token0;
     valid = rem >= p.chunk ? p.chunk : (int)rem;
+    if (valid > 0 && (bos < 0 || eos > (int64_t)p.batch * p.T)) {
+      // a sequence that leaves the packed buffer: skipped and reported, never read or written
+      if (threadIdx.x == 0 && p.error) atomicExch(p.error, kOffsetsOutOfRange);
+      return false;
+    }
     return valid > 0;
   }
   int cpr = (p.T + p.chunk - 1) / p.chunk;
@@ -452,6 +460,13 @@ __global__ void __launch_bounds__(256) gate_bwd_reduce_kernel(const float* __res
 
 static int check_launch() { return cudaGetLastError() == cudaSuccess ? KDA_OK : KDA_ERR_LAUNCH; }
 
+int gate_error_word() {
+  int v = 0, zero = 0;
+  if (cudaMemcpyFromSymbol(&v, g_gate_error, sizeof(int)) != cudaSuccess) return -1;
+  cudaMemcpyToSymbol(g_gate_error, &zero, sizeof(int));
+  return v;
+}
+
 }  // namespace kda
 
 extern "C" int kda_prepare_chunk_offsets(const int32_t* cu_seqlens, int nseq, int chunk_size,
@@ -470,6 +485,9 @@ static int gate_common(kda::GateParams& p, const int32_t* cu, const int32_t* co,
   if (chunks > 0x7fffffffLL) return KDA_ERR_UNSUPPORTED;
   p.cu_seqlens = cu; p.chunk_offsets = co; p.nseq = nseq;
   p.batch = batch; p.T = tokens; p.H = heads; p.K = dim; p.chunk = chunk;
+  p.error = nullptr;
+  if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p.error), kda::g_gate_error) != cudaSuccess)
+    return KDA_ERR_LAUNCH;
   return KDA_OK;
 }
 

@@ -794,13 +794,14 @@ extern "C" int kda_selftest_bounded_wait(int poll_limit, void* stream) {
 
 // 1 if a tensor-memory kernel gave up on a barrier wait since the last call (clears the flag).
 // Synchronises the device; meant for tests and debugging.
-namespace kda { int bwd_chunk_tc_error_word(); int prepare_tc_error_word(); }
+namespace kda { int bwd_chunk_tc_error_word(); int prepare_tc_error_word(); int gate_error_word(); }
 
 extern "C" int kda_device_error_word(void) {
   int v = 0, zero = 0;
   if (cudaMemcpyFromSymbol(&v, kda::g_state_tc_error, sizeof(int)) != cudaSuccess) return -1;
   cudaMemcpyToSymbol(kda::g_state_tc_error, &zero, sizeof(int));
-  return v | (kda::bwd_chunk_tc_error_word() << 8) | (kda::prepare_tc_error_word() << 16);
+  return v | (kda::bwd_chunk_tc_error_word() << 8) | (kda::prepare_tc_error_word() << 16) |
+         (kda::gate_error_word() << 24);
 }
 
 // Forces the value split of the state recurrences (1, 2 or 4 CTAs per chain; 0 = choose from the

@@ -41,7 +41,7 @@ int kda_b200_version(void);
 
 /* Non-zero if a tensor-memory kernel abandoned a bounded barrier wait or met offsets that leave the
  * packed buffer since the last call (clears the flag); synchronises the device.  Byte 0: the state
- * walks, byte 1: the chunk backward kernel, byte 2: the prepare kernel.  Every wait in those kernels
+ * walks, byte 1: the chunk backward kernel, byte 2: the prepare kernel, byte 3: the gate kernels.  Every wait in those kernels
  * polls a bounded number of times; one that runs out makes the CTA record a code here and leave, so
  * a lost arrival shows up as an error word, never as a hang.  Code 9: cu_seqlens / chunk_offsets
  * describe a sequence that does not lie inside the `tokens` rows of the buffers; its chunks were

@@ -49,6 +49,33 @@ def test_gate_chunk_sizes_and_packed_backward(chunk):
     torch.testing.assert_close(b_g.grad.cpu(), r_b, atol=2e-2, rtol=2e-2)
 
 
+def test_gate_offsets_that_leave_the_buffer_are_skipped_and_reported():
+    """A last sequence that ends beyond the buffer: the gate kernels skip it and raise byte 3 of the
+    device error word; the sequences inside the buffer are computed as ever."""
+    from kda_b200 import _cabi
+
+    gen = torch.Generator().manual_seed(4)
+    raw = torch.randn(1, 300, 2, 64, generator=gen).bfloat16()
+    A_log = 0.2 * torch.randn(2, generator=gen)
+    bias = 0.3 * torch.randn(2, 64, generator=gen)
+    good = torch.tensor([0, 65, 128], dtype=torch.int32)
+    bad = torch.tensor([0, 65, 128, 400], dtype=torch.int32)          # the buffer holds 300 tokens
+    ref = orc.bounded_gate_cumsum_ref(raw, A_log, bias, 64, -5.0, good)
+    torch.cuda.synchronize()
+    assert _cabi.lib().kda_device_error_word() == 0
+    out = kda_b200.bounded_gate_cumsum(raw.cuda(), A_log.cuda(), bias.cuda(), chunk_size=64,
+                                       cu_seqlens=bad.cuda())
+    torch.cuda.synchronize()
+    assert (_cabi.lib().kda_device_error_word() >> 24) & 0xff == 9
+    assert torch.isfinite(out).all()
+    torch.testing.assert_close(out[:, :128].cpu(), ref[:, :128], atol=3e-5, rtol=1e-5)
+    out = kda_b200.bounded_gate_cumsum(raw.cuda(), A_log.cuda(), bias.cuda(), chunk_size=64,
+                                       cu_seqlens=good.cuda())
+    torch.cuda.synchronize()
+    assert _cabi.lib().kda_device_error_word() == 0
+    torch.testing.assert_close(out[:, :128].cpu(), ref[:, :128], atol=3e-5, rtol=1e-5)
+
+
 def test_chunk_offsets_match_cpu():
     gen = torch.Generator().manual_seed(1)
     lens = torch.randint(0, 300, (5000,), generator=gen)
