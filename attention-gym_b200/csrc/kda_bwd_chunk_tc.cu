@@ -52,7 +52,10 @@ struct BwdTcParams {
 // the buffer set with kda_debug_set_profile_buffer.
 __device__ __forceinline__ void tc_mark(const BwdTcParams& p, int it, int slot) {
 #ifdef KDA_PHASE_PROFILE
-  if (p.prof && it == 20 && threadIdx.x == 0 && blockIdx.x < 64) {
+#ifndef KDA_PROFILE_THREAD
+#define KDA_PROFILE_THREAD 0
+#endif
+  if (p.prof && it == 20 && threadIdx.x == KDA_PROFILE_THREAD && blockIdx.x < 64) {
     long long t;
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
     p.prof[blockIdx.x * 32 + slot] = t;
@@ -582,6 +585,7 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
       kdk += ld_bf(sm + bl::K, 8192, r0 + ii, L) * a[ii] * fexp2(glast - ld_g(sG, r0 + ii, L));
     s_kdk[rq * 128 + L] = kdk;
   }
+  tc_mark(p, it, 22);
   if (!mbar_wait(&bar[2], ph)) *s_abort = 1;
   tc_fence_after();
   tc_mark(p, it, 5);
@@ -651,6 +655,7 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
   }
   build_row_tiles(1536, 2560);
   tc_mark(p, it, 7);
+  tc_mark(p, it, 23);
   if (!mbar_wait(&bar[3], ph)) *s_abort = 1;
   tc_fence_after();
   {
@@ -733,6 +738,7 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
                 gkeep[n]);
   }
   tc_mark(p, it, 9);
+  tc_mark(p, it, 24);
   if (!mbar_wait(&bar[4], ph)) *s_abort = 1;
   tc_fence_after();
   {
@@ -802,6 +808,7 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
     else if (lid < 6) tma_prefetch_2d(&p.tm_g, tx + 32 * (lid - 2), ty);
     else tma_prefetch_2d(&p.tm_q, tx + 64 * (lid - 6), ty);
   }
+  tc_mark(p, it, 25);
   if (!mbar_wait(&bar[5], ph)) *s_abort = 1;   // row-type tiles are free again
   tc_fence_after();
   {
@@ -821,6 +828,7 @@ __global__ void __launch_bounds__(NT, 1) kda_bwd_chunk_tc_kernel(const __grid_co
     else issue_col(3, bl::QN3, bl::KP3);
   }
   tc_mark(p, it, 11);
+  tc_mark(p, it, 26);
   if (!mbar_wait(&bar[6], ph)) *s_abort = 1;
   tc_fence_after();
   tc_mark(p, it, 12);
