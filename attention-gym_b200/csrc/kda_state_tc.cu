@@ -295,13 +295,9 @@ __global__ void __launch_bounds__(kStateThreads) kda_state_fwd_tc_kernel(const _
     }
 
     // ---- b. D1 = [w ; qg] h ;  the bf16 state tile also leaves as h[c] (kept for the backward pass)
+    // (the products first: they are on the chain from chunk to chunk, and a thread spends about
+    //  50 ns on every bulk store it issues; the store only reads the tile the products read)
     if (tid == 0) {
-      if (kTileStore && h_out) {
-        const int yh = ((chunk0 + c) * H + head) * D;
-        for (int b = 0; b < NB; ++b)
-          tma_store_2d(&p.tm_hout, smem + StateTcLayout::H + b * 16384, v0 + 64 * b, yh);
-        tma_store_commit();
-      }
       st_mark(p.prof, c, 10);
       if (!mbar_wait(&bar_full[c & 1], (c >> 1) & 1)) *s_abort = 1;
       tc_fence_after();
@@ -312,6 +308,12 @@ __global__ void __launch_bounds__(kStateThreads) kda_state_fwd_tc_kernel(const _
         umma(tmem + 128 + 128 * (c & 1), desc_kmajor(a1, ks, 16384), desc_mnmajor(sH, ks, 16384),
              idesc_kmn, ks > 0);
       umma_commit(bar_mma1);
+      if (kTileStore && h_out) {
+        const int yh = ((chunk0 + c) * H + head) * D;
+        for (int b = 0; b < NB; ++b)
+          tma_store_2d(&p.tm_hout, smem + StateTcLayout::H + b * 16384, v0 + 64 * b, yh);
+        tma_store_commit();
+      }
     }
     st_mark(p.prof, c, 3);
 
@@ -368,6 +370,13 @@ __global__ void __launch_bounds__(kStateThreads) kda_state_fwd_tc_kernel(const _
     // ---- d. h += kg^T v_new (thread 0);  D1 += [0 ; Aqk] v_new (thread 32); v_new and the previous
     //         chunk's output rows leave
     if (tid == 0) {
+      tc_fence_after();
+      const uint32_t kg = saddr(st + StateTcLayout::KG);
+#pragma unroll
+      for (int ks = 0; ks < 4; ++ks)
+        umma(tmem, desc_mnmajor(kg, ks, 8192), desc_mnmajor(sVN, ks, 8192), idesc_mnmn, 1);
+      umma_commit(bar_mma2);
+      st_mark(p.prof, c, 7);
       const int x0 = head * D + v0;
       if (kTileStore) {
         if (vnew_out && valid == 64)
@@ -378,13 +387,6 @@ __global__ void __launch_bounds__(kStateThreads) kda_state_fwd_tc_kernel(const _
             tma_store_2d(&p.tm_o, smem + StateTcLayout::OST + b * 8192, x0 + 64 * b, (int)token0 - 64);
         tma_store_commit();
       }
-      tc_fence_after();
-      const uint32_t kg = saddr(st + StateTcLayout::KG);
-#pragma unroll
-      for (int ks = 0; ks < 4; ++ks)
-        umma(tmem, desc_mnmajor(kg, ks, 8192), desc_mnmajor(sVN, ks, 8192), idesc_mnmn, 1);
-      umma_commit(bar_mma2);
-      st_mark(p.prof, c, 7);
     } else if (tid == 32 && use_o) {
       tc_fence_after();
       const uint32_t a2 = saddr(st + StateTcLayout::A2);
@@ -641,13 +643,8 @@ __global__ void __launch_bounds__(kStateThreads) kda_state_bwd_tc_kernel(const _
 
     // ---- b. dv2 = kg dh + Aqk^T dO ;  dh += qg^T dO ;  the bf16 dh tile leaves as dh[c] ------------------
     // (the slice's dO columns start dcol0 columns into the loaded box: the operand descriptor starts there)
+    // (products before the bulk stores, as in the forward walk)
     if (tid == 0) {
-      if (kTileStore) {
-        const int yh = ((chunk0 + c) * H + head) * D;
-        for (int b = 0; b < NB; ++b)
-          tma_store_2d(&p.tm_dhout, smem + StateBwdLayout::DH + b * 16384, v0 + 64 * b, yh);
-        tma_store_commit();
-      }
       tc_fence_after();
       const uint32_t kg = saddr(st + StateBwdLayout::KG), dO = saddr(st + StateBwdLayout::DO) + 2 * dcol0,
                      aqk = saddr(st + StateBwdLayout::AQK);
@@ -659,6 +656,12 @@ __global__ void __launch_bounds__(kStateThreads) kda_state_bwd_tc_kernel(const _
       for (int ks = 0; ks < 4; ++ks)
         umma(tmem + 128, desc_mnmajor(aqk, ks, 0), desc_mnmajor(dO, ks, 8192), instr_desc(64, N, 1, 1), 1);
       umma_commit(bar_mma1);
+      if (kTileStore) {
+        const int yh = ((chunk0 + c) * H + head) * D;
+        for (int b = 0; b < NB; ++b)
+          tma_store_2d(&p.tm_dhout, smem + StateBwdLayout::DH + b * 16384, v0 + 64 * b, yh);
+        tma_store_commit();
+      }
     } else if (tid == 32) {
       tc_fence_after();
       const uint32_t qg = saddr(st + StateBwdLayout::QG), dO = saddr(st + StateBwdLayout::DO) + 2 * dcol0;
@@ -694,17 +697,17 @@ __global__ void __launch_bounds__(kStateThreads) kda_state_bwd_tc_kernel(const _
 
     // ---- d. dh -= w^T dv2 ;  dv2 leaves -----------------------------------------------------------------
     if (tid == 0) {
-      if (kTileStore && valid == 64) {
-        for (int b = 0; b < NB; ++b)
-          tma_store_2d(&p.tm_dv2out, smem + StateBwdLayout::DV2 + b * 8192, head * D + v0 + 64 * b, (int)token0);
-        tma_store_commit();
-      }
       tc_fence_after();
       const uint32_t w = saddr(st + StateBwdLayout::W);
 #pragma unroll
       for (int ks = 0; ks < 4; ++ks)
         umma(tmem, desc_mnmajor(w, ks, 8192), desc_mnmajor(sDV2, ks, 8192), instr_desc(128, N, 1, 1, 1), 1);
       umma_commit(bar_mma2);
+      if (kTileStore && valid == 64) {
+        for (int b = 0; b < NB; ++b)
+          tma_store_2d(&p.tm_dv2out, smem + StateBwdLayout::DV2 + b * 8192, head * D + v0 + 64 * b, (int)token0);
+        tma_store_commit();
+      }
     }
     if (!mbar_wait(bar_mma2, it & 1)) *s_abort = 1;
     tc_fence_after();
